@@ -1,0 +1,142 @@
+/*
+ * llmt_b200 — C ABI of the B200-native matrix-multiply path for llmt.
+ *
+ * This is the boundary a host program binds: plain pointers and sizes, no
+ * C++ types, no framework types.  Every entry point enqueues work on the CUDA
+ * stream it is given and returns without synchronising; nothing here
+ * allocates device memory; nothing aborts or throws — errors come back as a
+ * non-zero status and llmt_b200_last_error() explains the most recent one on
+ * the calling thread.
+ *
+ * The library replaces the one call llmt makes into cuBLASLt
+ * (llmt: src/kernels/matmul.cpp:116-170, reached from kernels::matmul,
+ * include/llmt/kernels/matmul.h:23-24).  Tensors are row-major; weights are
+ * [out, in]; C is read and written in place when beta != 0.
+ *
+ * Element type codes are llmt's DType codes (include/llmt/core/dtype.h:15):
+ * 0 = fp32, 1 = bf16.
+ */
+#ifndef LLMT_B200_H
+#define LLMT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLMT_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define LLMT_B200_API __attribute__((visibility("default")))
+#else
+#define LLMT_B200_API
+#endif
+
+enum llmt_b200_dtype { LLMT_B200_FP32 = 0, LLMT_B200_BF16 = 1 };
+
+/* Epilogue flags (bit set).  Order of application on the fp32 accumulator:
+ *   v = alpha * (op(A) op(B)) + beta * C_in ;  v += bias[j] ;  v = gelu_tanh(v) ;
+ *   C = cast(v).
+ * gelu_tanh is llmt's formula (src/kernels/gelu.cu:23-26) evaluated in fp32.
+ * llmt itself has no bias and runs GELU as a separate kernel
+ * (src/layers/mlp.cpp:14-18); with flags == 0 the result is llmt's matmul. */
+enum llmt_b200_epilogue {
+    LLMT_B200_EPI_NONE = 0,
+    LLMT_B200_EPI_BIAS = 1,
+    LLMT_B200_EPI_GELU = 2
+};
+
+enum llmt_b200_status {
+    LLMT_B200_OK = 0,
+    LLMT_B200_ERR_INVALID = 1,     /* contract violation (shape, pointer, alignment, aliasing) */
+    LLMT_B200_ERR_UNSUPPORTED = 2, /* valid request this build has no kernel for */
+    LLMT_B200_ERR_WORKSPACE = 3,   /* workspace missing or smaller than required */
+    LLMT_B200_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed */
+    LLMT_B200_ERR_DEVICE = 5       /* a kernel gave up on a bounded wait (see device_status) */
+};
+
+/*
+ * One GEMM problem:  C[b] = epilogue(alpha * op(A[b]) * op(B[b]) + beta * C[b]).
+ * Mirrors the Problem llmt derives in src/kernels/matmul.cpp:79-86,175-214,
+ * with explicit row pitches added so padded buffers can be used.
+ *
+ *   op(A) is [m,k]: A is stored [m,k] (trans_a = 0) or [k,m] (trans_a = 1).
+ *   op(B) is [k,n]: B is stored [k,n] (trans_b = 0) or [n,k] (trans_b = 1).
+ *   lda/ldb/ldc  row pitch in elements of each row-major buffer (>= its column count).
+ *   stride_*     elements between consecutive batch items; ignored when batch == 1.
+ *   dtype_ab     element type of A and B; dtype_c of C.  Supported pairs:
+ *                (fp32, fp32) strict fp32 FMA path; (bf16, bf16) and (bf16, fp32)
+ *                tensor-core path with fp32 accumulation.
+ *   bias         [n] values added to every row when EPI_BIAS is set (bias_dtype: fp32 or bf16).
+ *   dbias        optional fp32 [m]:  dbias[i] = dbias_beta * dbias[i] + sum_p op(A)[i,p].
+ *                For llmt's dW call (src/layers/linear.cpp:27-29: A = dy, trans_a = 1)
+ *                this is the bias gradient, summed over tokens.  bf16 path only.
+ *   workspace    device scratch for split-K partial sums; llmt_b200_gemm_workspace_bytes()
+ *                gives the size this problem needs (0 for most problems).  Plays the role
+ *                of RunCtx::blas_workspace (include/llmt/core/run_ctx.h:35-36).
+ */
+typedef struct llmt_b200_gemm_desc {
+    int64_t m, n, k, batch;
+    int64_t lda, ldb, ldc;
+    int64_t stride_a, stride_b, stride_c;
+    int32_t trans_a, trans_b;
+    int32_t dtype_ab, dtype_c;
+    float alpha, beta;
+    int32_t epilogue;
+    int32_t bias_dtype;
+    const void* bias;
+    float* dbias;
+    float dbias_beta;
+    int32_t reserved0;
+    void* workspace;
+    uint64_t workspace_bytes;
+} llmt_b200_gemm_desc;
+
+/* Replaces llmt's kernels::matmul body (src/kernels/matmul.cpp:218-222 ->
+ * run(), :116-170).  `stream` is a cudaStream_t.  Deterministic: the same
+ * descriptor and inputs give bitwise-identical output on every call. */
+LLMT_B200_API int llmt_b200_gemm(const llmt_b200_gemm_desc* desc, void* c, const void* a, const void* b,
+                   void* stream);
+
+/* Bytes of workspace llmt_b200_gemm needs for this problem (may be 0).  Pure
+ * function of the descriptor and of the device's SM count. */
+LLMT_B200_API uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* desc);
+
+/* Writes a one-line description of the kernel plan chosen for `desc` (tile shape,
+ * pipeline depth, split count, grid) into buf.  The plan is a pure function of
+ * the problem, which is what makes results reproducible — the role llmt's
+ * AlgoCache plays (include/llmt/kernels/algo_cache.h:18-42).  Returns a status. */
+LLMT_B200_API int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* desc, char* buf, size_t buf_bytes);
+
+/* Row softmax helper with llmt's masking rule (src/kernels/softmax.cu:25-51):
+ * x, y are [rows, tk] with row r belonging to query r % tq; under causal != 0
+ * only columns <= r % tq take part and the others are written as exact zeros.
+ * In place (y == x) allowed.  fp32 arithmetic; dtype is the storage type. */
+LLMT_B200_API int llmt_b200_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,
+                          int32_t dtype, int32_t causal, void* stream);
+
+/* dS = P * (dP - rowsum(dP * P)) per row (llmt docs/TODO.md:227). */
+LLMT_B200_API int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
+                          int32_t dtype, void* stream);
+
+/* Device-side health word.  Kernels never spin without bound: a wait that runs
+ * out records (code, detail) here and the kernel drains and returns.  This call
+ * synchronises the device, copies the word back and clears it.  code == 0 means
+ * healthy.  Returns LLMT_B200_ERR_DEVICE when a code was pending. */
+LLMT_B200_API int llmt_b200_device_status(int32_t* code, int32_t* detail);
+
+/* Number of kernels this library has launched from this process so far. */
+LLMT_B200_API uint64_t llmt_b200_launch_count(void);
+
+/* Message for the most recent non-zero status on this thread ("" if none). */
+LLMT_B200_API const char* llmt_b200_last_error(void);
+
+LLMT_B200_API int llmt_b200_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LLMT_B200_H */

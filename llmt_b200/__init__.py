@@ -1,0 +1,215 @@
+"""llmt_b200 — Python binding of the C ABI in include/llmt_b200.h.
+
+The product is the shared library llmt_b200/lib/libllmt_b200.so (hand-written
+sm_100a kernels behind `extern "C"` entry points). This module only loads it
+with ctypes and passes device pointers of torch tensors through; torch is used
+for device memory and streams, never for arithmetic. There is no fallback: if
+the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libllmt_b200.so")
+
+FP32, BF16 = 0, 1
+EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4, 5
+
+EXPORTS = [
+    "llmt_b200_gemm", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
+    "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
+    "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
+]
+
+
+class GemmDesc(ctypes.Structure):
+    """struct llmt_b200_gemm_desc (include/llmt_b200.h)."""
+    _fields_ = [
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64), ("batch", ctypes.c_int64),
+        ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
+        ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
+        ("trans_a", ctypes.c_int32), ("trans_b", ctypes.c_int32),
+        ("dtype_ab", ctypes.c_int32), ("dtype_c", ctypes.c_int32),
+        ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+        ("epilogue", ctypes.c_int32), ("bias_dtype", ctypes.c_int32),
+        ("bias", ctypes.c_void_p), ("dbias", ctypes.c_void_p),
+        ("dbias_beta", ctypes.c_float), ("reserved0", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+    ]
+
+
+class LlmtB200Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"llmt_b200 status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the C-ABI library. Raises if it has not been built — there is no
+    other implementation to fall back to."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LlmtB200Error(-1, f"{LIB_PATH} is missing; run `python -m llmt_b200.build`")
+        L = ctypes.CDLL(LIB_PATH)
+        L.llmt_b200_gemm.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_void_p]
+        L.llmt_b200_gemm.restype = ctypes.c_int
+        L.llmt_b200_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
+        L.llmt_b200_gemm_workspace_bytes.restype = ctypes.c_uint64
+        L.llmt_b200_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_char_p, ctypes.c_size_t]
+        L.llmt_b200_gemm_plan.restype = ctypes.c_int
+        L.llmt_b200_softmax_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                                            ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_softmax_fwd.restype = ctypes.c_int
+        L.llmt_b200_softmax_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                            ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                                            ctypes.c_void_p]
+        L.llmt_b200_softmax_bwd.restype = ctypes.c_int
+        L.llmt_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_int32),
+                                              ctypes.POINTER(ctypes.c_int32)]
+        L.llmt_b200_device_status.restype = ctypes.c_int
+        L.llmt_b200_launch_count.restype = ctypes.c_uint64
+        L.llmt_b200_last_error.restype = ctypes.c_char_p
+        L.llmt_b200_abi_version.restype = ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().llmt_b200_last_error().decode()
+
+
+def _check(status: int) -> None:
+    if status != OK:
+        raise LlmtB200Error(status, last_error())
+
+
+def _dtype_code(t) -> int:
+    import torch
+    if t.dtype == torch.float32:
+        return FP32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise LlmtB200Error(ERR_UNSUPPORTED, f"dtype {t.dtype} not supported")
+
+
+def _row_pitch(t) -> int:
+    if t.stride(-1) != 1 and t.shape[-1] != 1:
+        raise LlmtB200Error(ERR_INVALID, "innermost dimension must be contiguous")
+    return t.stride(-2)
+
+
+def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
+              dbias=None, dbias_beta=0.0, workspace=None) -> GemmDesc:
+    """Builds the descriptor for C = epilogue(alpha*op(A)*op(B) + beta*C) from rank-2
+    or rank-3 torch tensors (row-major views with a contiguous last dimension)."""
+    if not (a.dim() == b.dim() == c.dim()) or a.dim() not in (2, 3):
+        raise LlmtB200Error(ERR_INVALID, "matmul: expected rank-2 or rank-3 tensors of one rank")
+    d = GemmDesc()
+    ar, ac = a.shape[-2], a.shape[-1]
+    br, bc = b.shape[-2], b.shape[-1]
+    d.m, d.k = (ac, ar) if trans_a else (ar, ac)
+    kb, d.n = (bc, br) if trans_b else (br, bc)
+    if kb != d.k:
+        raise LlmtB200Error(ERR_INVALID, f"matmul: inner dims disagree: {d.k} vs {kb}")
+    if tuple(c.shape[-2:]) != (d.m, d.n):
+        raise LlmtB200Error(ERR_INVALID, "matmul: C shape mismatch")
+    if a.dim() == 3:
+        d.batch = a.shape[0]
+        if b.shape[0] != d.batch or c.shape[0] != d.batch:
+            raise LlmtB200Error(ERR_INVALID, "matmul: batch sizes disagree")
+        d.stride_a, d.stride_b, d.stride_c = a.stride(0), b.stride(0), c.stride(0)
+    else:
+        d.batch = 1
+    d.lda, d.ldb, d.ldc = _row_pitch(a), _row_pitch(b), _row_pitch(c)
+    d.trans_a, d.trans_b = int(trans_a), int(trans_b)
+    if a.dtype != b.dtype:
+        raise LlmtB200Error(ERR_INVALID, "matmul: mixed dtypes in one matmul")
+    d.dtype_ab, d.dtype_c = _dtype_code(a), _dtype_code(c)
+    d.alpha, d.beta = float(alpha), float(beta)
+    d.epilogue = (EPI_BIAS if bias is not None else 0) | (EPI_GELU if gelu else 0)
+    if bias is not None:
+        d.bias = bias.data_ptr()
+        d.bias_dtype = _dtype_code(bias)
+    if dbias is not None:
+        d.dbias = dbias.data_ptr()
+        d.dbias_beta = float(dbias_beta)
+    if workspace is not None:
+        d.workspace = workspace.data_ptr()
+        d.workspace_bytes = workspace.numel() * workspace.element_size()
+    return d
+
+
+def workspace_bytes(desc: GemmDesc) -> int:
+    return int(lib().llmt_b200_gemm_workspace_bytes(ctypes.byref(desc)))
+
+
+def plan(desc: GemmDesc) -> str:
+    buf = ctypes.create_string_buffer(256)
+    _check(lib().llmt_b200_gemm_plan(ctypes.byref(desc), buf, 256))
+    return buf.value.decode()
+
+
+def gemm_desc(desc: GemmDesc, c, a, b, stream=None) -> None:
+    """Enqueues one llmt_b200_gemm call; `stream` is a torch.cuda.Stream (default: current)."""
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    _check(lib().llmt_b200_gemm(ctypes.byref(desc), c.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                ctypes.c_void_p(s.cuda_stream)))
+
+
+def gemm(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
+         dbias=None, dbias_beta=0.0, workspace=None, stream=None) -> None:
+    """C = epilogue(alpha*op(A)*op(B) + beta*C) on device tensors, in place in C.
+
+    Same argument meaning as llmt's kernels::matmul
+    (include/llmt/kernels/matmul.h:12-24) plus the fused bias / GELU / dbias
+    extensions. If the problem needs split-K scratch and none is passed, a
+    torch buffer is allocated for this call."""
+    import torch
+    d = make_desc(c, a, b, trans_a, trans_b, alpha, beta, bias, gelu, dbias, dbias_beta, workspace)
+    if workspace is None:
+        need = workspace_bytes(d)
+        if need:
+            ws = torch.empty(need, dtype=torch.uint8, device=c.device)
+            d.workspace = ws.data_ptr()
+            d.workspace_bytes = need
+    gemm_desc(d, c, a, b, stream)
+
+
+def softmax_fwd(y, x, causal: bool, stream=None) -> None:
+    """Row softmax of [batch, Tq, Tk] with llmt's causal rule; y may be x."""
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    tq, tk = x.shape[-2], x.shape[-1]
+    _check(lib().llmt_b200_softmax_fwd(y.data_ptr(), x.data_ptr(), x.numel() // tk, tq, tk,
+                                       _dtype_code(x), int(causal), ctypes.c_void_p(s.cuda_stream)))
+
+
+def softmax_bwd(ds, p, dp, stream=None) -> None:
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    tk = p.shape[-1]
+    _check(lib().llmt_b200_softmax_bwd(ds.data_ptr(), p.data_ptr(), dp.data_ptr(), p.numel() // tk, tk,
+                                       _dtype_code(p), ctypes.c_void_p(s.cuda_stream)))
+
+
+def device_status():
+    """Synchronises and returns (code, detail) of the device health word; raises if non-zero."""
+    code, detail = ctypes.c_int32(0), ctypes.c_int32(0)
+    st = lib().llmt_b200_device_status(ctypes.byref(code), ctypes.byref(detail))
+    if st != OK:
+        raise LlmtB200Error(st, last_error())
+    return code.value, detail.value
+
+
+def launch_count() -> int:
+    return int(lib().llmt_b200_launch_count())

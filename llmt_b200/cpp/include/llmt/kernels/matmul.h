@@ -1,0 +1,30 @@
+// kernels::matmul — the GEMM seam of llmt (include/llmt/kernels/matmul.h:12-24),
+// implemented over the llmt_b200 C ABI instead of cuBLASLt.
+#pragma once
+
+#include "llmt/core/run_ctx.h"
+#include "llmt/core/types.h"
+
+namespace llmt::kernels {
+
+// C[M,N] = alpha*op(A)*op(B) + beta*C for row-major tensors; rank 2 = one GEMM,
+// rank 3 = one independent GEMM per leading index.  Same contract, same abort
+// messages as llmt.  dtype rules: all fp32 (strict fp32 path, needs
+// ctx.precision == fp32()), or A/B bf16 with C bf16 or fp32 (tensor-core path,
+// needs gemm_compute == BF16, reduce == FP32).
+void matmul(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
+            bool trans_b, float alpha, float beta) noexcept;
+
+// Fused-epilogue extension.  Applied after alpha/beta:  + bias[n]  -> tanh-GELU
+// -> cast.  dbias (fp32 [M]) receives  dbias_beta*dbias + row sums of op(A).
+// A default-constructed Epilogue makes matmul_ex identical to matmul.
+struct Epilogue {
+    const Tensor* bias = nullptr;
+    bool gelu = false;
+    Tensor* dbias = nullptr;
+    float dbias_beta = 1.0f;
+};
+void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
+               bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept;
+
+}  // namespace llmt::kernels

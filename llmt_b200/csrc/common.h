@@ -1,0 +1,111 @@
+// Internal declarations shared by the kernels and the C-ABI front end.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace llmt_b200 {
+
+// Device-side health word (see llmt_b200_device_status in the public header).
+// code: 0 healthy; otherwise the first failure recorded wins.
+struct DeviceStatus {
+    int32_t code;
+    int32_t detail;
+    int32_t block;
+    int32_t reserved;
+};
+
+enum DeviceErr : int32_t {
+    kDevOk = 0,
+    kDevWaitSmemEmpty = 1,   // TMA producer gave up waiting for a free pipeline slot
+    kDevWaitSmemFull = 2,    // MMA issuer gave up waiting for operand bytes to land
+    kDevWaitTmemEmpty = 3,   // MMA issuer gave up waiting for the epilogue to drain an accumulator
+    kDevWaitTmemFull = 4     // epilogue gave up waiting for an accumulator to complete
+};
+
+constexpr int kEpiBias = 1;
+constexpr int kEpiGelu = 2;
+
+// Everything the tensor-core kernel needs besides the two operand tensor maps.
+struct TcGemmParams {
+    int64_t m, n, k;
+    int32_t batch;
+    int32_t tiles_m, tiles_n, splits;
+    int32_t kblocks_total;      // ceil(k / 64)
+    int32_t kblocks_per_split;  // k-blocks handled by each split (last one may be shorter)
+    int64_t total_tiles;        // tiles_m * tiles_n * splits * batch
+    void* c;
+    int64_t ldc, stride_c;
+    int32_t c_is_bf16;
+    int32_t c_vec_ok;           // rows of C start 16-byte aligned -> vector stores allowed
+    float alpha, beta;
+    const void* bias;
+    int32_t bias_is_bf16;
+    int32_t epi_flags;
+    float* ws;                  // split-K partial sums [batch][splits][m][n] fp32 (splits > 1)
+    float* dbias;               // fp32 [m] or null
+    float dbias_beta;
+    float* ws_dbias;            // [splits][m] fp32 (splits > 1 and dbias wanted)
+    DeviceStatus* status;
+};
+
+// Plan: the pure function of the problem that fixes every launch parameter.
+struct TcPlan {
+    int bn;          // tile width along N: 64, 128, 192 or 256 (tile height is always 128)
+    int stages;      // TMA/MMA pipeline depth
+    int splits;      // split-K factor (1 = none)
+    int grid;        // persistent CTAs launched
+    int tiles_m, tiles_n;
+    int kblocks_total, kblocks_per_split;
+    size_t smem_bytes;
+    size_t workspace_bytes;
+};
+
+struct Fp32GemmParams {
+    int64_t m, n, k, batch;
+    const float* a;
+    const float* b;
+    float* c;
+    int64_t lda, ldb, ldc;
+    int64_t stride_a, stride_b, stride_c;
+    int32_t trans_a, trans_b;
+    float alpha, beta;
+    const void* bias;
+    int32_t bias_is_bf16;
+    int32_t epi_flags;
+};
+
+// tanh-GELU in fp32, the expression of llmt's gelu kernel (src/kernels/gelu.cu:23-26).
+__device__ __forceinline__ float gelu_tanh_precise(float v) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * v * (1.0f + tanhf(k0 * (v + k1 * v * v * v)));
+}
+
+// Same formula with tanh(u) = 1 - 2/(exp(2u)+1) on the fast exp/divide units.
+// Absolute error of the tanh term is ~1e-7, far below one bf16 ulp of the result.
+__device__ __forceinline__ float gelu_tanh_fast(float v) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    const float u = k0 * (v + k1 * v * v * v);
+    const float t = __expf(2.0f * u);
+    const float th = 1.0f - __fdividef(2.0f, t + 1.0f);
+    return 0.5f * v * (1.0f + th);
+}
+
+// Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
+cudaError_t launch_tc_gemm(const TcPlan& plan, int a_mn_major, int b_mn_major,
+                           const CUtensorMap& map_a, const CUtensorMap& map_b,
+                           const TcGemmParams& p, cudaStream_t stream);
+cudaError_t launch_splitk_reduce(const TcGemmParams& p, cudaStream_t stream);
+cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
+cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,
+                               int is_bf16, int causal, cudaStream_t stream);
+cudaError_t launch_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
+                               int is_bf16, cudaStream_t stream);
+cudaError_t tc_gemm_configure(void);  // sets the dynamic shared-memory attribute once per device
+DeviceStatus* device_status_ptr(void);
+size_t tc_smem_bytes(int bn, int stages, bool dbias);
+
+void count_launch(int n);
+
+}  // namespace llmt_b200

@@ -1,0 +1,191 @@
+// Strict-fp32 GEMM: fp32 storage, fp32 FMA arithmetic, no tensor cores.
+//
+// This is the path that must agree with llmt's fp32 golden tensors at
+// rtol 1e-5 (llmt runs cuBLASLt with CUBLAS_COMPUTE_32F and refuses TF32,
+// src/kernels/matmul.cpp:33-36,72-77); tcgen05 has no full-precision fp32 MMA,
+// so this is a CUDA-core kernel.  64x64 output tile per 256-thread CTA,
+// 4x4 outputs per thread, k ascending -> the sum order is fixed, results are
+// bitwise reproducible.
+#include <cuda_bf16.h>
+
+#include "common.h"
+
+namespace llmt_b200 {
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+__global__ void __launch_bounds__(256)
+fp32_gemm_kernel(const Fp32GemmParams p) {
+    __shared__ float As[TK][TM + 4];
+    __shared__ float Bs[TK][TN + 4];
+
+    const int64_t b = blockIdx.z;
+    const float* A = p.a + b * p.stride_a;
+    const float* B = p.b + b * p.stride_b;
+    float* C = p.c + b * p.stride_c;
+    const int64_t m0 = static_cast<int64_t>(blockIdx.y) * TM;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * TN;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    for (int64_t k0 = 0; k0 < p.k; k0 += TK) {
+        // 64x16 elements of op(A) and of op(B): 4 elements per thread each.
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = threadIdx.x + e * 256;
+            int mi, ki;
+            if (p.trans_a) { mi = idx % TM; ki = idx / TM; }   // A stored [k, m]: m contiguous
+            else           { ki = idx % TK; mi = idx / TK; }   // A stored [m, k]: k contiguous
+            const int64_t gm = m0 + mi, gk = k0 + ki;
+            float v = 0.0f;
+            if (gm < p.m && gk < p.k) v = p.trans_a ? A[gk * p.lda + gm] : A[gm * p.lda + gk];
+            As[ki][mi] = v;
+            int ni, kj;
+            if (p.trans_b) { kj = idx % TK; ni = idx / TK; }   // B stored [n, k]: k contiguous
+            else           { ni = idx % TN; kj = idx / TN; }   // B stored [k, n]: n contiguous
+            const int64_t gn = n0 + ni, gk2 = k0 + kj;
+            float w = 0.0f;
+            if (gn < p.n && gk2 < p.k) w = p.trans_b ? B[gn * p.ldb + gk2] : B[gk2 * p.ldb + gn];
+            Bs[kj][ni] = w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            float a[4], bb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bb[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t gm = m0 + ty * 4 + i;
+        if (gm >= p.m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t gn = n0 + tx * 4 + j;
+            if (gn >= p.n) continue;
+            float v = p.alpha * acc[i][j];
+            float* dst = C + gm * p.ldc + gn;
+            if (p.beta != 0.0f) v += p.beta * *dst;
+            if (p.epi_flags & kEpiBias)
+                v += p.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[gn])
+                                    : static_cast<const float*>(p.bias)[gn];
+            if (p.epi_flags & kEpiGelu) v = gelu_tanh_precise(v);
+            *dst = v;
+        }
+    }
+}
+
+// ---- row softmax helpers (fp32 arithmetic; one warp per row) -----------------
+
+__device__ __forceinline__ float warp_reduce_max(float v) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_reduce_sum(float v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, int64_t i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, int64_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
+    return __bfloat162float(p[i]);
+}
+__device__ __forceinline__ void stf(float* p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, int64_t i, float v) {
+    p[i] = __float2bfloat16_rn(v);
+}
+
+template <typename T>
+__global__ void softmax_fwd_kernel(T* y, const T* x, int64_t rows, int64_t tq, int64_t tk,
+                                   int causal) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= rows) return;
+    const int lane = threadIdx.x % 32;
+    const int64_t limit = causal ? (row % tq) + 1 : tk;
+    const T* xr = x + row * tk;
+    T* yr = y + row * tk;
+    float mx = -INFINITY;
+    for (int64_t i = lane; i < limit; i += 32) mx = fmaxf(mx, ldf(xr, i));
+    mx = warp_reduce_max(mx);
+    float sum = 0.0f;
+    for (int64_t i = lane; i < limit; i += 32) sum += expf(ldf(xr, i) - mx);
+    sum = warp_reduce_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int64_t i = lane; i < tk; i += 32)
+        stf(yr, i, i < limit ? expf(ldf(xr, i) - mx) * inv : 0.0f);
+}
+
+template <typename T>
+__global__ void softmax_bwd_kernel(T* ds, const T* p, const T* dp, int64_t rows, int64_t tk) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= rows) return;
+    const int lane = threadIdx.x % 32;
+    const T* pr = p + row * tk;
+    const T* dr = dp + row * tk;
+    float dot = 0.0f;
+    for (int64_t i = lane; i < tk; i += 32) dot += ldf(pr, i) * ldf(dr, i);
+    dot = warp_reduce_sum(dot);
+    for (int64_t i = lane; i < tk; i += 32) stf(ds + row * tk, i, ldf(pr, i) * (ldf(dr, i) - dot));
+}
+
+}  // namespace
+
+cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream) {
+    dim3 grid(static_cast<unsigned>((p.n + TN - 1) / TN), static_cast<unsigned>((p.m + TM - 1) / TM),
+              static_cast<unsigned>(p.batch));
+    fp32_gemm_kernel<<<grid, 256, 0, stream>>>(p);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,
+                               int is_bf16, int causal, cudaStream_t stream) {
+    const int warps = 8;
+    const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+    if (is_bf16)
+        softmax_fwd_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+            static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), rows, tq, tk, causal);
+    else
+        softmax_fwd_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            static_cast<float*>(y), static_cast<const float*>(x), rows, tq, tk, causal);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
+                               int is_bf16, cudaStream_t stream) {
+    const int warps = 8;
+    const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+    if (is_bf16)
+        softmax_bwd_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+            static_cast<__nv_bfloat16*>(ds), static_cast<const __nv_bfloat16*>(p),
+            static_cast<const __nv_bfloat16*>(dp), rows, tk);
+    else
+        softmax_bwd_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            static_cast<float*>(ds), static_cast<const float*>(p), static_cast<const float*>(dp),
+            rows, tk);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+}  // namespace llmt_b200
