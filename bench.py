@@ -1,0 +1,467 @@
+#!/usr/bin/env python3
+"""Benchmark of the GEMM path: one "step" = the linear-layer GEMMs of a training
+step (forward, dX, dW+dbias for every layer) on synthetic seeded inputs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c5] [--impl reference]
+
+Workloads (shapes of BASELINE.json's configs):
+  c2  GPT-2-small, M = 8192 tokens per GPU, C = 768: QKV 768->2304, attention
+      out-proj 768->768, MLP fc 768->3072 (bias+GELU fused), MLP proj 3072->768;
+      bf16 operands, fp32 accumulation, bf16 activations, fp32 dW/dbias.
+  c5  GPT-2-XL MLP, C = 1600, 4C = 6400, M = 8192 tokens per GPU.
+With N > 1 every GPU runs the same per-GPU workload on its own token shard
+(weak scaling) and the fp32 dW/dbias span is summed with one NCCL all-reduce per
+step, overlapped with the dX GEMMs.
+
+Prints ONE JSON line. `value` is device-timed throughput with inputs resident in
+HBM; `e2e` is the same step called with HOST (pinned) buffers, copies included.
+`--impl reference` runs the unmodified llmt library (cuBLASLt, strict fp32 — the
+only precision llmt's matmul accepts) on the same shapes.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = {
+    "c2": dict(name="gpt2-small linear layers", C=768,
+               layers=[("qkv", 768, 2304, False), ("attn_out", 768, 768, False),
+                       ("mlp_fc", 768, 3072, True), ("mlp_proj", 3072, 768, False)]),
+    "c5": dict(name="gpt2-xl MLP", C=1600,
+               layers=[("mlp_fc", 1600, 6400, True), ("mlp_proj", 6400, 1600, False)]),
+}
+M_PER_GPU = 8192
+
+
+def step_flops(workload: str, m: int) -> float:
+    return sum(3 * 2.0 * m * i * o for _, i, o, _ in LAYERS[workload]["layers"])
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------- own arm ---
+
+class LinearStep:
+    """Device tensors and prebuilt C-ABI descriptors of one training step's GEMMs."""
+
+    def __init__(self, workload, m, dev, seed):
+        import torch
+        import llmt_b200 as L
+        from llmt_b200.dp import GradBucket
+        self.L, self.torch, self.m = L, torch, m
+        g = torch.Generator(device=dev).manual_seed(seed)
+        bf = torch.bfloat16
+        spec = LAYERS[workload]["layers"]
+        self.bucket = GradBucket({k: v for n, i, o, _ in spec
+                                  for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}, dev)
+        self.layers, self.calls = [], []
+        ws_need = 0
+        for n, i, o, gelu in spec:
+            t = dict(name=n, gelu=gelu, i=i, o=o)
+            t["x"] = torch.randn(m, i, device=dev, generator=g).to(bf)
+            t["w"] = (torch.randn(o, i, device=dev, generator=g) * 0.02).to(bf)
+            t["b"] = torch.randn(o, device=dev, generator=g) * 0.02
+            t["dy"] = (torch.randn(m, o, device=dev, generator=g) * 0.01).to(bf)
+            t["y"] = torch.empty(m, o, device=dev, dtype=bf)
+            t["dx"] = torch.empty(m, i, device=dev, dtype=bf)
+            t["dw"], t["db"] = self.bucket.view(n + ".dW"), self.bucket.view(n + ".dbias")
+            self.layers.append(t)
+        for t in self.layers:
+            fwd = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
+            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0, dbias=t["db"], dbias_beta=1.0)
+            dx = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
+            t["d_fwd"], t["d_dw"], t["d_dx"] = fwd, dw, dx
+            ws_need = max(ws_need, *(L.workspace_bytes(d) for d in (fwd, dw, dx)))
+        self.ws = torch.empty(max(ws_need, 256), dtype=torch.uint8, device=dev)
+        for t in self.layers:
+            for d in (t["d_fwd"], t["d_dw"], t["d_dx"]):
+                d.workspace, d.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        self.comm_stream = torch.cuda.Stream(device=dev)
+        self.grads_ready = torch.cuda.Event()
+
+    def gemm_list(self):
+        """(label, flops, desc, c, a, b) in launch order: forwards, then dW, then dX."""
+        out = []
+        for t in self.layers:
+            f = 2.0 * self.m * t["i"] * t["o"]
+            out.append((t["name"] + ".fwd", f, t["d_fwd"], t["y"], t["x"], t["w"]))
+        for t in reversed(self.layers):
+            f = 2.0 * self.m * t["i"] * t["o"]
+            out.append((t["name"] + ".dW", f, t["d_dw"], t["dw"], t["dy"], t["x"]))
+        for t in reversed(self.layers):
+            f = 2.0 * self.m * t["i"] * t["o"]
+            out.append((t["name"] + ".dX", f, t["d_dx"], t["dx"], t["dy"], t["w"]))
+        return out
+
+    def run(self, world, events=None):
+        """Enqueues one step on the current stream. With world > 1 the gradient span is
+        all-reduced on a side stream while the dX GEMMs run."""
+        torch, L = self.torch, self.L
+        self.bucket.zero_()
+        n_layers = len(self.layers)
+        for idx, (label, _, d, c, a, b) in enumerate(self.gemm_list()):
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            L.gemm_desc(d, c, a, b)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True); e1.record()
+                events.append((label, e0, e1))
+            if world > 1 and idx == 2 * n_layers - 1:  # last dW enqueued
+                self.grads_ready.record()
+                self.comm_stream.wait_event(self.grads_ready)
+                with torch.cuda.stream(self.comm_stream):
+                    self.bucket.allreduce()
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+
+class HostStep:
+    """The same step driven from HOST buffers: per step the layer inputs (x, dy) come from
+    pinned host memory and the reduced gradient span is read back."""
+
+    def __init__(self, step: LinearStep):
+        torch = step.torch
+        self.step = step
+        self.h_in = [(torch.empty_like(t[k], device="cpu").pin_memory().copy_(t[k]), t[k])
+                     for t in step.layers for k in ("x", "dy")]
+        self.h_grad = torch.empty_like(step.bucket.flat, device="cpu").pin_memory()
+        self.h2d_bytes = sum(h.numel() * h.element_size() for h, _ in self.h_in)
+        self.d2h_bytes = self.h_grad.numel() * 4
+
+    def run(self, world):
+        for h, d in self.h_in:
+            d.copy_(h, non_blocking=True)
+        self.step.run(world)
+        self.h_grad.copy_(self.step.bucket.flat, non_blocking=True)
+
+
+def cpu_baseline(workload, budget_s=12.0):
+    """The C port of the path (oracle/oracle.c, fp32 arithmetic, OpenMP) timed on this
+    host's cores on a bounded sample: the first 256 token rows of every GEMM of the step."""
+    import numpy as np
+    from oracle import oracle
+    rows = 256
+    rng = np.random.default_rng(0)
+    spec = LAYERS[workload]["layers"]
+    data = []
+    for _, i, o, _g in spec:
+        data.append((rng.standard_normal((rows, i)).astype(np.float32),
+                     (rng.standard_normal((o, i)) * 0.02).astype(np.float32),
+                     (rng.standard_normal((rows, o)) * 0.01).astype(np.float32)))
+    flops = step_flops(workload, rows)
+
+    def one_pass():
+        for x, w, dy in data:
+            oracle.gemm_f32(x, w, False, True)          # fwd
+            oracle.gemm_f32(dy, w, False, False)        # dX
+            oracle.gemm_f32(dy, x, True, False)         # dW
+    one_pass()
+    best, t_total, n = 1e30, 0.0, 0
+    while t_total < budget_s and n < 50:
+        t0 = time.perf_counter(); one_pass(); dt = time.perf_counter() - t0
+        best = min(best, dt); t_total += dt; n += 1
+    out = {"value": round(flops / best / 1e12, 4), "unit": "TFLOP/s", "cores": oracle.num_threads(),
+           "kind": "port",
+           "sample": f"first {rows} token rows of every GEMM of the step ({flops / 1e9:.1f} GFLOP), "
+                     f"best of {n} passes, fp32 OpenMP C port"}
+    try:  # PyTorch on CPU is the oracle llmt's own golden files were made with (tools/gen_golden.py)
+        import torch
+        tx = [(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(dy)) for x, w, dy in data]
+
+        def torch_pass():
+            for x, w, dy in tx:
+                x @ w.T; dy @ w; dy.T @ x
+        torch_pass()
+        tb = 1e30
+        for _ in range(10):
+            t0 = time.perf_counter(); torch_pass(); tb = min(tb, time.perf_counter() - t0)
+        out["torch_cpu_tflops"] = round(flops / tb / 1e12, 4)
+        out["torch_cpu_threads"] = torch.get_num_threads()
+    except Exception:
+        pass
+    return out
+
+
+# --------------------------------------------------------------- reference arm ---
+
+class ReferenceStep:
+    """The same GEMMs through the unmodified llmt library: kernels::matmul (cuBLASLt, strict
+    fp32), GELU as llmt's separate kernel (src/layers/mlp.cpp:14-18), no bias (llmt has none)."""
+
+    def __init__(self, workload, m, dev, seed):
+        import torch
+        from oracle import llmt_ref
+        self.torch = torch
+        self.ref = llmt_ref.Llmt(dev.index or 0)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.layers = []
+        for n, i, o, gelu in LAYERS[workload]["layers"]:
+            t = dict(name=n, gelu=gelu)
+            t["x"] = torch.randn(m, i, device=dev, generator=g)
+            t["w"] = torch.randn(o, i, device=dev, generator=g) * 0.02
+            t["dy"] = torch.randn(m, o, device=dev, generator=g) * 0.01
+            t["y"] = torch.empty(m, o, device=dev)
+            t["dx"] = torch.empty(m, i, device=dev)
+            t["dw"] = torch.zeros(o, i, device=dev)
+            self.layers.append(t)
+
+    def run(self):
+        r = self.ref
+        for t in self.layers:
+            r.matmul(t["y"], t["x"], t["w"], False, True)
+            if t["gelu"]:
+                r.gelu(t["y"], t["y"])
+        for t in reversed(self.layers):
+            t["dw"].zero_()
+            r.matmul(t["dw"], t["dy"], t["x"], True, False, 1.0, 1.0)
+        for t in reversed(self.layers):
+            r.matmul(t["dx"], t["dy"], t["w"], False, False)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import llmt_ref
+    flops = step_flops(args.workload, M_PER_GPU)
+    base = {"impl": "reference", "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job",
+            "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {LAYERS[args.workload]['name']}, "
+                                   f"M={M_PER_GPU} tokens, fwd+dX+dW per layer",
+                       "l2": "working set larger than L2"}}
+    try:
+        import torch
+        have_gpu = torch.cuda.is_available()
+    except Exception:
+        have_gpu = False
+    if not (have_gpu and llmt_ref.available()):
+        # llmt's matmul path is a GPU library call; without its build (or a GPU) the
+        # C port on the host cores stands in.
+        cb = cpu_baseline(args.workload)
+        base.update({"value": cb["value"], "dtype": "f32", "ms_per_step": None, "cpu_baseline": cb,
+                     "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0},
+                     "note": "llmt build or GPU unavailable: CPU port of the path timed instead"})
+        print(json.dumps(base))
+        return 0
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    step = ReferenceStep(args.workload, M_PER_GPU, dev, seed=0)
+    for _ in range(max(args.warmup, 3)):
+        step.run()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0); sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step.run()
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # end to end: fp32 host inputs in, gradients out
+    h_in = [(torch.empty_like(t[k], device="cpu").pin_memory().copy_(t[k]), t[k])
+            for t in step.layers for k in ("x", "dy")]
+    h_out = [torch.empty_like(t["dw"], device="cpu").pin_memory() for t in step.layers]
+
+    def host_step():
+        for h, d in h_in:
+            d.copy_(h, non_blocking=True)
+        step.run()
+        for h, t in zip(h_out, step.layers):
+            h.copy_(t["dw"], non_blocking=True)
+    host_step(); torch.cuda.synchronize()
+    n_e2e = max(2, min(args.steps, 5))
+    e0.record()
+    for _ in range(n_e2e):
+        host_step()
+    e1.record(); torch.cuda.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    clocks = sampler.stop()
+    v = flops / ms / 1e9
+    base.update({
+        "value": round(v, 2), "ms_per_step": round(ms, 4), "dtype": "f32",
+        "device": "gpu (llmt's matmul is cuBLASLt; llmt has no CPU implementation of this path)",
+        "cpu_baseline": {"value": round(v, 2), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                         "sample": "unmodified llmt library (oracle/_ref) on the GPU, full step"},
+        "e2e": {"value": round(flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": sum(h.numel() * 4 for h, _ in h_in),
+                "d2h_bytes_per_step": sum(h.numel() * 4 for h in h_out)},
+        "clocks": clocks})
+    print(json.dumps(base))
+    return 0
+
+
+# ------------------------------------------------------------------------ main ---
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", choices=sorted(LAYERS), default="c2")
+    ap.add_argument("--impl", choices=["own", "reference"], default="own")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import llmt_b200 as L
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    L.lib()  # fail loudly if the CUDA library is missing
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    step = LinearStep(args.workload, M_PER_GPU, dev, seed=rank)
+    flops = step_flops(args.workload, M_PER_GPU)
+    for _ in range(args.warmup):
+        step.run(world)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.launch_count()
+    events = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step.run(world, events)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = L.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    L.device_status()
+
+    # per-GEMM device time inside the timed region
+    per = {}
+    for label, a, b in events:
+        per.setdefault(label, []).append(a.elapsed_time(b))
+    gemm_ms = sum(sum(v) / len(v) for v in per.values())
+    gl = {lab: f for lab, f, *_ in step.gemm_list()}
+    per_gemm = {lab: round(gl[lab] / (sum(v) / len(v)) / 1e9, 1) for lab, v in per.items()}
+
+    # end to end from host buffers
+    hs = HostStep(step)
+    hs.run(world); barrier()
+    n_e2e = max(2, min(args.steps, 10))
+    e0.record()
+    for _ in range(n_e2e):
+        hs.run(world)
+    e1.record(); barrier()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+
+    t = torch.tensor([ms, ms_e2e, gemm_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms, ms_e2e, gemm_ms = (float(x) for x in t.cpu())
+    if rank == 0:
+        peak_tf, peak_bw, which = measured_peaks()
+        achieved = flops / gemm_ms / 1e9
+        line = {
+            "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job", "value": round(world * flops / ms / 1e9, 2),
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {LAYERS[args.workload]['name']}, "
+                                   f"M={M_PER_GPU} tokens per GPU, fwd+dX+dW(+dbias) per layer, "
+                                   f"bias+GELU fused in mlp_fc",
+                       "per_gpu_gflop_per_step": round(flops / 1e9, 1),
+                       "allreduce_bytes_per_step": step.bucket.nbytes() if world > 1 else 0,
+                       "l2": "working set (~400 MB of activations per step) larger than L2"},
+            "per_gpu_tflops": round(flops / ms / 1e9, 2),
+            "pct_of_bf16_peak": round(100.0 * flops / ms / 1e9 / peak_tf, 1),
+            "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": None,
+                         "peak_source": f"of {which}",
+                         "kernel": "tc_gemm_kernel (all GEMM launches of the step, device time)"},
+            "per_gemm_tflops": per_gemm,
+            "e2e": {"value": round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.workload)
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -73,6 +73,9 @@ enum llmt_b200_status {
  *   dbias        optional fp32 [m]:  dbias[i] = dbias_beta * dbias[i] + sum_p op(A)[i,p].
  *                For llmt's dW call (src/layers/linear.cpp:27-29: A = dy, trans_a = 1)
  *                this is the bias gradient, summed over tokens.  bf16 path only.
+ *   plan_*       tuning overrides of the tile width and split-K factor; 0 leaves the
+ *                choice to the library (the default plan is a pure function of the
+ *                problem, so results stay reproducible either way).
  *   workspace    device scratch for split-K partial sums; llmt_b200_gemm_workspace_bytes()
  *                gives the size this problem needs (0 for most problems).  Plays the role
  *                of RunCtx::blas_workspace (include/llmt/core/run_ctx.h:35-36).
@@ -89,6 +92,8 @@ typedef struct llmt_b200_gemm_desc {
     const void* bias;
     float* dbias;
     float dbias_beta;
+    int32_t plan_tile_n;   /* 0 = choose; else force the tile width: 64, 128, 192 or 256 */
+    int32_t plan_splits;   /* 0 = choose; else force the split-K factor (>= 1) */
     int32_t reserved0;
     void* workspace;
     uint64_t workspace_bytes;

@@ -81,6 +81,44 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+CPP_DIR = os.path.join(HERE, "cpp")
+CPP_SOURCES = ["runtime.cpp", "matmul.cpp", "layers.cpp", "attention.cpp"]
+HOST_LIB = os.path.join(LIB_DIR, "libllmt_b200_host.so")
+ROOT = os.path.dirname(HERE)
+CPP_TEST_SRC = os.path.join(ROOT, "tests", "cpp", "test_llmt_goldens.cpp")
+CPP_TEST_BIN = os.path.join(ROOT, "tests", "cpp", "_build", "test_llmt_goldens")
+
+
+def build_cpp(force: bool = False) -> str:
+    """Builds the C++ interface library (llmt's matmul / Linear / MLP / attention
+    API over the C ABI) and the golden-test binary that exercises it."""
+    build_library()
+    inc = [os.path.join(CPP_DIR, "include"), os.path.join(ROOT, "include")]
+    srcs = [os.path.join(CPP_DIR, "src", s) for s in CPP_SOURCES]
+    hdrs = []
+    for base, _d, files in os.walk(inc[0]):
+        hdrs += [os.path.join(base, f) for f in files]
+    flags = ["-std=c++20", "-O2", "-Wno-deprecated-gpu-targets", "-Xcompiler", "-fPIC,-Wall,-Wextra"] + [f"-I{i}" for i in inc]
+    rpath = ["-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    if force or _stale(HOST_LIB, srcs + hdrs + [LIB_PATH]):
+        cmd = [nvcc(), *flags, "-shared", "-o", HOST_LIB, *srcs, f"-L{LIB_DIR}", "-lllmt_b200", *rpath]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("C++ interface library failed to build")
+    os.makedirs(os.path.dirname(CPP_TEST_BIN), exist_ok=True)
+    if force or _stale(CPP_TEST_BIN, [CPP_TEST_SRC, HOST_LIB]):
+        cmd = [nvcc(), *flags, "-o", CPP_TEST_BIN, CPP_TEST_SRC, f"-L{LIB_DIR}", "-lllmt_b200_host",
+               "-lllmt_b200", "-Xlinker", "-rpath", "-Xlinker", LIB_DIR,
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../llmt_b200/lib"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("C++ golden test failed to build")
+    return CPP_TEST_BIN
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    print(build_cpp(force="--force" in sys.argv))

@@ -15,7 +15,8 @@
 
 namespace llmt {
 
-enum class Role : uint8_t { Matrix, ResidualProj, Embedding, Gain, Bias };
+// First four values as in llmt (param_store.h: Role); Bias is the extension.
+enum class Role : uint8_t { Embedding, Matrix, ResidualProj, Norm, Bias };
 enum class StateKind : uint8_t { Weight, Grad };
 
 struct StateDtypes {

@@ -1,0 +1,84 @@
+// Attention forward/backward as compositions of the strided-batched GEMMs and
+// the masked softmax helpers (llmt src/kernels/attention.cpp:34-64; backward
+// products from llmt docs/TODO.md:226-228).
+#include <cmath>
+#include <initializer_list>
+
+#include "llmt/core/error.h"
+#include "llmt/kernels/attention.h"
+#include "llmt/kernels/matmul.h"
+#include "llmt_b200.h"
+
+namespace llmt::kernels {
+
+namespace {
+// [B,H,T,x] -> [B*H,T,x]: same bytes (llmt attention.cpp:28-30).
+Tensor fold(const Tensor& t) noexcept {
+    Tensor r = t;
+    r.shape = Shape{t.shape[0] * t.shape[1], t.shape[2], t.shape[3]};
+    return r;
+}
+}  // namespace
+
+void softmax_fwd(const RunCtx& ctx, Tensor& y, const Tensor& x, MaskSpec mask) noexcept {
+    if (x.shape.rank != 3) detail::fatal("softmax_fwd", "x must be [batch, Tq, Tk]");
+    if (y.shape != x.shape) detail::fatal("softmax_fwd", "y/x shape mismatch");
+    if (y.dtype != x.dtype) detail::fatal("softmax_fwd", "y/x dtype mismatch");
+    if (!y.valid() || !x.valid()) detail::fatal("softmax_fwd", "invalid tensor (null data)");
+    const int st = llmt_b200_softmax_fwd(y.data, x.data, x.shape[0] * x.shape[1], x.shape[1], x.shape[2],
+                                         static_cast<int32_t>(x.dtype), mask.kind == MaskKind::Causal,
+                                         ctx.stream);
+    if (st != LLMT_B200_OK) detail::fatal("softmax_fwd", "%s", llmt_b200_last_error());
+}
+
+void attention_fwd(const RunCtx& ctx, Tensor& y, Tensor& scores, Tensor& y_heads, const Tensor& q,
+                   const Tensor& k, const Tensor& v, MaskSpec mask) noexcept {
+    if (ctx.backend != KernelBackend::Naive) detail::fatal("attention_fwd", "no fused variant implemented yet");
+    for (const Tensor* t : std::initializer_list<const Tensor*>{&scores, &y_heads, &q, &k, &v}) {
+        if (!t->valid()) detail::fatal("attention_fwd", "invalid tensor (null data)");
+        if (t->shape.rank != 4) detail::fatal("attention_fwd", "expected rank-4 head tensors");
+    }
+    if (k.shape != q.shape || v.shape != q.shape || y_heads.shape != q.shape)
+        detail::fatal("attention_fwd", "q/k/v/y_heads must share one [B, H, T, hd] shape");
+    const int64_t b = q.shape[0], h = q.shape[1], t = q.shape[2], hd = q.shape[3];
+    if (scores.shape != Shape{b, h, t, t}) detail::fatal("attention_fwd", "scores must be [B, H, T, T]");
+    Tensor s3 = fold(scores), o3 = fold(y_heads);
+    const Tensor q3 = fold(q), k3 = fold(k), v3 = fold(v);
+    matmul(ctx, s3, q3, k3, false, true, 1.0f / std::sqrt(static_cast<float>(hd)), 0.0f);
+    softmax_fwd(ctx, s3, s3, mask);
+    matmul(ctx, o3, s3, v3, false, false, 1.0f, 0.0f);
+    if (y.data != nullptr) {
+        if (y.shape != Shape{b, t, h * hd}) detail::fatal("attention_fwd", "y must be [B, T, H·hd]");
+        // Head merge [B,H,T,hd] -> [B,T,H*hd]: a strided copy per (batch, head).
+        const size_t es = dtype_size(y.dtype);
+        for (int64_t bi = 0; bi < b; ++bi)
+            for (int64_t hi = 0; hi < h; ++hi) {
+                const char* src = static_cast<const char*>(y_heads.data) + ((bi * h + hi) * t * hd) * es;
+                char* dst = static_cast<char*>(y.data) + (bi * t * h * hd + hi * hd) * es;
+                CUDA_CHECK(cudaMemcpy2DAsync(dst, h * hd * es, src, hd * es, hd * es, t,
+                                             cudaMemcpyDeviceToDevice, ctx.stream));
+            }
+    }
+}
+
+void attention_bwd(const RunCtx& ctx, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dscores,
+                   const Tensor& d_y_heads, const Tensor& probs, const Tensor& q, const Tensor& k,
+                   const Tensor& v) noexcept {
+    for (const Tensor* t :
+         std::initializer_list<const Tensor*>{&dq, &dk, &dv, &dscores, &d_y_heads, &probs, &q, &k, &v}) {
+        if (!t->valid()) detail::fatal("attention_bwd", "invalid tensor (null data)");
+        if (t->shape.rank != 4) detail::fatal("attention_bwd", "expected rank-4 head tensors");
+    }
+    const float scale = 1.0f / std::sqrt(static_cast<float>(q.shape[3]));
+    Tensor dq3 = fold(dq), dk3 = fold(dk), dv3 = fold(dv), ds3 = fold(dscores);
+    const Tensor do3 = fold(d_y_heads), p3 = fold(probs), q3 = fold(q), k3 = fold(k), v3 = fold(v);
+    matmul(ctx, dv3, p3, do3, true, false, 1.0f, 0.0f);   // dV = P^T dO
+    matmul(ctx, ds3, do3, v3, false, true, 1.0f, 0.0f);   // dP = dO V^T
+    const int st = llmt_b200_softmax_bwd(ds3.data, p3.data, ds3.data, p3.shape[0] * p3.shape[1],
+                                         p3.shape[2], static_cast<int32_t>(p3.dtype), ctx.stream);
+    if (st != LLMT_B200_OK) detail::fatal("attention_bwd", "%s", llmt_b200_last_error());
+    matmul(ctx, dq3, ds3, k3, false, false, scale, 0.0f);  // dQ = a dS K
+    matmul(ctx, dk3, ds3, q3, true, false, scale, 0.0f);   // dK = a dS^T Q
+}
+
+}  // namespace llmt::kernels

@@ -1,0 +1,46 @@
+// Linear and MLP over kernels::matmul (llmt src/layers/linear.cpp:12-30,
+// src/layers/mlp.cpp:10-18) with the optional bias / fused-GELU extensions.
+#include <utility>
+
+#include "llmt/kernels/matmul.h"
+#include "llmt/layers/linear.h"
+#include "llmt/layers/mlp.h"
+
+namespace llmt {
+
+Linear::Linear(ParamStore& ps, std::string name, int64_t in_features, int64_t out_features, Role role,
+               bool bias) noexcept
+    : weight_(ps.add(name, {out_features, in_features}, role)),
+      bias_(bias ? &ps.add(name + ".bias", {out_features}, Role::Bias) : nullptr) {}
+
+void Linear::forward(const RunCtx& ctx, Tensor& y, const Tensor& x) const noexcept {
+    kernels::Epilogue epi;
+    if (bias_ != nullptr) epi.bias = &bias_->weight;
+    kernels::matmul_ex(ctx, y, x, weight_.weight, false, true, 1.0f, 0.0f, epi);  // y = x W^T (+ b)
+}
+
+void Linear::forward_gelu(const RunCtx& ctx, Tensor& y, const Tensor& x) const noexcept {
+    kernels::Epilogue epi;
+    if (bias_ != nullptr) epi.bias = &bias_->weight;
+    epi.gelu = true;
+    kernels::matmul_ex(ctx, y, x, weight_.weight, false, true, 1.0f, 0.0f, epi);
+}
+
+void Linear::backward(const RunCtx& ctx, Tensor& dx, const Tensor& dy, const Tensor& x) const noexcept {
+    kernels::matmul(ctx, dx, dy, weight_.weight, false, false, 1.0f, 0.0f);       // dx = dy W
+    kernels::Epilogue epi;
+    // The fused dbias exists on the bf16 path; the bias gradient always accumulates.
+    if (bias_ != nullptr && dy.dtype == DType::BF16) epi.dbias = &bias_->grad;
+    kernels::matmul_ex(ctx, weight_.grad, dy, x, true, false, 1.0f, 1.0f, epi);   // dW += dy^T x
+}
+
+MLP::MLP(ParamStore& ps, const std::string& name, int64_t d_model, int64_t d_ff, bool bias) noexcept
+    : up_(ps, name + ".up", d_model, d_ff, Role::Matrix, bias),
+      down_(ps, name + ".down", d_ff, d_model, Role::ResidualProj, bias) {}
+
+void MLP::forward(const RunCtx& ctx, Tensor& y, Tensor& h, const Tensor& x) const noexcept {
+    up_.forward_gelu(ctx, h, x);  // h = gelu(x Wup^T): GELU in the GEMM epilogue, h ends post-GELU
+    down_.forward(ctx, y, h);     // y = h Wdown^T
+}
+
+}  // namespace llmt

@@ -1,0 +1,112 @@
+// kernels::matmul over the llmt_b200 C ABI.  The validation order and the abort
+// messages follow llmt's check() (src/kernels/matmul.cpp:175-214) so a caller
+// sees the same behaviour; the product itself is llmt_b200_gemm.
+#include <string>
+
+#include "llmt/core/error.h"
+#include "llmt/kernels/algo_cache.h"
+#include "llmt/kernels/matmul.h"
+#include "llmt_b200.h"
+
+namespace llmt::kernels {
+
+namespace {
+
+struct Problem {
+    int64_t m, n, k, batch, stride_a, stride_b, stride_c;
+};
+
+Problem check(const Tensor& c, const Tensor& a, const Tensor& b, bool trans_a, bool trans_b) noexcept {
+    const int rank = c.shape.rank;
+    if (rank != 2 && rank != 3) detail::fatal("matmul", "expected rank-2 or rank-3 tensors (got %d)", rank);
+    if (a.shape.rank != rank || b.shape.rank != rank) detail::fatal("matmul", "mixed ranks in one matmul");
+    if (a.dtype != b.dtype) detail::fatal("matmul", "mixed dtypes in one matmul");
+    if (!c.valid() || !a.valid() || !b.valid()) detail::fatal("matmul", "invalid tensor (null data)");
+    if (a.dtype != DType::FP32 && a.dtype != DType::BF16)
+        detail::fatal("matmul", "dtype %s not yet supported", dtype_name(a.dtype));
+    if (a.dtype == DType::FP32 && c.dtype != DType::FP32) detail::fatal("matmul", "mixed dtypes in one matmul");
+    if (c.dtype != DType::FP32 && c.dtype != DType::BF16)
+        detail::fatal("matmul", "dtype %s not yet supported", dtype_name(c.dtype));
+    const int r = rank - 2;
+    Problem p{};
+    p.m = trans_a ? a.shape[r + 1] : a.shape[r];
+    p.k = trans_a ? a.shape[r] : a.shape[r + 1];
+    const int64_t kb = trans_b ? b.shape[r + 1] : b.shape[r];
+    p.n = trans_b ? b.shape[r] : b.shape[r + 1];
+    if (p.k != kb)
+        detail::fatal("matmul", "inner dims disagree: %lld vs %lld", static_cast<long long>(p.k),
+                      static_cast<long long>(kb));
+    if (c.shape[r] != p.m || c.shape[r + 1] != p.n) detail::fatal("matmul", "C shape mismatch");
+    p.batch = 1;
+    if (rank == 3) {
+        p.batch = a.shape[0];
+        if (b.shape[0] != p.batch || c.shape[0] != p.batch) detail::fatal("matmul", "batch sizes disagree");
+        p.stride_a = a.shape[1] * a.shape[2];
+        p.stride_b = b.shape[1] * b.shape[2];
+        p.stride_c = c.shape[1] * c.shape[2];
+    }
+    return p;
+}
+
+// The precision policy must name the arithmetic the operand dtype implies
+// (llmt's single capability guard, matmul.cpp:72-77, extended by the bf16 mode).
+void check_policy(const RunCtx& ctx, DType ab) noexcept {
+    const PrecisionPolicy& pp = ctx.precision;
+    const bool ok = (ab == DType::FP32 && pp.gemm_compute == DType::FP32 && pp.reduce == DType::FP32) ||
+                    (ab == DType::BF16 && pp.gemm_compute == DType::BF16 && pp.reduce == DType::FP32);
+    if (!ok)
+        detail::fatal("matmul", "gemm_compute/reduce precision %s/%s not yet supported for %s operands",
+                      dtype_name(pp.gemm_compute), dtype_name(pp.reduce), dtype_name(ab));
+}
+
+}  // namespace
+
+void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
+               bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept {
+    const Problem p = check(c, a, b, trans_a, trans_b);
+    check_policy(ctx, a.dtype);
+    const int r = c.shape.rank - 2;
+    llmt_b200_gemm_desc d{};
+    d.m = p.m; d.n = p.n; d.k = p.k; d.batch = p.batch;
+    d.lda = a.shape[r + 1]; d.ldb = b.shape[r + 1]; d.ldc = c.shape[r + 1];  // contiguous views
+    d.stride_a = p.stride_a; d.stride_b = p.stride_b; d.stride_c = p.stride_c;
+    d.trans_a = trans_a; d.trans_b = trans_b;
+    d.dtype_ab = static_cast<int32_t>(a.dtype);
+    d.dtype_c = static_cast<int32_t>(c.dtype);
+    d.alpha = alpha; d.beta = beta;
+    if (epi.bias != nullptr) {
+        if (!epi.bias->valid() || epi.bias->numel() != p.n) detail::fatal("matmul", "bias must be [N]");
+        d.epilogue |= LLMT_B200_EPI_BIAS;
+        d.bias = epi.bias->data;
+        d.bias_dtype = static_cast<int32_t>(epi.bias->dtype);
+    }
+    if (epi.gelu) d.epilogue |= LLMT_B200_EPI_GELU;
+    if (epi.dbias != nullptr) {
+        if (!epi.dbias->valid() || epi.dbias->numel() != p.m || epi.dbias->dtype != DType::FP32)
+            detail::fatal("matmul", "dbias must be fp32 [M]");
+        d.dbias = static_cast<float*>(epi.dbias->data);
+        d.dbias_beta = epi.dbias_beta;
+    }
+    d.workspace = ctx.blas_workspace;
+    d.workspace_bytes = ctx.blas_workspace_bytes;
+    if (ctx.algo_cache != nullptr) {
+        const AlgoKey key{p.m, p.n, p.k, p.batch, (trans_a ? 1LL : 0LL) | (trans_b ? 2LL : 0LL),
+                          static_cast<int64_t>(a.dtype), static_cast<int64_t>(c.dtype),
+                          static_cast<int64_t>(d.epilogue) | (d.dbias != nullptr ? 4LL : 0LL)};
+        auto& map = ctx.algo_cache->map;
+        if (map.find(key) == map.end()) {
+            char buf[256];
+            llmt_b200_gemm_plan(&d, buf, sizeof buf);
+            map.emplace(key, std::string(buf));
+        }
+    }
+    const int st = llmt_b200_gemm(&d, c.data, a.data, b.data, ctx.stream);
+    if (st != LLMT_B200_OK) detail::fatal("matmul", "%s", llmt_b200_last_error());
+}
+
+void matmul(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
+            bool trans_b, float alpha, float beta) noexcept {
+    matmul_ex(ctx, c, a, b, trans_a, trans_b, alpha, beta, Epilogue{});
+}
+
+}  // namespace llmt::kernels

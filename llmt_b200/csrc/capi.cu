@@ -75,7 +75,8 @@ int choose_splits(int64_t tiles, int kblocks_total, int sms) {
     return splits;
 }
 
-TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms) {
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
+                 int force_bn = 0, int force_splits = 0) {
     TcPlan pl{};
     const int cands[4] = {256, 192, 128, 64};
     const int tiles_m = static_cast<int>((m + 127) / 128);
@@ -84,10 +85,12 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
     int64_t best_cost = 0;
     for (int bn : cands) {
         if (dbias && bn > 192) continue;
+        if (force_bn != 0 && bn != force_bn) continue;
         // Never pick a tile wider than needed when a narrower one covers n in one column.
-        if (bn > 64 && n <= bn - 64) continue;
+        if (force_bn == 0 && bn > 64 && n <= bn - 64) continue;
         const int64_t tiles = static_cast<int64_t>(tiles_m) * ((n + bn - 1) / bn) * batch;
-        const int splits = choose_splits(tiles, kblocks_total, sms);
+        int splits = force_splits > 0 ? force_splits : choose_splits(tiles, kblocks_total, sms);
+        if (splits > kblocks_total) splits = kblocks_total > 0 ? kblocks_total : 1;
         const int kps = (kblocks_total + splits - 1) / splits;
         const int64_t waves = (tiles * splits + sms - 1) / sms;
         // Estimated cycles: main loops, plus one pass over the partial sums when split.
@@ -162,6 +165,12 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
             d->stride_c < (d->m - 1) * d->ldc + d->n)
             return fail(LLMT_B200_ERR_INVALID, "matmul: batch stride smaller than one matrix");
     }
+    if (d->plan_tile_n != 0 && d->plan_tile_n != 64 && d->plan_tile_n != 128 &&
+        d->plan_tile_n != 192 && d->plan_tile_n != 256)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: plan_tile_n must be 0, 64, 128, 192 or 256");
+    if (d->plan_tile_n == 256 && d->dbias != nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: the fused dbias needs plan_tile_n <= 192");
+    if (d->plan_splits < 0) return fail(LLMT_B200_ERR_INVALID, "matmul: negative plan_splits");
     if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU)) != 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: unknown epilogue flags 0x%x", d->epilogue);
     if ((d->epilogue & LLMT_B200_EPI_BIAS) && d->bias == nullptr)
@@ -226,7 +235,7 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
                     "matmul: bf16 row pitch / batch stride must be a multiple of 8 elements "
                     "(lda=%lld ldb=%lld)", (long long)d->lda, (long long)d->ldb);
     const bool dbias = d->dbias != nullptr;
-    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, dbias, sm_count());
+    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, dbias, sm_count(), d->plan_tile_n, d->plan_splits);
     if (pl.workspace_bytes > 0) {
         if (d->workspace == nullptr || d->workspace_bytes < pl.workspace_bytes)
             return fail(LLMT_B200_ERR_WORKSPACE, "matmul: split-K needs %llu workspace bytes, got %llu",
@@ -337,7 +346,8 @@ uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
     if (d == nullptr || d->dtype_ab != LLMT_B200_BF16 || d->m <= 0 || d->n <= 0 || d->k <= 0 ||
         d->batch <= 0)
         return 0;
-    return make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count()).workspace_bytes;
+    return make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(), d->plan_tile_n,
+                     d->plan_splits).workspace_bytes;
 }
 
 int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
@@ -347,7 +357,8 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
                  (long long)((d->n + 63) / 64), (long long)((d->m + 63) / 64), (long long)d->batch);
         return LLMT_B200_OK;
     }
-    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count());
+    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(), d->plan_tile_n,
+                     d->plan_splits);
     snprintf(buf, n, "tcgen05 tile=128x%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
              pl.bn, pl.stages, pl.splits, pl.tiles_m, pl.tiles_n, pl.kblocks_total, pl.grid,
              pl.smem_bytes, pl.workspace_bytes);

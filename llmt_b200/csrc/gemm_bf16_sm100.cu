@@ -5,8 +5,9 @@
 //   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma / tcgen05.commit; the
 //                               warp also owns the TMEM allocation)
-//   warps 2-5   epilogue       (tcgen05.ld the accumulator, apply
-//                               alpha/beta/bias/GELU/cast, store C)
+//   warps 2-9   epilogue       (tcgen05.ld the accumulator, apply
+//                               alpha/beta/bias/GELU/cast, store C; two warps per
+//                               TMEM lane quarter, each taking half the columns)
 //
 // Two rings of mbarriers connect them: full/empty per shared-memory stage and
 // full/empty per TMEM accumulator buffer (two buffers, so the epilogue of tile
@@ -34,11 +35,15 @@ namespace {
 constexpr int BM = 128;  // UMMA M (cta_group::1)
 constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATileBytes = BM * BK * 2;
 constexpr uint32_t kBlock64Bytes = 64 * BK * 2;  // one 64-wide MN-major block of a stage
-constexpr uint32_t kOnesBytes = 64 * 128;        // all-ones tile for the fused dbias MMA
+// Fused dbias: every pipeline stage carries one extra 64-wide block of bf16 ones
+// right behind its B tile, so that a tile of the first tile column can run its
+// MMAs with N = BN + 16 and receive sum_k op(A)[row, k] in accumulator column BN.
+constexpr uint32_t kOnesBytes = 64 * 128;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kDbiasCols = 16;
 
@@ -124,6 +129,38 @@ __device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* dst, const float
     }
 }
 
+
+__device__ __forceinline__ void load_chunk_f32(const float* src, float* dst, int valid) {
+    if (valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(src + j);
+            dst[j] = t.x; dst[j + 1] = t.y; dst[j + 2] = t.z; dst[j + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = j < valid ? src[j] : 0.0f;
+    }
+}
+
+__device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float* dst, int valid) {
+    if (valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            const uint4 u = *reinterpret_cast<const uint4*>(src + j);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                dst[j + 2 * q] = __uint_as_float(w[q] << 16);
+                dst[j + 2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = j < valid ? __bfloat162float(src[j]) : 0.0f;
+    }
+}
+
 template <int BN, int A_MN, int B_MN, int DBIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -131,20 +168,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width");
     static_assert(!DBIAS || BN <= 192, "dbias columns need room in TMEM");
     constexpr uint32_t kBTileBytes = BN * BK * 2;
-    constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
-    constexpr uint32_t kAccCols = 2 * BN + (DBIAS ? 2 * kDbiasCols : 0);
+    constexpr uint32_t kLoadBytes = kATileBytes + kBTileBytes;  // what TMA brings per stage
+    constexpr uint32_t kStageBytes = kLoadBytes + (DBIAS ? kOnesBytes : 0);
+    constexpr uint32_t kAccStride = BN + (DBIAS ? kDbiasCols : 0);  // TMEM columns per accumulator
+    constexpr uint32_t kAccCols = 2 * kAccStride;
     constexpr uint32_t kTmemCols = kAccCols <= 128 ? 128 : (kAccCols <= 256 ? 256 : 512);
     constexpr uint32_t kIdesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
-    constexpr uint32_t kIdescDbias = make_idesc_bf16(BM, kDbiasCols, A_MN, B_MN);
+    constexpr uint32_t kIdescDbias = make_idesc_bf16(BM, BN + kDbiasCols, A_MN, B_MN);
 
     extern __shared__ uint8_t smem_raw[];
     // Swizzled tiles need 1024-byte alignment.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t tiles_end = smem_base + static_cast<uint32_t>(stages) * kStageBytes;
-    const uint32_t ones_base = tiles_end;  // only when DBIAS
-    Control* ctl = reinterpret_cast<Control*>(smem_gen + static_cast<size_t>(stages) * kStageBytes +
-                                              (DBIAS ? kOnesBytes : 0));
+    Control* ctl = reinterpret_cast<Control*>(smem_gen + static_cast<size_t>(stages) * kStageBytes);
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -157,7 +193,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
-            mbar_init(smem_u32(&ctl->tmem_empty[a]), 4);
+            mbar_init(smem_u32(&ctl->tmem_empty[a]), kEpilogueWarps);
         }
         ctl->abort_flag = 0;
         fence_barrier_init();
@@ -165,10 +201,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         prefetch_tensormap(&map_b);
     }
     if (DBIAS) {
-        // bf16 1.0 everywhere: the tile reads the same under any swizzle or major.
-        uint32_t* ones = reinterpret_cast<uint32_t*>(smem_gen + static_cast<size_t>(stages) * kStageBytes);
-        for (int i = threadIdx.x; i < static_cast<int>(kOnesBytes / 4); i += kThreads)
-            ones[i] = 0x3F803F80u;
+        // bf16 1.0 everywhere: the block reads the same under any swizzle or major.
+        for (int st = 0; st < stages; ++st) {
+            uint32_t* ones = reinterpret_cast<uint32_t*>(smem_gen + static_cast<size_t>(st) * kStageBytes +
+                                                         kLoadBytes);
+            for (int i = threadIdx.x; i < static_cast<int>(kOnesBytes / 4); i += kThreads)
+                ones[i] = 0x3F803F80u;
+        }
         fence_proxy_async_smem();
     }
     if (warp == 1) {
@@ -196,7 +235,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t full = smem_u32(&ctl->full[stage]);
                     const uint32_t a_dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes;
                     const uint32_t b_dst = a_dst + kATileBytes;
-                    mbar_arrive_expect_tx(full, kStageBytes);
+                    mbar_arrive_expect_tx(full, kLoadBytes);
                     const int k0 = kb * BK;
                     if (A_MN) {
 #pragma unroll
@@ -221,6 +260,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0) {
+            // K-major: a k-step is 32 bytes along the swizzled row, LBO unused (16), SBO 1024.
+            // MN-major: a k-step is 16 k-rows of 128 bytes, LBO = one 64-wide block, SBO 1024.
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t kStepA = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+            constexpr uint32_t kStepB = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+            const uint32_t a_lo_base = (smem_base >> 4) | (((A_MN ? kBlock64Bytes : 16u) >> 4) << 16);
+            const uint32_t b_lo_base = ((smem_base + kATileBytes) >> 4) | (((B_MN ? kBlock64Bytes : 16u) >> 4) << 16);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -232,34 +278,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                   p.status, kDevWaitTmemEmpty, acc);
                 if (!ok) break;
                 tc_fence_after_thread_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                const uint32_t d_dbias = tmem_base + static_cast<uint32_t>(2 * BN + acc * kDbiasCols);
-                const bool do_dbias = DBIAS && tc.n_tile == 0;
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
+                // Tiles of the first tile column also multiply the ones block behind B.
+                const uint32_t idesc = (DBIAS && tc.n_tile == 0) ? kIdescDbias : kIdesc;
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     ok = bounded_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, p.status,
                                       kDevWaitSmemFull, stage);
                     if (!ok) break;
                     tc_fence_after_thread_sync();
-                    const uint32_t a_src = smem_base + static_cast<uint32_t>(stage) * kStageBytes;
-                    const uint32_t b_src = a_src + kATileBytes;
+                    // Descriptors differ between k-steps and stages only in the 14-bit
+                    // start-address field, so the issuing thread does one add per operand.
+                    const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
+                    const uint32_t a_lo = a_lo_base + stage_off;
+                    const uint32_t b_lo = b_lo_base + stage_off;
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        // K-major: 16 bf16 = 32 bytes further along the swizzled row.
-                        // MN-major: 16 k-rows of 128 bytes further down.
-                        const uint64_t da =
-                            A_MN ? make_smem_desc_sw128(a_src + kk * (UMMA_K * 128), kBlock64Bytes, 1024)
-                                 : make_smem_desc_sw128(a_src + kk * (UMMA_K * 2), 16, 1024);
-                        const uint64_t db =
-                            B_MN ? make_smem_desc_sw128(b_src + kk * (UMMA_K * 128), kBlock64Bytes, 1024)
-                                 : make_smem_desc_sw128(b_src + kk * (UMMA_K * 2), 16, 1024);
-                        const uint32_t accumulate = (kb > tc.kb0 || kk > 0) ? 1u : 0u;
-                        umma_bf16(d_tmem, da, db, kIdesc, accumulate);
-                        if (do_dbias) {
-                            const uint64_t dones =
-                                B_MN ? make_smem_desc_sw128(ones_base + kk * (UMMA_K * 128), kBlock64Bytes, 1024)
-                                     : make_smem_desc_sw128(ones_base + kk * (UMMA_K * 2), 16, 1024);
-                            umma_bf16(d_dbias, da, dones, kIdescDbias, accumulate);
-                        }
+                        const uint64_t da = (static_cast<uint64_t>(kDescHi) << 32) |
+                                            static_cast<uint64_t>(a_lo + kk * kStepA);
+                        const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
+                                            static_cast<uint64_t>(b_lo + kk * kStepB);
+                        umma_bf16(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -272,7 +310,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ---------------------------------------------------------- epilogue
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp drains
+        constexpr int kHalfCols = BN / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -286,10 +326,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool row_ok = row < p.m;
             const int64_t n0 = static_cast<int64_t>(tc.n_tile) * BN;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(acc * BN);
+                                   static_cast<uint32_t>(acc) * kAccStride;
             const bool partial = p.splits > 1;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols; c0 += 32) {
                 if (n0 + c0 >= p.n) break;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
@@ -308,34 +348,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     continue;
                 }
+                if (p.alpha != 1.0f) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+                    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+                }
                 const int64_t c_off = static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + col;
                 if (p.beta != 0.0f && row_ok) {
-                    if (p.c_is_bf16) {
-                        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.c) + c_off;
+                    float cin[32];
+                    if (p.c_is_bf16)
+                        load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.c) + c_off, cin, valid);
+                    else
+                        load_chunk_f32(static_cast<const float*>(p.c) + c_off, cin, valid);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += p.beta * __bfloat162float(src[j]);
-                    } else {
-                        const float* src = static_cast<const float*>(p.c) + c_off;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += p.beta * src[j];
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cin[j], v[j]);
                 }
                 if (p.epi_flags & kEpiBias) {
-                    if (p.bias_is_bf16) {
-                        const __nv_bfloat16* bsrc = static_cast<const __nv_bfloat16*>(p.bias) + col;
+                    float bv[32];
+                    if (p.bias_is_bf16)
+                        load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.bias) + col, bv, valid);
+                    else
+                        load_chunk_f32(static_cast<const float*>(p.bias) + col, bv, valid);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += __bfloat162float(bsrc[j]);
-                    } else {
-                        const float* bsrc = static_cast<const float*>(p.bias) + col;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += bsrc[j];
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] += bv[j];
                 }
                 if (p.epi_flags & kEpiGelu) {
 #pragma unroll
@@ -348,11 +382,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         store_chunk_f32(static_cast<float*>(p.c) + c_off, v, valid);
                 }
             }
-            if (DBIAS && tc.n_tile == 0) {
-                // Column 0 of the extra accumulator holds sum_k op(A)[row, k].
+            if (DBIAS && tc.n_tile == 0 && half == 0) {
+                // Accumulator column BN holds sum_k op(A)[row, k] (the ones block).
                 uint32_t r[16];
-                tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                  static_cast<uint32_t>(2 * BN + acc * kDbiasCols), r);
+                tmem_ld_32x16(t_row + static_cast<uint32_t>(BN), r);
                 tmem_ld_wait();
                 if (row_ok) {
                     const float s = __uint_as_float(r[0]);
@@ -454,7 +487,7 @@ cudaError_t launch_major(const TcPlan& plan, int a_mn, int b_mn, const CUtensorM
 
 size_t tc_smem_bytes(int bn, int stages, bool dbias) {
     const size_t stage = kATileBytes + static_cast<size_t>(bn) * BK * 2;
-    return 1024 /* alignment slack */ + stage * stages + (dbias ? kOnesBytes : 0) + sizeof(Control);
+    return 1024 /* alignment slack */ + (stage + (dbias ? kOnesBytes : 0)) * stages + sizeof(Control);
 }
 
 cudaError_t launch_tc_gemm(const TcPlan& plan, int a_mn, int b_mn, const CUtensorMap& ma,

@@ -1,0 +1,204 @@
+// The known-answer tests llmt runs on its matmul path, written against the
+// same C++ interface (kernels::matmul, Linear, MLP, attention_fwd) but linked
+// with the llmt_b200 implementation.  Mirrors llmt tests/unit/test_matmul.cu,
+// test_linear.cu, test_mlp.cu and test_attention.cu: same golden tensors, same
+// tolerance (rtol 1e-5, atol 1e-6), same call sequences.  Plain main(), exit
+// code 0 = all checks passed.
+//
+//   test_llmt_goldens <dir with the llmt golden cases>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <string>
+#include <vector>
+
+#include "llmt/core/arena.h"
+#include "llmt/core/device.h"
+#include "llmt/core/error.h"
+#include "llmt/kernels/algo_cache.h"
+#include "llmt/kernels/attention.h"
+#include "llmt/kernels/matmul.h"
+#include "llmt/layers/linear.h"
+#include "llmt/layers/mlp.h"
+
+using namespace llmt;
+
+namespace {
+
+int g_checks = 0, g_failures = 0;
+std::string g_root;
+
+struct HostTensor {
+    Shape shape;
+    std::vector<float> v;
+};
+
+// llmt golden format: u32 magic "LLMT", u32 version, u32 dtype, u32 rank, i64 dims, payload.
+HostTensor load(const std::string& c, const std::string& name) {
+    const std::string path = g_root + "/" + c + "/" + name + ".bin";
+    std::ifstream f(path, std::ios::binary);
+    if (!f) { std::fprintf(stderr, "cannot open %s\n", path.c_str()); std::exit(2); }
+    uint32_t hdr[4];
+    f.read(reinterpret_cast<char*>(hdr), 16);
+    if (hdr[0] != 0x544D4C4Cu || hdr[1] != 1u || hdr[2] != 0u || hdr[3] > 4u) {
+        std::fprintf(stderr, "%s: not an fp32 llmt golden tensor\n", path.c_str());
+        std::exit(2);
+    }
+    HostTensor t;
+    t.shape.rank = static_cast<int>(hdr[3]);
+    for (int i = 0; i < t.shape.rank; ++i) {
+        int64_t d;
+        f.read(reinterpret_cast<char*>(&d), 8);
+        t.shape.d[static_cast<size_t>(i)] = d;
+    }
+    t.v.resize(static_cast<size_t>(t.shape.numel()));
+    f.read(reinterpret_cast<char*>(t.v.data()), static_cast<std::streamsize>(t.v.size() * 4));
+    return t;
+}
+
+Tensor upload(Arena& arena, const HostTensor& h, cudaStream_t s) {
+    Tensor t = arena.alloc(h.shape, DType::FP32);
+    CUDA_CHECK(cudaMemcpyAsync(t.data, h.v.data(), h.v.size() * 4, cudaMemcpyHostToDevice, s));
+    return t;
+}
+
+std::vector<float> download(const Tensor& t) {
+    std::vector<float> v(static_cast<size_t>(t.numel()));
+    CUDA_CHECK(cudaMemcpy(v.data(), t.data, v.size() * 4, cudaMemcpyDeviceToHost));
+    return v;
+}
+
+void check_close(const Tensor& got, const HostTensor& want, const char* what, double scale = 1.0) {
+    ++g_checks;
+    const std::vector<float> g = download(got);
+    if (g.size() != want.v.size()) { ++g_failures; std::fprintf(stderr, "FAIL %s: size\n", what); return; }
+    for (size_t i = 0; i < g.size(); ++i) {
+        const double e = scale * want.v[i];
+        if (!(std::fabs(g[i] - e) <= 1e-6 + 1e-5 * std::fabs(e))) {
+            ++g_failures;
+            std::fprintf(stderr, "FAIL %s: [%zu] got %.9g want %.9g\n", what, i, g[i], e);
+            return;
+        }
+    }
+    std::printf("ok   %s\n", what);
+}
+
+void test_matmul(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "matmul-test");
+    const Tensor a = upload(arena, load("matmul", "a"), ctx.stream);
+    const Tensor at = upload(arena, load("matmul", "at"), ctx.stream);
+    const Tensor b = upload(arena, load("matmul", "b"), ctx.stream);
+    const Tensor bt = upload(arena, load("matmul", "bt"), ctx.stream);
+    Tensor c = arena.alloc({7, 9}, DType::FP32);
+    kernels::matmul(ctx, c, a, b, false, false, 1.0f, 0.0f);
+    dev.synchronize(); check_close(c, load("matmul", "c_nn"), "matmul c_nn");
+    kernels::matmul(ctx, c, a, bt, false, true, 1.0f, 0.0f);
+    dev.synchronize(); check_close(c, load("matmul", "c_nt"), "matmul c_nt");
+    kernels::matmul(ctx, c, at, b, true, false, 1.0f, 0.0f);
+    dev.synchronize(); check_close(c, load("matmul", "c_tn"), "matmul c_tn");
+    kernels::matmul(ctx, c, at, bt, true, true, 1.0f, 0.0f);
+    dev.synchronize(); check_close(c, load("matmul", "c_tt"), "matmul c_tt");
+    Tensor c0 = upload(arena, load("matmul", "c0"), ctx.stream);
+    kernels::matmul(ctx, c0, a, b, false, false, 1.0f, 1.0f);
+    dev.synchronize(); check_close(c0, load("matmul", "c_beta"), "matmul beta=1 accumulates");
+    // bitwise determinism across calls
+    Tensor c1 = arena.alloc({7, 9}, DType::FP32), c2 = arena.alloc({7, 9}, DType::FP32);
+    kernels::matmul(ctx, c1, a, b, false, false, 1.0f, 0.0f);
+    kernels::matmul(ctx, c2, a, b, false, false, 1.0f, 0.0f);
+    dev.synchronize();
+    const auto h1 = download(c1), h2 = download(c2);
+    ++g_checks;
+    if (std::memcmp(h1.data(), h2.data(), h1.size() * 4) != 0) { ++g_failures; std::fprintf(stderr, "FAIL determinism\n"); }
+    else std::printf("ok   matmul bitwise deterministic\n");
+}
+
+void test_rank3(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "rank3-test");
+    const Tensor a = upload(arena, load("matmul_rank3", "a"), ctx.stream);
+    const Tensor b = upload(arena, load("matmul_rank3", "b"), ctx.stream);
+    Tensor c = arena.alloc({3, 4, 5}, DType::FP32);
+    kernels::matmul(ctx, c, a, b, false, false, 1.0f, 0.0f);
+    dev.synchronize(); check_close(c, load("matmul_rank3", "c"), "rank3 batched NN");
+    const Tensor q = upload(arena, load("matmul_rank3", "q"), ctx.stream);
+    const Tensor k = upload(arena, load("matmul_rank3", "k"), ctx.stream);
+    Tensor s = arena.alloc({3, 4, 4}, DType::FP32);
+    kernels::matmul(ctx, s, q, k, false, true, 1.0f, 0.0f);
+    dev.synchronize(); check_close(s, load("matmul_rank3", "scores"), "rank3 QK^T");
+}
+
+void test_linear(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "linear-test");
+    ParamStore ps(StateDtypes::uniform(DType::FP32));
+    const Linear lin(ps, "w", 12, 10, Role::Matrix);
+    ps.finalize();
+    const HostTensor w = load("linear", "weight");
+    CUDA_CHECK(cudaMemcpyAsync(lin.param().weight.data, w.v.data(), w.v.size() * 4,
+                               cudaMemcpyHostToDevice, ctx.stream));
+    const Tensor x = upload(arena, load("linear", "x"), ctx.stream);
+    const Tensor dy = upload(arena, load("linear", "dy"), ctx.stream);
+    Tensor y = arena.alloc({8, 10}, DType::FP32), dx = arena.alloc({8, 12}, DType::FP32);
+    lin.forward(ctx, y, x);
+    dev.synchronize(); check_close(y, load("linear", "y"), "Linear forward");
+    lin.backward(ctx, dx, dy, x);
+    dev.synchronize();
+    check_close(dx, load("linear", "dx"), "Linear dx");
+    check_close(lin.param().grad, load("linear", "dw"), "Linear dW");
+    lin.backward(ctx, dx, dy, x);  // accumulation contract: grad is now twice the oracle's
+    dev.synchronize(); check_close(lin.param().grad, load("linear", "dw"), "Linear dW accumulates", 2.0);
+}
+
+void test_mlp(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "mlp-test");
+    ParamStore ps(StateDtypes::uniform(DType::FP32));
+    const MLP mlp(ps, "mlp", 8, 16);
+    ps.finalize();
+    const HostTensor wu = load("mlp", "wu"), wd = load("mlp", "wd");
+    CUDA_CHECK(cudaMemcpyAsync(mlp.up().weight.data, wu.v.data(), wu.v.size() * 4, cudaMemcpyHostToDevice, ctx.stream));
+    CUDA_CHECK(cudaMemcpyAsync(mlp.down().weight.data, wd.v.data(), wd.v.size() * 4, cudaMemcpyHostToDevice, ctx.stream));
+    const Tensor x = upload(arena, load("mlp", "x"), ctx.stream);
+    Tensor h = arena.alloc({6, 16}, DType::FP32), y = arena.alloc({6, 8}, DType::FP32);
+    mlp.forward(ctx, y, h, x);
+    dev.synchronize(); check_close(y, load("mlp", "y"), "MLP forward (GELU fused in the up-projection)");
+}
+
+void test_attention(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "attn-test");
+    const Tensor q = upload(arena, load("attention", "q"), ctx.stream);
+    const Tensor k = upload(arena, load("attention", "k"), ctx.stream);
+    const Tensor v = upload(arena, load("attention", "v"), ctx.stream);
+    const Tensor q3{q.data, q.dtype, {4, 4, 6}}, k3{k.data, k.dtype, {4, 4, 6}}, v3{v.data, v.dtype, {4, 4, 6}};
+    Tensor s = arena.alloc({4, 4, 4}, DType::FP32);
+    kernels::matmul(ctx, s, q3, k3, false, true, 1.0f / std::sqrt(6.0f), 0.0f);
+    dev.synchronize(); check_close(s, load("attention", "scores"), "attention scores");
+    kernels::softmax_fwd(ctx, s, s, kernels::MaskSpec{kernels::MaskKind::Causal});
+    dev.synchronize(); check_close(s, load("attention", "probs"), "attention probs");
+    Tensor o = arena.alloc({4, 4, 6}, DType::FP32);
+    kernels::matmul(ctx, o, s, v3, false, false, 1.0f, 0.0f);
+    dev.synchronize(); check_close(o, load("attention", "out"), "attention P.V");
+    Tensor y = arena.alloc({2, 4, 12}, DType::FP32), s4 = arena.alloc({2, 2, 4, 4}, DType::FP32);
+    Tensor yh = arena.alloc({2, 2, 4, 6}, DType::FP32);
+    kernels::attention_fwd(ctx, y, s4, yh, q, k, v, kernels::MaskSpec{kernels::MaskKind::Causal});
+    dev.synchronize();
+    check_close(y, load("attention", "merged"), "attention_fwd merged");
+    check_close(s4, load("attention", "probs"), "attention_fwd leaves probs in scores");
+    check_close(yh, load("attention", "out"), "attention_fwd y_heads");
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    if (argc < 2) { std::fprintf(stderr, "usage: %s <golden dir>\n", argv[0]); return 2; }
+    g_root = argv[1];
+    Device dev(0);
+    const RunCtx ctx = dev.make_ctx(1, KernelBackend::Naive, PrecisionPolicy::fp32());
+    test_matmul(dev, ctx);
+    test_rank3(dev, ctx);
+    test_linear(dev, ctx);
+    test_mlp(dev, ctx);
+    test_attention(dev, ctx);
+    std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
+                ctx.algo_cache->map.size());
+    return g_failures == 0 ? 0 : 1;
+}

@@ -1,0 +1,127 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the
+public header declares, and rejects contract violations with status codes
+(never aborts) — no compute call is made here."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import llmt_b200 as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "llmt_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    return re.findall(r"LLMT_B200_API\s+[\w\s\*]+?\b(llmt_b200_\w+)\s*\(", text)
+
+
+def test_header_declares_the_expected_entry_points():
+    syms = declared_symbols()
+    assert "llmt_b200_gemm" in syms and "llmt_b200_gemm_workspace_bytes" in syms
+    assert len(syms) == len(set(syms)) >= 9
+
+
+def test_library_exports_every_declared_symbol():
+    lib = L.lib()
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert sorted(set(declared_symbols())) == sorted(set(L.EXPORTS) | set(declared_symbols()))
+    assert lib.llmt_b200_abi_version() == 1
+
+
+def test_descriptor_layout_matches_the_header():
+    # field order and sizes of struct llmt_b200_gemm_desc as the C compiler lays them out
+    assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8
+    assert L.GemmDesc.workspace.offset % 8 == 0
+
+
+def _desc(**kw):
+    d = L.GemmDesc()
+    d.m, d.n, d.k, d.batch = 128, 128, 64, 1
+    d.lda, d.ldb, d.ldc = 64, 64, 128
+    d.trans_b = 1
+    d.dtype_ab, d.dtype_c = L.BF16, L.FP32
+    d.alpha = 1.0
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+A, B, C = 0x10000, 0x20000, 0x40000  # fake, non-overlapping, 16-byte aligned device addresses
+
+
+def _call(d, c=C, a=A, b=B):
+    return L.lib().llmt_b200_gemm(ctypes.byref(d), ctypes.c_void_p(c), ctypes.c_void_p(a),
+                                  ctypes.c_void_p(b), None)
+
+
+@pytest.mark.parametrize("kw,status,needle", [
+    (dict(lda=32), L.ERR_INVALID, "row pitch"),
+    (dict(m=-1), L.ERR_INVALID, "negative"),
+    (dict(dtype_ab=7), L.ERR_UNSUPPORTED, "dtype code 7"),
+    (dict(dtype_ab=L.FP32, dtype_c=L.BF16), L.ERR_UNSUPPORTED, "mixed dtypes"),
+    (dict(epilogue=8), L.ERR_INVALID, "epilogue"),
+    (dict(epilogue=L.EPI_BIAS), L.ERR_INVALID, "bias is null"),
+    (dict(plan_tile_n=100), L.ERR_INVALID, "plan_tile_n"),
+    (dict(lda=68), L.ERR_UNSUPPORTED, "multiple of 8"),
+    (dict(batch=2, stride_a=10, stride_b=128 * 64, stride_c=128 * 128), L.ERR_INVALID, "batch stride"),
+])
+def test_contract_violations_return_status(kw, status, needle):
+    assert _call(_desc(**kw)) == status
+    assert needle in L.last_error()
+
+
+def test_null_and_overlapping_pointers_are_rejected():
+    d = _desc()
+    assert _call(d, a=0) == L.ERR_INVALID and "null data" in L.last_error()
+    assert L.lib().llmt_b200_gemm(None, ctypes.c_void_p(C), ctypes.c_void_p(A), ctypes.c_void_p(B),
+                                  None) == L.ERR_INVALID
+    assert _call(d, c=A + 64) == L.ERR_INVALID and "overlaps" in L.last_error()
+
+
+def test_unaligned_bf16_base_is_reported_not_run():
+    assert _call(_desc(), a=A + 2) == L.ERR_UNSUPPORTED
+    assert "16-byte" in L.last_error()
+
+
+def test_dbias_contract():
+    d = _desc(dbias=0x80000, dtype_ab=L.FP32)
+    assert _call(d) == L.ERR_UNSUPPORTED and "dbias" in L.last_error()
+    d = _desc(dbias=0x80000, plan_tile_n=256)
+    assert _call(d) == L.ERR_INVALID
+
+
+def test_empty_output_is_a_no_op():
+    assert _call(_desc(m=0)) == L.OK
+    assert _call(_desc(batch=0)) == L.OK
+
+
+def test_plan_is_a_pure_function_of_the_problem():
+    # the determinism device: one problem -> one plan, every time
+    # (role of llmt's AlgoCache, include/llmt/kernels/algo_cache.h:18-42)
+    d = _desc(m=8192, n=2304, k=768, lda=768, ldb=768, ldc=2304)
+    p1, p2 = L.plan(d), L.plan(d)
+    assert p1 == p2 and "tcgen05" in p1 and "128x" in p1
+    assert L.workspace_bytes(d) == 0
+    dw = _desc(m=768, n=768, k=8192, trans_a=1, trans_b=0, lda=768, ldb=768, ldc=768)
+    assert "splits=" in L.plan(dw)
+    ws = L.workspace_bytes(dw)
+    assert ws > 0 and ws % 256 == 0
+    # workspace shortfall is reported before anything is launched
+    dw.workspace, dw.workspace_bytes = 0x100000, 16
+    assert _call(dw, c=0x7000000000, a=0x1000000000, b=0x2000000000) == L.ERR_WORKSPACE
+    forced = _desc(m=768, n=768, k=8192, plan_tile_n=64, plan_splits=1)
+    assert "128x64x64" in L.plan(forced) and "splits=1 " in L.plan(forced)
+
+
+def test_softmax_contract():
+    lib = L.lib()
+    assert lib.llmt_b200_softmax_fwd(ctypes.c_void_p(A), ctypes.c_void_p(A), 8, 4, 5, 0, 1, None) \
+        == L.ERR_INVALID
+    assert "square" in L.last_error()
+    assert lib.llmt_b200_softmax_fwd(None, ctypes.c_void_p(A), 8, 4, 4, 0, 1, None) == L.ERR_INVALID
+    assert lib.llmt_b200_softmax_fwd(ctypes.c_void_p(A), ctypes.c_void_p(A), 8, 4, 4, 2, 0, None) \
+        == L.ERR_UNSUPPORTED
