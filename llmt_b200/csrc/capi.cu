@@ -200,28 +200,36 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     return LLMT_B200_OK;
 }
 
-// Tensor map over one row-major operand [rows, cols] (pitch ld, `batch` items
-// `stride` elements apart), boxed for 128-byte-swizzled tiles.
-int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
-                       int64_t batch, int64_t stride, int box_rows) {
+// Tensor map over one row-major matrix [rows, cols] (pitch ld, `batch` items `stride`
+// elements apart) with a box of box_cols x box_rows elements.  elem_bytes 2 = bf16, 4 = fp32.
+int encode_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
+               int64_t ld, int64_t batch, int64_t stride, int box_cols, int box_rows,
+               CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail(LLMT_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
     const cuuint64_t stride_elems = batch > 1 ? static_cast<cuuint64_t>(stride)
                                               : static_cast<cuuint64_t>(rows) * ld;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
                           static_cast<cuuint64_t>(batch > 1 ? batch : 1)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, stride_elems * 2};
-    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elem_bytes, stride_elems * elem_bytes};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
-                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                          3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(LLMT_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d "
                     "(rows=%lld cols=%lld ld=%lld batch=%lld)", static_cast<int>(r),
                     (long long)rows, (long long)cols, (long long)ld, (long long)batch);
     return LLMT_B200_OK;
+}
+
+// bf16 operand map boxed for 128-byte-swizzled tiles (64 elements wide).
+int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                       int64_t batch, int64_t stride, int box_rows) {
+    return encode_map(map, base, 2, rows, cols, ld, batch, stride, 64, box_rows,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const void* a, const void* b,
@@ -281,7 +289,19 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
     st = encode_operand_map(&mb, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
                             b_mn ? 64 : pl.bn);
     if (st != LLMT_B200_OK) return st;
-    cudaError_t e = launch_tc_gemm(pl, a_mn, b_mn, ma, mb, p, stream);
+    // C leaves through shared memory and TMA stores when its layout allows a tensor map
+    // (16-byte aligned base, pitch and batch stride); otherwise straight from registers.
+    CUtensorMap mc;
+    memset(&mc, 0, sizeof mc);
+    const int ces = p.c_is_bf16 ? 2 : 4;
+    if ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
+        (d->batch <= 1 || (d->stride_c * ces) % 16 == 0) && pl.splits == 1) {
+        st = encode_map(&mc, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, 32, 128,
+                        p.c_is_bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != LLMT_B200_OK) return st;
+        p.c_tma = 1;
+    }
+    cudaError_t e = launch_tc_gemm(pl, a_mn, b_mn, ma, mb, mc, p, stream);
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     if (pl.splits > 1) {
         e = launch_splitk_reduce(p, stream);

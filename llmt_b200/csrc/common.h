@@ -38,7 +38,7 @@ struct TcGemmParams {
     void* c;
     int64_t ldc, stride_c;
     int32_t c_is_bf16;
-    int32_t c_vec_ok;           // rows of C start 16-byte aligned -> vector stores allowed
+    int32_t c_tma;              // C has a tensor map: tiles leave through shared memory + TMA store
     float alpha, beta;
     const void* bias;
     int32_t bias_is_bf16;
@@ -95,7 +95,7 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
 cudaError_t launch_tc_gemm(const TcPlan& plan, int a_mn_major, int b_mn_major,
                            const CUtensorMap& map_a, const CUtensorMap& map_b,
-                           const TcGemmParams& p, cudaStream_t stream);
+                           const CUtensorMap& map_c, const TcGemmParams& p, cudaStream_t stream);
 cudaError_t launch_splitk_reduce(const TcGemmParams& p, cudaStream_t stream);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
 cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,

@@ -46,6 +46,10 @@ constexpr uint32_t kBlock64Bytes = 64 * BK * 2;  // one 64-wide MN-major block o
 constexpr uint32_t kOnesBytes = 64 * 128;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kDbiasCols = 16;
+// Epilogue staging: one 128-row x 32-column slab per column half (fp32: 128-byte rows,
+// 128B swizzle; bf16: 64-byte rows, 64B swizzle), written by 4 warps, stored by TMA.
+constexpr uint32_t kSlabBytes = 128 * 32 * 4;
+constexpr uint32_t kStagingBytes = 2 * kSlabBytes;
 
 struct __align__(8) Control {
     uint64_t full[kMaxStages];
@@ -164,7 +168,7 @@ __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float*
 template <int BN, int A_MN, int B_MN, int DBIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const TcGemmParams p, const int stages) {
+               const __grid_constant__ CUtensorMap map_c, const TcGemmParams p, const int stages) {
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width");
     static_assert(!DBIAS || BN <= 192, "dbias columns need room in TMEM");
     constexpr uint32_t kBTileBytes = BN * BK * 2;
@@ -180,7 +184,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Swizzled tiles need 1024-byte alignment.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    Control* ctl = reinterpret_cast<Control*>(smem_gen + static_cast<size_t>(stages) * kStageBytes);
+    const uint32_t staging_base = smem_base + static_cast<uint32_t>(stages) * kStageBytes;
+    Control* ctl = reinterpret_cast<Control*>(smem_gen + static_cast<size_t>(stages) * kStageBytes +
+                                              kStagingBytes);
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -199,6 +205,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         fence_barrier_init();
         prefetch_tensormap(&map_a);
         prefetch_tensormap(&map_b);
+        if (p.c_tma) prefetch_tensormap(&map_c);
     }
     if (DBIAS) {
         // bf16 1.0 everywhere: the block reads the same under any swizzle or major.
@@ -328,6 +335,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc) * kAccStride;
             const bool partial = p.splits > 1;
+            const bool via_tma = p.c_tma && !partial;
+            const int tile_row = quarter * 32 + lane;  // row inside the 128-row tile
+            const uint32_t slab = staging_base + static_cast<uint32_t>(half) * kSlabBytes;
+            const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
 #pragma unroll 1
             for (int c0 = half * kHalfCols; c0 < (half + 1) * kHalfCols; c0 += 32) {
                 if (n0 + c0 >= p.n) break;  // warp-uniform
@@ -375,7 +386,47 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
                 }
-                if (row_ok) {
+                // TMA clips a box at 16-byte granularity, so a ragged last chunk goes out
+                // through registers instead (warp-uniform and the same in all warps of a half).
+                if (via_tma && valid == 32) {
+                    // The slab is free once the previous TMA store has read it.
+                    if (store_leader) bulk_wait_group_read0();
+                    named_barrier_sync(1 + half, 128);
+                    if (p.c_is_bf16) {
+                        const uint32_t row_addr = slab + static_cast<uint32_t>(tile_row) * 64u;
+                        const uint32_t sw = static_cast<uint32_t>(tile_row >> 1) & 3u;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * q + 0], v[8 * q + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
+                                           "r"(*reinterpret_cast<uint32_t*>(&h0)),
+                                           "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                                           "r"(*reinterpret_cast<uint32_t*>(&h2)),
+                                           "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
+                        }
+                    } else {
+                        const uint32_t row_addr = slab + static_cast<uint32_t>(tile_row) * 128u;
+                        const uint32_t sw = static_cast<uint32_t>(tile_row) & 7u;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
+                                           "r"(__float_as_uint(v[4 * q + 0])), "r"(__float_as_uint(v[4 * q + 1])),
+                                           "r"(__float_as_uint(v[4 * q + 2])), "r"(__float_as_uint(v[4 * q + 3]))
+                                         : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1 + half, 128);
+                    if (store_leader) {
+                        tma_store_3d(&map_c, slab, static_cast<int32_t>(col), tc.m_tile * BM, tc.batch);
+                        bulk_commit_group();
+                    }
+                } else if (row_ok) {
                     if (p.c_is_bf16)
                         store_chunk_bf16(static_cast<__nv_bfloat16*>(p.c) + c_off, v, valid);
                     else
@@ -403,6 +454,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
+        // Outstanding TMA stores must complete before the shared memory goes away.
+        if ((warp == 2 || warp == 6) && lane == 0) bulk_wait_group0();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -454,7 +507,7 @@ __global__ void splitk_reduce_kernel(const TcGemmParams p) {
 
 template <int BN, int A_MN, int B_MN, int DBIAS>
 cudaError_t launch_one(const TcPlan& plan, const CUtensorMap& ma, const CUtensorMap& mb,
-                       const TcGemmParams& p, cudaStream_t stream) {
+                       const CUtensorMap& mc, const TcGemmParams& p, cudaStream_t stream) {
     auto kern = tc_gemm_kernel<BN, A_MN, B_MN, DBIAS>;
     static bool configured = false;  // per instantiation; the attribute is sticky per device context
     static int configured_device = -1;
@@ -467,45 +520,48 @@ cudaError_t launch_one(const TcPlan& plan, const CUtensorMap& ma, const CUtensor
         configured = true;
         configured_device = dev;
     }
-    kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ma, mb, p, plan.stages);
+    kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ma, mb, mc, p, plan.stages);
     count_launch(1);
     return cudaGetLastError();
 }
 
 template <int BN, int DBIAS>
 cudaError_t launch_major(const TcPlan& plan, int a_mn, int b_mn, const CUtensorMap& ma,
-                         const CUtensorMap& mb, const TcGemmParams& p, cudaStream_t stream) {
+                         const CUtensorMap& mb, const CUtensorMap& mc, const TcGemmParams& p,
+                         cudaStream_t stream) {
     if (a_mn) {
-        if (b_mn) return launch_one<BN, 1, 1, DBIAS>(plan, ma, mb, p, stream);
-        return launch_one<BN, 1, 0, DBIAS>(plan, ma, mb, p, stream);
+        if (b_mn) return launch_one<BN, 1, 1, DBIAS>(plan, ma, mb, mc, p, stream);
+        return launch_one<BN, 1, 0, DBIAS>(plan, ma, mb, mc, p, stream);
     }
-    if (b_mn) return launch_one<BN, 0, 1, DBIAS>(plan, ma, mb, p, stream);
-    return launch_one<BN, 0, 0, DBIAS>(plan, ma, mb, p, stream);
+    if (b_mn) return launch_one<BN, 0, 1, DBIAS>(plan, ma, mb, mc, p, stream);
+    return launch_one<BN, 0, 0, DBIAS>(plan, ma, mb, mc, p, stream);
 }
 
 }  // namespace
 
 size_t tc_smem_bytes(int bn, int stages, bool dbias) {
     const size_t stage = kATileBytes + static_cast<size_t>(bn) * BK * 2;
-    return 1024 /* alignment slack */ + (stage + (dbias ? kOnesBytes : 0)) * stages + sizeof(Control);
+    return 1024 /* alignment slack */ + (stage + (dbias ? kOnesBytes : 0)) * stages + kStagingBytes +
+           sizeof(Control);
 }
 
 cudaError_t launch_tc_gemm(const TcPlan& plan, int a_mn, int b_mn, const CUtensorMap& ma,
-                           const CUtensorMap& mb, const TcGemmParams& p, cudaStream_t stream) {
+                           const CUtensorMap& mb, const CUtensorMap& mc, const TcGemmParams& p,
+                           cudaStream_t stream) {
     const bool dbias = p.dbias != nullptr;
     if (dbias) {
         switch (plan.bn) {
-            case 64: return launch_major<64, 1>(plan, a_mn, b_mn, ma, mb, p, stream);
-            case 128: return launch_major<128, 1>(plan, a_mn, b_mn, ma, mb, p, stream);
-            case 192: return launch_major<192, 1>(plan, a_mn, b_mn, ma, mb, p, stream);
+            case 64: return launch_major<64, 1>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
+            case 128: return launch_major<128, 1>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
+            case 192: return launch_major<192, 1>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
             default: return cudaErrorInvalidValue;
         }
     }
     switch (plan.bn) {
-        case 64: return launch_major<64, 0>(plan, a_mn, b_mn, ma, mb, p, stream);
-        case 128: return launch_major<128, 0>(plan, a_mn, b_mn, ma, mb, p, stream);
-        case 192: return launch_major<192, 0>(plan, a_mn, b_mn, ma, mb, p, stream);
-        case 256: return launch_major<256, 0>(plan, a_mn, b_mn, ma, mb, p, stream);
+        case 64: return launch_major<64, 0>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
+        case 128: return launch_major<128, 0>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
+        case 192: return launch_major<192, 0>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
+        case 256: return launch_major<256, 0>(plan, a_mn, b_mn, ma, mb, mc, p, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -79,6 +79,31 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// 3-D tiled store from this CTA's shared memory to global (bulk async-group
+// completion).  Elements of the box that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src_smem, int32_t x,
+                                             int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until the bulk stores issued by this thread have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_group_read0() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Waits until the bulk stores issued by this thread have completed.
+__device__ __forceinline__ void bulk_wait_group0() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Barrier among `count` threads of the CTA (id 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ------------------------------------------------------------------- TMEM ---
 
 // Whole-warp instructions (.sync.aligned): every lane of one warp must execute them.
