@@ -105,6 +105,33 @@ typedef struct llmt_b200_gemm_desc {
 LLMT_B200_API int llmt_b200_gemm(const llmt_b200_gemm_desc* desc, void* c, const void* a, const void* b,
                    void* stream);
 
+/* Size of the scratch array compiled into the library for llmt_b200_gemm_static_scratch. */
+#define LLMT_B200_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* Same computation and same results as llmt_b200_gemm, for hosts that are not able to
+ * hand the library a workspace.  (No counterpart in llmt: llmt's Device always owns a
+ * cudaMalloc'ed cuBLASLt workspace.)  Some callers cannot call cudaMalloc at the point
+ * where they need a GEMM: a serving or training loop whose memory plan is frozen and in
+ * which an allocation would stall every stream of the device, a plugin that is given
+ * tensors but no allocator, a foreign-language host that binds only this one function.
+ * Here the split-K scratch is a fixed LLMT_B200_STATIC_SCRATCH_BYTES array inside the
+ * library image (every GPU that loads the library holds it until the process exits);
+ * desc->workspace and desc->workspace_bytes are ignored.  The call allocates nothing —
+ * no cudaMalloc, no cudaFree, no allocating library routine.
+ *   - A problem whose split-K plan needs more than LLMT_B200_STATIC_SCRATCH_BYTES is
+ *     refused with LLMT_B200_ERR_WORKSPACE before anything is launched (lower
+ *     plan_splits, or use llmt_b200_gemm with your own workspace).
+ *   - The first call on each device that needs scratch looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first
+ *     call outside any stream capture.
+ *   - All calls share the one array and it keeps whatever the previous call left there.
+ *     Nothing in it has to start at zero: every partial sum that is read back has been
+ *     written earlier in the same call.  Two calls that need scratch and may run on the GPU
+ *     at the same time (different streams, or different host threads) race on it: keep
+ *     such calls on one stream, or order them with events. */
+LLMT_B200_API int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* desc, void* c, const void* a,
+                                                const void* b, void* stream);
+
 /* Bytes of workspace llmt_b200_gemm needs for this problem (may be 0).  Pure
  * function of the descriptor and of the device's SM count. */
 LLMT_B200_API uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* desc);

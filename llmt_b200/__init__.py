@@ -19,7 +19,7 @@ EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4, 5
 
 EXPORTS = [
-    "llmt_b200_gemm", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
+    "llmt_b200_gemm", "llmt_b200_gemm_static_scratch", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
     "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
 ]
@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_gemm.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_void_p]
         L.llmt_b200_gemm.restype = ctypes.c_int
+        L.llmt_b200_gemm_static_scratch.argtypes = L.llmt_b200_gemm.argtypes
+        L.llmt_b200_gemm_static_scratch.restype = ctypes.c_int
         L.llmt_b200_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
         L.llmt_b200_gemm_workspace_bytes.restype = ctypes.c_uint64
         L.llmt_b200_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_char_p, ctypes.c_size_t]
@@ -166,6 +168,20 @@ def gemm_desc(desc: GemmDesc, c, a, b, stream=None) -> None:
     s = stream if stream is not None else torch.cuda.current_stream()
     _check(lib().llmt_b200_gemm(ctypes.byref(desc), c.data_ptr(), a.data_ptr(), b.data_ptr(),
                                 ctypes.c_void_p(s.cuda_stream)))
+
+
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def gemm_static_scratch(desc: GemmDesc, c, a, b, stream=None) -> None:
+    """llmt_b200_gemm_static_scratch: same result as gemm_desc, but split-K partial sums go to
+    the fixed array built into the library, so the call allocates nothing and needs no
+    workspace from the caller. Problems needing more than STATIC_SCRATCH_BYTES are refused.
+    Calls that may overlap on the GPU share (and race on) that one array."""
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    _check(lib().llmt_b200_gemm_static_scratch(ctypes.byref(desc), c.data_ptr(), a.data_ptr(),
+                                               b.data_ptr(), ctypes.c_void_p(s.cuda_stream)))
 
 
 def gemm(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,

@@ -27,6 +27,31 @@ int fail(int status, const char* fmt, ...) {
 
 __device__ DeviceStatus g_device_status;
 
+// Split-K scratch for llmt_b200_gemm_static_scratch(): a fixed array inside the
+// library image, so that entry point never has to ask anyone for memory.  Every
+// GPU that loads the library carries these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = LLMT_B200_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not something a kernel can
+// dereference; the real address comes from cudaGetSymbolAddress, asked once per
+// device with that device current, and is cached here.
+void* static_scratch_ptr(cudaError_t* err) {
+    static void* ptrs[64] = {nullptr};
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        *err = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -360,6 +385,39 @@ int llmt_b200_gemm(const llmt_b200_gemm_desc* d, void* c, const void* a, const v
     if (d->m == 0 || d->n == 0 || d->batch == 0) return LLMT_B200_OK;  // nothing to write
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return ck.bf16 ? run_bf16(d, ck, c, a, b, s) : run_fp32(d, c, a, b, s);
+}
+
+int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const void* a, const void* b,
+                                  void* stream) {
+    Checked ck{};
+    const int st = validate(d, c, a, b, &ck);
+    if (st != LLMT_B200_OK) return st;
+    if (d->m == 0 || d->n == 0 || d->batch == 0) return LLMT_B200_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!ck.bf16) return run_fp32(d, c, a, b, s);  // the fp32 path uses no scratch at all
+    // Size check first: a problem that does not fit is turned away before the scratch is
+    // resolved and before anything is enqueued.
+    const size_t need = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(),
+                                  d->plan_tile_n, d->plan_splits).workspace_bytes;
+    if (need > kStaticScratchBytes)
+        return fail(LLMT_B200_ERR_WORKSPACE,
+                    "gemm_static_scratch: this problem's split-K plan needs %llu scratch bytes but the "
+                    "built-in scratch holds %llu; use llmt_b200_gemm with a caller workspace, or force "
+                    "fewer splits with plan_splits",
+                    (unsigned long long)need, (unsigned long long)kStaticScratchBytes);
+    llmt_b200_gemm_desc local = *d;  // the caller's workspace fields are ignored
+    local.workspace = nullptr;
+    local.workspace_bytes = 0;
+    if (need > 0) {
+        cudaError_t e = cudaSuccess;
+        void* scratch = static_scratch_ptr(&e);
+        if (scratch == nullptr)
+            return fail(LLMT_B200_ERR_CUDA, "gemm_static_scratch: cannot resolve the built-in scratch: %s",
+                        cudaGetErrorString(e));
+        local.workspace = scratch;
+        local.workspace_bytes = kStaticScratchBytes;
+    }
+    return run_bf16(&local, ck, c, a, b, s);
 }
 
 uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
