@@ -126,50 +126,57 @@ class LinearStep:
             t["dw"], t["db"] = self.bucket.view(n + ".dW"), self.bucket.view(n + ".dbias")
             self.layers.append(t)
         for t in self.layers:
-            fwd = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
-            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0, dbias=t["db"], dbias_beta=1.0)
+            t["d_fwd"] = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
+            # Linear::backward as one launch: dx = dy W and dW += dy^T x (+ dbias) share a tile queue
             dx = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
-            t["d_fwd"], t["d_dw"], t["d_dx"] = fwd, dw, dx
-            ws_need = max(ws_need, *(L.workspace_bytes(d) for d in (fwd, dw, dx)))
-        self.ws = torch.empty(max(ws_need, 256), dtype=torch.uint8, device=dev)
+            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0, dbias=t["db"], dbias_beta=1.0)
+            t["bwd"] = L.Group([(dx, t["dx"], t["dy"], t["w"]), (dw, t["dw"], t["dy"], t["x"])])
+        # one scratch buffer per problem that needs one (split-K partial sums)
+        self.ws = []
         for t in self.layers:
-            for d in (t["d_fwd"], t["d_dw"], t["d_dx"]):
-                d.workspace, d.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+            need = L.workspace_bytes(t["d_fwd"])
+            buf = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+            t["d_fwd"].workspace, t["d_fwd"].workspace_bytes = buf.data_ptr(), buf.numel()
+            bufs = [torch.empty(max(b, 256), dtype=torch.uint8, device=dev) for b in t["bwd"].workspace_bytes()]
+            t["bwd"].set_workspaces(bufs)
+            self.ws += [buf] + bufs
         self.comm_stream = torch.cuda.Stream(device=dev)
-        self.grads_ready = torch.cuda.Event()
 
-    def gemm_list(self):
-        """(label, flops, desc, c, a, b) in launch order: forwards, then dW, then dX."""
+    def launches(self):
+        """(label, flops, callable) in launch order: forwards, then the backward of every layer."""
         out = []
         for t in self.layers:
             f = 2.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".fwd", f, t["d_fwd"], t["y"], t["x"], t["w"]))
+            out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), None))
         for t in reversed(self.layers):
-            f = 2.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".dW", f, t["d_dw"], t["dw"], t["dy"], t["x"]))
-        for t in reversed(self.layers):
-            f = 2.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".dX", f, t["d_dx"], t["dx"], t["dy"], t["w"]))
+            f = 4.0 * self.m * t["i"] * t["o"]
+            out.append((t["name"] + ".bwd(dX+dW)", f, t["bwd"].run, t))
         return out
 
+    def grad_slice(self, t):
+        """The layer's dW and dbias are adjacent in the flat span: one view covers both."""
+        lo = self.bucket.offsets[t["name"] + ".dW"][0]
+        off, n, _ = self.bucket.offsets[t["name"] + ".dbias"]
+        return self.bucket.flat[lo:off + n]
+
     def run(self, world, events=None):
-        """Enqueues one step on the current stream. With world > 1 the gradient span is
-        all-reduced on a side stream while the dX GEMMs run."""
-        torch, L = self.torch, self.L
+        """Enqueues one step on the current stream. With world > 1 every layer's gradient
+        slice is all-reduced on a side stream as soon as that layer's backward is enqueued,
+        so the exchange overlaps the backward of the remaining layers."""
+        torch = self.torch
         self.bucket.zero_()
-        n_layers = len(self.layers)
-        for idx, (label, _, d, c, a, b) in enumerate(self.gemm_list()):
+        for label, _, fn, layer in self.launches():
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record()
-            L.gemm_desc(d, c, a, b)
+            fn()
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record()
                 events.append((label, e0, e1))
-            if world > 1 and idx == 2 * n_layers - 1:  # last dW enqueued
-                self.grads_ready.record()
-                self.comm_stream.wait_event(self.grads_ready)
+            if world > 1 and layer is not None:
+                ready = torch.cuda.Event(); ready.record()
+                self.comm_stream.wait_event(ready)
                 with torch.cuda.stream(self.comm_stream):
-                    self.bucket.allreduce()
+                    torch.distributed.all_reduce(self.grad_slice(layer))
         if world > 1:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
@@ -376,7 +383,7 @@ def main():
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
-        import torch.distributed as dist
+        import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
@@ -412,7 +419,7 @@ def main():
     for label, a, b in events:
         per.setdefault(label, []).append(a.elapsed_time(b))
     gemm_ms = sum(sum(v) / len(v) for v in per.values())
-    gl = {lab: f for lab, f, *_ in step.gemm_list()}
+    gl = {lab: f for lab, f, *_ in step.launches()}
     per_gemm = {lab: round(gl[lab] / (sum(v) / len(v)) / 1e9, 1) for lab, v in per.items()}
 
     # end to end from host buffers
@@ -440,6 +447,7 @@ def main():
             "config": {"workload": f"{args.workload}: {LAYERS[args.workload]['name']}, "
                                    f"M={M_PER_GPU} tokens per GPU, fwd+dX+dW(+dbias) per layer, "
                                    f"bias+GELU fused in mlp_fc",
+                       "launches_per_step": "4 forward GEMMs + 4 grouped backward launches (dX and dW+dbias of a layer in one kernel) + split-K reductions",
                        "per_gpu_gflop_per_step": round(flops / 1e9, 1),
                        "allreduce_bytes_per_step": step.bucket.nbytes() if world > 1 else 0,
                        "l2": "working set (~400 MB of activations per step) larger than L2"},
@@ -448,7 +456,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
                          "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": None,
                          "peak_source": f"of {which}",
-                         "kernel": "tc_gemm_kernel (all GEMM launches of the step, device time)"},
+                         "kernel": "tc_grouped_kernel (all GEMM launches of the step, device time)"},
             "per_gemm_tflops": per_gemm,
             "e2e": {"value": round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes},

@@ -105,6 +105,23 @@ typedef struct llmt_b200_gemm_desc {
 LLMT_B200_API int llmt_b200_gemm(const llmt_b200_gemm_desc* desc, void* c, const void* a, const void* b,
                    void* stream);
 
+/* Several independent bf16 problems in ONE launch: a single persistent kernel draws the
+ * tiles of all of them from one queue, longest reductions first, so the tail of one
+ * product overlaps the head of the next and short products fill the SMs a long one
+ * leaves idle.  The natural use is llmt's Linear::backward (src/layers/linear.cpp:22-30),
+ * whose two kernels::matmul calls (dx = dy W and dW += dy^T x) depend on nothing but dy:
+ * pass both descriptors here.  count <= 8; every problem must be a bf16 problem and no
+ * problem may write memory another problem of the call reads or writes.  Each problem's
+ * desc carries its own workspace; llmt_b200_gemm_grouped_workspace_bytes gives the sizes
+ * (the split-K choice depends on the work the problems share the launch with).
+ * Results are bitwise those of the same plan run alone: which SM computes a tile changes
+ * nothing in the tile's arithmetic. */
+LLMT_B200_API int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c,
+                                         const void* const* a, const void* const* b, int32_t count,
+                                         void* stream);
+LLMT_B200_API int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int32_t count,
+                                                         uint64_t* bytes_per_problem);
+
 /* Size of the scratch array compiled into the library for llmt_b200_gemm_static_scratch. */
 #define LLMT_B200_STATIC_SCRATCH_BYTES (32u << 20)
 

@@ -19,7 +19,8 @@ EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4, 5
 
 EXPORTS = [
-    "llmt_b200_gemm", "llmt_b200_gemm_static_scratch", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
+    "llmt_b200_gemm", "llmt_b200_gemm_grouped", "llmt_b200_gemm_grouped_workspace_bytes",
+    "llmt_b200_gemm_static_scratch", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
     "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
 ]
@@ -62,6 +63,14 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_gemm.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_void_p]
         L.llmt_b200_gemm.restype = ctypes.c_int
+        L.llmt_b200_gemm_grouped.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_void_p),
+                                             ctypes.POINTER(ctypes.c_void_p),
+                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32,
+                                             ctypes.c_void_p]
+        L.llmt_b200_gemm_grouped.restype = ctypes.c_int
+        L.llmt_b200_gemm_grouped_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_int32,
+                                                             ctypes.POINTER(ctypes.c_uint64)]
+        L.llmt_b200_gemm_grouped_workspace_bytes.restype = ctypes.c_int
         L.llmt_b200_gemm_static_scratch.argtypes = L.llmt_b200_gemm.argtypes
         L.llmt_b200_gemm_static_scratch.restype = ctypes.c_int
         L.llmt_b200_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
@@ -168,6 +177,38 @@ def gemm_desc(desc: GemmDesc, c, a, b, stream=None) -> None:
     s = stream if stream is not None else torch.cuda.current_stream()
     _check(lib().llmt_b200_gemm(ctypes.byref(desc), c.data_ptr(), a.data_ptr(), b.data_ptr(),
                                 ctypes.c_void_p(s.cuda_stream)))
+
+
+class Group:
+    """A fixed list of independent bf16 problems launched as one kernel
+    (llmt_b200_gemm_grouped). Built once from (desc, c, a, b) tuples; run() enqueues it."""
+
+    def __init__(self, problems):
+        n = len(problems)
+        self.n = n
+        self.descs = (GemmDesc * n)(*[p[0] for p in problems])
+        self.tensors = [p[1:] for p in problems]  # keep the tensors alive
+        self.c = (ctypes.c_void_p * n)(*[p[1].data_ptr() for p in problems])
+        self.a = (ctypes.c_void_p * n)(*[p[2].data_ptr() for p in problems])
+        self.b = (ctypes.c_void_p * n)(*[p[3].data_ptr() for p in problems])
+
+    def workspace_bytes(self):
+        out = (ctypes.c_uint64 * self.n)()
+        _check(lib().llmt_b200_gemm_grouped_workspace_bytes(self.descs, self.n, out))
+        return [int(v) for v in out]
+
+    def set_workspaces(self, buffers):
+        """buffers: one torch uint8 tensor (or None) per problem."""
+        self._ws = buffers
+        for d, buf in zip(self.descs, buffers):
+            if buf is not None:
+                d.workspace, d.workspace_bytes = buf.data_ptr(), buf.numel()
+
+    def run(self, stream=None):
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        _check(lib().llmt_b200_gemm_grouped(self.descs, self.c, self.a, self.b, self.n,
+                                            ctypes.c_void_p(s.cuda_stream)))
 
 
 STATIC_SCRATCH_BYTES = 32 << 20

@@ -27,4 +27,18 @@ struct Epilogue {
 void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
                bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept;
 
+// Several independent products in one launch (bf16 operands only): the tiles of all of
+// them share one queue on the GPU.  Used by Linear::backward for dx = dy W and
+// dW += dy^T x, which llmt issues as two matmul calls (src/layers/linear.cpp:22-30).
+// Falls back to one matmul_ex per call when an operand is fp32.
+struct MatmulCall {
+    Tensor* c = nullptr;
+    const Tensor* a = nullptr;
+    const Tensor* b = nullptr;
+    bool trans_a = false, trans_b = false;
+    float alpha = 1.0f, beta = 0.0f;
+    Epilogue epi;
+};
+void matmul_grouped(const RunCtx& ctx, const MatmulCall* calls, int count) noexcept;
+
 }  // namespace llmt::kernels

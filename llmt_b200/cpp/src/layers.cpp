@@ -27,11 +27,15 @@ void Linear::forward_gelu(const RunCtx& ctx, Tensor& y, const Tensor& x) const n
 }
 
 void Linear::backward(const RunCtx& ctx, Tensor& dx, const Tensor& dy, const Tensor& x) const noexcept {
-    kernels::matmul(ctx, dx, dy, weight_.weight, false, false, 1.0f, 0.0f);       // dx = dy W
-    kernels::Epilogue epi;
+    // dx = dy W and dW += dy^T x depend on nothing but dy: one grouped launch on the bf16
+    // path (two plain matmul calls, as in llmt, on the fp32 path).
+    kernels::MatmulCall calls[2];
+    calls[0].c = &dx; calls[0].a = &dy; calls[0].b = &weight_.weight;            // dx = dy W
+    calls[1].c = &weight_.grad; calls[1].a = &dy; calls[1].b = &x;                // dW += dy^T x
+    calls[1].trans_a = true; calls[1].beta = 1.0f;
     // The fused dbias exists on the bf16 path; the bias gradient always accumulates.
-    if (bias_ != nullptr && dy.dtype == DType::BF16) epi.dbias = &bias_->grad;
-    kernels::matmul_ex(ctx, weight_.grad, dy, x, true, false, 1.0f, 1.0f, epi);   // dW += dy^T x
+    if (bias_ != nullptr && dy.dtype == DType::BF16) calls[1].epi.dbias = &bias_->grad;
+    kernels::matmul_grouped(ctx, calls, 2);
 }
 
 MLP::MLP(ParamStore& ps, const std::string& name, int64_t d_model, int64_t d_ff, bool bias) noexcept

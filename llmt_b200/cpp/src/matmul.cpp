@@ -59,10 +59,10 @@ void check_policy(const RunCtx& ctx, DType ab) noexcept {
                       dtype_name(pp.gemm_compute), dtype_name(pp.reduce), dtype_name(ab));
 }
 
-}  // namespace
-
-void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
-               bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept {
+// Validates one call the way llmt does and fills the C-ABI descriptor for it.
+llmt_b200_gemm_desc make_desc(const RunCtx& ctx, const Tensor& c, const Tensor& a, const Tensor& b,
+                              bool trans_a, bool trans_b, float alpha, float beta,
+                              const Epilogue& epi) noexcept {
     const Problem p = check(c, a, b, trans_a, trans_b);
     check_policy(ctx, a.dtype);
     const int r = c.shape.rank - 2;
@@ -87,8 +87,6 @@ void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, b
         d.dbias = static_cast<float*>(epi.dbias->data);
         d.dbias_beta = epi.dbias_beta;
     }
-    d.workspace = ctx.blas_workspace;
-    d.workspace_bytes = ctx.blas_workspace_bytes;
     if (ctx.algo_cache != nullptr) {
         const AlgoKey key{p.m, p.n, p.k, p.batch, (trans_a ? 1LL : 0LL) | (trans_b ? 2LL : 0LL),
                           static_cast<int64_t>(a.dtype), static_cast<int64_t>(c.dtype),
@@ -100,8 +98,60 @@ void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, b
             map.emplace(key, std::string(buf));
         }
     }
+    return d;
+}
+
+}  // namespace
+
+void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
+               bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept {
+    llmt_b200_gemm_desc d = make_desc(ctx, c, a, b, trans_a, trans_b, alpha, beta, epi);
+    d.workspace = ctx.blas_workspace;
+    d.workspace_bytes = ctx.blas_workspace_bytes;
     const int st = llmt_b200_gemm(&d, c.data, a.data, b.data, ctx.stream);
     if (st != LLMT_B200_OK) detail::fatal("matmul", "%s", llmt_b200_last_error());
+}
+
+void matmul_grouped(const RunCtx& ctx, const MatmulCall* calls, int count) noexcept {
+    constexpr int kMax = 8;
+    if (count < 1 || count > kMax) detail::fatal("matmul_grouped", "count must be 1..%d", kMax);
+    bool all_bf16 = true;
+    for (int i = 0; i < count; ++i) {
+        if (calls[i].c == nullptr || calls[i].a == nullptr || calls[i].b == nullptr)
+            detail::fatal("matmul_grouped", "invalid tensor (null data)");
+        all_bf16 = all_bf16 && calls[i].a->dtype == DType::BF16;
+    }
+    if (!all_bf16) {  // the strict fp32 path has no grouped kernel
+        for (int i = 0; i < count; ++i)
+            matmul_ex(ctx, *calls[i].c, *calls[i].a, *calls[i].b, calls[i].trans_a, calls[i].trans_b,
+                      calls[i].alpha, calls[i].beta, calls[i].epi);
+        return;
+    }
+    llmt_b200_gemm_desc d[kMax];
+    void* c[kMax];
+    const void* a[kMax];
+    const void* b[kMax];
+    for (int i = 0; i < count; ++i) {
+        d[i] = make_desc(ctx, *calls[i].c, *calls[i].a, *calls[i].b, calls[i].trans_a, calls[i].trans_b,
+                         calls[i].alpha, calls[i].beta, calls[i].epi);
+        c[i] = calls[i].c->data; a[i] = calls[i].a->data; b[i] = calls[i].b->data;
+    }
+    // Carve the Device-owned scratch into one 256-byte aligned piece per problem.
+    uint64_t need[kMax];
+    if (llmt_b200_gemm_grouped_workspace_bytes(d, count, need) != LLMT_B200_OK)
+        detail::fatal("matmul_grouped", "%s", llmt_b200_last_error());
+    size_t off = 0;
+    for (int i = 0; i < count; ++i) {
+        if (need[i] == 0) continue;
+        if (off + need[i] > ctx.blas_workspace_bytes)
+            detail::fatal("matmul_grouped", "workspace too small: need %zu B, have %zu B",
+                          off + static_cast<size_t>(need[i]), ctx.blas_workspace_bytes);
+        d[i].workspace = static_cast<char*>(ctx.blas_workspace) + off;
+        d[i].workspace_bytes = need[i];
+        off += (static_cast<size_t>(need[i]) + 255) / 256 * 256;
+    }
+    if (llmt_b200_gemm_grouped(d, c, a, b, count, ctx.stream) != LLMT_B200_OK)
+        detail::fatal("matmul_grouped", "%s", llmt_b200_last_error());
 }
 
 void matmul(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 #include "../../include/llmt_b200.h"
 #include "common.h"
@@ -82,13 +83,37 @@ int sm_count() {
     return cached;
 }
 
-// Cost of one 64-deep k-block of a 128 x bn tile in SM cycles: the larger of the
-// tensor-core time (128*bn*64*2 flop at 8192 flop/clk) and the shared-memory
-// operand read time ((128+bn) rows x 128 B at 128 B/clk).
-int kblock_cost(int bn) { return bn * 2 > 128 + bn ? bn * 2 : 128 + bn; }
+// Cost of one 64-deep k-block of a 128 x bn tile in SM cycles: tensor time is 2*bn
+// cycles (128*bn*64*2 flop at 8192 flop/clk); below it sit a floor of ~420 cycles per
+// tcgen05.commit and the time to stream (128+bn) rows of operands from L2.
+int kblock_cost(int bn) {
+    const int mma = bn * 2, floor_cycles = 420 + bn / 2;
+    return mma > floor_cycles ? mma : floor_cycles;
+}
 
-// Split-K factor for a problem that has `tiles` output tiles: only when the
-// tiles cannot fill the machine and the reduction is long enough to share.
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int bn, int splits) {
+    pl->bn = bn;
+    pl->tiles_m = ceil_div(m, 128);
+    pl->tiles_n = ceil_div(n, bn);
+    pl->kblocks_total = ceil_div(k, 64);
+    if (splits > pl->kblocks_total) splits = pl->kblocks_total;
+    if (splits < 1) splits = 1;
+    pl->kblocks_per_split = ceil_div(pl->kblocks_total, splits);
+    pl->splits = pl->kblocks_total > 0 ? ceil_div(pl->kblocks_total, pl->kblocks_per_split) : 1;
+    pl->num_tiles = static_cast<int64_t>(pl->tiles_m) * pl->tiles_n * pl->splits * batch;
+    pl->workspace_bytes = 0;
+    if (pl->splits > 1) {
+        size_t ws = static_cast<size_t>(batch) * pl->splits * m * n * sizeof(float);
+        ws = (ws + 255) / 256 * 256;
+        if (dbias) ws += (static_cast<size_t>(pl->splits) * m * sizeof(float) + 255) / 256 * 256;
+        pl->workspace_bytes = ws;
+    }
+}
+
+// Split-K factor for a problem launched on its own: only when its tiles cannot fill
+// the machine and the reduction is long enough to share.
 int choose_splits(int64_t tiles, int kblocks_total, int sms) {
     int splits = 1;
     if (tiles * 2 <= sms && kblocks_total >= 8) {
@@ -100,12 +125,13 @@ int choose_splits(int64_t tiles, int kblocks_total, int sms) {
     return splits;
 }
 
+// Plan of a problem launched on its own: tile width and split count from a cycle model
+// of waves of equal tiles.  A pure function of its arguments.
 TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
                  int force_bn = 0, int force_splits = 0) {
-    TcPlan pl{};
     const int cands[4] = {256, 192, 128, 64};
-    const int tiles_m = static_cast<int>((m + 127) / 128);
-    const int kblocks_total = static_cast<int>((k + 63) / 64);
+    const int tiles_m = ceil_div(m, 128);
+    const int kblocks_total = ceil_div(k, 64);
     int best_bn = 0, best_splits = 1;
     int64_t best_cost = 0;
     for (int bn : cands) {
@@ -113,42 +139,48 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
         if (force_bn != 0 && bn != force_bn) continue;
         // Never pick a tile wider than needed when a narrower one covers n in one column.
         if (force_bn == 0 && bn > 64 && n <= bn - 64) continue;
-        const int64_t tiles = static_cast<int64_t>(tiles_m) * ((n + bn - 1) / bn) * batch;
+        const int64_t tiles = static_cast<int64_t>(tiles_m) * ceil_div(n, bn) * batch;
         int splits = force_splits > 0 ? force_splits : choose_splits(tiles, kblocks_total, sms);
         if (splits > kblocks_total) splits = kblocks_total > 0 ? kblocks_total : 1;
-        const int kps = (kblocks_total + splits - 1) / splits;
+        const int kps = ceil_div(kblocks_total, splits);
         const int64_t waves = (tiles * splits + sms - 1) / sms;
-        // Estimated cycles: main loops, plus one pass over the partial sums when split.
-        int64_t cost = waves * kblock_cost(bn) * (kps > 0 ? kps : 1);
-        if (splits > 1) cost += static_cast<int64_t>(splits) * 64;
+        // Estimated cycles: main loops, an epilogue per wave, one pass over the partials when split.
+        int64_t cost = waves * (static_cast<int64_t>(kblock_cost(bn)) * (kps > 0 ? kps : 1) + 8 * bn);
+        if (splits > 1) cost += static_cast<int64_t>(splits) * 64 + 4000;
         if (best_bn == 0 || cost < best_cost) {
             best_bn = bn;
             best_cost = cost;
             best_splits = splits;
         }
     }
-    pl.bn = best_bn;
-    pl.tiles_m = tiles_m;
-    pl.tiles_n = static_cast<int>((n + pl.bn - 1) / pl.bn);
-    pl.kblocks_total = kblocks_total;
-    const int64_t tiles = static_cast<int64_t>(pl.tiles_m) * pl.tiles_n * batch;
-    const int splits = best_splits;
-    pl.kblocks_per_split = (pl.kblocks_total + splits - 1) / splits;
-    if (pl.kblocks_per_split < 1) pl.kblocks_per_split = 1;
-    pl.splits = pl.kblocks_total > 0 ? (pl.kblocks_total + pl.kblocks_per_split - 1) / pl.kblocks_per_split : 1;
-    const int64_t total = tiles * pl.splits;
-    pl.grid = static_cast<int>(total < sms ? total : sms);
-    int stages = 8;
-    while (stages > 2 && tc_smem_bytes(pl.bn, stages, dbias) > 227u * 1024u) --stages;
-    pl.stages = stages;
-    pl.smem_bytes = tc_smem_bytes(pl.bn, stages, dbias);
-    pl.workspace_bytes = 0;
-    if (pl.splits > 1) {
-        size_t ws = static_cast<size_t>(batch) * pl.splits * m * n * sizeof(float);
-        ws = (ws + 255) / 256 * 256;
-        if (dbias) ws += (static_cast<size_t>(pl.splits) * m * sizeof(float) + 255) / 256 * 256;
-        pl.workspace_bytes = ws;
+    TcPlan pl{};
+    finish_plan(&pl, m, n, k, batch, dbias, best_bn, best_splits);
+    return pl;
+}
+
+// Plan of a problem that shares its launch with others: the queue is dynamic, so wave
+// quantisation of one problem does not matter; take the widest tile that wastes nothing
+// and split only reductions that are longer than the average load of an SM.
+TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
+                       int64_t group_kblock_tiles, int force_bn, int force_splits) {
+    int bn = dbias ? 192 : 256;
+    if (n <= 64) bn = 64;
+    else if (n <= 128) bn = 128;
+    else if (n <= 192) bn = 192;
+    if (force_bn != 0) bn = force_bn;
+    const int kblocks_total = ceil_div(k, 64);
+    int splits = 1;
+    if (force_splits > 0) {
+        splits = force_splits;
+    } else {
+        const int64_t avg = group_kblock_tiles / sms;  // k-blocks per SM if perfectly balanced
+        const int64_t target = avg > 16 ? avg : 16;
+        if (kblocks_total > target + target / 4) splits = ceil_div(kblocks_total, target);
+        const int max_by_k = kblocks_total / 4 > 0 ? kblocks_total / 4 : 1;
+        if (splits > max_by_k) splits = max_by_k;
     }
+    TcPlan pl{};
+    finish_plan(&pl, m, n, k, batch, dbias, bn, splits);
     return pl;
 }
 
@@ -257,9 +289,48 @@ int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t
                       CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const void* a, const void* b,
-             cudaStream_t stream) {
-    // TMA needs 16-byte aligned bases and pitches.
+// bf16 1.0 block for the fused dbias, inside the library image; filled once per device.
+static __device__ __align__(1024) uint16_t g_ones[64 * 64];
+// Tile-queue counters: zero between launches (the kernel re-arms its counter); launches
+// take them round-robin so that kernels in flight at the same time do not share one.
+constexpr int kSchedSlots = 64;
+static __device__ int32_t g_sched_counters[kSchedSlots];
+
+struct DeviceGlobals {
+    bool ready = false;
+    CUtensorMap map_ones;
+    int32_t* counters = nullptr;
+    unsigned next = 0;
+};
+
+int device_globals(DeviceGlobals** out) {
+    static DeviceGlobals globals[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return fail(LLMT_B200_ERR_CUDA, "no current CUDA device");
+    DeviceGlobals& g = globals[dev];
+    if (!g.ready) {
+        static uint16_t host_ones[64 * 64];
+        for (uint16_t& v : host_ones) v = 0x3F80;  // bf16 1.0
+        void* ones = nullptr;
+        void* ctr = nullptr;
+        cudaError_t e = cudaMemcpyToSymbol(g_ones, host_ones, sizeof host_ones);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ones, g_ones);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ctr, g_sched_counters);
+        if (e == cudaSuccess) e = cudaMemset(ctr, 0, sizeof(int32_t) * kSchedSlots);
+        if (e != cudaSuccess)
+            return fail(LLMT_B200_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
+        const int st = encode_map(&g.map_ones, ones, 2, 64, 64, 64, 1, 0, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != LLMT_B200_OK) return st;
+        g.counters = static_cast<int32_t*>(ctr);
+        g.ready = true;
+    }
+    *out = &g;
+    return LLMT_B200_OK;
+}
+
+// TMA needs 16-byte aligned bases and pitches.
+int check_tma_operands(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
     if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u))
         return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: bf16 operands must start on a 16-byte boundary");
     if ((d->lda % 8) != 0 || (d->ldb % 8) != 0 ||
@@ -267,70 +338,140 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
         return fail(LLMT_B200_ERR_UNSUPPORTED,
                     "matmul: bf16 row pitch / batch stride must be a multiple of 8 elements "
                     "(lda=%lld ldb=%lld)", (long long)d->lda, (long long)d->ldb);
-    const bool dbias = d->dbias != nullptr;
-    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, dbias, sm_count(), d->plan_tile_n, d->plan_splits);
-    if (pl.workspace_bytes > 0) {
-        if (d->workspace == nullptr || d->workspace_bytes < pl.workspace_bytes)
-            return fail(LLMT_B200_ERR_WORKSPACE, "matmul: split-K needs %llu workspace bytes, got %llu",
-                        (unsigned long long)pl.workspace_bytes, (unsigned long long)d->workspace_bytes);
-        if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
-            return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
-    }
-    TcGemmParams p{};
-    p.m = d->m; p.n = d->n; p.k = d->k;
-    p.batch = static_cast<int32_t>(d->batch);
-    p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n; p.splits = pl.splits;
-    p.kblocks_total = pl.kblocks_total;
-    p.kblocks_per_split = pl.kblocks_per_split;
-    p.total_tiles = static_cast<int64_t>(pl.tiles_m) * pl.tiles_n * pl.splits * d->batch;
-    p.c = c; p.ldc = d->ldc; p.stride_c = d->batch > 1 ? d->stride_c : 0;
-    p.c_is_bf16 = d->dtype_c == LLMT_B200_BF16;
-    p.alpha = d->alpha; p.beta = d->beta;
-    p.bias = d->bias; p.bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
-    p.epi_flags = d->epilogue;
-    p.dbias = d->dbias; p.dbias_beta = d->dbias_beta;
-    p.status = device_status_ptr();
-    if (p.status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
+    return LLMT_B200_OK;
+}
+
+int check_workspace(const llmt_b200_gemm_desc* d, const TcPlan& pl) {
+    if (pl.workspace_bytes == 0) return LLMT_B200_OK;
+    if (d->workspace == nullptr || d->workspace_bytes < pl.workspace_bytes)
+        return fail(LLMT_B200_ERR_WORKSPACE, "matmul: split-K needs %llu workspace bytes, got %llu",
+                    (unsigned long long)pl.workspace_bytes, (unsigned long long)d->workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
+    return LLMT_B200_OK;
+}
+
+// Fills the kernel-side description of one problem (tensor maps included).
+int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& ck, const TcPlan& pl,
+                 void* c, const void* a, const void* b) {
+    memset(p, 0, sizeof *p);
+    p->m = d->m; p->n = d->n; p->k = d->k;
+    p->batch = static_cast<int32_t>(d->batch);
+    p->tiles_m = pl.tiles_m; p->tiles_n = pl.tiles_n; p->splits = pl.splits;
+    p->kblocks_total = pl.kblocks_total;
+    p->kblocks_per_split = pl.kblocks_per_split;
+    p->bn = pl.bn;
+    p->a_mn = d->trans_a ? 1 : 0;  // A stored [k, m]: m contiguous
+    p->b_mn = d->trans_b ? 0 : 1;  // B stored [k, n]: n contiguous
+    p->num_tiles = static_cast<int32_t>(pl.num_tiles);
+    p->c = c; p->ldc = d->ldc; p->stride_c = d->batch > 1 ? d->stride_c : 0;
+    p->c_is_bf16 = d->dtype_c == LLMT_B200_BF16;
+    p->alpha = d->alpha; p->beta = d->beta;
+    p->bias = d->bias; p->bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
+    p->epi_flags = d->epilogue;
+    p->dbias = d->dbias; p->dbias_beta = d->dbias_beta;
     if (pl.splits > 1) {
-        p.ws = static_cast<float*>(d->workspace);
+        p->ws = static_cast<float*>(d->workspace);
         size_t ws = static_cast<size_t>(d->batch) * pl.splits * d->m * d->n * sizeof(float);
         ws = (ws + 255) / 256 * 256;
-        p.ws_dbias = dbias ? reinterpret_cast<float*>(static_cast<char*>(d->workspace) + ws) : nullptr;
+        p->ws_dbias = d->dbias ? reinterpret_cast<float*>(static_cast<char*>(d->workspace) + ws) : nullptr;
     }
-    if (d->k == 0) {
-        // Empty reduction: C = epilogue(beta * C).  The reduce kernel with zero
-        // partial sums computes exactly that.
-        p.splits = 0;
-        cudaError_t e = launch_splitk_reduce(p, stream);
-        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
-        return LLMT_B200_OK;
-    }
-    const int a_mn = d->trans_a ? 1 : 0;  // A stored [k, m]: m contiguous
-    const int b_mn = d->trans_b ? 0 : 1;  // B stored [k, n]: n contiguous
-    CUtensorMap ma, mb;
-    int st = encode_operand_map(&ma, a, ck.a_rows, ck.a_cols, d->lda, d->batch, d->stride_a,
-                                a_mn ? 64 : 128);
+    if (d->k == 0) return LLMT_B200_OK;  // no operand is read
+    int st = encode_operand_map(&p->map_a, a, ck.a_rows, ck.a_cols, d->lda, d->batch, d->stride_a,
+                                p->a_mn ? 64 : 128);
     if (st != LLMT_B200_OK) return st;
-    st = encode_operand_map(&mb, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
-                            b_mn ? 64 : pl.bn);
+    st = encode_operand_map(&p->map_b, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
+                            p->b_mn ? 64 : pl.bn);
     if (st != LLMT_B200_OK) return st;
     // C leaves through shared memory and TMA stores when its layout allows a tensor map
     // (16-byte aligned base, pitch and batch stride); otherwise straight from registers.
-    CUtensorMap mc;
-    memset(&mc, 0, sizeof mc);
-    const int ces = p.c_is_bf16 ? 2 : 4;
+    const int ces = p->c_is_bf16 ? 2 : 4;
     if ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
         (d->batch <= 1 || (d->stride_c * ces) % 16 == 0) && pl.splits == 1) {
-        st = encode_map(&mc, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, 32, 128,
-                        p.c_is_bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+        st = encode_map(&p->map_c, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, 32, 128,
+                        p->c_is_bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != LLMT_B200_OK) return st;
-        p.c_tma = 1;
+        p->c_tma = 1;
     }
-    cudaError_t e = launch_tc_gemm(pl, a_mn, b_mn, ma, mb, mc, p, stream);
-    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
-    if (pl.splits > 1) {
-        e = launch_splitk_reduce(p, stream);
+    return LLMT_B200_OK;
+}
+
+// Launches the tensor-core kernel over `count` filled problems (longest tiles first),
+// then the fixed-order reduction of every problem that was split.
+int launch_group(GroupProblem* probs, int count, cudaStream_t stream) {
+    DeviceGlobals* g = nullptr;
+    int st = device_globals(&g);
+    if (st != LLMT_B200_OK) return st;
+    static GroupParams gp;  // one host thread issues launches (as in llmt, matmul.cpp:23-27)
+    // Longest reductions first: with a dynamic queue this is longest-processing-time-first.
+    int order[kMaxGroupProblems];
+    for (int i = 0; i < count; ++i) order[i] = i;
+    for (int i = 1; i < count; ++i)
+        for (int j = i; j > 0 && probs[order[j]].kblocks_per_split > probs[order[j - 1]].kblocks_per_split; --j) {
+            const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+        }
+    int64_t total = 0;
+    int n = 0;
+    for (int i = 0; i < count; ++i) {
+        GroupProblem& p = probs[order[i]];
+        if (p.k == 0 || p.num_tiles == 0) continue;
+        p.tile_begin = static_cast<int32_t>(total);
+        total += p.num_tiles;
+        gp.prob[n++] = p;
+    }
+    if (total > 0x7fffff00) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: too many tiles in one launch");
+    if (n > 0) {
+        gp.map_ones = g->map_ones;
+        gp.num_problems = n;
+        gp.total_tiles = static_cast<int32_t>(total);
+        gp.sched_counter = g->counters + (g->next++ % kSchedSlots);
+        { const char* e = getenv("LLMT_B200_STATIC"); gp.static_schedule = (e && e[0] == '1') ? 1 : 0; }
+        gp.status = device_status_ptr();
+        if (gp.status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
+        const int sms = sm_count();
+        const int grid = static_cast<int>(total < sms ? total : sms);
+        cudaError_t e = launch_tc_grouped(gp, grid, stream);
         if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    }
+    for (int i = 0; i < count; ++i) {
+        GroupProblem p = probs[i];
+        if (p.k == 0) p.splits = 0;  // empty reduction: C = epilogue(beta * C)
+        if (p.splits == 1) continue;
+        cudaError_t e = launch_splitk_reduce(p, stream);
+        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    }
+    return LLMT_B200_OK;
+}
+
+int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const void* a, const void* b,
+             cudaStream_t stream) {
+    int st = check_tma_operands(d, a, b);
+    if (st != LLMT_B200_OK) return st;
+    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(),
+                                d->plan_tile_n, d->plan_splits);
+    st = check_workspace(d, pl);
+    if (st != LLMT_B200_OK) return st;
+    GroupProblem p;
+    st = fill_problem(&p, d, ck, pl, c, a, b);
+    if (st != LLMT_B200_OK) return st;
+    return launch_group(&p, 1, stream);
+}
+
+// Group plans: every problem is planned knowing the total work of the launch.
+int plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
+    const int sms = sm_count();
+    int64_t work = 0;
+    for (int i = 0; i < count; ++i) {
+        const llmt_b200_gemm_desc& d = descs[i];
+        const int bn = d.dbias ? 192 : 256;
+        work += static_cast<int64_t>(ceil_div(d.m, 128)) * ceil_div(d.n, bn) * (d.batch > 0 ? d.batch : 1) *
+                ceil_div(d.k, 64);
+    }
+    for (int i = 0; i < count; ++i) {
+        const llmt_b200_gemm_desc& d = descs[i];
+        plans[i] = count == 1 ? make_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, d.plan_tile_n, d.plan_splits)
+                              : make_group_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, work,
+                                                d.plan_tile_n, d.plan_splits);
     }
     return LLMT_B200_OK;
 }
@@ -420,6 +561,55 @@ int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const v
     return run_bf16(&local, ck, c, a, b, s);
 }
 
+int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, const void* const* a,
+                           const void* const* b, int32_t count, void* stream) {
+    if (descs == nullptr || c == nullptr || a == nullptr || b == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: null argument");
+    if (count < 1 || count > kMaxGroupProblems)
+        return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: count must be 1..%d", kMaxGroupProblems);
+    Checked ck[kMaxGroupProblems];
+    for (int i = 0; i < count; ++i) {
+        const int st = validate(&descs[i], c[i], a[i], b[i], &ck[i]);
+        if (st != LLMT_B200_OK) return st;
+        if (!ck[i].bf16)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "gemm_grouped: problem %d is not a bf16 problem", i);
+        const int st2 = check_tma_operands(&descs[i], a[i], b[i]);
+        if (st2 != LLMT_B200_OK) return st2;
+        // A problem must not write what another problem of the same launch reads or writes.
+        for (int j = 0; j < i; ++j)
+            if (c[i] == c[j] || c[i] == a[j] || c[i] == b[j] || c[j] == a[i] || c[j] == b[i])
+                return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: problems %d and %d are not independent", j, i);
+    }
+    TcPlan plans[kMaxGroupProblems];
+    plan_group(descs, count, plans);
+    GroupProblem probs[kMaxGroupProblems];
+    int n = 0;
+    for (int i = 0; i < count; ++i) {
+        if (descs[i].m == 0 || descs[i].n == 0 || descs[i].batch == 0) continue;
+        int st = check_workspace(&descs[i], plans[i]);
+        if (st != LLMT_B200_OK) return st;
+        st = fill_problem(&probs[n], &descs[i], ck[i], plans[i], c[i], a[i], b[i]);
+        if (st != LLMT_B200_OK) return st;
+        ++n;
+    }
+    if (n == 0) return LLMT_B200_OK;
+    return launch_group(probs, n, static_cast<cudaStream_t>(stream));
+}
+
+int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int32_t count,
+                                           uint64_t* bytes_per_problem) {
+    if (descs == nullptr || bytes_per_problem == nullptr || count < 1 || count > kMaxGroupProblems)
+        return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_workspace_bytes: bad argument");
+    TcPlan plans[kMaxGroupProblems];
+    plan_group(descs, count, plans);
+    for (int i = 0; i < count; ++i) {
+        const llmt_b200_gemm_desc& d = descs[i];
+        bytes_per_problem[i] = (d.dtype_ab == LLMT_B200_BF16 && d.m > 0 && d.n > 0 && d.k > 0 && d.batch > 0)
+                                   ? plans[i].workspace_bytes : 0;
+    }
+    return LLMT_B200_OK;
+}
+
 uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
     if (d == nullptr || d->dtype_ab != LLMT_B200_BF16 || d->m <= 0 || d->n <= 0 || d->k <= 0 ||
         d->batch <= 0)
@@ -437,9 +627,11 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
     }
     const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(), d->plan_tile_n,
                      d->plan_splits);
-    snprintf(buf, n, "tcgen05 tile=128x%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
-             pl.bn, pl.stages, pl.splits, pl.tiles_m, pl.tiles_n, pl.kblocks_total, pl.grid,
-             pl.smem_bytes, pl.workspace_bytes);
+    const int sms = sm_count();
+    snprintf(buf, n, "tcgen05 tile=128x%dx64 stages=4 splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
+             pl.bn, pl.splits, pl.tiles_m, pl.tiles_n, pl.kblocks_total,
+             static_cast<int>(pl.num_tiles < sms ? pl.num_tiles : sms), tc_grouped_smem_bytes(),
+             pl.workspace_bytes);
     return LLMT_B200_OK;
 }
 

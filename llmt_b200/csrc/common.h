@@ -21,24 +21,31 @@ enum DeviceErr : int32_t {
     kDevWaitSmemEmpty = 1,   // TMA producer gave up waiting for a free pipeline slot
     kDevWaitSmemFull = 2,    // MMA issuer gave up waiting for operand bytes to land
     kDevWaitTmemEmpty = 3,   // MMA issuer gave up waiting for the epilogue to drain an accumulator
-    kDevWaitTmemFull = 4     // epilogue gave up waiting for an accumulator to complete
+    kDevWaitTmemFull = 4,    // epilogue gave up waiting for an accumulator to complete
+    kDevWaitSched = 5        // a role gave up waiting on the tile scheduler ring
 };
 
 constexpr int kEpiBias = 1;
 constexpr int kEpiGelu = 2;
 
-// Everything the tensor-core kernel needs besides the two operand tensor maps.
-struct TcGemmParams {
+constexpr int kMaxGroupProblems = 8;
+
+// One GEMM of a group as the tensor-core kernel sees it.
+struct alignas(64) GroupProblem {
+    CUtensorMap map_a, map_b, map_c;  // operand loads (128B swizzle), C store (32-column slabs)
     int64_t m, n, k;
     int32_t batch;
     int32_t tiles_m, tiles_n, splits;
     int32_t kblocks_total;      // ceil(k / 64)
-    int32_t kblocks_per_split;  // k-blocks handled by each split (last one may be shorter)
-    int64_t total_tiles;        // tiles_m * tiles_n * splits * batch
+    int32_t kblocks_per_split;  // k-blocks handled by each split (the last one may be shorter)
+    int32_t bn;                 // tile width along N: 64, 128, 192 or 256 (tile height is 128)
+    int32_t a_mn, b_mn;         // operand stored with M / N contiguous (transposed use)
+    int32_t tile_begin;         // first tile of this problem in the group's queue
+    int32_t num_tiles;          // tiles_m * tiles_n * splits * batch
     void* c;
     int64_t ldc, stride_c;
     int32_t c_is_bf16;
-    int32_t c_tma;              // C has a tensor map: tiles leave through shared memory + TMA store
+    int32_t c_tma;              // map_c is valid: tiles leave through shared memory + TMA store
     float alpha, beta;
     const void* bias;
     int32_t bias_is_bf16;
@@ -47,18 +54,26 @@ struct TcGemmParams {
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
     float* ws_dbias;            // [splits][m] fp32 (splits > 1 and dbias wanted)
+};
+
+struct GroupParams {
+    CUtensorMap map_ones;       // 64 x 64 block of bf16 1.0 (fused dbias)
+    GroupProblem prob[kMaxGroupProblems];
+    int32_t num_problems;
+    int32_t total_tiles;
+    int32_t static_schedule;    // 1 = tile i goes to CTA i % grid instead of the dynamic queue
+    int32_t* sched_counter;     // zero between launches; the kernel re-arms it
     DeviceStatus* status;
 };
 
-// Plan: the pure function of the problem that fixes every launch parameter.
+// Plan of one problem: the pure function of the problem (and of the work it shares a
+// launch with) that fixes tile width and split count.
 struct TcPlan {
-    int bn;          // tile width along N: 64, 128, 192 or 256 (tile height is always 128)
-    int stages;      // TMA/MMA pipeline depth
-    int splits;      // split-K factor (1 = none)
-    int grid;        // persistent CTAs launched
+    int bn;
+    int splits;
     int tiles_m, tiles_n;
     int kblocks_total, kblocks_per_split;
-    size_t smem_bytes;
+    int64_t num_tiles;
     size_t workspace_bytes;
 };
 
@@ -93,18 +108,15 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
-cudaError_t launch_tc_gemm(const TcPlan& plan, int a_mn_major, int b_mn_major,
-                           const CUtensorMap& map_a, const CUtensorMap& map_b,
-                           const CUtensorMap& map_c, const TcGemmParams& p, cudaStream_t stream);
-cudaError_t launch_splitk_reduce(const TcGemmParams& p, cudaStream_t stream);
+cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, cudaStream_t stream);
+cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
+size_t tc_grouped_smem_bytes(void);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
 cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,
                                int is_bf16, int causal, cudaStream_t stream);
 cudaError_t launch_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
                                int is_bf16, cudaStream_t stream);
-cudaError_t tc_gemm_configure(void);  // sets the dynamic shared-memory attribute once per device
 DeviceStatus* device_status_ptr(void);
-size_t tc_smem_bytes(int bn, int stages, bool dbias);
 
 void count_launch(int n);
 

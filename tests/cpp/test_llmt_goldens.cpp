@@ -186,6 +186,91 @@ void test_attention(Device& dev, const RunCtx& ctx) {
     check_close(yh, load("attention", "out"), "attention_fwd y_heads");
 }
 
+// bf16 Linear with bias through the same C++ interface: forward with the fused bias,
+// backward as ONE grouped launch (dx, dW and dbias).  Checked against the strict-fp32
+// path of the same layer run on the same bf16-rounded values (relative Frobenius:
+// 1e-2 for bf16 outputs, 1e-3 for the fp32 gradients) and a host column sum for dbias.
+uint16_t to_bf16(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return static_cast<uint16_t>(u >> 16);
+}
+float from_bf16(uint16_t h) {
+    const uint32_t u = static_cast<uint32_t>(h) << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+double rel_fro(const std::vector<float>& a, const std::vector<float>& b) {
+    double num = 0, den = 0;
+    for (size_t i = 0; i < a.size(); ++i) { num += (a[i] - b[i]) * double(a[i] - b[i]); den += double(b[i]) * b[i]; }
+    return std::sqrt(num / (den > 0 ? den : 1));
+}
+
+void test_bf16_linear(Device& dev) {
+    const int64_t M = 512, IN = 256, OUT = 384;
+    const RunCtx c32 = dev.make_ctx(1, KernelBackend::Naive, PrecisionPolicy::fp32());
+    const RunCtx c16 = dev.make_ctx(1, KernelBackend::Naive, PrecisionPolicy::bf16_mixed());
+    Arena arena(64 << 20, "bf16-test");
+    uint32_t lcg = 12345u;
+    auto rnd = [&](float scale) { lcg = lcg * 1664525u + 1013904223u; return scale * (static_cast<float>(lcg >> 8) / 8388608.0f - 1.0f); };
+    auto make = [&](int64_t r, int64_t c, float scale, Tensor* t32, Tensor* t16, std::vector<float>* keep) {
+        std::vector<float> h(static_cast<size_t>(r * c));
+        std::vector<uint16_t> hb(h.size());
+        for (size_t i = 0; i < h.size(); ++i) { hb[i] = to_bf16(rnd(scale)); h[i] = from_bf16(hb[i]); }
+        *t32 = arena.alloc({r, c}, DType::FP32);
+        *t16 = arena.alloc({r, c}, DType::BF16);
+        CUDA_CHECK(cudaMemcpy(t32->data, h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+        CUDA_CHECK(cudaMemcpy(t16->data, hb.data(), hb.size() * 2, cudaMemcpyHostToDevice));
+        if (keep) *keep = h;
+    };
+    Tensor x32, x16, dy32, dy16, w32, w16;
+    std::vector<float> dy_host;
+    make(M, IN, 1.0f, &x32, &x16, nullptr);
+    make(M, OUT, 0.01f, &dy32, &dy16, &dy_host);
+    make(OUT, IN, 0.05f, &w32, &w16, nullptr);
+
+    ParamStore ps32(StateDtypes::uniform(DType::FP32));
+    const Linear l32(ps32, "w", IN, OUT, Role::Matrix);
+    ps32.finalize();
+    ParamStore ps16(StateDtypes{DType::BF16, DType::FP32});
+    const Linear l16(ps16, "w", IN, OUT, Role::Matrix, /*bias=*/true);
+    ps16.finalize();
+    CUDA_CHECK(cudaMemcpy(l32.param().weight.data, w32.data, w32.bytes(), cudaMemcpyDeviceToDevice));
+    CUDA_CHECK(cudaMemcpy(l16.param().weight.data, w16.data, w16.bytes(), cudaMemcpyDeviceToDevice));
+    // bias stays zero (finalize zero-fills), so both layers compute the same function
+
+    Tensor y32 = arena.alloc({M, OUT}, DType::FP32), dx32 = arena.alloc({M, IN}, DType::FP32);
+    Tensor y16 = arena.alloc({M, OUT}, DType::BF16), dx16 = arena.alloc({M, IN}, DType::BF16);
+    l32.forward(c32, y32, x32);
+    l32.backward(c32, dx32, dy32, x32);
+    l16.forward(c16, y16, x16);
+    l16.backward(c16, dx16, dy16, x16);
+    dev.synchronize();
+
+    auto widen = [&](const Tensor& t) {
+        std::vector<uint16_t> hb(static_cast<size_t>(t.numel()));
+        CUDA_CHECK(cudaMemcpy(hb.data(), t.data, hb.size() * 2, cudaMemcpyDeviceToHost));
+        std::vector<float> h(hb.size());
+        for (size_t i = 0; i < h.size(); ++i) h[i] = from_bf16(hb[i]);
+        return h;
+    };
+    auto expect = [&](double err, double tol, const char* what) {
+        ++g_checks;
+        if (!(err <= tol)) { ++g_failures; std::fprintf(stderr, "FAIL %s: rel %.3e > %.1e\n", what, err, tol); }
+        else std::printf("ok   %s (rel %.2e)\n", what, err);
+    };
+    expect(rel_fro(widen(y16), download(y32)), 1e-2, "bf16 Linear forward vs fp32 path");
+    expect(rel_fro(widen(dx16), download(dx32)), 1e-2, "bf16 Linear dx (grouped launch) vs fp32 path");
+    expect(rel_fro(download(l16.param().grad), download(l32.param().grad)), 1e-3,
+           "bf16 Linear dW (grouped launch) vs fp32 path");
+    std::vector<float> db(static_cast<size_t>(OUT), 0.0f);
+    for (int64_t r = 0; r < M; ++r)
+        for (int64_t c = 0; c < OUT; ++c) db[static_cast<size_t>(c)] += dy_host[static_cast<size_t>(r * OUT + c)];
+    expect(rel_fro(download(l16.bias_param()->grad), db), 1e-3, "bf16 Linear dbias (fused) vs host column sum");
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -198,6 +283,7 @@ int main(int argc, char** argv) {
     test_linear(dev, ctx);
     test_mlp(dev, ctx);
     test_attention(dev, ctx);
+    test_bf16_linear(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());
     return g_failures == 0 ? 0 : 1;

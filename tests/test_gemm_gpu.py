@@ -452,3 +452,82 @@ def test_config5_xl_mlp_shapes_sampled():
     frows = rng.choice(F, 16, replace=False)
     _check_rows(dw, dy, x, True, False, frows, TOL_BF16_ACC_FRO)
     assert oracle.rel_fro(host(db), oracle.rowsum(dy, trans_a=True)) <= TOL_BF16_ACC_FRO
+
+
+# --------------------------------------------------- several problems, one launch ---
+
+def test_grouped_linear_backward_matches_oracle():
+    """Linear::backward as ONE launch: dx = dy W and dW += dy^T x (+ dbias) share a tile queue
+    (llmt src/layers/linear.cpp:22-30 issues them as two matmul calls)."""
+    tokens, out_f, in_f = 2048, 384, 520
+    rng = np.random.default_rng(31)
+    dy = oracle.round_bf16(rng.standard_normal((tokens, out_f)) * 0.01)
+    x = oracle.round_bf16(rng.standard_normal((tokens, in_f)))
+    w = oracle.round_bf16(rng.standard_normal((out_f, in_f)) * 0.02)
+    dw0 = rng.standard_normal((out_f, in_f)).astype(np.float32)
+    db0 = rng.standard_normal(out_f).astype(np.float32)
+    dyd, xd, wd = dev_bf16(dy), dev_bf16(x), dev_bf16(w)
+    dx = torch.empty(tokens, in_f, device=DEV, dtype=torch.bfloat16)
+    dw, db = dev_f32(dw0), dev_f32(db0)
+    grp = L.Group([
+        (L.make_desc(dx, dyd, wd, False, False), dx, dyd, wd),
+        (L.make_desc(dw, dyd, xd, True, False, beta=1.0, dbias=db, dbias_beta=1.0), dw, dyd, xd),
+    ])
+    need = grp.workspace_bytes()
+    grp.set_workspaces([torch.empty(max(b, 256), dtype=torch.uint8, device=DEV) for b in need])
+    grp.run()
+    assert oracle.rel_fro(host(dx), oracle.gemm(dy, w)) <= TOL_BF16_OUT_FRO
+    assert oracle.rel_fro(host(dw), oracle.gemm(dy, x, trans_a=True, beta=1.0, c=dw0)) <= TOL_BF16_ACC_FRO
+    assert oracle.rel_fro(host(db), oracle.rowsum(dy, trans_a=True, out=db0, out_beta=1.0)) <= TOL_BF16_ACC_FRO
+    # run-to-run: the dynamic tile queue must not change a single bit
+    dx2 = torch.empty_like(dx)
+    dw2, db2 = dev_f32(dw0), dev_f32(db0)
+    grp2 = L.Group([
+        (L.make_desc(dx2, dyd, wd, False, False), dx2, dyd, wd),
+        (L.make_desc(dw2, dyd, xd, True, False, beta=1.0, dbias=db2, dbias_beta=1.0), dw2, dyd, xd),
+    ])
+    grp2.set_workspaces([torch.empty(max(b, 256), dtype=torch.uint8, device=DEV) for b in need])
+    grp2.run()
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2) and torch.equal(db, db2)
+
+
+def test_grouped_mixed_shapes_transposes_and_epilogues():
+    rng = np.random.default_rng(37)
+    specs = [  # m, n, k, ta, tb, out dtype, bias, gelu, alpha, forced splits
+        (300, 520, 200, 0, 1, torch.bfloat16, True, True, 1.0, 0),
+        (136, 72, 1024, 1, 0, torch.float32, False, False, 0.5, 4),
+        (64, 264, 72, 0, 0, torch.float32, True, False, 1.0, 0),
+        (257 + 7, 64, 136, 1, 1, torch.bfloat16, False, False, 2.0, 0),
+    ]
+    probs, refs, outs = [], [], []
+    for (m, n, k, ta, tb, cdt, bias, gelu, alpha, splits) in specs:
+        a = oracle.round_bf16(rng.standard_normal((k, m) if ta else (m, k)))
+        b = oracle.round_bf16(rng.standard_normal((n, k) if tb else (k, n)) * 0.3)
+        bv = (rng.standard_normal(n) * 0.5).astype(np.float32) if bias else None
+        c = torch.empty(m, n, device=DEV, dtype=cdt)
+        ad, bd = dev_bf16(a), dev_bf16(b)
+        bt = dev_f32(bv) if bias else None
+        probs.append((L.make_desc(c, ad, bd, bool(ta), bool(tb), alpha=alpha, bias=bt, gelu=gelu,
+                                  splits=splits), c, ad, bd, bt))
+        refs.append(oracle.epilogue(oracle.gemm(a, b, bool(ta), bool(tb), alpha), bias=bv, gelu=gelu))
+        outs.append((c, cdt))
+    grp = L.Group([p[:4] for p in probs])
+    need = grp.workspace_bytes()
+    assert need[1] > 0  # the forced split needs scratch
+    grp.set_workspaces([torch.empty(max(b, 256), dtype=torch.uint8, device=DEV) for b in need])
+    grp.run()
+    for (c, cdt), ref in zip(outs, refs):
+        tol = TOL_BF16_OUT_FRO if cdt == torch.bfloat16 else TOL_BF16_ACC_FRO
+        assert oracle.rel_fro(host(c), ref) <= tol
+
+
+def test_grouped_rejects_dependent_problems():
+    x = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
+    y = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    z = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    grp = L.Group([(L.make_desc(y, x, w, False, True), y, x, w),
+                   (L.make_desc(z, y, w, False, True), z, y, w)])  # second reads what the first writes
+    with pytest.raises(L.LlmtB200Error) as e:
+        grp.run()
+    assert e.value.status == L.ERR_INVALID and "independent" in str(e.value)
