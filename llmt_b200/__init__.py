@@ -12,7 +12,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libllmt_b200.so")
+# LLMT_B200_LIB selects another build of the same library (e.g. an instrumented one).
+LIB_PATH = os.environ.get("LLMT_B200_LIB") or os.path.join(_HERE, "lib", "libllmt_b200.so")
 
 FP32, BF16 = 0, 1
 EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2

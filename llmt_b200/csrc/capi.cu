@@ -93,9 +93,11 @@ int kblock_cost(int bn) {
 
 int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
-void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int bn, int splits) {
+void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int bn, int splits,
+                 bool pairs) {
     pl->bn = bn;
-    pl->tiles_m = ceil_div(m, 128);
+    pl->pairs = pairs ? 1 : 0;
+    pl->tiles_m = ceil_div(m, pairs ? 256 : 128);
     pl->tiles_n = ceil_div(n, bn);
     pl->kblocks_total = ceil_div(k, 64);
     if (splits > pl->kblocks_total) splits = pl->kblocks_total;
@@ -127,18 +129,22 @@ int choose_splits(int64_t tiles, int kblocks_total, int sms) {
 
 // Plan of a problem launched on its own: tile width and split count from a cycle model
 // of waves of equal tiles.  A pure function of its arguments.
-TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
-                 int force_bn = 0, int force_splits = 0) {
+// `pairs`: the launch uses CTA pairs (256-row tiles, `units` = number of pairs); with
+// MN-major B a pair needs a tile width that is a multiple of 128.
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int units,
+                 int force_bn, int force_splits, bool pairs, bool b_mn) {
+    const int sms = units;
     const int cands[4] = {256, 192, 128, 64};
-    const int tiles_m = ceil_div(m, 128);
+    const int tiles_m = ceil_div(m, pairs ? 256 : 128);
     const int kblocks_total = ceil_div(k, 64);
     int best_bn = 0, best_splits = 1;
     int64_t best_cost = 0;
     for (int bn : cands) {
         if (dbias && bn > 192) continue;
         if (force_bn != 0 && bn != force_bn) continue;
+        if (pairs && (bn == 64 || (b_mn && bn % 128 != 0))) continue;
         // Never pick a tile wider than needed when a narrower one covers n in one column.
-        if (force_bn == 0 && bn > 64 && n <= bn - 64) continue;
+        if (force_bn == 0 && bn > 64 && n <= bn - 64 && !(pairs && bn == 128)) continue;
         const int64_t tiles = static_cast<int64_t>(tiles_m) * ceil_div(n, bn) * batch;
         int splits = force_splits > 0 ? force_splits : choose_splits(tiles, kblocks_total, sms);
         if (splits > kblocks_total) splits = kblocks_total > 0 ? kblocks_total : 1;
@@ -154,7 +160,8 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
         }
     }
     TcPlan pl{};
-    finish_plan(&pl, m, n, k, batch, dbias, best_bn, best_splits);
+    if (best_bn == 0) best_bn = pairs ? 128 : 64;
+    finish_plan(&pl, m, n, k, batch, dbias, best_bn, best_splits, pairs);
     return pl;
 }
 
@@ -162,11 +169,11 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
 // quantisation of one problem does not matter; take the widest tile that wastes nothing
 // and split only reductions that are longer than the average load of an SM.
 TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
-                       int64_t group_kblock_tiles, int force_bn, int force_splits) {
+                       int64_t group_kblock_tiles, int force_bn, int force_splits, bool pairs, bool b_mn) {
     int bn = dbias ? 192 : 256;
-    if (n <= 64) bn = 64;
+    if (n <= 64) bn = pairs ? 128 : 64;
     else if (n <= 128) bn = 128;
-    else if (n <= 192) bn = 192;
+    else if (n <= 192) bn = (pairs && b_mn) ? 256 : 192;
     if (force_bn != 0) bn = force_bn;
     const int kblocks_total = ceil_div(k, 64);
     int splits = 1;
@@ -180,8 +187,37 @@ TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbia
         if (splits > max_by_k) splits = max_by_k;
     }
     TcPlan pl{};
-    finish_plan(&pl, m, n, k, batch, dbias, bn, splits);
+    finish_plan(&pl, m, n, k, batch, dbias, bn, splits, pairs);
     return pl;
+}
+
+// CTA pairs (cta_group::2, 256-row tiles) halve the operand bytes per flop; they need
+// a problem without the fused dbias and at least two 128-row tiles of rows.
+// LLMT_B200_PAIRS=0 keeps every launch on single CTAs (for comparisons).
+bool pairs_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LLMT_B200_PAIRS");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+bool pair_eligible(const llmt_b200_gemm_desc* d) {
+    if (!pairs_enabled() || d->dbias != nullptr || d->m <= 128) return false;
+    if (d->plan_tile_n == 64) return false;
+    const bool b_mn = d->trans_b == 0;
+    if (b_mn && d->plan_tile_n == 192) return false;
+    return true;
+}
+int pair_units() {
+    const int r = max_resident_pairs();
+    const int by_sm = sm_count() / 2;
+    return (r > 0 && r < by_sm) ? r : by_sm;
+}
+TcPlan plan_single(const llmt_b200_gemm_desc* d) {
+    const bool pairs = pair_eligible(d);
+    return make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, pairs ? pair_units() : sm_count(),
+                     d->plan_tile_n, d->plan_splits, pairs, d->trans_b == 0);
 }
 
 bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
@@ -381,7 +417,7 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
                                 p->a_mn ? 64 : 128);
     if (st != LLMT_B200_OK) return st;
     st = encode_operand_map(&p->map_b, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
-                            p->b_mn ? 64 : pl.bn);
+                            p->b_mn ? 64 : (pl.pairs ? pl.bn / 2 : pl.bn));
     if (st != LLMT_B200_OK) return st;
     // C leaves through shared memory and TMA stores when its layout allows a tensor map
     // (16-byte aligned base, pitch and batch stride); otherwise straight from registers.
@@ -398,7 +434,7 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
 
 // Launches the tensor-core kernel over `count` filled problems (longest tiles first),
 // then the fixed-order reduction of every problem that was split.
-int launch_group(GroupProblem* probs, int count, cudaStream_t stream) {
+int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream) {
     DeviceGlobals* g = nullptr;
     int st = device_globals(&g);
     if (st != LLMT_B200_OK) return st;
@@ -428,9 +464,9 @@ int launch_group(GroupProblem* probs, int count, cudaStream_t stream) {
         { const char* e = getenv("LLMT_B200_STATIC"); gp.static_schedule = (e && e[0] == '1') ? 1 : 0; }
         gp.status = device_status_ptr();
         if (gp.status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
-        const int sms = sm_count();
-        const int grid = static_cast<int>(total < sms ? total : sms);
-        cudaError_t e = launch_tc_grouped(gp, grid, stream);
+        const int units = pairs ? pair_units() : sm_count();
+        const int grid = static_cast<int>(total < units ? total : units) * (pairs ? 2 : 1);
+        cudaError_t e = launch_tc_grouped(gp, grid, pairs, stream);
         if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     }
     for (int i = 0; i < count; ++i) {
@@ -447,31 +483,32 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
              cudaStream_t stream) {
     int st = check_tma_operands(d, a, b);
     if (st != LLMT_B200_OK) return st;
-    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(),
-                                d->plan_tile_n, d->plan_splits);
+    const TcPlan pl = plan_single(d);
     st = check_workspace(d, pl);
     if (st != LLMT_B200_OK) return st;
     GroupProblem p;
     st = fill_problem(&p, d, ck, pl, c, a, b);
     if (st != LLMT_B200_OK) return st;
-    return launch_group(&p, 1, stream);
+    return launch_group(&p, 1, pl.pairs != 0, stream);
 }
 
 // Group plans: every problem is planned knowing the total work of the launch.
 int plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
-    const int sms = sm_count();
+    bool pairs = true;  // a launch is either all pairs or all single CTAs
+    for (int i = 0; i < count; ++i) pairs = pairs && pair_eligible(&descs[i]);
+    const int sms = pairs ? pair_units() : sm_count();
     int64_t work = 0;
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
         const int bn = d.dbias ? 192 : 256;
-        work += static_cast<int64_t>(ceil_div(d.m, 128)) * ceil_div(d.n, bn) * (d.batch > 0 ? d.batch : 1) *
-                ceil_div(d.k, 64);
+        work += static_cast<int64_t>(ceil_div(d.m, pairs ? 256 : 128)) * ceil_div(d.n, bn) *
+                (d.batch > 0 ? d.batch : 1) * ceil_div(d.k, 64);
     }
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
-        plans[i] = count == 1 ? make_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, d.plan_tile_n, d.plan_splits)
+        plans[i] = count == 1 ? plan_single(&d)
                               : make_group_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, work,
-                                                d.plan_tile_n, d.plan_splits);
+                                                d.plan_tile_n, d.plan_splits, pairs, d.trans_b == 0);
     }
     return LLMT_B200_OK;
 }
@@ -538,8 +575,7 @@ int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const v
     if (!ck.bf16) return run_fp32(d, c, a, b, s);  // the fp32 path uses no scratch at all
     // Size check first: a problem that does not fit is turned away before the scratch is
     // resolved and before anything is enqueued.
-    const size_t need = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(),
-                                  d->plan_tile_n, d->plan_splits).workspace_bytes;
+    const size_t need = plan_single(d).workspace_bytes;
     if (need > kStaticScratchBytes)
         return fail(LLMT_B200_ERR_WORKSPACE,
                     "gemm_static_scratch: this problem's split-K plan needs %llu scratch bytes but the "
@@ -593,7 +629,7 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
         ++n;
     }
     if (n == 0) return LLMT_B200_OK;
-    return launch_group(probs, n, static_cast<cudaStream_t>(stream));
+    return launch_group(probs, n, plans[0].pairs != 0, static_cast<cudaStream_t>(stream));
 }
 
 int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int32_t count,
@@ -614,8 +650,7 @@ uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
     if (d == nullptr || d->dtype_ab != LLMT_B200_BF16 || d->m <= 0 || d->n <= 0 || d->k <= 0 ||
         d->batch <= 0)
         return 0;
-    return make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(), d->plan_tile_n,
-                     d->plan_splits).workspace_bytes;
+    return plan_single(d).workspace_bytes;
 }
 
 int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
@@ -625,13 +660,13 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
                  (long long)((d->n + 63) / 64), (long long)((d->m + 63) / 64), (long long)d->batch);
         return LLMT_B200_OK;
     }
-    const TcPlan pl = make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, sm_count(), d->plan_tile_n,
-                     d->plan_splits);
-    const int sms = sm_count();
-    snprintf(buf, n, "tcgen05 tile=128x%dx64 stages=4 splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
-             pl.bn, pl.splits, pl.tiles_m, pl.tiles_n, pl.kblocks_total,
-             static_cast<int>(pl.num_tiles < sms ? pl.num_tiles : sms), tc_grouped_smem_bytes(),
-             pl.workspace_bytes);
+    const TcPlan pl = plan_single(d);
+    const int units = pl.pairs ? pair_units() : sm_count();
+    snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
+             pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? 6 : 4, pl.splits, pl.tiles_m,
+             pl.tiles_n, pl.kblocks_total,
+             static_cast<int>(pl.num_tiles < units ? pl.num_tiles : units) * (pl.pairs ? 2 : 1),
+             tc_grouped_smem_bytes(), pl.workspace_bytes);
     return LLMT_B200_OK;
 }
 

@@ -70,6 +70,7 @@ struct GroupParams {
 // launch with) that fixes tile width and split count.
 struct TcPlan {
     int bn;
+    int pairs;       // 1 = CTA pairs (256-row tiles, cta_group::2)
     int splits;
     int tiles_m, tiles_n;
     int kblocks_total, kblocks_per_split;
@@ -97,18 +98,20 @@ __device__ __forceinline__ float gelu_tanh_precise(float v) {
     return 0.5f * v * (1.0f + tanhf(k0 * (v + k1 * v * v * v)));
 }
 
-// Same formula with tanh(u) = 1 - 2/(exp(2u)+1) on the fast exp/divide units.
-// Absolute error of the tanh term is ~1e-7, far below one bf16 ulp of the result.
+// Same function in the form  gelu(v) = v * sigmoid(2u) = v / (1 + exp(-2u)),
+// u = k0*(v + k1*v^3): algebraically identical to 0.5*v*(1+tanh(u)), no cancellation
+// for negative v, and five FP32 operations plus one exp2 and one reciprocal on the
+// special-function unit per element (relative error of the result ~1e-6).
 __device__ __forceinline__ float gelu_tanh_fast(float v) {
-    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-    const float u = k0 * (v + k1 * v * v * v);
-    const float t = __expf(2.0f * u);
-    const float th = 1.0f - __fdividef(2.0f, t + 1.0f);
-    return 0.5f * v * (1.0f + th);
+    const float a0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2*k0*log2(e)
+    const float a1 = a0 * 0.044715f;
+    const float e = exp2f(v * fmaf(a1, v * v, a0));  // exp(-2u)
+    return __fdividef(v, 1.0f + e);
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
-cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, cudaStream_t stream);
+cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream);
+int max_resident_pairs(void);
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
 size_t tc_grouped_smem_bytes(void);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);

@@ -3,10 +3,11 @@
 // memory, operands staged in 128-byte-swizzled shared memory by TMA, results
 // leaving through swizzled shared-memory slabs and TMA stores.
 //
-// One CTA per SM, 320 threads, warp-specialised:
-//   warp 0      scheduler + TMA producer (one lane): draws the next tile from a
-//               global counter, publishes it to the other roles through a small
-//               ring in shared memory, then streams that tile's operands
+// One CTA per SM, 352 threads, warp-specialised:
+//   warp 0      scheduler + TMA producer: draws the next tile from a global counter,
+//               publishes it to the other roles through a small ring in shared memory,
+//               then streams the even k-blocks of that tile's operands
+//   warp 10     second TMA producer (the odd k-blocks)
 //   warp 1      MMA issuer (one lane issues tcgen05.mma / tcgen05.commit; the warp
 //               owns the TMEM allocation)
 //   warps 2-9   epilogue: tcgen05.ld, alpha/beta/bias/GELU/cast, store C (two warps
@@ -39,13 +40,20 @@ namespace {
 constexpr int BM = 128;  // UMMA M (cta_group::1)
 constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr int kEpilogueWarps = 8;
-constexpr int kStages = 4;
+constexpr int kProducerHelperWarp = 10;  // second TMA producer warp
+constexpr int kMaxStages = 6;
 constexpr int kRing = 4;                             // scheduler ring entries
 constexpr uint32_t kATileBytes = BM * BK * 2;        // 16 KB
-constexpr uint32_t kBRegionBytes = 256 * BK * 2;     // 32 KB: widest B tile (or narrower tile + ones block)
-constexpr uint32_t kStageBytes = kATileBytes + kBRegionBytes;
+// Per CTA and stage: the A tile plus room for the widest B tile (or a narrower tile and the
+// ones block).  A CTA pair (CG = 2) splits B between its two CTAs, so a stage is smaller
+// and six of them fit where a single CTA has four.
+template <int CG> struct Geo {
+    static constexpr uint32_t kBRegionBytes = (256 / CG) * BK * 2;
+    static constexpr uint32_t kStageBytes = kATileBytes + kBRegionBytes;
+    static constexpr int kStages = CG == 2 ? 6 : 4;
+};
 constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block / the ones block
 constexpr uint32_t kAccStride = 256;                 // TMEM columns per accumulator buffer
 constexpr uint32_t kTmemCols = 512;
@@ -55,8 +63,8 @@ constexpr uint32_t kStagingBytes = 2 * kSlabBytes;   // one slab per column half
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 struct __align__(8) Control {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t sched_full[kRing];
@@ -66,13 +74,18 @@ struct __align__(8) Control {
     int abort_flag;
 };
 
+// The template flag only marks barriers that the peer CTA of a pair also signals; those
+// signals carry no generic-proxy data (ring entries arrive by st.async, operands by TMA,
+// accumulators through tcgen05 fences), so the default CTA-scope acquire is enough.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                              DeviceStatus* st, int code, int detail) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto poll = [&]() { return mbar_try_wait(bar, parity); };
+    if (poll()) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (poll()) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -178,8 +191,18 @@ __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float*
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
+template <int CG>
+__device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
+    constexpr int kStages = Geo<CG>::kStages;
+    constexpr uint32_t kStageBytes = Geo<CG>::kStageBytes;
+    constexpr bool kPair = CG == 2;
+    constexpr int kTileRows = BM * CG;  // rows of C one scheduled tile covers
+    // A pair's leader (cluster rank 0) runs the scheduler and issues the MMAs for both CTAs.
+    const uint32_t rank = kPair ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
+    const int n_sched = static_cast<int>(gridDim.x) / CG;  // CTAs (pairs) drawing tickets
+    const int sched_id = static_cast<int>(blockIdx.x) / CG;
+
     extern __shared__ uint8_t smem_raw[];
     // Swizzled tiles need 1024-byte alignment.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -199,30 +222,48 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
-            mbar_init(smem_u32(&ctl->tmem_empty[a]), kEpilogueWarps);
+            mbar_init(smem_u32(&ctl->tmem_empty[a]), CG * kEpilogueWarps);      // both CTAs' epilogues
         }
         for (int r = 0; r < kRing; ++r) {
             mbar_init(smem_u32(&ctl->sched_full[r]), 1);
-            mbar_init(smem_u32(&ctl->sched_empty[r]), 1 + kEpilogueWarps);
+            mbar_init(smem_u32(&ctl->sched_empty[r]), kPair ? 2 * (2 + kEpilogueWarps) : 1 + kEpilogueWarps);  // every ring reader
         }
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-        tmem_relinquish_alloc_permit();
+        tmem_alloc_cg<CG>(smem_u32(&ctl->tmem_base), kTmemCols);
+        tmem_relinquish_cg<CG>();
     }
     tc_fence_before_thread_sync();
     __syncthreads();
+    if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if (warp == 0) {
-        // ------------------------------------------- scheduler + TMA producer
-        // The whole warp walks the loop; lane 0 owns the scheduler and the barrier
-        // bookkeeping, and lane L issues the L-th box of a stage, so the up to seven TMA
-        // boxes of a k-block (MN-major operands come in 64-wide blocks) leave in one issue
-        // slot instead of queueing behind one thread.
+    // Barriers that live in the leader CTA of a pair, as cluster addresses usable from both.
+    auto on_leader = [&](const void* bar) { return kPair ? mapa_shared(smem_u32(bar), 0u) : smem_u32(bar); };
+    // A ring reader releases its slot to the scheduler (the leader's barrier).
+    auto release_ring_slot = [&](int slot) {
+        if (kPair) mbar_arrive_cluster(on_leader(&ctl->sched_empty[slot]));
+        else mbar_arrive(smem_u32(&ctl->sched_empty[slot]));
+    };
+
+    if (warp == 0 || (kPair && warp == kProducerHelperWarp)) {
+        // ------------------------------------------- scheduler + TMA producers
+        // Two producer warps share the k-blocks (even ones to warp 0, odd ones to the helper
+        // warp): one iteration costs a few hundred cycles of barrier and issue latency, which
+        // a single warp cannot hide and which would otherwise cap how far loads run ahead.
+        // In each the whole warp walks the loop; lane 0 does the barrier bookkeeping and
+        // lane L issues the L-th box of a stage, so the up to seven TMA boxes of a k-block
+        // (MN-major operands come in 64-wide blocks) leave in one issue slot.  Warp 0 of the
+        // leader also runs the scheduler.
+        const bool scheduler = warp == 0 && leader;
+        // A single CTA streams 48 KB per k-block and is bound by that, not by issue latency:
+        // there the helper stays idle and warp 0 takes every k-block.
+        const uint32_t my_parity = warp == 0 ? 0u : 1u;
+        const uint32_t parity_mask = kPair ? 1u : 0u;
+        uint32_t seq = 0;  // k-blocks streamed so far by this CTA; k-block `seq` uses stage seq % kStages
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -230,25 +271,40 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
         // so the atomic's round trip stays off the critical path.
         const bool dynamic = gp.static_schedule == 0;
         int next = 0;
-        if (lane == 0) next = dynamic ? atomicAdd(gp.sched_counter, 1) : static_cast<int>(blockIdx.x);
+        if (lane == 0 && scheduler) next = dynamic ? atomicAdd(gp.sched_counter, 1) : sched_id;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
             int t = -1;
             if (lane == 0) {
-                ok = bounded_wait(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
-                                  kDevWaitSched, slot);
-                if (ok) {
-                    t = next;
-                    if (t >= gp.total_tiles) {
-                        // Every CTA draws exactly one out-of-range ticket; the last one re-arms the counter.
-                        if (dynamic && t == gp.total_tiles + static_cast<int>(gridDim.x) - 1) *gp.sched_counter = 0;
-                        t = -1;
-                    } else {
-                        next = dynamic ? atomicAdd(gp.sched_counter, 1) : t + static_cast<int>(gridDim.x);
+                if (scheduler) {
+                    ok = bounded_wait<kPair>(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
+                                             kDevWaitSched, slot);
+                    if (ok) {
+                        t = next;
+                        if (t >= gp.total_tiles) {
+                            // Every drawer takes exactly one out-of-range ticket; the last re-arms the counter.
+                            if (dynamic && t == gp.total_tiles + n_sched - 1) *gp.sched_counter = 0;
+                            t = -1;
+                        } else {
+                            next = dynamic ? atomicAdd(gp.sched_counter, 1) : t + n_sched;
+                        }
+                        ctl->ring[slot] = t;
+                        mbar_arrive(smem_u32(&ctl->sched_full[slot]));
+                        // The peer's copy travels as an async store that completes its barrier.
+                        if (kPair)
+                            st_async_cluster_u32(mapa_shared(smem_u32(&ctl->ring[slot]), 1u), static_cast<uint32_t>(t),
+                                                 mapa_shared(smem_u32(&ctl->sched_full[slot]), 1u));
                     }
-                    ctl->ring[slot] = t;
-                    mbar_arrive(smem_u32(&ctl->sched_full[slot]));
+                } else {
+                    // In the peer CTA warp 0 arms the ring barrier for the leader's 4-byte store.
+                    if (kPair && warp == 0) mbar_arrive_expect_tx(smem_u32(&ctl->sched_full[slot]), 4u);
+                    ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
+                                             kDevWaitSched, 48 + slot);
+                    if (ok) {
+                        t = ctl->ring[slot];
+                        release_ring_slot(slot);
+                    }
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -257,52 +313,58 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int bn = p.bn, a_mn = p.a_mn, b_mn = p.b_mn;
-            const int m0 = tc.m_tile * BM, n0 = tc.n_tile * bn;
-            const bool ones = p.dbias != nullptr && tc.n_tile == 0;
-            const uint32_t tx = kATileBytes + static_cast<uint32_t>(bn) * (BK * 2) + (ones ? kBlock64Bytes : 0u);
+            const int bn_cta = bn / CG;                         // B columns this CTA stages
+            const int m0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM;
+            const int n0 = tc.n_tile * bn + static_cast<int>(rank) * bn_cta;
+            const bool ones = !kPair && p.dbias != nullptr && tc.n_tile == 0;
+            const uint32_t tx = kATileBytes + static_cast<uint32_t>(bn_cta) * (BK * 2) + (ones ? kBlock64Bytes : 0u);
             // This lane's box: destination offset inside the stage, tensor map, and the
             // coordinates (the k coordinate advances with the k-block).
-            const int n_a = a_mn ? 2 : 1, n_b = b_mn ? (bn >> 6) : 1;
+            const int n_a = a_mn ? 2 : 1, n_b = b_mn ? (bn_cta >> 6) : 1;
             const CUtensorMap* my_map = nullptr;
             uint32_t my_off = 0;
             int my_x = 0, my_y = 0;
-            bool k_is_x = false;
+            bool k_is_x = false, k_is_y = false;
+            int batch = tc.batch;
             if (lane < n_a) {
                 my_map = &p.map_a;
-                if (a_mn) { my_off = lane * kBlock64Bytes; my_x = m0 + 64 * lane; }
+                if (a_mn) { my_off = lane * kBlock64Bytes; my_x = m0 + 64 * lane; k_is_y = true; }
                 else      { my_y = m0; k_is_x = true; }
             } else if (lane < n_a + n_b) {
                 const int j = lane - n_a;
                 my_map = &p.map_b;
                 my_off = kATileBytes;
-                if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; }
+                if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
             } else if (lane == n_a + n_b && ones) {
                 my_map = &gp.map_ones;
                 my_off = kATileBytes + static_cast<uint32_t>(bn) * (BK * 2);
+                batch = 0;
             }
-            const bool k_is_y = (my_map == &p.map_a && a_mn) || (my_map == &p.map_b && b_mn);
-            const int batch = my_map == &gp.map_ones ? 0 : tc.batch;
-            for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
-                if (lane == 0) {
-                    ok = bounded_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, status,
-                                      kDevWaitSmemEmpty, stage);
-                    if (ok) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx);
-                }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-                if (my_map != nullptr) {
-                    const int k0 = kb * BK;
-                    tma_load_3d(smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off, my_map,
-                                smem_u32(&ctl->full[stage]), my_x + (k_is_x ? k0 : 0),
-                                my_y + (k_is_y ? k0 : 0), batch);
+            for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
+                if ((seq & parity_mask) == my_parity) {
+                    if (lane == 0) {
+                        ok = bounded_wait<kPair>(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, status,
+                                                 kDevWaitSmemEmpty, stage);
+                        // The leader's barrier counts the bytes of both CTAs of a pair.
+                        if (ok && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    if (my_map != nullptr) {
+                        const int k0 = kb * BK;
+                        const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
+                        const int x = my_x + (k_is_x ? k0 : 0), y = my_y + (k_is_y ? k0 : 0);
+                        if (kPair) tma_load_3d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, batch);
+                        else tma_load_3d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, batch);
+                    }
                 }
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             // Shared-memory descriptor, 128-byte swizzle: K-major = k-step 32 bytes along the
             // row, LBO unused (16), SBO 1024; MN-major = k-step 16 k-rows of 128 bytes, LBO =
             // one 64-wide block, SBO 1024.  Only the 14-bit start-address field changes between
@@ -320,25 +382,25 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                                   kDevWaitSched, 16 + slot);
                 if (!ok) break;
                 const int t = ctl->ring[slot];
-                mbar_arrive(smem_u32(&ctl->sched_empty[slot]));
+                release_ring_slot(slot);
                 if (t < 0) break;
                 const TileCoord tc = decode_tile(gp, t);
                 const GroupProblem& p = gp.prob[tc.prob];
-                const bool ones = p.dbias != nullptr && tc.n_tile == 0;
-                const uint32_t idesc = make_idesc_bf16(BM, p.bn + (ones ? kDbiasCols : 0), p.a_mn, p.b_mn);
+                const bool ones = !kPair && p.dbias != nullptr && tc.n_tile == 0;
+                const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn + (ones ? kDbiasCols : 0), p.a_mn, p.b_mn);
                 const uint32_t step_a = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
                 const uint32_t step_b = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
                 const uint32_t a_lo_base = (smem_base >> 4) | (((p.a_mn ? kBlock64Bytes : 16u) >> 4) << 16);
                 const uint32_t b_lo_base = ((smem_base + kATileBytes) >> 4) |
                                            (((p.b_mn ? kBlock64Bytes : 16u) >> 4) << 16);
-                ok = bounded_wait(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status,
-                                  kDevWaitTmemEmpty, acc);
+                ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status,
+                                         kDevWaitTmemEmpty, acc);
                 if (!ok) break;
                 tc_fence_after_thread_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    ok = bounded_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
-                                      kDevWaitSmemFull, stage);
+                    ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
+                                             kDevWaitSmemFull, stage);
                     if (!ok) break;
                     tc_fence_after_thread_sync();
                     const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
@@ -350,36 +412,37 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                                             static_cast<uint64_t>(a_lo + kk * step_a);
                         const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
                                             static_cast<uint64_t>(b_lo + kk * step_b);
-                        umma_bf16(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                        umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
+                    umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&ctl->tmem_full[acc]));
+                umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc]));
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
         }
-    } else {
+    } else if (warp < 2 + kEpilogueWarps) {
         // ---------------------------------------------------------- epilogue
         const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
         const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp drains
         const int tile_row = quarter * 32 + lane;
         const uint32_t slab = staging_base + static_cast<uint32_t>(half) * kSlabBytes;
         const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
+        uint32_t slab_toggle = 0;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
-            ok = bounded_wait(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
-                              kDevWaitSched, 32 + slot);
+            ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
+                                     kDevWaitSched, 32 + slot);
             if (!ok) break;
             const int t = ctl->ring[slot];
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->sched_empty[slot]));
+            if (lane == 0) release_ring_slot(slot);
             if (t < 0) break;
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
@@ -387,7 +450,8 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                               kDevWaitTmemFull, acc);
             if (!ok) break;
             tc_fence_after_thread_sync();
-            const int64_t row = static_cast<int64_t>(tc.m_tile) * BM + tile_row;
+            const int row0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM;  // first row of this CTA's half
+            const int64_t row = static_cast<int64_t>(row0) + tile_row;
             const bool row_ok = row < p.m;
             const int64_t n0 = static_cast<int64_t>(tc.n_tile) * p.bn;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -444,11 +508,20 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                 // TMA clips a box at 16-byte granularity, so a ragged last chunk goes out
                 // through registers instead.
                 if (via_tma && valid == 32) {
-                    // The slab is free once the previous TMA store has read it.
-                    if (store_leader) bulk_wait_group_read0();
+                    // bf16 slabs are half the size of fp32 ones, so a half alternates between
+                    // two of them and only waits for the store before the previous one; an
+                    // fp32 slab is free once the previous TMA store has read it.
+                    uint32_t slab_now = slab;
+                    if (p.c_is_bf16) {
+                        slab_now += (slab_toggle & 1u) * (kSlabBytes / 2);
+                        ++slab_toggle;
+                        if (store_leader) bulk_wait_group_read1();
+                    } else if (store_leader) {
+                        bulk_wait_group_read0();
+                    }
                     named_barrier_sync(1 + half, 128);
                     if (p.c_is_bf16) {
-                        const uint32_t row_addr = slab + static_cast<uint32_t>(tile_row) * 64u;
+                        const uint32_t row_addr = slab_now + static_cast<uint32_t>(tile_row) * 64u;
                         const uint32_t sw = static_cast<uint32_t>(tile_row >> 1) & 3u;
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -464,7 +537,7 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                                            "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
                         }
                     } else {
-                        const uint32_t row_addr = slab + static_cast<uint32_t>(tile_row) * 128u;
+                        const uint32_t row_addr = slab_now + static_cast<uint32_t>(tile_row) * 128u;
                         const uint32_t sw = static_cast<uint32_t>(tile_row) & 7u;
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
@@ -478,7 +551,7 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                     fence_proxy_async_smem();
                     named_barrier_sync(1 + half, 128);
                     if (store_leader) {
-                        tma_store_3d(&p.map_c, slab, static_cast<int32_t>(col), tc.m_tile * BM, tc.batch);
+                        tma_store_3d(&p.map_c, slab_now, static_cast<int32_t>(col), row0, tc.batch);
                         bulk_commit_group();
                     }
                 } else if (row_ok) {
@@ -488,7 +561,7 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
                         store_chunk_f32(static_cast<float*>(p.c) + c_off, v, valid);
                 }
             }
-            if (p.dbias != nullptr && tc.n_tile == 0 && half == 0) {
+            if (!kPair && p.dbias != nullptr && tc.n_tile == 0 && half == 0) {
                 // Accumulator column bn holds sum_k op(A)[row, k] (the ones block).
                 uint32_t r[16];
                 tmem_ld_32x16(t_row + static_cast<uint32_t>(p.bn), r);
@@ -505,7 +578,11 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
             }
             tc_fence_before_thread_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+            if (lane == 0) {
+                // The accumulator buffer goes back to the MMA issuer (in the leader CTA).
+                if (kPair) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc]));
+                else mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
@@ -521,10 +598,25 @@ tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
     }
     tc_fence_before_thread_sync();
     __syncthreads();
+    // Neither CTA of a pair may leave while the other can still signal its barriers,
+    // read its operand tiles or use the pair's TMEM allocation.
+    if (kPair) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_thread_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        tmem_dealloc_cg<CG>(tmem_base, kTmemCols);
     }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
+    tc_grouped_body<1>(gp);
+}
+
+// The same kernel over CTA pairs: clusters of two CTAs, each pair computing 256-row tiles
+// with cta_group::2 MMAs, every CTA staging its own 128 rows of A and half of the B tile.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+tc_grouped_pair_kernel(const __grid_constant__ GroupParams gp) {
+    tc_grouped_body<2>(gp);
 }
 
 // C = epilogue(alpha * sum_s ws[s] + beta * C): fixed summation order s = 0..splits-1.
@@ -577,22 +669,46 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
 }  // namespace
 
 size_t tc_grouped_smem_bytes() {
-    return 1024 /* alignment slack */ + kStages * kStageBytes + kStagingBytes + sizeof(Control);
+    // Both geometries use the same amount: 4 x 48 KB or 6 x 32 KB of operand stages.
+    static_assert(Geo<1>::kStages * Geo<1>::kStageBytes == Geo<2>::kStages * Geo<2>::kStageBytes, "stage budget");
+    return 1024 /* alignment slack */ + Geo<1>::kStages * Geo<1>::kStageBytes + kStagingBytes + sizeof(Control);
 }
 
-cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, cudaStream_t stream) {
+cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream) {
     static int configured_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_device != dev) {
         cudaError_t e = cudaFuncSetAttribute(tc_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              227 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     227 * 1024);
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
-    tc_grouped_kernel<<<grid, kThreads, tc_grouped_smem_bytes(), stream>>>(gp);
+    if (pairs)
+        tc_grouped_pair_kernel<<<grid, kThreads, tc_grouped_smem_bytes(), stream>>>(gp);
+    else
+        tc_grouped_kernel<<<grid, kThreads, tc_grouped_smem_bytes(), stream>>>(gp);
     count_launch(1);
     return cudaGetLastError();
+}
+
+// How many CTA pairs can be resident at once (1 CTA per SM, pairs share a cluster).
+int max_resident_pairs() {
+    static int cached = 0;
+    if (cached == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = tc_grouped_smem_bytes();
+        cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, tc_grouped_pair_kernel, &cfg) == cudaSuccess && n > 0) cached = n;
+        else cached = -1;
+    }
+    return cached;
 }
 
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream) {

@@ -2,8 +2,10 @@
 // mbarrier, TMA tiled loads (cp.async.bulk.tensor), tensor memory (TMEM)
 // management and the tcgen05 MMA / load / commit instructions.
 //
-// Everything here is `cta_group::1`: one CTA drives one SM's tensor core.  No
-// load in this file carries a cluster-multicast qualifier.
+// Wrappers templated on CG are `cta_group::CG`: CG = 1, one CTA drives one SM's tensor
+// core; CG = 2, the two CTAs of a cluster pair drive both SMs as one 256-row MMA whose
+// B operand is split between their shared memories.  No load in this file carries a
+// cluster-multicast qualifier.
 #pragma once
 
 #include <cuda.h>
@@ -95,6 +97,10 @@ __device__ __forceinline__ void bulk_commit_group() {
 __device__ __forceinline__ void bulk_wait_group_read0() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// Same, but the most recent store may still be reading.
+__device__ __forceinline__ void bulk_wait_group_read1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // Waits until the bulk stores issued by this thread have completed.
 __device__ __forceinline__ void bulk_wait_group0() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -172,6 +178,102 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+
+// ------------------------------------------------------------ CTA pairs (CG = 2) --
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier that may live in the peer CTA (cluster address).  Used only for
+// "I am done with this buffer" signals, which publish no data of their own.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Asynchronous 4-byte store into the peer CTA's shared memory that completes 4 bytes of the
+// transaction count of an mbarrier there: data and signal travel together, so neither side
+// needs a cluster-scope fence.
+__device__ __forceinline__ void st_async_cluster_u32(uint32_t cluster_addr, uint32_t v, uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
+                 ::"r"(cluster_addr), "r"(v), "r"(cluster_bar) : "memory");
+}
+// try_wait whose acquire covers writes made by the peer CTA.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// 3-D tiled load into this CTA's shared memory whose completion is counted on an
+// mbarrier of the pair's leader CTA (cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const CUtensorMap* map,
+                                                 uint32_t leader_bar, int32_t x, int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+template <int CG> __device__ __forceinline__ void tmem_alloc_cg(uint32_t dst_smem_slot, uint32_t ncols) {
+    if (CG == 1)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem_slot), "r"(ncols) : "memory");
+    else
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem_slot), "r"(ncols) : "memory");
+}
+template <int CG> __device__ __forceinline__ void tmem_relinquish_cg() {
+    if (CG == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    else         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int CG> __device__ __forceinline__ void tmem_dealloc_cg(uint32_t taddr, uint32_t ncols) {
+    if (CG == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+    else         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem].  CG = 2: M = 256 over both CTAs of the pair, issued by
+// one thread of the leader CTA; the descriptors address the leader's shared memory and the
+// peer's tiles sit at the same offsets.
+template <int CG> __device__ __forceinline__ void umma_bf16_cg(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                             uint32_t idesc, uint32_t accumulate) {
+    if (CG == 1)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed; CG = 2
+// arrives on the barrier at the same offset in both CTAs of the pair.
+template <int CG> __device__ __forceinline__ void umma_commit_cg(uint32_t bar) {
+    if (CG == 1) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    } else {
+        const uint16_t mask = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(mask) : "memory");
+    }
 }
 
 // -------------------------------------------------------------- descriptors --

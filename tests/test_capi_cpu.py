@@ -104,7 +104,7 @@ def test_plan_is_a_pure_function_of_the_problem():
     # (role of llmt's AlgoCache, include/llmt/kernels/algo_cache.h:18-42)
     d = _desc(m=8192, n=2304, k=768, lda=768, ldb=768, ldc=2304)
     p1, p2 = L.plan(d), L.plan(d)
-    assert p1 == p2 and "tcgen05" in p1 and "128x" in p1
+    assert p1 == p2 and "tcgen05" in p1 and "tile=256x256x64" in p1  # CTA pairs, 256-row tiles
     assert L.workspace_bytes(d) == 0
     dw = _desc(m=768, n=768, k=8192, trans_a=1, trans_b=0, lda=768, ldb=768, ldc=768)
     assert "splits=" in L.plan(dw)
@@ -113,8 +113,8 @@ def test_plan_is_a_pure_function_of_the_problem():
     # workspace shortfall is reported before anything is launched
     dw.workspace, dw.workspace_bytes = 0x100000, 16
     assert _call(dw, c=0x7000000000, a=0x1000000000, b=0x2000000000) == L.ERR_WORKSPACE
-    forced = _desc(m=768, n=768, k=8192, plan_tile_n=64, plan_splits=1)
-    assert "128x64x64" in L.plan(forced) and "splits=1 " in L.plan(forced)
+    forced = _desc(m=768, n=768, k=8192, plan_tile_n=64, plan_splits=1)  # 64-wide tiles: single CTAs
+    assert "1-cta tile=128x64x64" in L.plan(forced) and "splits=1 " in L.plan(forced)
 
 
 def test_softmax_contract():

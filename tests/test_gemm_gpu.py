@@ -531,3 +531,34 @@ def test_grouped_rejects_dependent_problems():
     with pytest.raises(L.LlmtB200Error) as e:
         grp.run()
     assert e.value.status == L.ERR_INVALID and "independent" in str(e.value)
+
+
+# ------------------------------------------- against cuBLASLt in bf16 (llmt's call pattern) ---
+
+@pytest.mark.parametrize("shape", ["qkv_fwd", "fc_dx", "fc_dw"])
+def test_error_no_worse_than_twice_cublaslt(shape):
+    """BASELINE north star: on the same seeded inputs the error against the fp64 product is no
+    worse than 2x that of cuBLASLt called the way llmt calls it (bf16 operands, fp32 accumulate)."""
+    from oracle import cublaslt_ref
+    if not cublaslt_ref.available():
+        pytest.skip("comparator not built (make -C oracle cmp)")
+    M = 2048
+    cases = {"qkv_fwd": (M, 2304, 768, 0, 1, torch.bfloat16),
+             "fc_dx": (M, 768, 3072, 0, 0, torch.bfloat16),
+             "fc_dw": (3072, 768, M, 1, 0, torch.float32)}
+    m, n, k, ta, tb, cdt = cases[shape]
+    rng = np.random.default_rng(41)
+    a = oracle.round_bf16(rng.standard_normal((k, m) if ta else (m, k)))
+    b = oracle.round_bf16(rng.standard_normal((n, k) if tb else (k, n)) * 0.02)
+    ad, bd = dev_bf16(a), dev_bf16(b)
+    ref = oracle.gemm(a, b, bool(ta), bool(tb))
+    ours = torch.empty(m, n, device=DEV, dtype=cdt)
+    L.gemm(ours, ad, bd, bool(ta), bool(tb))
+    lt = cublaslt_ref.CublasLtBf16()
+    theirs = torch.empty(m, n, device=DEV, dtype=cdt)
+    lt.matmul(theirs, ad, bd, bool(ta), bool(tb))
+    torch.cuda.synchronize()
+    e_ours, e_lt = oracle.rel_fro(host(ours), ref), oracle.rel_fro(host(theirs), ref)
+    lt.close()
+    assert e_ours <= 2.0 * e_lt + 1e-7, (e_ours, e_lt)
+    assert e_ours <= (TOL_BF16_OUT_FRO if cdt == torch.bfloat16 else TOL_BF16_ACC_FRO)
