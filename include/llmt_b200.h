@@ -73,7 +73,7 @@ enum llmt_b200_status {
  *   dbias        optional fp32 [m]:  dbias[i] = dbias_beta * dbias[i] + sum_p op(A)[i,p].
  *                For llmt's dW call (src/layers/linear.cpp:27-29: A = dy, trans_a = 1)
  *                this is the bias gradient, summed over tokens.  bf16 path only.
- *   plan_*       tuning overrides of the tile width and split-K factor; 0 leaves the
+ *   plan_*       tuning overrides of the tile width, split-K factor and CTA pairing; 0 leaves the
  *                choice to the library (the default plan is a pure function of the
  *                problem, so results stay reproducible either way).
  *   workspace    device scratch for split-K partial sums; llmt_b200_gemm_workspace_bytes()
@@ -94,7 +94,7 @@ typedef struct llmt_b200_gemm_desc {
     float dbias_beta;
     int32_t plan_tile_n;   /* 0 = choose; else force the tile width: 64, 128, 192 or 256 */
     int32_t plan_splits;   /* 0 = choose; else force the split-K factor (>= 1) */
-    int32_t reserved0;
+    int32_t plan_cta_pairs; /* 0 = choose; 1 = single CTAs (128-row tiles); 2 = CTA pairs (256-row tiles) */
     void* workspace;
     uint64_t workspace_bytes;
 } llmt_b200_gemm_desc;

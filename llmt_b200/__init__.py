@@ -39,7 +39,7 @@ class GemmDesc(ctypes.Structure):
         ("epilogue", ctypes.c_int32), ("bias_dtype", ctypes.c_int32),
         ("bias", ctypes.c_void_p), ("dbias", ctypes.c_void_p),
         ("dbias_beta", ctypes.c_float), ("plan_tile_n", ctypes.c_int32),
-        ("plan_splits", ctypes.c_int32), ("reserved0", ctypes.c_int32),
+        ("plan_splits", ctypes.c_int32), ("plan_cta_pairs", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -121,7 +121,7 @@ def _row_pitch(t) -> int:
 
 
 def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
-              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0) -> GemmDesc:
+              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0, cta_pairs=0) -> GemmDesc:
     """Builds the descriptor for C = epilogue(alpha*op(A)*op(B) + beta*C) from rank-2
     or rank-3 torch tensors (row-major views with a contiguous last dimension)."""
     if not (a.dim() == b.dim() == c.dim()) or a.dim() not in (2, 3):
@@ -155,7 +155,7 @@ def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=N
     if dbias is not None:
         d.dbias = dbias.data_ptr()
         d.dbias_beta = float(dbias_beta)
-    d.plan_tile_n, d.plan_splits = int(tile_n), int(splits)
+    d.plan_tile_n, d.plan_splits, d.plan_cta_pairs = int(tile_n), int(splits), int(cta_pairs)
     if workspace is not None:
         d.workspace = workspace.data_ptr()
         d.workspace_bytes = workspace.numel() * workspace.element_size()
@@ -227,7 +227,7 @@ def gemm_static_scratch(desc: GemmDesc, c, a, b, stream=None) -> None:
 
 
 def gemm(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
-         dbias=None, dbias_beta=0.0, workspace=None, stream=None, tile_n=0, splits=0) -> None:
+         dbias=None, dbias_beta=0.0, workspace=None, stream=None, tile_n=0, splits=0, cta_pairs=0) -> None:
     """C = epilogue(alpha*op(A)*op(B) + beta*C) on device tensors, in place in C.
 
     Same argument meaning as llmt's kernels::matmul
@@ -236,7 +236,7 @@ def gemm(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, 
     torch buffer is allocated for this call."""
     import torch
     d = make_desc(c, a, b, trans_a, trans_b, alpha, beta, bias, gelu, dbias, dbias_beta, workspace,
-                  tile_n, splits)
+                  tile_n, splits, cta_pairs)
     if workspace is None:
         need = workspace_bytes(d)
         if need:

@@ -15,6 +15,8 @@ namespace llmt_b200 {
 
 namespace {
 
+bool pairs_enabled();
+
 thread_local char g_err[512] = "";
 std::atomic<uint64_t> g_launches{0};
 
@@ -140,7 +142,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
     int best_bn = 0, best_splits = 1;
     int64_t best_cost = 0;
     for (int bn : cands) {
-        if (dbias && bn > 192) continue;
+        if (dbias && !pairs && bn > 192) continue;  // a single CTA needs 16 spare columns next to the tile
         if (force_bn != 0 && bn != force_bn) continue;
         if (pairs && (bn == 64 || (b_mn && bn % 128 != 0))) continue;
         // Never pick a tile wider than needed when a narrower one covers n in one column.
@@ -170,7 +172,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
 // and split only reductions that are longer than the average load of an SM.
 TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
                        int64_t group_kblock_tiles, int force_bn, int force_splits, bool pairs, bool b_mn) {
-    int bn = dbias ? 192 : 256;
+    int bn = (dbias && !pairs) ? 192 : 256;
     if (n <= 64) bn = pairs ? 128 : 64;
     else if (n <= 128) bn = 128;
     else if (n <= 192) bn = (pairs && b_mn) ? 256 : 192;
@@ -202,12 +204,20 @@ bool pairs_enabled() {
     }
     return v == 1;
 }
-bool pair_eligible(const llmt_b200_gemm_desc* d) {
-    if (!pairs_enabled() || d->dbias != nullptr || d->m <= 128) return false;
-    if (d->plan_tile_n == 64) return false;
+// Whether a problem CAN run on CTA pairs, and whether the library chooses to.
+bool pair_capable(const llmt_b200_gemm_desc* d) {
+    if (d->m <= 128 || d->plan_tile_n == 64) return false;
     const bool b_mn = d->trans_b == 0;
     if (b_mn && d->plan_tile_n == 192) return false;
     return true;
+}
+bool pair_eligible(const llmt_b200_gemm_desc* d) {
+    if (!pair_capable(d) || d->plan_cta_pairs == 1) return false;
+    if (d->plan_cta_pairs == 2) return true;
+    // Default: pairs, except for the fused-dbias products.  Those are the long dW
+    // reductions; their dbias tiles cost ~40 % more in pair form (a second MMA per
+    // k-step) and, being the longest tiles of a backward launch, set its makespan.
+    return pairs_enabled() && d->dbias == nullptr;
 }
 int pair_units() {
     const int r = max_resident_pairs();
@@ -261,8 +271,13 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     if (d->plan_tile_n != 0 && d->plan_tile_n != 64 && d->plan_tile_n != 128 &&
         d->plan_tile_n != 192 && d->plan_tile_n != 256)
         return fail(LLMT_B200_ERR_INVALID, "matmul: plan_tile_n must be 0, 64, 128, 192 or 256");
-    if (d->plan_tile_n == 256 && d->dbias != nullptr)
-        return fail(LLMT_B200_ERR_INVALID, "matmul: the fused dbias needs plan_tile_n <= 192");
+    if (d->plan_cta_pairs < 0 || d->plan_cta_pairs > 2)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: plan_cta_pairs must be 0, 1 or 2");
+    if (d->plan_cta_pairs == 2 && (d->m <= 128 || d->plan_tile_n == 64 || (d->trans_b == 0 && d->plan_tile_n == 192)))
+        return fail(LLMT_B200_ERR_INVALID, "matmul: CTA pairs need m > 128 and a tile width of 128 or 256 "
+                    "(192 only when B is stored [n, k])");
+    if (d->plan_tile_n == 256 && d->dbias != nullptr && d->plan_cta_pairs != 2)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: the fused dbias on single CTAs needs plan_tile_n <= 192");
     if (d->plan_splits < 0) return fail(LLMT_B200_ERR_INVALID, "matmul: negative plan_splits");
     if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU)) != 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: unknown epilogue flags 0x%x", d->epilogue);
@@ -500,7 +515,7 @@ int plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
     int64_t work = 0;
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
-        const int bn = d.dbias ? 192 : 256;
+        const int bn = (d.dbias && !pairs) ? 192 : 256;
         work += static_cast<int64_t>(ceil_div(d.m, pairs ? 256 : 128)) * ceil_div(d.n, bn) *
                 (d.batch > 0 ? d.batch : 1) * ceil_div(d.k, 64);
     }

@@ -105,8 +105,11 @@ __device__ __forceinline__ float gelu_tanh_precise(float v) {
 __device__ __forceinline__ float gelu_tanh_fast(float v) {
     const float a0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2*k0*log2(e)
     const float a1 = a0 * 0.044715f;
-    const float e = exp2f(v * fmaf(a1, v * v, a0));  // exp(-2u)
-    return __fdividef(v, 1.0f + e);
+    const float w = v * fmaf(a1, v * v, a0);  // -2u * log2(e)
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));         // exp(-2u); +inf for very negative v
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));  // sigmoid(2u); 0 when e = +inf
+    return v * r;
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.

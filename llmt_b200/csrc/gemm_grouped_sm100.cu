@@ -60,6 +60,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kDbiasCols = 16;
 constexpr uint32_t kSlabBytes = 128 * 32 * 4;        // 128 rows x 32 columns of fp32
 constexpr uint32_t kStagingBytes = 2 * kSlabBytes;   // one slab per column half
+constexpr uint32_t kOnesRegionBytes = 1024;          // 8 rows x 128 B of bf16 1.0 (pair-mode dbias MMA)
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 struct __align__(8) Control {
@@ -204,11 +205,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     const int sched_id = static_cast<int>(blockIdx.x) / CG;
 
     extern __shared__ uint8_t smem_raw[];
-    // Swizzled tiles need 1024-byte alignment.
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // Layout: control block, then (1024-byte aligned, as swizzled tiles need) a 1 KB block of
+    // bf16 ones, the operand stages and the epilogue staging slabs.
+    Control* ctl = reinterpret_cast<Control*>(smem_raw);
+    const uint32_t ones_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
+    const uint32_t smem_base = ones_base + kOnesRegionBytes;
     const uint32_t staging_base = smem_base + kStages * kStageBytes;
-    Control* ctl = reinterpret_cast<Control*>(smem_gen + kStages * kStageBytes + kStagingBytes);
     volatile int* abort_flag = &ctl->abort_flag;
     DeviceStatus* status = gp.status;
 
@@ -231,6 +233,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
+    if (kPair) {
+        // bf16 1.0 everywhere: reads the same under any swizzle.
+        for (uint32_t i = threadIdx.x; i < kOnesRegionBytes / 4; i += kThreads)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(ones_base + 4u * i), "r"(0x3F803F80u) : "memory");
+        fence_proxy_async_smem();
+    }
     if (warp == 1) {
         tmem_alloc_cg<CG>(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish_cg<CG>();
@@ -240,6 +248,10 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
+    // Everything above touched only this CTA's own state, so it may overlap the tail of the
+    // previous kernel in the stream; nothing below may start before that kernel is done.
+    grid_launch_dependents();
+    grid_dependency_wait();
 
     // Barriers that live in the leader CTA of a pair, as cluster addresses usable from both.
     auto on_leader = [&](const void* bar) { return kPair ? mapa_shared(smem_u32(bar), 0u) : smem_u32(bar); };
@@ -372,8 +384,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
             int stage = 0;
             uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
+            // Accumulator slot q lives in TMEM buffer q & 1 and is on its (q >> 1)-th use.
+            uint32_t acc_seq = 0;
             bool ok = true;
             for (int it = 0; ok; ++it) {
                 const int slot = it % kRing;
@@ -393,11 +405,22 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 const uint32_t a_lo_base = (smem_base >> 4) | (((p.a_mn ? kBlock64Bytes : 16u) >> 4) << 16);
                 const uint32_t b_lo_base = ((smem_base + kATileBytes) >> 4) |
                                            (((p.b_mn ? kBlock64Bytes : 16u) >> 4) << 16);
-                ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status,
-                                         kDevWaitTmemEmpty, acc);
+                // In a pair the fused dbias is a second, 16-column MMA per k-step against the ones
+                // block; its accumulator takes the next slot (the other TMEM buffer).
+                const bool dbias2 = kPair && p.dbias != nullptr && tc.n_tile == 0;
+                const int acc = static_cast<int>(acc_seq & 1u);
+                ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc]), ((acc_seq >> 1) & 1u) ^ 1u, abort_flag,
+                                         status, kDevWaitTmemEmpty, acc);
+                if (ok && dbias2)
+                    ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc ^ 1]), (((acc_seq + 1) >> 1) & 1u) ^ 1u,
+                                             abort_flag, status, kDevWaitTmemEmpty, acc ^ 1);
                 if (!ok) break;
                 tc_fence_after_thread_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
+                const uint32_t d_dbias = tmem_base + static_cast<uint32_t>(acc ^ 1) * kAccStride;
+                const uint32_t idesc_dbias = make_idesc_bf16(kTileRows, kDbiasCols, p.a_mn, 0);
+                const uint64_t ones_desc = (static_cast<uint64_t>(kDescHi) << 32) |
+                                           static_cast<uint64_t>((ones_base >> 4) | (1u << 16));
                 for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
                                              kDevWaitSmemFull, stage);
@@ -413,14 +436,18 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
                                             static_cast<uint64_t>(b_lo + kk * step_b);
                         umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                        if (dbias2) umma_bf16_cg<CG>(d_dbias, da, ones_desc, idesc_dbias, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc]));
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                ++acc_seq;
+                if (dbias2) {
+                    umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc ^ 1]));
+                    ++acc_seq;
+                }
             }
         }
     } else if (warp < 2 + kEpilogueWarps) {
@@ -431,8 +458,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         const uint32_t slab = staging_base + static_cast<uint32_t>(half) * kSlabBytes;
         const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
         uint32_t slab_toggle = 0;
-        int acc = 0;
-        uint32_t acc_phase = 0;
+        uint32_t acc_seq = 0;  // accumulator slot counter, in step with the MMA issuer's
         bool ok = true;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
@@ -446,7 +472,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (t < 0) break;
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
-            ok = bounded_wait(smem_u32(&ctl->tmem_full[acc]), acc_phase, abort_flag, status,
+            const int acc = static_cast<int>(acc_seq & 1u);
+            ok = bounded_wait(smem_u32(&ctl->tmem_full[acc]), (acc_seq >> 1) & 1u, abort_flag, status,
                               kDevWaitTmemFull, acc);
             if (!ok) break;
             tc_fence_after_thread_sync();
@@ -583,8 +610,34 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 if (kPair) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc]));
                 else mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
             }
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            ++acc_seq;
+            if (kPair && p.dbias != nullptr && tc.n_tile == 0) {
+                // The pair's dbias accumulator: column 0 of the next slot holds sum_k op(A)[row, k].
+                const int acc2 = static_cast<int>(acc_seq & 1u);
+                ok = bounded_wait(smem_u32(&ctl->tmem_full[acc2]), (acc_seq >> 1) & 1u, abort_flag, status,
+                                  kDevWaitTmemFull, acc2);
+                if (!ok) break;
+                tc_fence_after_thread_sync();
+                if (half == 0) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                      static_cast<uint32_t>(acc2) * kAccStride, r);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        const float sum = __uint_as_float(r[0]);
+                        if (partial) {
+                            p.ws_dbias[static_cast<int64_t>(tc.split) * p.m + row] = sum;
+                        } else {
+                            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[row] : 0.0f;
+                            p.dbias[row] = prev + sum;
+                        }
+                    }
+                }
+                tc_fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc2]));
+                ++acc_seq;
+            }
         }
         // Outstanding TMA stores must complete before the shared memory goes away.
         if (store_leader) bulk_wait_group0();
@@ -622,6 +675,8 @@ tc_grouped_pair_kernel(const __grid_constant__ GroupParams gp) {
 // C = epilogue(alpha * sum_s ws[s] + beta * C): fixed summation order s = 0..splits-1.
 // Four consecutive columns per thread when the row length allows it.
 __global__ void splitk_reduce_kernel(const GroupProblem p) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t n4 = (p.n + 3) / 4;
     const int64_t total4 = static_cast<int64_t>(p.batch) * p.m * n4;
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -671,7 +726,9 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
 size_t tc_grouped_smem_bytes() {
     // Both geometries use the same amount: 4 x 48 KB or 6 x 32 KB of operand stages.
     static_assert(Geo<1>::kStages * Geo<1>::kStageBytes == Geo<2>::kStages * Geo<2>::kStageBytes, "stage budget");
-    return 1024 /* alignment slack */ + Geo<1>::kStages * Geo<1>::kStageBytes + kStagingBytes + sizeof(Control);
+    static_assert(sizeof(Control) <= 1024, "control block must fit below the first aligned KB");
+    return 1024 /* control block + alignment */ + kOnesRegionBytes + Geo<1>::kStages * Geo<1>::kStageBytes +
+           kStagingBytes;
 }
 
 cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream) {
@@ -687,12 +744,22 @@ cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaS
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
-    if (pairs)
-        tc_grouped_pair_kernel<<<grid, kThreads, tc_grouped_smem_bytes(), stream>>>(gp);
-    else
-        tc_grouped_kernel<<<grid, kThreads, tc_grouped_smem_bytes(), stream>>>(gp);
+    // Programmatic dependent launch: the kernel's prologue (barriers, TMEM) overlaps the tail
+    // of the previous kernel in the stream; the kernel itself waits before touching memory.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = tc_grouped_smem_bytes();
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_kernel, gp)
+                                : cudaLaunchKernelEx(&cfg, tc_grouped_kernel, gp);
     count_launch(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // How many CTA pairs can be resident at once (1 CTA per SM, pairs share a cluster).
@@ -717,9 +784,18 @@ cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream) {
     const int64_t work = total > p.m ? total : p.m;
     const int block = 256;
     const int64_t grid = (work + block - 1) / block;
-    splitk_reduce_kernel<<<static_cast<unsigned>(grid), block, 0, stream>>>(p);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, p);
     count_launch(1);
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace llmt_b200

@@ -25,6 +25,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// --------------------------------------------- programmatic dependent launch --
+
+// Blocks until the grids this grid depends on have completed and their memory is visible.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next grid in the stream start its own prologue while this one is still running.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier --
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -35,6 +35,7 @@ def test_library_exports_every_declared_symbol():
 def test_descriptor_layout_matches_the_header():
     # field order and sizes of struct llmt_b200_gemm_desc as the C compiler lays them out
     assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8
+    assert L.GemmDesc.plan_cta_pairs.offset == L.GemmDesc.plan_splits.offset + 4
     assert L.GemmDesc.workspace.offset % 8 == 0
 
 
@@ -66,6 +67,8 @@ def _call(d, c=C, a=A, b=B):
     (dict(epilogue=8), L.ERR_INVALID, "epilogue"),
     (dict(epilogue=L.EPI_BIAS), L.ERR_INVALID, "bias is null"),
     (dict(plan_tile_n=100), L.ERR_INVALID, "plan_tile_n"),
+    (dict(plan_cta_pairs=3), L.ERR_INVALID, "plan_cta_pairs"),
+    (dict(plan_cta_pairs=2), L.ERR_INVALID, "CTA pairs need m > 128"),
     (dict(lda=68), L.ERR_UNSUPPORTED, "multiple of 8"),
     (dict(batch=2, stride_a=10, stride_b=128 * 64, stride_c=128 * 128), L.ERR_INVALID, "batch stride"),
 ])
@@ -91,7 +94,7 @@ def test_dbias_contract():
     d = _desc(dbias=0x80000, dtype_ab=L.FP32)
     assert _call(d) == L.ERR_UNSUPPORTED and "dbias" in L.last_error()
     d = _desc(dbias=0x80000, plan_tile_n=256)
-    assert _call(d) == L.ERR_INVALID
+    assert _call(d) == L.ERR_INVALID and "single CTAs" in L.last_error()
 
 
 def test_empty_output_is_a_no_op():

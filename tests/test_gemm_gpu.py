@@ -263,6 +263,36 @@ def test_bf16_strided_batched(ta, tb):
     assert oracle.rel_fro(host(c), oracle.gemm(a, b, bool(ta), bool(tb), 0.125)) <= TOL_BF16_ACC_FRO
 
 
+@pytest.mark.parametrize("splits", [0, 1, 3])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_bf16_dw_with_fused_dbias_on_cta_pairs(tile_n, splits):
+    """The same product on CTA pairs (256-row tiles): dbias comes from a second 16-column MMA
+    per k-step against a block of ones, in an accumulator slot of its own."""
+    tokens, out_f, in_f = 1024, 520, 2 * tile_n + 40
+    rng = np.random.default_rng(53 + tile_n + splits)
+    dy = oracle.round_bf16(rng.standard_normal((tokens, out_f)) * 0.01)
+    x = oracle.round_bf16(rng.standard_normal((tokens, in_f)))
+    dw0 = rng.standard_normal((out_f, in_f)).astype(np.float32)
+    db0 = rng.standard_normal(out_f).astype(np.float32)
+    dw, db = dev_f32(dw0), dev_f32(db0)
+    L.gemm(dw, dev_bf16(dy), dev_bf16(x), trans_a=True, beta=1.0, dbias=db, dbias_beta=1.0,
+           tile_n=tile_n, splits=splits, cta_pairs=2)
+    assert oracle.rel_fro(host(dw), oracle.gemm(dy, x, trans_a=True, beta=1.0, c=dw0)) <= TOL_BF16_ACC_FRO
+    assert oracle.rel_fro(host(db), oracle.rowsum(dy, trans_a=True, out=db0, out_beta=1.0)) <= TOL_BF16_ACC_FRO
+
+
+@pytest.mark.parametrize("cta_pairs", [1, 2])
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+def test_bf16_single_cta_and_pair_kernels_agree(ta, tb, cta_pairs):
+    """Both tensor-core kernels (128-row tiles on one CTA, 256-row tiles on a CTA pair) on
+    every transpose combination, against the oracle."""
+    m, n, k = 520, 392, 328
+    a, b, _ = _bf16_case(m, n, k, ta, tb, seed=61 + 2 * ta + tb)
+    c = torch.empty(m, n, device=DEV)
+    L.gemm(c, dev_bf16(a), dev_bf16(b), bool(ta), bool(tb), cta_pairs=cta_pairs)
+    assert oracle.rel_fro(host(c), oracle.gemm(a, b, bool(ta), bool(tb))) <= TOL_BF16_ACC_FRO
+
+
 @pytest.mark.parametrize("splits", [0, 1, 3, 8])
 @pytest.mark.parametrize("tile_n", [64, 128, 192])
 def test_bf16_dw_with_fused_dbias_and_splitk(tile_n, splits):
