@@ -193,14 +193,16 @@ TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbia
     return pl;
 }
 
-// CTA pairs (cta_group::2, 256-row tiles) halve the operand bytes per flop; they need
-// a problem without the fused dbias and at least two 128-row tiles of rows.
-// LLMT_B200_PAIRS=0 keeps every launch on single CTAs (for comparisons).
+// CTA pairs (cta_group::2, 256-row tiles) halve the B bytes each SM stages per flop.  They
+// win when the operands are resident in L2 (the same GEMM called back to back: +5..10 %)
+// and lose 10..20 % when operands stream from HBM, which is the regime of a training step
+// whose working set exceeds L2 - so the default is single CTAs, and pairs are chosen per
+// call with plan_cta_pairs = 2, or for every eligible call with LLMT_B200_PAIRS=1.
 bool pairs_enabled() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("LLMT_B200_PAIRS");
-        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
 }
@@ -220,6 +222,7 @@ bool pair_eligible(const llmt_b200_gemm_desc* d) {
     return pairs_enabled() && d->dbias == nullptr;
 }
 int pair_units() {
+    { const char* e = getenv("LLMT_B200_PAIR_UNITS"); if (e != nullptr && atoi(e) > 0) return atoi(e); }
     const int r = max_resident_pairs();
     const int by_sm = sm_count() / 2;
     return (r > 0 && r < by_sm) ? r : by_sm;
@@ -380,23 +383,76 @@ int device_globals(DeviceGlobals** out) {
     return LLMT_B200_OK;
 }
 
-// TMA needs 16-byte aligned bases and pitches.
+// TMA needs 16-byte aligned bases, pitches and batch strides.  An operand whose pitch (or
+// batch stride) is not a multiple of 8 elements - e.g. a contiguous [tokens, 50257] dLogits -
+// is first copied into the workspace with its pitch rounded up ("repacked"); an operand that
+// merely starts at an odd address is not supported.
 int check_tma_operands(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
+    (void)d;
     if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u))
         return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: bf16 operands must start on a 16-byte boundary");
-    if ((d->lda % 8) != 0 || (d->ldb % 8) != 0 ||
-        (d->batch > 1 && ((d->stride_a % 8) != 0 || (d->stride_b % 8) != 0)))
-        return fail(LLMT_B200_ERR_UNSUPPORTED,
-                    "matmul: bf16 row pitch / batch stride must be a multiple of 8 elements "
-                    "(lda=%lld ldb=%lld)", (long long)d->lda, (long long)d->ldb);
     return LLMT_B200_OK;
 }
 
-int check_workspace(const llmt_b200_gemm_desc* d, const TcPlan& pl) {
-    if (pl.workspace_bytes == 0) return LLMT_B200_OK;
-    if (d->workspace == nullptr || d->workspace_bytes < pl.workspace_bytes)
-        return fail(LLMT_B200_ERR_WORKSPACE, "matmul: split-K needs %llu workspace bytes, got %llu",
-                    (unsigned long long)pl.workspace_bytes, (unsigned long long)d->workspace_bytes);
+struct Repack {
+    bool a = false, b = false;
+    int64_t lda = 0, ldb = 0, stride_a = 0, stride_b = 0;  // layout of the repacked copies
+    size_t bytes_a = 0, bytes_b = 0;                       // 256-byte rounded
+    size_t total() const { return bytes_a + bytes_b; }
+};
+
+Repack repack_plan(const llmt_b200_gemm_desc* d, const Checked& ck) {
+    Repack r;
+    const int64_t nb = d->batch > 1 ? d->batch : 1;
+    auto round8 = [](int64_t v) { return (v + 7) / 8 * 8; };
+    if (d->k > 0 && ((d->lda % 8) != 0 || (d->batch > 1 && (d->stride_a % 8) != 0))) {
+        r.a = true;
+        r.lda = round8(ck.a_cols);
+        r.stride_a = ck.a_rows * r.lda;
+        r.bytes_a = (static_cast<size_t>(nb) * r.stride_a * 2 + 255) / 256 * 256;
+    }
+    if (d->k > 0 && ((d->ldb % 8) != 0 || (d->batch > 1 && (d->stride_b % 8) != 0))) {
+        r.b = true;
+        r.ldb = round8(ck.b_cols);
+        r.stride_b = ck.b_rows * r.ldb;
+        r.bytes_b = (static_cast<size_t>(nb) * r.stride_b * 2 + 255) / 256 * 256;
+    }
+    return r;
+}
+
+// Copies the operands that need it behind the split-K region of the workspace and rewrites
+// the (local) descriptor and pointers to use the copies.
+int apply_repack(llmt_b200_gemm_desc* d, const Checked& ck, const Repack& rp, size_t ws_offset,
+                 const void** a, const void** b, cudaStream_t stream) {
+    char* base = static_cast<char*>(d->workspace) + ws_offset;
+    if (rp.a) {
+        cudaError_t e = launch_repack_bf16(base, *a, ck.a_rows, ck.a_cols, d->lda, rp.lda, d->batch > 1 ? d->batch : 1,
+                                           d->batch > 1 ? d->stride_a : 0, rp.stride_a, stream);
+        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+        *a = base;
+        d->lda = rp.lda;
+        d->stride_a = rp.stride_a;
+        base += rp.bytes_a;
+    }
+    if (rp.b) {
+        cudaError_t e = launch_repack_bf16(base, *b, ck.b_rows, ck.b_cols, d->ldb, rp.ldb, d->batch > 1 ? d->batch : 1,
+                                           d->batch > 1 ? d->stride_b : 0, rp.stride_b, stream);
+        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+        *b = base;
+        d->ldb = rp.ldb;
+        d->stride_b = rp.stride_b;
+    }
+    return LLMT_B200_OK;
+}
+
+int check_workspace(const llmt_b200_gemm_desc* d, const TcPlan& pl, size_t repack_bytes = 0) {
+    const size_t need = pl.workspace_bytes + repack_bytes;
+    if (need == 0) return LLMT_B200_OK;
+    if (d->workspace == nullptr || d->workspace_bytes < need)
+        return fail(LLMT_B200_ERR_WORKSPACE,
+                    "matmul: needs %llu workspace bytes (split-K partial sums %llu, repacked operands %llu), got %llu",
+                    (unsigned long long)need, (unsigned long long)pl.workspace_bytes,
+                    (unsigned long long)repack_bytes, (unsigned long long)d->workspace_bytes);
     if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
         return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
     return LLMT_B200_OK;
@@ -499,10 +555,16 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
     int st = check_tma_operands(d, a, b);
     if (st != LLMT_B200_OK) return st;
     const TcPlan pl = plan_single(d);
-    st = check_workspace(d, pl);
+    const Repack rp = repack_plan(d, ck);
+    st = check_workspace(d, pl, rp.total());
     if (st != LLMT_B200_OK) return st;
+    llmt_b200_gemm_desc local = *d;
+    if (rp.total() > 0) {
+        st = apply_repack(&local, ck, rp, pl.workspace_bytes, &a, &b, stream);
+        if (st != LLMT_B200_OK) return st;
+    }
     GroupProblem p;
-    st = fill_problem(&p, d, ck, pl, c, a, b);
+    st = fill_problem(&p, &local, ck, pl, c, a, b);
     if (st != LLMT_B200_OK) return st;
     return launch_group(&p, 1, pl.pairs != 0, stream);
 }
@@ -590,7 +652,7 @@ int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const v
     if (!ck.bf16) return run_fp32(d, c, a, b, s);  // the fp32 path uses no scratch at all
     // Size check first: a problem that does not fit is turned away before the scratch is
     // resolved and before anything is enqueued.
-    const size_t need = plan_single(d).workspace_bytes;
+    const size_t need = plan_single(d).workspace_bytes + repack_plan(d, ck).total();
     if (need > kStaticScratchBytes)
         return fail(LLMT_B200_ERR_WORKSPACE,
                     "gemm_static_scratch: this problem's split-K plan needs %llu scratch bytes but the "
@@ -637,9 +699,18 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
     int n = 0;
     for (int i = 0; i < count; ++i) {
         if (descs[i].m == 0 || descs[i].n == 0 || descs[i].batch == 0) continue;
-        int st = check_workspace(&descs[i], plans[i]);
+        const Repack rp = repack_plan(&descs[i], ck[i]);
+        int st = check_workspace(&descs[i], plans[i], rp.total());
         if (st != LLMT_B200_OK) return st;
-        st = fill_problem(&probs[n], &descs[i], ck[i], plans[i], c[i], a[i], b[i]);
+        llmt_b200_gemm_desc local = descs[i];
+        const void* ai = a[i];
+        const void* bi = b[i];
+        if (rp.total() > 0) {
+            st = apply_repack(&local, ck[i], rp, plans[i].workspace_bytes, &ai, &bi,
+                              static_cast<cudaStream_t>(stream));
+            if (st != LLMT_B200_OK) return st;
+        }
+        st = fill_problem(&probs[n], &local, ck[i], plans[i], c[i], ai, bi);
         if (st != LLMT_B200_OK) return st;
         ++n;
     }
@@ -655,8 +726,11 @@ int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int
     plan_group(descs, count, plans);
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
+        Checked ck{};
+        ck.a_rows = d.trans_a ? d.k : d.m; ck.a_cols = d.trans_a ? d.m : d.k;
+        ck.b_rows = d.trans_b ? d.n : d.k; ck.b_cols = d.trans_b ? d.k : d.n;
         bytes_per_problem[i] = (d.dtype_ab == LLMT_B200_BF16 && d.m > 0 && d.n > 0 && d.k > 0 && d.batch > 0)
-                                   ? plans[i].workspace_bytes : 0;
+                                   ? plans[i].workspace_bytes + repack_plan(&d, ck).total() : 0;
     }
     return LLMT_B200_OK;
 }
@@ -665,7 +739,10 @@ uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
     if (d == nullptr || d->dtype_ab != LLMT_B200_BF16 || d->m <= 0 || d->n <= 0 || d->k <= 0 ||
         d->batch <= 0)
         return 0;
-    return plan_single(d).workspace_bytes;
+    Checked ck{};
+    ck.a_rows = d->trans_a ? d->k : d->m; ck.a_cols = d->trans_a ? d->m : d->k;
+    ck.b_rows = d->trans_b ? d->n : d->k; ck.b_cols = d->trans_b ? d->k : d->n;
+    return plan_single(d).workspace_bytes + repack_plan(d, ck).total();
 }
 
 int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
@@ -677,11 +754,11 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
     }
     const TcPlan pl = plan_single(d);
     const int units = pl.pairs ? pair_units() : sm_count();
-    snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu",
+    snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu resident_pairs=%d",
              pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? 6 : 4, pl.splits, pl.tiles_m,
              pl.tiles_n, pl.kblocks_total,
              static_cast<int>(pl.num_tiles < units ? pl.num_tiles : units) * (pl.pairs ? 2 : 1),
-             tc_grouped_smem_bytes(), pl.workspace_bytes);
+             tc_grouped_smem_bytes(), pl.workspace_bytes, pl.pairs ? max_resident_pairs() : 0);
     return LLMT_B200_OK;
 }
 

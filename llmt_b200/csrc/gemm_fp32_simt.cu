@@ -148,7 +148,35 @@ __global__ void softmax_bwd_kernel(T* ds, const T* p, const T* dp, int64_t rows,
     for (int64_t i = lane; i < tk; i += 32) stf(ds + row * tk, i, ldf(pr, i) * (ldf(dr, i) - dot));
 }
 
+// Copies a row-major bf16 matrix (any pitch, any 2-byte alignment) into a buffer whose pitch
+// is a multiple of 8 elements, so that TMA can address it.  One thread per element pair.
+__global__ void repack_bf16_kernel(uint16_t* __restrict__ dst, const uint16_t* __restrict__ src, int64_t rows,
+                                   int64_t cols, int64_t ld_src, int64_t ld_dst, int64_t batch,
+                                   int64_t stride_src, int64_t stride_dst) {
+    const int64_t total = batch * rows * ld_dst;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t c = i % ld_dst;
+        const int64_t r = (i / ld_dst) % rows;
+        const int64_t b = i / (ld_dst * rows);
+        dst[b * stride_dst + r * ld_dst + c] = c < cols ? src[b * stride_src + r * ld_src + c] : uint16_t(0);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_repack_bf16(void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld_src,
+                               int64_t ld_dst, int64_t batch, int64_t stride_src, int64_t stride_dst,
+                               cudaStream_t stream) {
+    const int64_t total = batch * rows * ld_dst;
+    int64_t grid = (total + 255) / 256;
+    if (grid > 148 * 32) grid = 148 * 32;
+    repack_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, stream>>>(
+        static_cast<uint16_t*>(dst), static_cast<const uint16_t*>(src), rows, cols, ld_src, ld_dst, batch,
+        stride_src, stride_dst);
+    count_launch(1);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream) {
     dim3 grid(static_cast<unsigned>((p.n + TN - 1) / TN), static_cast<unsigned>((p.m + TM - 1) / TM),

@@ -69,7 +69,7 @@ def _call(d, c=C, a=A, b=B):
     (dict(plan_tile_n=100), L.ERR_INVALID, "plan_tile_n"),
     (dict(plan_cta_pairs=3), L.ERR_INVALID, "plan_cta_pairs"),
     (dict(plan_cta_pairs=2), L.ERR_INVALID, "CTA pairs need m > 128"),
-    (dict(lda=68), L.ERR_UNSUPPORTED, "multiple of 8"),
+    (dict(lda=68), L.ERR_WORKSPACE, "repacked operands"),  # odd pitch: needs scratch for an aligned copy
     (dict(batch=2, stride_a=10, stride_b=128 * 64, stride_c=128 * 128), L.ERR_INVALID, "batch stride"),
 ])
 def test_contract_violations_return_status(kw, status, needle):
@@ -107,7 +107,10 @@ def test_plan_is_a_pure_function_of_the_problem():
     # (role of llmt's AlgoCache, include/llmt/kernels/algo_cache.h:18-42)
     d = _desc(m=8192, n=2304, k=768, lda=768, ldb=768, ldc=2304)
     p1, p2 = L.plan(d), L.plan(d)
-    assert p1 == p2 and "tcgen05" in p1 and "tile=256x256x64" in p1  # CTA pairs, 256-row tiles
+    assert p1 == p2 and "tcgen05 1-cta tile=128x256x64" in p1
+    d.plan_cta_pairs = 2  # CTA pairs on request: 256-row tiles
+    assert "cta-pair tile=256x256x64" in L.plan(d)
+    d.plan_cta_pairs = 0
     assert L.workspace_bytes(d) == 0
     dw = _desc(m=768, n=768, k=8192, trans_a=1, trans_b=0, lda=768, ldb=768, ldc=768)
     assert "splits=" in L.plan(dw)

@@ -210,6 +210,39 @@ def test_bf16_padded_pitches():
     assert (got[:, n:] == 7.0).all(), "padding columns of C must not be written"
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0)])
+def test_bf16_unaligned_pitches_are_repacked(ta, tb):
+    """Operands whose pitch is not a multiple of 8 elements (TMA cannot address them) are
+    copied into the workspace with a padded pitch first; C with an odd pitch is written
+    straight from registers."""
+    m, n, k = 257, 203, 137  # every pitch is odd
+    a, b, _ = _bf16_case(m, n, k, ta, tb, seed=71 + 2 * ta + tb)
+    c = torch.full((m, n), -1.0, device=DEV)
+    ad, bd = dev_bf16(a), dev_bf16(b)
+    d = L.make_desc(c, ad, bd, bool(ta), bool(tb))
+    need = L.workspace_bytes(d)
+    assert need >= 2 * (a.size + b.size)  # both operands get an aligned copy
+    with pytest.raises(L.LlmtB200Error) as e:
+        L.gemm_desc(d, c, ad, bd)        # no scratch handed in
+    assert e.value.status == L.ERR_WORKSPACE
+    L.gemm(c, ad, bd, bool(ta), bool(tb))  # the wrapper allocates the scratch
+    assert oracle.rel_fro(host(c), oracle.gemm(a, b, bool(ta), bool(tb))) <= TOL_BF16_ACC_FRO
+
+
+def test_bf16_unaligned_batch_stride():
+    batch, m, n, k = 3, 64, 72, 40
+    rng = np.random.default_rng(73)
+    a = oracle.round_bf16(rng.standard_normal((batch, m, k)))
+    b = oracle.round_bf16(rng.standard_normal((batch, n, k)))
+    # batch items 4 elements further apart than one matrix: stride not a multiple of 8
+    abuf = torch.zeros(batch * (m * k + 4), device=DEV, dtype=torch.bfloat16)
+    av = abuf.as_strided((batch, m, k), (m * k + 4, k, 1))
+    av.copy_(dev_bf16(a))
+    c = torch.empty(batch, m, n, device=DEV)
+    L.gemm(c, av, dev_bf16(b), False, True)
+    assert oracle.rel_fro(host(c), oracle.gemm(a, b, False, True)) <= TOL_BF16_ACC_FRO
+
+
 def test_bf16_output_rounding_and_ulp():
     m, n, k = 512, 768, 768
     a, b, _ = _bf16_case(m, n, k, 0, 1, seed=11, scale_b=0.02)
@@ -417,6 +450,29 @@ def test_config3_lm_head_padded_vocab_sampled():
     dw = torch.zeros(V, C, device=DEV)
     L.gemm(dw, dl, xd, True, False, beta=1.0)
     vrows = np.concatenate([rng.choice(V, 14, replace=False), [V - 1, V - 2]])
+    _check_rows(dw, dl_host, x, True, False, vrows, TOL_BF16_ACC_FRO)
+
+
+def test_config3_lm_head_contiguous_vocab_50257():
+    """BASELINE config 3 with the vocabulary NOT padded: logits and dLogits are contiguous
+    [tokens, 50257] (pitch 100514 / 201028 bytes, which TMA cannot address).  fp32 logits are
+    written from registers; the bf16 dLogits operand of dX and dW goes through the repack copy."""
+    M, C, V = 512, 768, 50257
+    rng = np.random.default_rng(33)
+    x = oracle.round_bf16(rng.standard_normal((M, C)))
+    w = oracle.round_bf16(rng.standard_normal((V, C)) * 0.02)
+    dl_host = oracle.round_bf16(rng.standard_normal((M, V)) * 1e-4)
+    xd, wd, dl = dev_bf16(x), dev_bf16(w), dev_bf16(dl_host)
+    rows = rng.choice(M, 12, replace=False)
+    logits = torch.empty(M, V, device=DEV)
+    L.gemm(logits, xd, wd, False, True)
+    _check_rows(logits, x, w, False, True, rows, TOL_BF16_ACC_FRO)
+    dx = torch.empty(M, C, device=DEV, dtype=torch.bfloat16)
+    L.gemm(dx, dl, wd, False, False)
+    _check_rows(dx, dl_host, w, False, False, rows, TOL_BF16_OUT_FRO)
+    dw = torch.zeros(V, C, device=DEV)
+    L.gemm(dw, dl, xd, True, False, beta=1.0)
+    vrows = np.concatenate([rng.choice(V, 10, replace=False), [V - 1, 0]])
     _check_rows(dw, dl_host, x, True, False, vrows, TOL_BF16_ACC_FRO)
 
 
