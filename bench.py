@@ -37,6 +37,9 @@ LAYERS = {
                        ("mlp_fc", 768, 3072, True), ("mlp_proj", 3072, 768, False)]),
     "c5": dict(name="gpt2-xl MLP", C=1600,
                layers=[("mlp_fc", 1600, 6400, True), ("mlp_proj", 6400, 1600, False)]),
+    # tied-embedding LM head: fp32 logits, no bias, vocabulary 50257 in a row pitch of 50264
+    "c3": dict(name="LM head, vocab 50257 (row pitch 50264), fp32 logits", C=768, bias=False, y_fp32=True,
+               ld_out=50264, layers=[("lm_head", 768, 50257, False)]),
 }
 M_PER_GPU = 8192
 
@@ -110,18 +113,20 @@ class LinearStep:
         self.L, self.torch, self.m = L, torch, m
         g = torch.Generator(device=dev).manual_seed(seed)
         bf = torch.bfloat16
-        spec = LAYERS[workload]["layers"]
+        cfg = LAYERS[workload]
+        spec = cfg["layers"]
+        has_bias = cfg.get("bias", True)
         self.bucket = GradBucket({k: v for n, i, o, _ in spec
                                   for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}, dev)
         self.layers, self.calls = [], []
-        ws_need = 0
         for n, i, o, gelu in spec:
             t = dict(name=n, gelu=gelu, i=i, o=o)
+            ld = cfg.get("ld_out", o)  # row pitch of the [m, out] tensors (padded vocabulary)
             t["x"] = torch.randn(m, i, device=dev, generator=g).to(bf)
             t["w"] = (torch.randn(o, i, device=dev, generator=g) * 0.02).to(bf)
-            t["b"] = torch.randn(o, device=dev, generator=g) * 0.02
-            t["dy"] = (torch.randn(m, o, device=dev, generator=g) * 0.01).to(bf)
-            t["y"] = torch.empty(m, o, device=dev, dtype=bf)
+            t["b"] = torch.randn(o, device=dev, generator=g) * 0.02 if has_bias else None
+            t["dy"] = (torch.randn(m, ld, device=dev, generator=g) * 0.01).to(bf)[:, :o]
+            t["y"] = torch.empty(m, ld, device=dev, dtype=torch.float32 if cfg.get("y_fp32") else bf)[:, :o]
             t["dx"] = torch.empty(m, i, device=dev, dtype=bf)
             t["dw"], t["db"] = self.bucket.view(n + ".dW"), self.bucket.view(n + ".dbias")
             self.layers.append(t)
@@ -129,7 +134,8 @@ class LinearStep:
             t["d_fwd"] = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
             # Linear::backward as one launch: dx = dy W and dW += dy^T x (+ dbias) share a tile queue
             dx = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
-            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0, dbias=t["db"], dbias_beta=1.0)
+            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0,
+                             dbias=t["db"] if has_bias else None, dbias_beta=1.0)
             t["bwd"] = L.Group([(dx, t["dx"], t["dy"], t["w"]), (dw, t["dw"], t["dy"], t["x"])])
         # one scratch buffer per problem that needs one (split-K partial sums)
         self.ws = []
@@ -179,6 +185,61 @@ class LinearStep:
                     torch.distributed.all_reduce(self.grad_slice(layer))
         if world > 1:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+
+class AttentionStep:
+    """BASELINE config 4: the six strided-batched attention products at B*H = 96, T = 1024, hd = 64
+    (llmt src/kernels/attention.cpp:60-62 forward, docs/TODO.md:226-228 backward), bf16.
+    P and dS are produced once by the softmax helpers outside the timed set. HBM-bound:
+    every product moves one [96, T, T] matrix."""
+    BH, T, HD = 96, 1024, 64
+
+    def __init__(self, dev, seed):
+        import torch
+        import llmt_b200 as L
+        self.L, self.torch = L, torch
+        g = torch.Generator(device=dev).manual_seed(seed)
+        bf = torch.bfloat16
+        BH, T, HD = self.BH, self.T, self.HD
+        mk = lambda *shape, scale=1.0: (torch.randn(*shape, device=dev, generator=g) * scale).to(bf)
+        self.q, self.k, self.v = mk(BH, T, HD), mk(BH, T, HD), mk(BH, T, HD)
+        self.d_o = mk(BH, T, HD, scale=0.01)
+        self.s = torch.empty(BH, T, T, device=dev, dtype=bf)
+        self.p = torch.empty_like(self.s)
+        self.dp = torch.empty_like(self.s)
+        self.ds = torch.empty_like(self.s)
+        self.o, self.dv, self.dq, self.dk = (torch.empty(BH, T, HD, device=dev, dtype=bf) for _ in range(4))
+        a = 1.0 / 8.0
+        L.gemm(self.s, self.q, self.k, False, True, alpha=a)
+        L.softmax_fwd(self.p, self.s, causal=True)
+        L.gemm(self.dp, self.d_o, self.v, False, True)
+        L.softmax_bwd(self.ds, self.p, self.dp)
+        md = L.make_desc
+        self.calls = [
+            ("S=aQK^T", md(self.s, self.q, self.k, False, True, alpha=a), self.s, self.q, self.k),
+            ("O=PV", md(self.o, self.p, self.v, False, False), self.o, self.p, self.v),
+            ("dV=P^TdO", md(self.dv, self.p, self.d_o, True, False), self.dv, self.p, self.d_o),
+            ("dP=dOV^T", md(self.dp, self.d_o, self.v, False, True), self.dp, self.d_o, self.v),
+            ("dQ=adSK", md(self.dq, self.ds, self.k, False, False, alpha=a), self.dq, self.ds, self.k),
+            ("dK=adS^TQ", md(self.dk, self.ds, self.q, True, False, alpha=a), self.dk, self.ds, self.q),
+        ]
+        self.flops_each = 2.0 * BH * T * T * HD
+        # minimum bytes of one product: the [BH,T,T] matrix once plus three [BH,T,hd] tensors
+        self.bytes_each = 2.0 * (BH * T * T + 3 * BH * T * HD)
+
+    def launches(self):
+        return [(lab, self.flops_each, (lambda d=d, c=c, a=a, b=b: self.L.gemm_desc(d, c, a, b)), None)
+                for lab, d, c, a, b in self.calls]
+
+    def run(self, world=1, events=None):
+        torch = self.torch
+        for label, _, fn, _l in self.launches():
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            fn()
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True); e1.record()
+                events.append((label, e0, e1))
 
 
 class HostStep:
@@ -364,7 +425,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=sorted(LAYERS), default="c2")
+    ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4"], default="c2")
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -392,8 +453,9 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    step = LinearStep(args.workload, M_PER_GPU, dev, seed=rank)
-    flops = step_flops(args.workload, M_PER_GPU)
+    attention = args.workload == "c4"
+    step = AttentionStep(dev, seed=rank) if attention else LinearStep(args.workload, M_PER_GPU, dev, seed=rank)
+    flops = 6 * step.flops_each if attention else step_flops(args.workload, M_PER_GPU)
     for _ in range(args.warmup):
         step.run(world)
     barrier()
@@ -429,47 +491,68 @@ def main():
     per_gemm = {lab: round(gl[lab] / (sum(v) / len(v)) / 1e9, 1) for lab, v in per.items()}
 
     # end to end from host buffers
-    hs = HostStep(step)
-    hs.run(world); barrier()
-    n_e2e = max(2, min(args.steps, 10))
-    e0.record()
-    for _ in range(n_e2e):
-        hs.run(world)
-    e1.record(); barrier()
-    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    if attention:
+        ms_e2e, h2d, d2h = float("nan"), 0, 0
+    else:
+        hs = HostStep(step)
+        hs.run(world); barrier()
+        n_e2e = max(2, min(args.steps, 10))
+        e0.record()
+        for _ in range(n_e2e):
+            hs.run(world)
+        e1.record(); barrier()
+        ms_e2e = e0.elapsed_time(e1) / n_e2e
+        h2d, d2h = hs.h2d_bytes, hs.d2h_bytes
 
-    t = torch.tensor([ms, ms_e2e, gemm_ms], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, 0.0 if attention else ms_e2e, gemm_ms], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms, ms_e2e, gemm_ms = (float(x) for x in t.cpu())
     if rank == 0:
         peak_tf, peak_bw, which = measured_peaks()
         achieved = flops / gemm_ms / 1e9
+        if attention:
+            wl = ("c4: strided-batched attention products, B*H=96, T=1024, hd=64: S, O, dV, dP, dQ, dK "
+                  "(dense FLOP count); P and dS from the softmax helpers outside the timed set")
+            launches_txt = "6 batched GEMM launches"
+            gbs = 6 * step.bytes_each / gemm_ms / 1e6
+            roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak_bw, "unit": "GB/s",
+                    "frac": round(gbs / peak_bw, 4), "traffic": None, "peak_source": f"of {which}",
+                    "kernel": "tc_grouped_kernel (six batched launches; algorithmic bytes = one [96,T,T] "
+                              "bf16 matrix + three [96,T,64] tensors per product)"}
+            ar_bytes = 0
+        else:
+            cfg = LAYERS[args.workload]
+            wl = (f"{args.workload}: {cfg['name']}, M={M_PER_GPU} tokens per GPU, fwd+dX+dW(+dbias) per layer"
+                  + (", bias+GELU fused in mlp_fc" if cfg.get("bias", True) else ""))
+            nl = len(cfg["layers"])
+            launches_txt = (f"{nl} forward GEMMs + {nl} grouped backward launches (dX and dW+dbias of a layer "
+                            "in one kernel) + split-K reductions")
+            roof = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
+                    "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": None,
+                    "peak_source": f"of {which}",
+                    "kernel": "tc_grouped_kernel (all GEMM launches of the step; per-launch device time "
+                              "from a second, instrumented pass over the same steps)"}
+            ar_bytes = step.bucket.nbytes() if world > 1 else 0
         line = {
             "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job", "value": round(world * flops / ms / 1e9, 2),
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {LAYERS[args.workload]['name']}, "
-                                   f"M={M_PER_GPU} tokens per GPU, fwd+dX+dW(+dbias) per layer, "
-                                   f"bias+GELU fused in mlp_fc",
-                       "launches_per_step": "4 forward GEMMs + 4 grouped backward launches (dX and dW+dbias of a layer in one kernel) + split-K reductions",
+            "config": {"workload": wl, "launches_per_step": launches_txt,
                        "per_gpu_gflop_per_step": round(flops / 1e9, 1),
-                       "allreduce_bytes_per_step": step.bucket.nbytes() if world > 1 else 0,
-                       "l2": "working set (~400 MB of activations per step) larger than L2"},
+                       "allreduce_bytes_per_step": ar_bytes,
+                       "l2": "working set of a step larger than L2 (operands stream from HBM)"},
             "per_gpu_tflops": round(flops / ms / 1e9, 2),
             "pct_of_bf16_peak": round(100.0 * flops / ms / 1e9 / peak_tf, 1),
-            "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
-                         "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": None,
-                         "peak_source": f"of {which}",
-                         "kernel": "tc_grouped_kernel (all GEMM launches of the step, device time)"},
+            "roofline": roof,
             "per_gemm_tflops": per_gemm,
-            "e2e": {"value": round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes},
+            "e2e": {"value": None if attention else round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not attention:
             line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line))
     if world > 1:
