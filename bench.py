@@ -106,18 +106,23 @@ class ClockSampler:
 class LinearStep:
     """Device tensors and prebuilt C-ABI descriptors of one training step's GEMMs."""
 
-    def __init__(self, workload, m, dev, seed):
+    def __init__(self, workload, m, dev, seed, world=1, exchange="peer", comm_ctas=8, split_last=False):
         import torch
         import llmt_b200 as L
-        from llmt_b200.dp import GradBucket
+        from llmt_b200.dp import GradBucket, PeerExchange
         self.L, self.torch, self.m = L, torch, m
         g = torch.Generator(device=dev).manual_seed(seed)
         bf = torch.bfloat16
         cfg = LAYERS[workload]
         spec = cfg["layers"]
         has_bias = cfg.get("bias", True)
-        self.bucket = GradBucket({k: v for n, i, o, _ in spec
-                                  for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}, dev)
+        shapes = {k: v for n, i, o, _ in spec for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}
+        # N > 1: the span lives in peer-mapped memory and is summed by the library's own kernel
+        # over NVLink ("peer"), or stays private and goes through NCCL ("nccl")
+        self.exchange = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=comm_ctas,
+                                     multicast=(exchange == "nvls")) \
+            if world > 1 and exchange in ("peer", "nvls") else None
+        self.bucket = GradBucket(shapes, dev, storage=self.exchange.attach if self.exchange else None)
         self.layers, self.calls = [], []
         for n, i, o, gelu in spec:
             t = dict(name=n, gelu=gelu, i=i, o=o)
@@ -137,15 +142,26 @@ class LinearStep:
             dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0,
                              dbias=t["db"] if has_bias else None, dbias_beta=1.0)
             t["bwd"] = L.Group([(dx, t["dx"], t["dy"], t["w"]), (dw, t["dw"], t["dy"], t["x"])])
+            # N > 1: the layer whose backward runs last launches dW on its own, ahead of dX, so that
+            # the exchange of its gradients overlaps its dX instead of trailing the step
+            if world > 1 and split_last and t is self.layers[0]:
+                dx2 = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
+                dw2 = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0,
+                                  dbias=t["db"] if has_bias else None, dbias_beta=1.0)
+                t["bwd_dw"] = L.Group([(dw2, t["dw"], t["dy"], t["x"])])
+                t["bwd_dx"] = L.Group([(dx2, t["dx"], t["dy"], t["w"])])
         # one scratch buffer per problem that needs one (split-K partial sums)
         self.ws = []
         for t in self.layers:
             need = L.workspace_bytes(t["d_fwd"])
             buf = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
             t["d_fwd"].workspace, t["d_fwd"].workspace_bytes = buf.data_ptr(), buf.numel()
-            bufs = [torch.empty(max(b, 256), dtype=torch.uint8, device=dev) for b in t["bwd"].workspace_bytes()]
-            t["bwd"].set_workspaces(bufs)
-            self.ws += [buf] + bufs
+            self.ws.append(buf)
+            for key in ("bwd", "bwd_dw", "bwd_dx"):
+                if key in t:
+                    bufs = [torch.empty(max(b, 256), dtype=torch.uint8, device=dev) for b in t[key].workspace_bytes()]
+                    t[key].set_workspaces(bufs)
+                    self.ws += bufs
         self.comm_stream = torch.cuda.Stream(device=dev)
 
     def launches(self):
@@ -156,7 +172,11 @@ class LinearStep:
             out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), None))
         for t in reversed(self.layers):
             f = 4.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".bwd(dX+dW)", f, t["bwd"].run, t))
+            if "bwd_dw" in t:
+                out.append((t["name"] + ".bwd(dW)", f / 2, t["bwd_dw"].run, t))
+                out.append((t["name"] + ".bwd(dX)", f / 2, t["bwd_dx"].run, None))
+            else:
+                out.append((t["name"] + ".bwd(dX+dW)", f, t["bwd"].run, t))
         return out
 
     def grad_slice(self, t):
@@ -181,8 +201,12 @@ class LinearStep:
             if world > 1 and layer is not None:
                 ready = torch.cuda.Event(); ready.record()
                 self.comm_stream.wait_event(ready)
-                with torch.cuda.stream(self.comm_stream):
-                    torch.distributed.all_reduce(self.grad_slice(layer))
+                if self.exchange is not None:
+                    off, cnt = self.bucket.span_of([layer["name"] + ".dW", layer["name"] + ".dbias"])
+                    self.exchange.allreduce(off, cnt, stream=self.comm_stream)
+                else:
+                    with torch.cuda.stream(self.comm_stream):
+                        torch.distributed.all_reduce(self.grad_slice(layer))
         if world > 1:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
@@ -428,6 +452,20 @@ def main():
     ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4"], default="c2")
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["nvls", "peer", "nccl"], default="nvls",
+                    help="N > 1: how the gradient span is summed: the library's kernel through NVSwitch "
+                         "multicast (falls back to peer copies where no multicast mapping is offered), "
+                         "its peer-copy kernel, or NCCL")
+    ap.add_argument("--comm-ctas", type=int, default=None,
+                    help="N > 1: CTAs of the exchange kernel (default 16 for nvls, 8 for peer; "
+                         "with nccl: NCCL_MAX_CTAS, default unlimited)")
+    ap.add_argument("--comm-sms", type=int, default=None,
+                    help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 2 for nvls, "
+                         "--comm-ctas for peer, 0 for nccl)")
+    ap.add_argument("--split-last", action="store_true",
+                    help="N > 1: launch dW of the last backward on its own, ahead of dX")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="enqueue every launch from the host instead of replaying one captured step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -446,6 +484,18 @@ def main():
     if world > 1:
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if args.comm_ctas is None:
+            args.comm_ctas = {"nvls": 16, "peer": 8, "nccl": 0}[args.exchange]
+        if args.exchange != "nccl":
+            args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
+        elif args.comm_ctas > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_ctas))
+        if args.comm_sms is None:
+            args.comm_sms = {"nvls": 2, "peer": args.comm_ctas, "nccl": 0}[args.exchange]
+        if args.comm_sms > 0:
+            # The GEMM kernels are persistent and fill every SM they are given; the gradient
+            # exchange on the side stream only overlaps them if some SMs stay free for it.
+            L.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - args.comm_sms)
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -454,10 +504,28 @@ def main():
         torch.cuda.synchronize()
 
     attention = args.workload == "c4"
-    step = AttentionStep(dev, seed=rank) if attention else LinearStep(args.workload, M_PER_GPU, dev, seed=rank)
+    step = AttentionStep(dev, seed=rank) if attention else LinearStep(args.workload, M_PER_GPU, dev, seed=rank, world=world, exchange=args.exchange, comm_ctas=args.comm_ctas or 8, split_last=args.split_last)
     flops = 6 * step.flops_each if attention else step_flops(args.workload, M_PER_GPU)
     for _ in range(args.warmup):
         step.run(world)
+    barrier()
+    # One step (its GEMM launches and, for N > 1, the gradient all-reduces on the side stream)
+    # captured into a CUDA graph: the timed loop replays it, so the host enqueues one graph
+    # per step instead of a dozen launches.
+    graph, per_step_launches = None, None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            n0 = L.launch_count()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step.run(world)
+            per_step_launches = L.launch_count() - n0
+            for _ in range(args.warmup):
+                graph.replay()
+        except Exception as exc:  # capture refused: fall back to direct launches and say so
+            print(f"[bench] graph capture failed ({exc}); launching directly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -467,11 +535,14 @@ def main():
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step.run(world)
+        if graph is not None:
+            graph.replay()
+        else:
+            step.run(world)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
-    launches = L.launch_count() - launches0
+    launches = per_step_launches * args.steps if graph is not None else L.launch_count() - launches0
     # The same K steps again with an event pair around every launch: the per-launch device
     # times behind roofline.achieved (kept out of the loop above, where events between
     # kernels would defeat the overlap of one kernel's prologue with the previous one's tail).
@@ -542,6 +613,11 @@ def main():
             "config": {"workload": wl, "launches_per_step": launches_txt,
                        "per_gpu_gflop_per_step": round(flops / 1e9, 1),
                        "allreduce_bytes_per_step": ar_bytes,
+                       "exchange": (None if world == 1 else args.exchange if step.exchange is None else
+                                    "llmt_b200_grad_allreduce, " + ("NVSwitch multicast" if step.exchange.multicast
+                                                                    else "peer copies")),
+                       "comm_ctas": args.comm_ctas if world > 1 else 0,
+                       "comm_sms": args.comm_sms if world > 1 else 0,
                        "l2": "working set of a step larger than L2 (operands stream from HBM)"},
             "per_gpu_tflops": round(flops / ms / 1e9, 2),
             "pct_of_bf16_peak": round(100.0 * flops / ms / 1e9 / peak_tf, 1),
@@ -550,13 +626,26 @@ def main():
             "e2e": {"value": None if attention else round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
+            "cuda_graph": graph is not None,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline and not attention:
             line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line))
     if world > 1:
+        # The captured step holds NCCL work: release it before the communicator goes, and
+        # never let a stuck teardown outlive the measurement.
+        import threading
+        sys.stdout.flush()
+        guard = threading.Timer(60.0, os._exit, (0,))
+        guard.daemon = True
+        guard.start()
+        if graph is not None:
+            graph.reset()
+            del graph
+        torch.cuda.synchronize()
         torch.distributed.destroy_process_group()
+        guard.cancel()
     return 0
 
 

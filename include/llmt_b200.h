@@ -176,6 +176,62 @@ LLMT_B200_API int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp,
  * healthy.  Returns LLMT_B200_ERR_DEVICE when a code was pending. */
 LLMT_B200_API int llmt_b200_device_status(int32_t* code, int32_t* detail);
 
+/* SMs the persistent GEMM kernels may occupy from now on: 0 (the default) = every SM.
+ * Planning and grid size follow it.  A data-parallel caller lowers it by the number of
+ * CTAs its collective library runs (e.g. 148 - 8), so that the all-reduce of one layer's
+ * gradients, enqueued on a second stream, finds free SMs while the next layer's GEMM
+ * launch is resident.  Returns the previous value, or a negative value for sms < 0.
+ * llmt has no counterpart (single GPU: docs/TODO.md:12-16). */
+LLMT_B200_API int llmt_b200_set_sm_budget(int32_t sms);
+
+/* ---- gradient exchange of the data-parallel path ------------------------------------------
+ * Sum of a range of the flat fp32 gradient span over `world` ranks (one process per GPU),
+ * in place, over NVLink peer memory: one kernel of `ctas` CTAs that pushes every foreign
+ * shard to its owner, sums each shard once in rank order and copies the sum back to every
+ * rank.  All ranks end with the same bits; reruns reproduce them.  llmt is single-GPU; the
+ * span is the seam its ParamStore documents for this (include/llmt/model/param_store.h:131-135).
+ *
+ * The caller allocates three buffers on every rank and exchanges their addresses with
+ * whatever peer-mapping mechanism it has (CUDA IPC, VMM handles, a symmetric-memory
+ * allocator); [i] is rank i's buffer as THIS rank can address it, [rank] the local one:
+ *   grad  : the fp32 span itself
+ *   stage : world * slot_elems floats of scratch
+ *   flags : LLMT_B200_COMM_FLAG_BYTES, zeroed once before the first call
+ * and, private to the rank, `epoch`: LLMT_B200_COMM_EPOCH_BYTES, zeroed once.
+ * offset and count are in floats, multiples of 4; ceil(count / 4 / world) * 4 <= slot_elems.
+ * Every rank must make the same sequence of calls with the same ctas; one call at a time
+ * per communicator (enqueue them on one stream).  A peer that never arrives ends the wait
+ * after a few seconds with LLMT_B200_DEV_WAIT_PEER in the device status word, not a hang.
+ * Run it beside the GEMM kernels by lowering their SM budget by `ctas`. */
+#define LLMT_B200_COMM_MAX_RANKS 8
+#define LLMT_B200_COMM_MAX_CTAS 64
+#define LLMT_B200_COMM_FLAG_BYTES (2 * LLMT_B200_COMM_MAX_RANKS * LLMT_B200_COMM_MAX_CTAS * 4)
+#define LLMT_B200_COMM_EPOCH_BYTES (LLMT_B200_COMM_MAX_CTAS * 4)
+#define LLMT_B200_DEV_WAIT_PEER 6
+
+typedef struct llmt_b200_comm_desc {
+    int32_t rank, world;
+    void* grad[LLMT_B200_COMM_MAX_RANKS];
+    void* stage[LLMT_B200_COMM_MAX_RANKS];
+    void* flags[LLMT_B200_COMM_MAX_RANKS];
+    void* epoch;
+    int64_t slot_elems;
+    void* grad_mc;   /* the span through an NVSwitch multicast mapping that covers every rank's
+                        copy, or NULL.  When set, the sum is formed inside the switch
+                        (multimem.ld_reduce) and broadcast by it (multimem.st): each rank moves
+                        1/world of the range instead of world-1 shards, `stage` is not touched,
+                        and the order of the additions is the switch's, not rank order. */
+} llmt_b200_comm_desc;
+
+LLMT_B200_API int llmt_b200_grad_allreduce(const llmt_b200_comm_desc* comm, int64_t offset, int64_t count,
+                             int32_t ctas, void* stream);
+
+/* The same exchange with all `world` ranks living on ONE device (comms[r] is rank r's
+ * descriptor, every pointer local): a single cooperative launch of world * ctas CTAs.
+ * For tests of the algorithm where fewer GPUs than ranks are at hand. */
+LLMT_B200_API int llmt_b200_grad_allreduce_emulated(const llmt_b200_comm_desc* comms, int32_t world, int64_t offset,
+                                      int64_t count, int32_t ctas, void* stream);
+
 /* Number of kernels this library has launched from this process so far. */
 LLMT_B200_API uint64_t llmt_b200_launch_count(void);
 

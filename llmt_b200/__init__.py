@@ -24,7 +24,21 @@ EXPORTS = [
     "llmt_b200_gemm_static_scratch", "llmt_b200_gemm_workspace_bytes", "llmt_b200_gemm_plan",
     "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
+    "llmt_b200_set_sm_budget", "llmt_b200_grad_allreduce", "llmt_b200_grad_allreduce_emulated",
 ]
+
+COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 64
+COMM_FLAG_BYTES = 2 * COMM_MAX_RANKS * COMM_MAX_CTAS * 4
+COMM_EPOCH_BYTES = COMM_MAX_CTAS * 4
+DEV_WAIT_PEER = 6
+
+
+class CommDesc(ctypes.Structure):
+    """llmt_b200_comm_desc of include/llmt_b200.h."""
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32),
+                ("grad", ctypes.c_void_p * COMM_MAX_RANKS), ("stage", ctypes.c_void_p * COMM_MAX_RANKS),
+                ("flags", ctypes.c_void_p * COMM_MAX_RANKS), ("epoch", ctypes.c_void_p),
+                ("slot_elems", ctypes.c_int64), ("grad_mc", ctypes.c_void_p)]
 
 
 class GemmDesc(ctypes.Structure):
@@ -90,6 +104,14 @@ def lib() -> ctypes.CDLL:
                                               ctypes.POINTER(ctypes.c_int32)]
         L.llmt_b200_device_status.restype = ctypes.c_int
         L.llmt_b200_launch_count.restype = ctypes.c_uint64
+        L.llmt_b200_grad_allreduce.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_grad_allreduce.restype = ctypes.c_int
+        L.llmt_b200_grad_allreduce_emulated.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_int32, ctypes.c_int64,
+                                                        ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_grad_allreduce_emulated.restype = ctypes.c_int
+        L.llmt_b200_set_sm_budget.argtypes = [ctypes.c_int32]
+        L.llmt_b200_set_sm_budget.restype = ctypes.c_int
         L.llmt_b200_last_error.restype = ctypes.c_char_p
         L.llmt_b200_abi_version.restype = ctypes.c_int
         _lib = L
@@ -103,6 +125,12 @@ def last_error() -> str:
 def _check(status: int) -> None:
     if status != OK:
         raise LlmtB200Error(status, last_error())
+
+
+def _stream(stream):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
 
 
 def _dtype_code(t) -> int:
@@ -270,6 +298,23 @@ def device_status():
     if st != OK:
         raise LlmtB200Error(st, last_error())
     return code.value, detail.value
+
+
+def grad_allreduce(desc: "CommDesc", offset: int, count: int, ctas: int = 8, stream=None) -> None:
+    """Sums floats [offset, offset + count) of the span over the ranks of `desc`, in place."""
+    _check(lib().llmt_b200_grad_allreduce(ctypes.byref(desc), int(offset), int(count), int(ctas), _stream(stream)))
+
+
+def grad_allreduce_emulated(descs, offset: int, count: int, ctas: int = 4, stream=None) -> None:
+    """All ranks of the exchange on one device, one cooperative launch (tests)."""
+    arr = (CommDesc * len(descs))(*descs)
+    _check(lib().llmt_b200_grad_allreduce_emulated(arr, len(descs), int(offset), int(count), int(ctas),
+                                                   _stream(stream)))
+
+
+def set_sm_budget(sms: int) -> int:
+    """SMs the persistent GEMM kernels may occupy (0 = all); returns the previous value."""
+    return int(lib().llmt_b200_set_sm_budget(int(sms)))
 
 
 def launch_count() -> int:

@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(HERE, "_build")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libllmt_b200.so")
 
-SOURCES = ["capi.cu", "gemm_grouped_sm100.cu", "gemm_fp32_simt.cu"]
+SOURCES = ["capi.cu", "gemm_grouped_sm100.cu", "gemm_fp32_simt.cu", "grad_allreduce_sm100.cu"]
 HEADERS = ["common.h", "ptx_sm100.cuh", os.path.join("..", "..", "include", "llmt_b200.h")]
 
 NVCC_FLAGS = [

@@ -72,6 +72,11 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// SMs the persistent kernels may occupy: 0 = all of them.  A data-parallel caller lowers it
+// by the number of CTAs its collective library runs, so that a gradient all-reduce on a
+// second stream finds free SMs while a GEMM launch is resident.
+int g_sm_budget = 0;
+
 int sm_count() {
     static int cached = 0;
     if (cached == 0) {
@@ -82,7 +87,7 @@ int sm_count() {
         else
             return 148;  // B200; used only for planning queries made without a device
     }
-    return cached;
+    return g_sm_budget > 0 && g_sm_budget < cached ? g_sm_budget : cached;
 }
 
 // Cost of one 64-deep k-block of a 128 x bn tile in SM cycles: tensor time is 2*bn
@@ -809,6 +814,91 @@ int llmt_b200_device_status(int32_t* code, int32_t* detail) {
                     h.code, h.detail, h.block);
     }
     return LLMT_B200_OK;
+}
+
+namespace {
+int fill_comm(llmt_b200::CommRank* c, const llmt_b200_comm_desc* d, int64_t offset, int64_t count) {
+    using namespace llmt_b200;
+    if (d == nullptr) return fail(LLMT_B200_ERR_INVALID, "allreduce: null communicator");
+    if (d->world < 1 || d->world > kMaxCommRanks || d->rank < 0 || d->rank >= d->world)
+        return fail(LLMT_B200_ERR_INVALID, "allreduce: rank %d / world %d out of range (1..%d ranks)", d->rank,
+                    d->world, kMaxCommRanks);
+    if (offset < 0 || count < 0 || offset % 4 != 0 || count % 4 != 0)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "allreduce: offset and count must be non-negative multiples of 4 floats");
+    const int64_t shard = (count / 4 + d->world - 1) / d->world * 4;
+    if (d->slot_elems % 4 != 0 || shard > d->slot_elems)
+        return fail(LLMT_B200_ERR_WORKSPACE, "allreduce: staging slot of %lld floats too small (need %lld)",
+                    static_cast<long long>(d->slot_elems), static_cast<long long>(shard));
+    if (d->epoch == nullptr) return fail(LLMT_B200_ERR_INVALID, "allreduce: null epoch buffer");
+    for (int r = 0; r < d->world; ++r) {
+        if (d->grad[r] == nullptr || d->stage[r] == nullptr || d->flags[r] == nullptr)
+            return fail(LLMT_B200_ERR_INVALID, "allreduce: null buffer for rank %d", r);
+        if ((reinterpret_cast<uintptr_t>(d->grad[r]) | reinterpret_cast<uintptr_t>(d->stage[r])) % 16 != 0)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "allreduce: buffers of rank %d not 16-byte aligned", r);
+        c->grad[r] = static_cast<float*>(d->grad[r]);
+        c->stage[r] = static_cast<float*>(d->stage[r]);
+        c->flags[r] = static_cast<uint32_t*>(d->flags[r]);
+    }
+    if (reinterpret_cast<uintptr_t>(d->grad_mc) % 16 != 0)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "allreduce: multicast address not 16-byte aligned");
+    c->grad_mc = static_cast<float*>(d->grad_mc);
+    c->epoch = static_cast<uint32_t*>(d->epoch);
+    c->status = device_status_ptr();
+    if (c->status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
+    c->slot_elems = d->slot_elems;
+    c->rank = d->rank;
+    c->world = d->world;
+    return LLMT_B200_OK;
+}
+}  // namespace
+
+int llmt_b200_grad_allreduce(const llmt_b200_comm_desc* comm, int64_t offset, int64_t count, int32_t ctas,
+                             void* stream) {
+    using namespace llmt_b200;
+    if (ctas < 1 || ctas > kMaxCommCtas)
+        return fail(LLMT_B200_ERR_INVALID, "allreduce: ctas must be 1..%d", kMaxCommCtas);
+    static AllreduceParams p;  // one host thread issues launches
+    int st = fill_comm(&p.ctx[0], comm, offset, count);
+    if (st != LLMT_B200_OK) return st;
+    if (comm->world == 1 || count == 0) return LLMT_B200_OK;
+    p.offset = offset;
+    p.count = count;
+    cudaError_t e = comm->grad_mc != nullptr ? launch_grad_allreduce_mc(p, ctas, static_cast<cudaStream_t>(stream))
+                                             : launch_grad_allreduce(p, ctas, 0, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_grad_allreduce_emulated(const llmt_b200_comm_desc* comms, int32_t world, int64_t offset,
+                                      int64_t count, int32_t ctas, void* stream) {
+    using namespace llmt_b200;
+    if (comms == nullptr || world < 1 || world > kMaxCommRanks)
+        return fail(LLMT_B200_ERR_INVALID, "allreduce: world must be 1..%d", kMaxCommRanks);
+    if (ctas < 1 || ctas > kMaxCommCtas)
+        return fail(LLMT_B200_ERR_INVALID, "allreduce: ctas must be 1..%d", kMaxCommCtas);
+    static AllreduceParams p;
+    for (int r = 0; r < world; ++r) {
+        if (comms[r].world != world || comms[r].rank != r)
+            return fail(LLMT_B200_ERR_INVALID, "allreduce: descriptor %d is not rank %d of %d", r, r, world);
+        int st = fill_comm(&p.ctx[r], &comms[r], offset, count);
+        if (st != LLMT_B200_OK) return st;
+    }
+    if (world == 1 || count == 0) return LLMT_B200_OK;
+    p.offset = offset;
+    p.count = count;
+    cudaError_t e = launch_grad_allreduce(p, ctas, world, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_set_sm_budget(int32_t sms) {
+    if (sms < 0) {
+        fail(LLMT_B200_ERR_INVALID, "sm budget: must be >= 0 (0 = every SM)");
+        return -1;
+    }
+    const int prev = g_sm_budget;
+    g_sm_budget = sms;
+    return prev;
 }
 
 uint64_t llmt_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

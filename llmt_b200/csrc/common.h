@@ -22,7 +22,8 @@ enum DeviceErr : int32_t {
     kDevWaitSmemFull = 2,    // MMA issuer gave up waiting for operand bytes to land
     kDevWaitTmemEmpty = 3,   // MMA issuer gave up waiting for the epilogue to drain an accumulator
     kDevWaitTmemFull = 4,    // epilogue gave up waiting for an accumulator to complete
-    kDevWaitSched = 5        // a role gave up waiting on the tile scheduler ring
+    kDevWaitSched = 5,       // a role gave up waiting on the tile scheduler ring
+    kDevWaitPeer = 6         // the gradient all-reduce gave up waiting for a peer rank's flag
 };
 
 constexpr int kEpiBias = 1;
@@ -65,6 +66,32 @@ struct GroupParams {
     int32_t* sched_counter;     // zero between launches; the kernel re-arms it
     DeviceStatus* status;
 };
+
+// ---- gradient all-reduce over peer memory -------------------------------------------------
+constexpr int kMaxCommRanks = 8;
+constexpr int kMaxCommCtas = 64;
+constexpr int kCommThreads = 256;
+
+// One rank's view of the exchange: the same three buffers on every rank, as pointers this
+// rank can dereference ([rank] = its own copy), plus its private call counters.
+struct CommRank {
+    float* grad[kMaxCommRanks];      // flat fp32 gradient span
+    float* grad_mc;                  // the span through an NVSwitch multicast mapping, or null
+    float* stage[kMaxCommRanks];     // staging area: `world` slots of slot_elems floats
+    uint32_t* flags[kMaxCommRanks];  // [2 phases][kMaxCommRanks writers][kMaxCommCtas] call counters
+    uint32_t* epoch;                 // [kMaxCommCtas] calls completed by each CTA of this rank
+    DeviceStatus* status;
+    int64_t slot_elems;
+    int32_t rank, world;
+};
+
+struct AllreduceParams {
+    CommRank ctx[kMaxCommRanks];     // [0] on a real rank; one per rank when emulated on one device
+    int64_t offset, count;           // range of the span, in floats (multiples of 4)
+};
+
+cudaError_t launch_grad_allreduce(const AllreduceParams& p, int ctas, int emulated_ranks, cudaStream_t stream);
+cudaError_t launch_grad_allreduce_mc(const AllreduceParams& p, int ctas, cudaStream_t stream);
 
 // Plan of one problem: the pure function of the problem (and of the work it shares a
 // launch with) that fixes tile width and split count.

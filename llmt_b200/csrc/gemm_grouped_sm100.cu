@@ -83,13 +83,18 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
                                              DeviceStatus* st, int code, int detail) {
     auto poll = [&]() { return mbar_try_wait(bar, parity); };
     if (poll()) return true;
-    const uint64_t t0 = globaltimer_ns();
+    // The wall clock is slow to read: it is first looked at after 256 failed polls, so a wait
+    // of ordinary length never touches it.
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     for (;;) {
         if (poll()) return true;
-        if ((++spins & 63u) == 0u) {
+        if ((++spins & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
                 if (atomicCAS(&st->code, 0, code) == 0) {
                     st->detail = detail;
                     st->block = static_cast<int32_t>(blockIdx.x);

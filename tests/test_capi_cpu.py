@@ -131,3 +131,62 @@ def test_softmax_contract():
     assert lib.llmt_b200_softmax_fwd(None, ctypes.c_void_p(A), 8, 4, 4, 0, 1, None) == L.ERR_INVALID
     assert lib.llmt_b200_softmax_fwd(ctypes.c_void_p(A), ctypes.c_void_p(A), 8, 4, 4, 2, 0, None) \
         == L.ERR_UNSUPPORTED
+
+
+# ---- gradient exchange: host-side contract (no launch happens on these paths) --------------
+
+def _comm(world=2, rank=0, slot=64):
+    d = L.CommDesc()
+    d.rank, d.world, d.slot_elems = rank, world, slot
+    for r in range(min(world, L.COMM_MAX_RANKS)):
+        d.grad[r], d.stage[r], d.flags[r] = 0x100000 * (r + 1), 0x100000 * (r + 1) + 0x40000, 0x100000 * (r + 1) + 0x80000
+    d.epoch = 0x900000
+    return d
+
+
+def test_comm_descriptor_layout_matches_the_header():
+    assert ctypes.sizeof(L.CommDesc) == 2 * 4 + 3 * 8 * 8 + 8 + 8 + 8
+    text = open(HEADER).read()
+    assert f"#define LLMT_B200_COMM_MAX_RANKS {L.COMM_MAX_RANKS}" in text
+    assert f"#define LLMT_B200_COMM_MAX_CTAS {L.COMM_MAX_CTAS}" in text
+    assert f"#define LLMT_B200_DEV_WAIT_PEER {L.DEV_WAIT_PEER}" in text
+
+
+def test_allreduce_rejects_contract_violations():
+    f = L.lib().llmt_b200_grad_allreduce
+    assert f(None, 0, 8, 4, None) == L.ERR_INVALID
+    assert f(ctypes.byref(_comm(world=9)), 0, 8, 4, None) == L.ERR_INVALID
+    assert f(ctypes.byref(_comm(rank=2)), 0, 8, 4, None) == L.ERR_INVALID
+    assert f(ctypes.byref(_comm()), 0, 8, 0, None) == L.ERR_INVALID
+    assert f(ctypes.byref(_comm()), 0, 8, L.COMM_MAX_CTAS + 1, None) == L.ERR_INVALID
+    assert f(ctypes.byref(_comm()), 2, 8, 4, None) == L.ERR_UNSUPPORTED
+    assert f(ctypes.byref(_comm()), 0, 10, 4, None) == L.ERR_UNSUPPORTED
+    assert f(ctypes.byref(_comm(slot=64)), 0, 4096, 4, None) == L.ERR_WORKSPACE
+    assert "staging slot" in L.last_error()
+    d = _comm()
+    d.stage[1] = None
+    assert f(ctypes.byref(d), 0, 8, 4, None) == L.ERR_INVALID
+    d = _comm()
+    d.grad[0] = 0x100004
+    assert f(ctypes.byref(d), 0, 8, 4, None) == L.ERR_UNSUPPORTED
+
+
+def test_sm_budget_round_trips():
+    lib = L.lib()
+    prev = lib.llmt_b200_set_sm_budget(140)
+    assert lib.llmt_b200_set_sm_budget(prev) == 140
+    assert lib.llmt_b200_set_sm_budget(-1) < 0 and "sm budget" in L.last_error()
+    assert lib.llmt_b200_set_sm_budget(prev) == prev
+
+
+def test_exchange_layout_is_aligned_and_large_enough():
+    from llmt_b200.dp import exchange_layout
+    for numel in (4, 64, 7080960, 4 * 1237):
+        for world in (1, 2, 3, 8):
+            lay = exchange_layout(numel, world)
+            assert lay["slot_elems"] % 64 == 0 and lay["slot_elems"] * world >= numel
+            assert lay["stage_off"] % 256 == 0 and lay["flags_off"] % 256 == 0
+            assert lay["stage_off"] >= numel * 4
+            assert lay["total"] == lay["flags_off"] + L.COMM_FLAG_BYTES
+    with pytest.raises(ValueError):
+        exchange_layout(6, 2)

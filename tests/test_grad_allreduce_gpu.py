@@ -1,0 +1,166 @@
+"""The gradient all-reduce kernel (llmt_b200_grad_allreduce): every rank's partial sums of the
+flat fp32 span are added in rank order and all ranks end with the same bits.
+
+On one GPU the ranks are emulated inside one cooperative launch (every pointer local); with
+two or more GPUs the real path runs as one process per GPU over peer-mapped memory."""
+import os
+import socket
+
+import pytest
+import torch
+
+import llmt_b200 as L
+from llmt_b200.dp import exchange_layout
+
+pytestmark = pytest.mark.gpu
+
+
+def _emulated(world, numel, dev):
+    lay = exchange_layout(numel, world)
+    bufs = [torch.zeros(lay["total"], dtype=torch.uint8, device=dev) for _ in range(world)]
+    epochs = [torch.zeros(L.COMM_EPOCH_BYTES // 4, dtype=torch.int32, device=dev) for _ in range(world)]
+    descs = []
+    for r in range(world):
+        d = L.CommDesc()
+        d.rank, d.world, d.slot_elems = r, world, lay["slot_elems"]
+        for p in range(world):
+            d.grad[p] = bufs[p].data_ptr() + lay["grad_off"]
+            d.stage[p] = bufs[p].data_ptr() + lay["stage_off"]
+            d.flags[p] = bufs[p].data_ptr() + lay["flags_off"]
+        d.epoch = epochs[r].data_ptr()
+        descs.append(d)
+    spans = [b[:numel * 4].view(torch.float32) for b in bufs]
+    return descs, spans, (bufs, epochs)
+
+
+def _rank_order_sum(parts):
+    acc = parts[0].clone()
+    for p in parts[1:]:
+        acc += p
+    return acc
+
+
+@pytest.mark.parametrize("world,ctas,numel,offset,count", [
+    (2, 1, 4096, 0, 4096),
+    (2, 4, 1 << 20, 64, (1 << 20) - 128),
+    (3, 4, 40000, 128, 4 * 1237),     # shards that do not divide evenly; the last one short
+    (8, 4, 1 << 20, 0, 1 << 20),
+    (8, 3, 4096, 0, 36),              # fewer float4s than ranks * ctas: empty shards and slices
+    (5, 2, 7 * 64, 64, 64),
+])
+def test_emulated_ranks_sum_in_rank_order(world, ctas, numel, offset, count):
+    dev = torch.device("cuda", 0)
+    descs, spans, keep = _emulated(world, numel, dev)
+    g = torch.Generator(device=dev).manual_seed(world * 1000 + ctas)
+    for call in range(3):  # call counters advance: the same buffers serve call after call
+        parts = [torch.randn(numel, device=dev, generator=g) * (1.0 + r) for r in range(world)]
+        for s, p in zip(spans, parts):
+            s.copy_(p)
+        L.grad_allreduce_emulated(descs, offset, count, ctas)
+        L.device_status()
+        want = _rank_order_sum([p[offset:offset + count] for p in parts])
+        for r in range(world):
+            assert torch.equal(spans[r][offset:offset + count], want), (call, r)
+            # outside the range every rank keeps its own values
+            assert torch.equal(spans[r][:offset], parts[r][:offset])
+            assert torch.equal(spans[r][offset + count:], parts[r][offset + count:])
+
+
+def test_single_rank_and_empty_range_launch_nothing():
+    dev = torch.device("cuda", 0)
+    descs, spans, keep = _emulated(1, 256, dev)
+    spans[0].fill_(3.0)
+    n0 = L.launch_count()
+    L.grad_allreduce(descs[0], 0, 256, 4)
+    descs2, spans2, keep2 = _emulated(2, 256, dev)
+    L.grad_allreduce_emulated(descs2, 0, 0, 4)
+    assert L.launch_count() == n0
+    assert float(spans[0].sum()) == 3.0 * 256
+
+
+def test_rejects_bad_arguments():
+    dev = torch.device("cuda", 0)
+    descs, spans, keep = _emulated(2, 256, dev)
+    for off, cnt, ctas, status in [(2, 8, 4, L.ERR_UNSUPPORTED), (0, 6, 4, L.ERR_UNSUPPORTED),
+                                   (0, 8, 0, L.ERR_INVALID), (0, 8, L.COMM_MAX_CTAS + 1, L.ERR_INVALID),
+                                   (0, 100000, 4, L.ERR_WORKSPACE)]:
+        with pytest.raises(L.LlmtB200Error) as ei:
+            L.grad_allreduce_emulated(descs, off, cnt, ctas)
+        assert ei.value.status == status, (off, cnt, ctas)
+    descs[1].rank = 0
+    with pytest.raises(L.LlmtB200Error):
+        L.grad_allreduce_emulated(descs, 0, 8, 4)
+
+
+# ---- the real path: one process per GPU --------------------------------------------------
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _peer_worker(rank, world, port, out_dir, multicast=False):
+    import torch.distributed as dist
+    from llmt_b200.dp import GradBucket, PeerExchange
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    msg = "ok"
+    try:
+        shapes = {"a.dW": (768, 2304), "a.dbias": (2304,), "b.dW": (100, 52), "b.dbias": (100,)}
+        ex = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=4, multicast=multicast)
+        if multicast and not ex.multicast:
+            msg = "no multicast"
+        bucket = GradBucket(shapes, dev, storage=ex.attach)
+        g = torch.Generator(device=dev).manual_seed(7)  # same stream of numbers on every rank
+        for call in range(3):
+            parts = [torch.randn(bucket.flat.numel(), device=dev, generator=g) * (1.0 + r) for r in range(world)]
+            bucket.flat.copy_(parts[rank])
+            dist.barrier()
+            off, cnt = bucket.span_of(["a.dW", "a.dbias"])
+            ex.allreduce(off, cnt)
+            off2, cnt2 = bucket.span_of(["b.dW", "b.dbias"])
+            ex.allreduce(off2, cnt2)
+            L.device_status()
+            want = _rank_order_sum(parts)
+            same = torch.equal(bucket.flat, want) if world == 2 or not ex.multicast else \
+                torch.allclose(bucket.flat, want, rtol=1e-6, atol=1e-6)  # the switch's order of additions
+            if not same:
+                msg = f"call {call}: mismatch, max abs err {float((bucket.flat - want).abs().max())}"
+                break
+        gathered = [torch.empty_like(bucket.flat) for _ in range(world)]
+        dist.all_gather(gathered, bucket.flat)
+        if not all(torch.equal(gathered[0], t) for t in gathered):
+            msg = "ranks disagree"
+        dist.barrier()
+    except Exception as exc:  # noqa: BLE001 - report instead of hanging the parent
+        msg = f"exception: {exc!r}"
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(msg)
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_over_peer_memory(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"rank{r}.txt").read_text() == "ok"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_through_switch_multicast(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path), True), nprocs=world, join=True)
+    texts = [(tmp_path / f"rank{r}.txt").read_text() for r in range(world)]
+    if all(t == "no multicast" for t in texts):
+        pytest.skip("the allocator offers no multicast mapping on this machine")
+    assert texts == ["ok"] * world
