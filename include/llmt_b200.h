@@ -65,6 +65,10 @@ enum llmt_b200_status {
  *   op(A) is [m,k]: A is stored [m,k] (trans_a = 0) or [k,m] (trans_a = 1).
  *   op(B) is [k,n]: B is stored [k,n] (trans_b = 0) or [n,k] (trans_b = 1).
  *   lda/ldb/ldc  row pitch in elements of each row-major buffer (>= its column count).
+ *                Any pitch and any element-aligned base work.  bf16 operands whose base is
+ *                16-byte aligned and whose pitch and batch stride are multiples of 8 elements
+ *                are read in place; others are first copied to such a pitch inside the
+ *                workspace (one extra pass over that operand).
  *   stride_*     elements between consecutive batch items; ignored when batch == 1.
  *   dtype_ab     element type of A and B; dtype_c of C.  Supported pairs:
  *                (fp32, fp32) strict fp32 FMA path; (bf16, bf16) and (bf16, fp32)
@@ -76,9 +80,10 @@ enum llmt_b200_status {
  *   plan_*       tuning overrides of the tile width, split-K factor and CTA pairing; 0 leaves the
  *                choice to the library (the default plan is a pure function of the
  *                problem, so results stay reproducible either way).
- *   workspace    device scratch for split-K partial sums; llmt_b200_gemm_workspace_bytes()
- *                gives the size this problem needs (0 for most problems).  Plays the role
- *                of RunCtx::blas_workspace (include/llmt/core/run_ctx.h:35-36).
+ *   workspace    device scratch for split-K partial sums and repacked operands;
+ *                llmt_b200_gemm_workspace_bytes() gives the size this problem needs (0 for
+ *                most problems).  Plays the role of RunCtx::blas_workspace
+ *                (include/llmt/core/run_ctx.h:35-36).
  */
 typedef struct llmt_b200_gemm_desc {
     int64_t m, n, k, batch;
