@@ -599,8 +599,13 @@ def main():
             nl = len(cfg["layers"])
             launches_txt = (f"{nl} forward GEMMs + {nl} grouped backward launches (dX and dW+dbias of a layer "
                             "in one kernel) + split-K reductions")
+            # DRAM bytes of one step's launches (dram__bytes_read.sum + dram__bytes_write.sum over the
+            # 8 GEMM launches + 1 split-K reduction, one ncu capture of this workload at the default
+            # settings; writes of a replayed launch partly stay in L2): 380.1 MB + 25.4 MB against
+            # 343.6 MB of algorithmic operand reads.
+            traffic = 405.5e6 if args.workload == "c2" and world == 1 else None
             roof = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": None,
+                    "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": traffic,
                     "peak_source": f"of {which}",
                     "kernel": "tc_grouped_kernel (all GEMM launches of the step; per-launch device time "
                               "from a second, instrumented pass over the same steps)"}

@@ -28,6 +28,8 @@
 // why in the DeviceStatus word and makes the CTA drain and exit.
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 #include "common.h"
 #include "ptx_sm100.cuh"
 
@@ -426,26 +428,33 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 const uint32_t idesc_dbias = make_idesc_bf16(kTileRows, kDbiasCols, p.a_mn, 0);
                 const uint64_t ones_desc = (static_cast<uint64_t>(kDescHi) << 32) |
                                            static_cast<uint64_t>((ones_base >> 4) | (1u << 16));
-                for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
-                                             kDevWaitSmemFull, stage);
-                    if (!ok) break;
-                    tc_fence_after_thread_sync();
-                    const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
-                    const uint32_t a_lo = a_lo_base + stage_off;
-                    const uint32_t b_lo = b_lo_base + stage_off;
+                // The k loop exists twice: the ordinary tile must not carry the fused-dbias MMA even
+                // as a not-taken branch (in pair form that alone costs a fifth of the MMA rate).
+                auto k_loop = [&](auto with_dbias) {
+                    for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+                        ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
+                                                 kDevWaitSmemFull, stage);
+                        if (!ok) break;
+                        tc_fence_after_thread_sync();
+                        const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
+                        const uint32_t a_lo = a_lo_base + stage_off;
+                        const uint32_t b_lo = b_lo_base + stage_off;
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t da = (static_cast<uint64_t>(kDescHi) << 32) |
-                                            static_cast<uint64_t>(a_lo + kk * step_a);
-                        const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
-                                            static_cast<uint64_t>(b_lo + kk * step_b);
-                        umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
-                        if (dbias2) umma_bf16_cg<CG>(d_dbias, da, ones_desc, idesc_dbias, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            const uint64_t da = (static_cast<uint64_t>(kDescHi) << 32) |
+                                                static_cast<uint64_t>(a_lo + kk * step_a);
+                            const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
+                                                static_cast<uint64_t>(b_lo + kk * step_b);
+                            umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                            if constexpr (decltype(with_dbias)::value)
+                                umma_bf16_cg<CG>(d_dbias, da, ones_desc, idesc_dbias, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                        }
+                        umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
-                    umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
+                };
+                if (dbias2) k_loop(std::true_type{});
+                else k_loop(std::false_type{});
                 if (!ok) break;
                 umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc]));
                 ++acc_seq;
