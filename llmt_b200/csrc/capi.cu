@@ -198,16 +198,17 @@ TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbia
     return pl;
 }
 
-// CTA pairs (cta_group::2, 256-row tiles) halve the B bytes each SM stages per flop.  They
-// win when the operands are resident in L2 (the same GEMM called back to back: +5..10 %)
-// and lose 10..20 % when operands stream from HBM, which is the regime of a training step
-// whose working set exceeds L2 - so the default is single CTAs, and pairs are chosen per
-// call with plan_cta_pairs = 2, or for every eligible call with LLMT_B200_PAIRS=1.
+// CTA pairs (cta_group::2, 256-row tiles) halve the B bytes each SM stages per flop: a single
+// CTA's 128x256 tile is bound by the rate at which one SM pulls operands out of L2 (48 KB per
+// k-block), a pair's is not (32 KB).  Measured +4..10 % on products without a fused dbias,
+// with operands in L2 or streaming from HBM alike, so pairs are the default for those;
+// LLMT_B200_PAIRS=0 keeps every launch on single CTAs (for comparisons), plan_cta_pairs
+// chooses per call.
 bool pairs_enabled() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("LLMT_B200_PAIRS");
-        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     return v == 1;
 }

@@ -107,8 +107,10 @@ def test_plan_is_a_pure_function_of_the_problem():
     # (role of llmt's AlgoCache, include/llmt/kernels/algo_cache.h:18-42)
     d = _desc(m=8192, n=2304, k=768, lda=768, ldb=768, ldc=2304)
     p1, p2 = L.plan(d), L.plan(d)
-    assert p1 == p2 and "tcgen05 1-cta tile=128x256x64" in p1
-    d.plan_cta_pairs = 2  # CTA pairs on request: 256-row tiles
+    assert p1 == p2 and "tcgen05 cta-pair tile=256x256x64" in p1  # pairs by default (no fused dbias)
+    d.plan_cta_pairs = 1  # single CTAs on request: 128-row tiles
+    assert "1-cta tile=128x256x64" in L.plan(d)
+    d.plan_cta_pairs = 2
     assert "cta-pair tile=256x256x64" in L.plan(d)
     d.plan_cta_pairs = 0
     assert L.workspace_bytes(d) == 0
