@@ -119,9 +119,21 @@ class LinearStep:
         shapes = {k: v for n, i, o, _ in spec for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}
         # N > 1: the span lives in peer-mapped memory and is summed by the library's own kernel
         # over NVLink ("peer"), or stays private and goes through NCCL ("nccl")
-        self.exchange = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=comm_ctas,
-                                     multicast=(exchange == "nvls")) \
-            if world > 1 and exchange in ("peer", "nvls") else None
+        self.exchange = None
+        if world > 1 and exchange in ("peer", "nvls"):
+            try:
+                self.exchange = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=comm_ctas,
+                                             multicast=(exchange == "nvls"))
+            except Exception as exc:  # no peer mapping on this machine: every rank falls back to NCCL
+                print(f"[bench] peer-mapped span unavailable ({exc}); using NCCL", file=sys.stderr)
+            ok = torch.tensor([1 if self.exchange is not None else 0], device=dev)
+            torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                self.exchange = None
+            elif exchange == "nvls" and not self.exchange.multicast:
+                # no multicast mapping offered: the peer-copy kernel needs SMs of its own
+                self.exchange.ctas = 16
+                L.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - 16)
         self.bucket = GradBucket(shapes, dev, storage=self.exchange.attach if self.exchange else None)
         self.layers, self.calls = [], []
         for n, i, o, gelu in spec:
@@ -457,10 +469,10 @@ def main():
                          "multicast (falls back to peer copies where no multicast mapping is offered), "
                          "its peer-copy kernel, or NCCL")
     ap.add_argument("--comm-ctas", type=int, default=None,
-                    help="N > 1: CTAs of the exchange kernel (default 16 for nvls, 8 for peer; "
+                    help="N > 1: CTAs of the exchange kernel (default 32 for nvls, 16 for peer; "
                          "with nccl: NCCL_MAX_CTAS, default unlimited)")
     ap.add_argument("--comm-sms", type=int, default=None,
-                    help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 2 for nvls, "
+                    help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 0 for nvls, "
                          "--comm-ctas for peer, 0 for nccl)")
     ap.add_argument("--split-last", action="store_true",
                     help="N > 1: launch dW of the last backward on its own, ahead of dX")
@@ -485,13 +497,14 @@ def main():
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.comm_ctas is None:
-            args.comm_ctas = {"nvls": 16, "peer": 8, "nccl": 0}[args.exchange]
+            args.comm_ctas = {"nvls": 32, "peer": 16, "nccl": 0}[args.exchange]
         if args.exchange != "nccl":
             args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
         elif args.comm_ctas > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_ctas))
         if args.comm_sms is None:
-            args.comm_sms = {"nvls": 2, "peer": args.comm_ctas, "nccl": 0}[args.exchange]
+            # the multicast kernel's CTAs (no shared memory, 50 registers) fit beside a GEMM CTA
+            args.comm_sms = {"nvls": 0, "peer": args.comm_ctas, "nccl": 0}[args.exchange]
         if args.comm_sms > 0:
             # The GEMM kernels are persistent and fill every SM they are given; the gradient
             # exchange on the side stream only overlaps them if some SMs stay free for it.
@@ -618,7 +631,7 @@ def main():
             "config": {"workload": wl, "launches_per_step": launches_txt,
                        "per_gpu_gflop_per_step": round(flops / 1e9, 1),
                        "allreduce_bytes_per_step": ar_bytes,
-                       "exchange": (None if world == 1 else args.exchange if step.exchange is None else
+                       "exchange": (None if world == 1 else "nccl" if step.exchange is None else
                                     "llmt_b200_grad_allreduce, " + ("NVSwitch multicast" if step.exchange.multicast
                                                                     else "peer copies")),
                        "comm_ctas": args.comm_ctas if world > 1 else 0,
