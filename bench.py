@@ -57,17 +57,34 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and clock-event reasons of one GPU while the timed region runs:
+    NVML polled every 2 ms from a thread (read-only queries), nvidia-smi at 100 ms as fallback."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
-        self.rows = []
+    def __init__(self, index: int, pci_bus_id: str = None):
+        self.index, self.pci = index, pci_bus_id
+        self.rows = []          # nvidia-smi rows
+        self.samples = []       # (sm_mhz, power_w, reasons_mask) from NVML
         self.proc = None
+        self.nvml = None
+        self.stop_flag = False
+        self.max_mhz = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(self.pci.encode()) if self.pci else \
+                pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self.nvml = (pynvml, h)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
@@ -77,13 +94,47 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        pynvml, h = self.nvml
+        reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons",
+                          getattr(pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        while not self.stop_flag:
+            try:
+                mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                watts = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+                mask = int(reasons(h)) if reasons else 0
+                self.samples.append((mhz, watts, mask))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=1.0)
+            pynvml, _ = self.nvml
+            def bit(event_name, throttle_name, default):
+                return getattr(pynvml, event_name, getattr(pynvml, throttle_name, default))
+            bits = {"hw_slowdown": bit("nvmlClocksEventReasonHwSlowdown", "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                    "hw_thermal_slowdown": bit("nvmlClocksEventReasonHwThermalSlowdown",
+                                               "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                    "sw_thermal_slowdown": bit("nvmlClocksEventReasonSwThermalSlowdown",
+                                               "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                    "sw_power_cap": bit("nvmlClocksEventReasonSwPowerCap", "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+            sm = sorted(s[0] for s in self.samples)
+            mask = 0
+            for s in self.samples:
+                mask |= s[2]
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                    "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                    "power_w_max": round(max((s[1] for s in self.samples), default=0.0), 1),
+                    "reasons": sorted(n for n, b in bits.items() if mask & b), "source": "nvml, 2 ms period"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
         time.sleep(0.15)
         self.proc.terminate()
         sm, mx, reasons = [], [], set()
@@ -98,7 +149,7 @@ class ClockSampler:
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms period"}
 
 
 # --------------------------------------------------------------------- own arm ---
@@ -459,7 +510,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4"], default="c2")
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
@@ -540,7 +591,12 @@ def main():
             graph = None
             torch.cuda.synchronize()
     barrier()
-    sampler = ClockSampler(local)
+    props = torch.cuda.get_device_properties(dev)
+    try:
+        pci = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+    except AttributeError:
+        pci = None
+    sampler = ClockSampler(local, pci)
     if rank == 0:
         sampler.start()
     launches0 = L.launch_count()

@@ -212,6 +212,7 @@ bool pairs_enabled() {
     }
     return v == 1;
 }
+int pair_units_hint() { return sm_count() / 2; }
 // Whether a problem CAN run on CTA pairs, and whether the library chooses to.
 bool pair_capable(const llmt_b200_gemm_desc* d) {
     if (d->m <= 128 || d->plan_tile_n == 64) return false;
@@ -222,10 +223,14 @@ bool pair_capable(const llmt_b200_gemm_desc* d) {
 bool pair_eligible(const llmt_b200_gemm_desc* d) {
     if (!pair_capable(d) || d->plan_cta_pairs == 1) return false;
     if (d->plan_cta_pairs == 2) return true;
-    // Default: pairs, except for the fused-dbias products.  Those are the long dW
-    // reductions; their dbias tiles cost ~40 % more in pair form (a second MMA per
-    // k-step) and, being the longest tiles of a backward launch, set its makespan.
-    return pairs_enabled() && d->dbias == nullptr;
+    if (!pairs_enabled()) return false;
+    if (d->dbias == nullptr) return true;
+    // Fused-dbias products (the long dW reductions): their first tile column carries a second
+    // MMA per k-step in pair form, which makes those tiles a third longer.  With fewer tiles
+    // than pairs they set the launch's makespan (measured -10 % on 768x3072x8192), with
+    // several tiles per pair the dynamic queue absorbs them (+10 % on 6400x1600x8192).
+    const int64_t tiles = static_cast<int64_t>(ceil_div(d->m, 256)) * ceil_div(d->n, 256) * (d->batch > 0 ? d->batch : 1);
+    return tiles >= 2 * pair_units_hint();
 }
 int pair_units() {
     { const char* e = getenv("LLMT_B200_PAIR_UNITS"); if (e != nullptr && atoi(e) > 0) return atoi(e); }
