@@ -329,24 +329,57 @@ class AttentionStep:
                 events.append((label, e0, e1))
 
 
-class HostStep:
-    """The same step driven from HOST buffers: per step the layer inputs (x, dy) come from
-    pinned host memory and the reduced gradient span is read back."""
+class HostPipeline:
+    """A step driven from HOST buffers, as an input pipeline would: every step its inputs travel
+    from pinned host memory to the device and its result travels back, all inside the timed
+    region.  The copy of step i+1's inputs (on a copy stream, into a staging set) overlaps step
+    i's kernels; the compute stream moves the staged inputs into place with a device copy, runs
+    the step, and a third stream carries the result to the host."""
 
-    def __init__(self, step: LinearStep):
+    def __init__(self, torch, inputs, outputs, run_fn):
+        """inputs / outputs: lists of (pinned host tensor, device tensor)."""
+        self.torch, self.inputs, self.outputs, self.run_fn = torch, inputs, outputs, run_fn
+        self.stage = [torch.empty_like(d) for _, d in inputs]
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.staged, self.stage_free, self.done, self.out_copied = (torch.cuda.Event() for _ in range(4))
+        self.h2d_bytes = sum(h.numel() * h.element_size() for h, _ in inputs)
+        self.d2h_bytes = sum(h.numel() * h.element_size() for h, _ in outputs)
+
+    def run(self, steps):
+        torch = self.torch
+        main = torch.cuda.current_stream()
+        self.stage_free.record(main)
+        self.out_copied.record(main)
+        for _ in range(steps):
+            self.s_in.wait_event(self.stage_free)
+            with torch.cuda.stream(self.s_in):
+                for (h, _), s in zip(self.inputs, self.stage):
+                    s.copy_(h, non_blocking=True)
+                self.staged.record(self.s_in)
+            main.wait_event(self.staged)
+            for (_, d), s in zip(self.inputs, self.stage):
+                d.copy_(s, non_blocking=True)
+            self.stage_free.record(main)
+            main.wait_event(self.out_copied)   # the previous result has left before it is overwritten
+            self.run_fn()
+            self.done.record(main)
+            self.s_out.wait_event(self.done)
+            with torch.cuda.stream(self.s_out):
+                for h, d in self.outputs:
+                    h.copy_(d, non_blocking=True)
+                self.out_copied.record(self.s_out)
+        main.wait_event(self.out_copied)
+
+
+class HostStep(HostPipeline):
+    """The own arm's step from host buffers: the layer inputs (x, dy) in, the reduced gradient span out."""
+
+    def __init__(self, step: "LinearStep", world: int):
         torch = step.torch
-        self.step = step
-        self.h_in = [(torch.empty_like(t[k], device="cpu").pin_memory().copy_(t[k]), t[k])
-                     for t in step.layers for k in ("x", "dy")]
-        self.h_grad = torch.empty_like(step.bucket.flat, device="cpu").pin_memory()
-        self.h2d_bytes = sum(h.numel() * h.element_size() for h, _ in self.h_in)
-        self.d2h_bytes = self.h_grad.numel() * 4
-
-    def run(self, world):
-        for h, d in self.h_in:
-            d.copy_(h, non_blocking=True)
-        self.step.run(world)
-        self.h_grad.copy_(self.step.bucket.flat, non_blocking=True)
+        inputs = [(torch.empty_like(t[k], device="cpu").pin_memory().copy_(t[k]), t[k])
+                  for t in step.layers for k in ("x", "dy")]
+        outputs = [(torch.empty_like(step.bucket.flat, device="cpu").pin_memory(), step.bucket.flat)]
+        super().__init__(torch, inputs, outputs, lambda: step.run(world))
 
 
 def cpu_baseline(workload, budget_s=12.0):
@@ -475,19 +508,12 @@ def run_reference(args):
     # end to end: fp32 host inputs in, gradients out
     h_in = [(torch.empty_like(t[k], device="cpu").pin_memory().copy_(t[k]), t[k])
             for t in step.layers for k in ("x", "dy")]
-    h_out = [torch.empty_like(t["dw"], device="cpu").pin_memory() for t in step.layers]
-
-    def host_step():
-        for h, d in h_in:
-            d.copy_(h, non_blocking=True)
-        step.run()
-        for h, t in zip(h_out, step.layers):
-            h.copy_(t["dw"], non_blocking=True)
-    host_step(); torch.cuda.synchronize()
+    h_out = [(torch.empty_like(t["dw"], device="cpu").pin_memory(), t["dw"]) for t in step.layers]
+    hp = HostPipeline(torch, h_in, h_out, step.run)   # the same pipeline as the own arm's
+    hp.run(1); torch.cuda.synchronize()
     n_e2e = max(2, min(args.steps, 5))
     e0.record()
-    for _ in range(n_e2e):
-        host_step()
+    hp.run(n_e2e)
     e1.record(); torch.cuda.synchronize()
     ms_e2e = e0.elapsed_time(e1) / n_e2e
     clocks = sampler.stop()
@@ -498,8 +524,7 @@ def run_reference(args):
         "cpu_baseline": {"value": round(v, 2), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
                          "sample": "unmodified llmt library (oracle/_ref) on the GPU, full step"},
         "e2e": {"value": round(flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": sum(h.numel() * 4 for h, _ in h_in),
-                "d2h_bytes_per_step": sum(h.numel() * 4 for h in h_out)},
+                "h2d_bytes_per_step": hp.h2d_bytes, "d2h_bytes_per_step": hp.d2h_bytes},
         "clocks": clocks})
     print(json.dumps(base))
     return 0
@@ -634,12 +659,11 @@ def main():
     if attention:
         ms_e2e, h2d, d2h = float("nan"), 0, 0
     else:
-        hs = HostStep(step)
-        hs.run(world); barrier()
+        hs = HostStep(step, world)
+        hs.run(1); barrier()
         n_e2e = max(2, min(args.steps, 10))
         e0.record()
-        for _ in range(n_e2e):
-            hs.run(world)
+        hs.run(n_e2e)
         e1.record(); barrier()
         ms_e2e = e0.elapsed_time(e1) / n_e2e
         h2d, d2h = hs.h2d_bytes, hs.d2h_bytes
@@ -673,11 +697,17 @@ def main():
             # settings; writes of a replayed launch partly stay in L2): 380.1 MB + 25.4 MB against
             # 343.6 MB of algorithmic operand reads.
             traffic = 405.5e6 if args.workload == "c2" and world == 1 else None
-            roof = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": round(achieved / peak_tf, 4), "traffic": traffic,
+            # The timed loop is the GEMM kernel back to back (98.6 % of its kernel time, see profiles/):
+            # its CUDA-event duration is the kernel's duration.  The per-launch sum of the second,
+            # instrumented pass is reported beside it; it is longer because an event between two
+            # launches keeps one launch's prologue from overlapping the previous launch's tail.
+            in_loop = flops / ms / 1e9
+            roof = {"bound": "tensor", "achieved": round(in_loop, 1), "peak": peak_tf,
+                    "unit": "TFLOP/s", "frac": round(in_loop / peak_tf, 4), "traffic": traffic,
                     "peak_source": f"of {which}",
-                    "kernel": "tc_grouped_kernel (all GEMM launches of the step; per-launch device time "
-                              "from a second, instrumented pass over the same steps)"}
+                    "achieved_per_launch_events": round(achieved, 1),
+                    "kernel": "tc_grouped_kernel (all GEMM launches of the step; step FLOP / CUDA-event time "
+                              "of the timed loop per step, per GPU)"}
             ar_bytes = step.bucket.nbytes() if world > 1 else 0
         line = {
             "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job", "value": round(world * flops / ms / 1e9, 2),
