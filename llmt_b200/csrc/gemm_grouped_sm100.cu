@@ -255,6 +255,21 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
+    // Still independent of the previous kernel in the stream: the first tile ticket (this
+    // launch's counter was re-armed by the launch that used it 64 launches ago) and the tensor
+    // maps, which the host encoded.
+    int first_ticket = 0;
+    if (warp == 0 && leader) {
+        if (lane == 0) first_ticket = gp.static_schedule == 0 ? atomicAdd(gp.sched_counter, 1) : sched_id;
+        else if (lane <= 3 * gp.num_problems && lane <= 24) {
+            const GroupProblem& q = gp.prob[(lane - 1) / 3];
+            const int which = (lane - 1) % 3;
+            if (which < 2 || q.c_tma) prefetch_tensormap(which == 0 ? &q.map_a : which == 1 ? &q.map_b : &q.map_c);
+        }
+    } else if (warp == 0 && lane >= 1 && lane <= 2 * gp.num_problems && lane <= 16) {
+        const GroupProblem& q = gp.prob[(lane - 1) / 2];
+        prefetch_tensormap((lane - 1) % 2 == 0 ? &q.map_a : &q.map_b);
+    }
     // Everything above touched only this CTA's own state, so it may overlap the tail of the
     // previous kernel in the stream; nothing below may start before that kernel is done.
     grid_launch_dependents();
@@ -290,7 +305,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         // so the atomic's round trip stays off the critical path.
         const bool dynamic = gp.static_schedule == 0;
         int next = 0;
-        if (lane == 0 && scheduler) next = dynamic ? atomicAdd(gp.sched_counter, 1) : sched_id;
+        if (lane == 0 && scheduler) next = first_ticket;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
