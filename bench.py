@@ -545,7 +545,7 @@ def main():
                          "multicast (falls back to peer copies where no multicast mapping is offered), "
                          "its peer-copy kernel, or NCCL")
     ap.add_argument("--comm-ctas", type=int, default=None,
-                    help="N > 1: CTAs of the exchange kernel (default 32 for nvls, 16 for peer; "
+                    help="N > 1: CTAs of the exchange kernel (default 64 for nvls, 16 for peer; "
                          "with nccl: NCCL_MAX_CTAS, default unlimited)")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 0 for nvls, "
@@ -573,7 +573,7 @@ def main():
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.comm_ctas is None:
-            args.comm_ctas = {"nvls": 32, "peer": 16, "nccl": 0}[args.exchange]
+            args.comm_ctas = {"nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
         if args.exchange != "nccl":
             args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
         elif args.comm_ctas > 0:
