@@ -2,16 +2,18 @@
 """Benchmark of the GEMM path: one "step" = the linear-layer GEMMs of a training
 step (forward, dX, dW+dbias for every layer) on synthetic seeded inputs.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
 
-Workloads (shapes of BASELINE.json's configs):
+Workloads (shapes of the reference's benchmark configurations):
   c2  GPT-2-small, M = 8192 tokens per GPU, C = 768: QKV 768->2304, attention
       out-proj 768->768, MLP fc 768->3072 (bias+GELU fused), MLP proj 3072->768;
       bf16 operands, fp32 accumulation, bf16 activations, fp32 dW/dbias.
   c5  GPT-2-XL MLP, C = 1600, 4C = 6400, M = 8192 tokens per GPU.
+  c3  LM head 768->50257 (row pitch 50264, fp32 logits); c4 the six attention products.
 With N > 1 every GPU runs the same per-GPU workload on its own token shard
-(weak scaling) and the fp32 dW/dbias span is summed with one NCCL all-reduce per
-step, overlapped with the dX GEMMs.
+(weak scaling) and the fp32 dW/dbias span is summed layer by layer on a side stream
+(--exchange: the library's kernel through NVSwitch multicast or peer copies, or NCCL),
+overlapped with the backward launches of the remaining layers.
 
 Prints ONE JSON line. `value` is device-timed throughput with inputs resident in
 HBM; `e2e` is the same step called with HOST (pinned) buffers, copies included.
@@ -275,7 +277,7 @@ class LinearStep:
 
 
 class AttentionStep:
-    """BASELINE config 4: the six strided-batched attention products at B*H = 96, T = 1024, hd = 64
+    """Configuration 4: the six strided-batched attention products at B*H = 96, T = 1024, hd = 64
     (llmt src/kernels/attention.cpp:60-62 forward, docs/TODO.md:226-228 backward), bf16.
     P and dS are produced once by the softmax helpers outside the timed set. HBM-bound:
     every product moves one [96, T, T] matrix."""
