@@ -487,6 +487,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         const uint32_t slab = staging_base + static_cast<uint32_t>(half) * kSlabBytes;
         const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
         uint32_t slab_toggle = 0;
+        bool after_fp32_slab = false;  // the last slab store of this half was an fp32 one
         uint32_t acc_seq = 0;  // accumulator slot counter, in step with the MMA issuer's
         bool ok = true;
         for (int it = 0; ok; ++it) {
@@ -567,15 +568,24 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     // bf16 slabs are half the size of fp32 ones, so a half alternates between
                     // two of them and only waits for the store before the previous one; an
                     // fp32 slab is free once the previous TMA store has read it.
+                    // A bf16 chunk needs ONE barrier: the sub-slab it writes was read by the store
+                    // of two chunks ago, and the leader waited for that store before the previous
+                    // chunk's barrier.  After an fp32 chunk (whose store read the whole slab and was
+                    // issued after the last barrier) the half synchronises first.
                     uint32_t slab_now = slab;
                     if (p.c_is_bf16) {
                         slab_now += (slab_toggle & 1u) * (kSlabBytes / 2);
                         ++slab_toggle;
-                        if (store_leader) bulk_wait_group_read1();
-                    } else if (store_leader) {
-                        bulk_wait_group_read0();
+                        if (after_fp32_slab) {
+                            if (store_leader) bulk_wait_group_read0();
+                            named_barrier_sync(1 + half, 128);
+                            after_fp32_slab = false;
+                        }
+                    } else {
+                        if (store_leader) bulk_wait_group_read0();
+                        named_barrier_sync(1 + half, 128);
+                        after_fp32_slab = true;
                     }
-                    named_barrier_sync(1 + half, 128);
                     if (p.c_is_bf16) {
                         const uint32_t row_addr = slab_now + static_cast<uint32_t>(tile_row) * 64u;
                         const uint32_t sw = static_cast<uint32_t>(tile_row >> 1) & 3u;
@@ -605,6 +615,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         }
                     }
                     fence_proxy_async_smem();
+                    // bf16: the store of the previous chunk (the other sub-slab) must have finished
+                    // reading before anybody passes this barrier and starts the next chunk.
+                    if (p.c_is_bf16 && store_leader) bulk_wait_group_read0();
                     named_barrier_sync(1 + half, 128);
                     if (store_leader) {
                         tma_store_3d(&p.map_c, slab_now, static_cast<int32_t>(col), row0, tc.batch);
