@@ -181,6 +181,12 @@ LLMT_B200_API int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp,
  * healthy.  Returns LLMT_B200_ERR_DEVICE when a code was pending. */
 LLMT_B200_API int llmt_b200_device_status(int32_t* code, int32_t* detail);
 
+/* Zeroes `count` floats of the flat gradient span: the zero_grad that llmt leaves to the optimizer
+ * between steps (include/llmt/model/param_store.h:142-148; llmt would use its fill_value kernel,
+ * src/kernels/fill.cu:13-31).  Same effect as a memset; launched with programmatic stream
+ * serialization so that the next GEMM's set-up overlaps it. */
+LLMT_B200_API int llmt_b200_zero_grads(float* span, int64_t count, void* stream);
+
 /* SMs the persistent GEMM kernels may occupy from now on: 0 (the default) = every SM.
  * Planning and grid size follow it.  A data-parallel caller lowers it by the number of
  * CTAs its collective library runs (e.g. 148 - 8), so that the all-reduce of one layer's

@@ -25,6 +25,7 @@ EXPORTS = [
     "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
     "llmt_b200_set_sm_budget", "llmt_b200_grad_allreduce", "llmt_b200_grad_allreduce_emulated",
+    "llmt_b200_zero_grads",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 64
@@ -110,6 +111,8 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_grad_allreduce_emulated.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_int32, ctypes.c_int64,
                                                         ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
         L.llmt_b200_grad_allreduce_emulated.restype = ctypes.c_int
+        L.llmt_b200_zero_grads.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        L.llmt_b200_zero_grads.restype = ctypes.c_int
         L.llmt_b200_set_sm_budget.argtypes = [ctypes.c_int32]
         L.llmt_b200_set_sm_budget.restype = ctypes.c_int
         L.llmt_b200_last_error.restype = ctypes.c_char_p
@@ -310,6 +313,14 @@ def grad_allreduce_emulated(descs, offset: int, count: int, ctas: int = 4, strea
     arr = (CommDesc * len(descs))(*descs)
     _check(lib().llmt_b200_grad_allreduce_emulated(arr, len(descs), int(offset), int(count), int(ctas),
                                                    _stream(stream)))
+
+
+def zero_grads(span, stream=None) -> None:
+    """Zeroes a contiguous fp32 tensor (the flat gradient span) on its device."""
+    import torch
+    if span.dtype != torch.float32 or not span.is_contiguous():
+        raise LlmtB200Error(ERR_INVALID, "zero_grads: contiguous fp32 tensor expected")
+    _check(lib().llmt_b200_zero_grads(span.data_ptr(), span.numel(), _stream(stream)))
 
 
 def set_sm_budget(sms: int) -> int:

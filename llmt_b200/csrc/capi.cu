@@ -897,6 +897,18 @@ int llmt_b200_grad_allreduce_emulated(const llmt_b200_comm_desc* comms, int32_t 
     return LLMT_B200_OK;
 }
 
+int llmt_b200_zero_grads(float* span, int64_t count, void* stream) {
+    using namespace llmt_b200;
+    if (count < 0) return fail(LLMT_B200_ERR_INVALID, "zero_grads: negative count");
+    if (count == 0) return LLMT_B200_OK;
+    if (span == nullptr) return fail(LLMT_B200_ERR_INVALID, "zero_grads: invalid tensor (null data)");
+    if (reinterpret_cast<uintptr_t>(span) % sizeof(float) != 0)
+        return fail(LLMT_B200_ERR_INVALID, "zero_grads: span is not aligned to its element type");
+    cudaError_t e = launch_zero_f32(span, count, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
 int llmt_b200_set_sm_budget(int32_t sms) {
     if (sms < 0) {
         fail(LLMT_B200_ERR_INVALID, "sm budget: must be >= 0 (0 = every SM)");

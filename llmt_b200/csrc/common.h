@@ -145,6 +145,7 @@ int max_resident_pairs(void);
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
 size_t tc_grouped_smem_bytes(void);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
+cudaError_t launch_zero_f32(float* dst, int64_t n, cudaStream_t stream);
 cudaError_t launch_repack_bf16(void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld_src,
                                int64_t ld_dst, int64_t batch, int64_t stride_src, int64_t stride_dst,
                                cudaStream_t stream);

@@ -163,7 +163,49 @@ __global__ void repack_bf16_kernel(uint16_t* __restrict__ dst, const uint16_t* _
     }
 }
 
+// Zeroes the flat gradient span between steps (the zero_grad of llmt's ParamStore contract,
+// include/llmt/model/param_store.h:142-148).  Written here rather than left to a memset so that it
+// joins the stream's programmatic dependent launches: the first GEMM of the step starts its
+// prologue while this still runs.
+__global__ void zero_f32_kernel(float4* __restrict__ dst, int64_t n4, float* __restrict__ tail, int n_tail) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        dst[i] = z;
+    if (blockIdx.x == 0 && threadIdx.x < n_tail) tail[threadIdx.x] = 0.0f;
+}
+
 }  // namespace
+
+cudaError_t launch_zero_f32(float* dst, int64_t n, cudaStream_t stream) {
+    // 16-byte aligned body, scalar head and tail
+    int64_t head = 0;
+    while (head < n && (reinterpret_cast<uintptr_t>(dst + head) & 15u) != 0u) ++head;
+    if (head > 0) {
+        cudaError_t e = cudaMemsetAsync(dst, 0, static_cast<size_t>(head) * sizeof(float), stream);
+        if (e != cudaSuccess) return e;
+    }
+    const int64_t n4 = (n - head) / 4;
+    const int n_tail = static_cast<int>((n - head) % 4);
+    int64_t grid = (n4 + 255) / 256;
+    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid < 1) grid = 1;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, zero_f32_kernel, reinterpret_cast<float4*>(dst + head), n4,
+                                             dst + head + n4 * 4, n_tail);
+    count_launch(1);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
 
 cudaError_t launch_repack_bf16(void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld_src,
                                int64_t ld_dst, int64_t batch, int64_t stride_src, int64_t stride_dst,

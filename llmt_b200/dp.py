@@ -73,7 +73,11 @@ class GradBucket:
         return self.flat[off:off + n].view(shape)
 
     def zero_(self):
-        self.flat.zero_()
+        if self.flat.is_cuda:
+            from . import zero_grads
+            zero_grads(self.flat)
+        else:
+            self.flat.zero_()
 
     def nbytes(self) -> int:
         return self.flat.numel() * 4

@@ -164,3 +164,17 @@ def test_two_processes_through_switch_multicast(tmp_path):
     if all(t == "no multicast" for t in texts):
         pytest.skip("the allocator offers no multicast mapping on this machine")
     assert texts == ["ok"] * world
+
+
+@pytest.mark.parametrize("offset,count", [(0, 4096), (1, 1031), (3, 5), (2, 0), (0, 7080960)])
+def test_zero_grads_clears_exactly_the_span(offset, count):
+    dev = torch.device("cuda", 0)
+    buf = torch.ones(offset + count + 9, device=dev)
+    n0 = L.launch_count()
+    L.zero_grads(buf[offset:offset + count])
+    torch.cuda.synchronize()
+    assert L.launch_count() - n0 == (1 if count else 0)
+    assert float(buf[offset:offset + count].abs().sum()) == 0.0
+    assert float(buf[:offset].sum()) == offset and float(buf[offset + count:].sum()) == 9.0
+    with pytest.raises(L.LlmtB200Error):
+        L.zero_grads(torch.ones(8, device=dev, dtype=torch.bfloat16))
