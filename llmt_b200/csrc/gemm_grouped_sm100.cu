@@ -301,11 +301,13 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        // The ticket for the NEXT tile is drawn while the current tile's operands stream,
-        // so the atomic's round trip stays off the critical path.
+        // A ticket is drawn only when the producer is ready to stream that tile (the first one
+        // before the dependency wait).  Drawing one tile ahead would hide the atomic's round trip,
+        // but every CTA busy with a long tile would then sit on a short one that idle CTAs could
+        // have taken (measured on the QKV backward: the dX CTAs idle from 35 us of an 84 us launch).
+        // The operand stages already in shared memory cover the round trip instead.
         const bool dynamic = gp.static_schedule == 0;
-        int next = 0;
-        if (lane == 0 && scheduler) next = first_ticket;
+        int prev_ticket = 0;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
@@ -315,13 +317,13 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
                                              kDevWaitSched, slot);
                     if (ok) {
-                        t = next;
+                        t = it == 0 ? first_ticket
+                                    : (dynamic ? atomicAdd(gp.sched_counter, 1) : prev_ticket + n_sched);
+                        prev_ticket = t;
                         if (t >= gp.total_tiles) {
                             // Every drawer takes exactly one out-of-range ticket; the last re-arms the counter.
                             if (dynamic && t == gp.total_tiles + n_sched - 1) *gp.sched_counter = 0;
                             t = -1;
-                        } else {
-                            next = dynamic ? atomicAdd(gp.sched_counter, 1) : t + n_sched;
                         }
                         ctl->ring[slot] = t;
                         mbar_arrive(smem_u32(&ctl->sched_full[slot]));
