@@ -518,6 +518,18 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const bool partial = p.splits > 1;
             const bool via_tma = p.c_tma && !partial;
             const int half_cols = p.bn >> 1;
+            if (p.beta != 0.0f && !partial && row_ok) {
+                // beta * C_in is read row by row (one row per thread): ask L2 for this thread's whole
+                // stretch of the row now, so that the chunks below do not each wait for DRAM.  The dW
+                // tiles of a backward launch end last, which puts this read on the launch's tail.
+                const int esz = p.c_is_bf16 ? 2 : 4;
+                const char* base = static_cast<const char*>(p.c) +
+                                   (static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0 + half * half_cols) * esz;
+                int64_t cols = p.n - (n0 + half * half_cols);
+                if (cols > half_cols) cols = half_cols;
+                for (int64_t off = 0; off < cols * esz; off += 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+            }
 #pragma unroll 1
             for (int c0 = half * half_cols; c0 < (half + 1) * half_cols; c0 += 32) {
                 if (n0 + c0 >= p.n) break;  // warp-uniform, and the same in all warps of a half
