@@ -215,7 +215,7 @@ LLMT_B200_API int llmt_b200_set_sm_budget(int32_t sms);
  * after a few seconds with LLMT_B200_DEV_WAIT_PEER in the device status word, not a hang.
  * Run it beside the GEMM kernels by lowering their SM budget by `ctas`. */
 #define LLMT_B200_COMM_MAX_RANKS 8
-#define LLMT_B200_COMM_MAX_CTAS 64
+#define LLMT_B200_COMM_MAX_CTAS 128
 #define LLMT_B200_COMM_FLAG_BYTES (2 * LLMT_B200_COMM_MAX_RANKS * LLMT_B200_COMM_MAX_CTAS * 4)
 #define LLMT_B200_COMM_EPOCH_BYTES (LLMT_B200_COMM_MAX_CTAS * 4)
 #define LLMT_B200_DEV_WAIT_PEER 6

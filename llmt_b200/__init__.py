@@ -28,7 +28,7 @@ EXPORTS = [
     "llmt_b200_zero_grads",
 ]
 
-COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 64
+COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
 COMM_FLAG_BYTES = 2 * COMM_MAX_RANKS * COMM_MAX_CTAS * 4
 COMM_EPOCH_BYTES = COMM_MAX_CTAS * 4
 DEV_WAIT_PEER = 6

@@ -69,7 +69,7 @@ struct GroupParams {
 
 // ---- gradient all-reduce over peer memory -------------------------------------------------
 constexpr int kMaxCommRanks = 8;
-constexpr int kMaxCommCtas = 64;
+constexpr int kMaxCommCtas = 128;
 constexpr int kCommThreads = 256;
 
 // One rank's view of the exchange: the same three buffers on every rank, as pointers this

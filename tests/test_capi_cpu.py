@@ -150,7 +150,7 @@ def test_comm_descriptor_layout_matches_the_header():
     assert ctypes.sizeof(L.CommDesc) == 2 * 4 + 3 * 8 * 8 + 8 + 8 + 8
     text = open(HEADER).read()
     assert f"#define LLMT_B200_COMM_MAX_RANKS {L.COMM_MAX_RANKS}" in text
-    assert f"#define LLMT_B200_COMM_MAX_CTAS {L.COMM_MAX_CTAS}" in text
+    assert f"#define LLMT_B200_COMM_MAX_CTAS {L.COMM_MAX_CTAS}" in text  # 128
     assert f"#define LLMT_B200_DEV_WAIT_PEER {L.DEV_WAIT_PEER}" in text
 
 
