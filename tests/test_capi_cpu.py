@@ -192,3 +192,16 @@ def test_exchange_layout_is_aligned_and_large_enough():
             assert lay["total"] == lay["flags_off"] + L.COMM_FLAG_BYTES
     with pytest.raises(ValueError):
         exchange_layout(6, 2)
+
+
+def test_fused_dbias_products_take_pairs_only_when_tiles_outnumber_them():
+    # dW + dbias of GPT-2-XL's MLP (6400 x 1600 over 8192 tokens): 25 x 7 pair tiles >= 2 x 74 pairs
+    big = _desc(m=6400, n=1600, k=8192, trans_a=1, trans_b=0, lda=6400, ldb=1600, ldc=1600,
+                dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
+    assert "cta-pair" in L.plan(big)
+    # the same product of GPT-2-small's QKV layer has 9 x 3 pair tiles: single CTAs
+    small = _desc(m=2304, n=768, k=8192, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
+                  dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
+    assert "1-cta" in L.plan(small)
+    small.plan_cta_pairs = 2  # still available on request
+    assert "cta-pair" in L.plan(small)
