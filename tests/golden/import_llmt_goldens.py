@@ -9,7 +9,7 @@ tests/unit/test_matmul.cu, test_linear.cu, test_mlp.cu, test_attention.cu and
 test_kernels_fwd.cu at rtol 1e-5 / atol 1e-6).
 
 The files are data, copied byte for byte. Usage:
-    python tests/golden/import_llmt_goldens.py [path-to-llmt-tree]
+    python tests/golden/import_llmt_goldens.py <path-to-llmt-tree>
 """
 import os
 import shutil
@@ -19,7 +19,10 @@ CASES = ["matmul", "matmul_rank3", "linear", "mlp", "attention", "gelu"]
 
 
 def main() -> int:
-    src_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        print(__doc__, file=sys.stderr)
+        return 2
+    src_root = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     for case in CASES:
         src = os.path.join(src_root, "tests", "golden", case)
