@@ -8,6 +8,11 @@
  * non-zero status and llmt_b200_last_error() explains the most recent one on
  * the calling thread.
  *
+ * Threading: as in llmt (src/kernels/matmul.cpp:23-27) one host thread at a time issues the
+ * calls for a device.  Several devices per process are supported (one thread each, or one
+ * thread switching devices): all per-device host state is kept per device, and the first GEMM
+ * call on a device does a small synchronous set-up, so make it outside any stream capture.
+ *
  * The library replaces the one call llmt makes into cuBLASLt
  * (llmt: src/kernels/matmul.cpp:116-170, reached from kernels::matmul,
  * include/llmt/kernels/matmul.h:23-24).  Tensors are row-major; weights are
@@ -26,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LLMT_B200_ABI_VERSION 1
+#define LLMT_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define LLMT_B200_API __attribute__((visibility("default")))
@@ -67,8 +72,10 @@ enum llmt_b200_status {
  *   lda/ldb/ldc  row pitch in elements of each row-major buffer (>= its column count).
  *                Any pitch and any element-aligned base work.  bf16 operands whose base is
  *                16-byte aligned and whose pitch and batch stride are multiples of 8 elements
- *                are read in place; others are first copied to such a pitch inside the
- *                workspace (one extra pass over that operand).
+ *                are read in place; others (a contiguous [tokens, 50257] matrix, a slice
+ *                x[:, 1:]) are first copied to such a layout inside the workspace (one extra
+ *                pass over that operand; llmt_b200_gemm_workspace_bytes_for counts it).
+ *                m, n, k and batch must be below 2^31.
  *   stride_*     elements between consecutive batch items; ignored when batch == 1.
  *   dtype_ab     element type of A and B; dtype_c of C.  Supported pairs:
  *                (fp32, fp32) strict fp32 FMA path; (bf16, bf16) and (bf16, fp32)
@@ -76,7 +83,10 @@ enum llmt_b200_status {
  *   bias         [n] values added to every row when EPI_BIAS is set (bias_dtype: fp32 or bf16).
  *   dbias        optional fp32 [m]:  dbias[i] = dbias_beta * dbias[i] + sum_p op(A)[i,p].
  *                For llmt's dW call (src/layers/linear.cpp:27-29: A = dy, trans_a = 1)
- *                this is the bias gradient, summed over tokens.  bf16 path only.
+ *                this is the bias gradient, summed over tokens, in a fixed order, by the same
+ *                launch that computes dW (on the strict-fp32 path: by a second small kernel).
+ *   Aliasing     C is read and written in place.  C, dbias and the workspace must not overlap
+ *                one another, A, B or bias (checked by address range).
  *   plan_*       tuning overrides of the tile width, split-K factor and CTA pairing; 0 leaves the
  *                choice to the library (the default plan is a pure function of the
  *                problem, so results stay reproducible either way).
@@ -116,7 +126,9 @@ LLMT_B200_API int llmt_b200_gemm(const llmt_b200_gemm_desc* desc, void* c, const
  * leaves idle.  The natural use is llmt's Linear::backward (src/layers/linear.cpp:22-30),
  * whose two kernels::matmul calls (dx = dy W and dW += dy^T x) depend on nothing but dy:
  * pass both descriptors here.  count <= 8; every problem must be a bf16 problem and no
- * problem may write memory another problem of the call reads or writes.  Each problem's
+ * problem may write memory (C, dbias, workspace) that another problem of the call reads or
+ * writes (checked by address range).  A launch runs on CTA pairs or on single CTAs as a
+ * whole: plan_cta_pairs = 2 on one problem is refused when another cannot pair.  Each problem's
  * desc carries its own workspace; llmt_b200_gemm_grouped_workspace_bytes gives the sizes
  * (the split-K choice depends on the work the problems share the launch with).
  * Results are bitwise those of the same plan run alone: which SM computes a tile changes
@@ -155,8 +167,12 @@ LLMT_B200_API int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* desc,
                                                 const void* b, void* stream);
 
 /* Bytes of workspace llmt_b200_gemm needs for this problem (may be 0).  Pure
- * function of the descriptor and of the device's SM count. */
+ * function of the descriptor and of the device's SM count.  Assumes A and B start on
+ * 16-byte boundaries; llmt_b200_gemm_workspace_bytes_for also takes their addresses and
+ * counts the aligned copy an operand with an odd base address needs. */
 LLMT_B200_API uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* desc);
+LLMT_B200_API uint64_t llmt_b200_gemm_workspace_bytes_for(const llmt_b200_gemm_desc* desc, const void* a,
+                                                          const void* b);
 
 /* Writes a one-line description of the kernel plan chosen for `desc` (tile shape,
  * pipeline depth, split count, grid) into buf.  The plan is a pure function of
@@ -178,8 +194,22 @@ LLMT_B200_API int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp,
 /* Device-side health word.  Kernels never spin without bound: a wait that runs
  * out records (code, detail) here and the kernel drains and returns.  This call
  * synchronises the device, copies the word back and clears it.  code == 0 means
- * healthy.  Returns LLMT_B200_ERR_DEVICE when a code was pending. */
+ * healthy.  Returns LLMT_B200_ERR_DEVICE when a code was pending; the results of the
+ * launches that were in flight are then void, and the library's tile queues are reset so
+ * that later launches are unaffected. */
 LLMT_B200_API int llmt_b200_device_status(int32_t* code, int32_t* detail);
+
+/* How long a wait inside a kernel may last before it gives up, in nanoseconds: gemm_ns for
+ * the GEMM kernels' barrier waits (default 2 s), exchange_ns for the gradient exchange's
+ * waits on its peers (default 4 s); 0 leaves a value as it is.  Applies to launches made
+ * after the call.  Meant for tests and for hosts with their own watchdog period. */
+LLMT_B200_API int llmt_b200_set_wait_limit_ns(uint64_t gemm_ns, uint64_t exchange_ns);
+
+/* Host-side cache of encoded TMA descriptors (the counterpart of llmt's AlgoCache,
+ * include/llmt/kernels/algo_cache.h:18-42: what is expensive to resolve is resolved once per
+ * problem and replayed): number of look-ups answered from the cache and number that had to
+ * encode, on all threads, since the library was loaded. */
+LLMT_B200_API void llmt_b200_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses);
 
 /* Zeroes `count` floats of the flat gradient span: the zero_grad that llmt leaves to the optimizer
  * between steps (include/llmt/model/param_store.h:142-148; llmt would use its fill_value kernel,

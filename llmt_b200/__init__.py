@@ -25,7 +25,8 @@ EXPORTS = [
     "llmt_b200_softmax_fwd", "llmt_b200_softmax_bwd", "llmt_b200_device_status",
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
     "llmt_b200_set_sm_budget", "llmt_b200_grad_allreduce", "llmt_b200_grad_allreduce_emulated",
-    "llmt_b200_zero_grads",
+    "llmt_b200_zero_grads", "llmt_b200_gemm_workspace_bytes_for", "llmt_b200_set_wait_limit_ns",
+    "llmt_b200_tensor_map_cache_stats",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
@@ -91,6 +92,12 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_gemm_static_scratch.restype = ctypes.c_int
         L.llmt_b200_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
         L.llmt_b200_gemm_workspace_bytes.restype = ctypes.c_uint64
+        L.llmt_b200_gemm_workspace_bytes_for.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p]
+        L.llmt_b200_gemm_workspace_bytes_for.restype = ctypes.c_uint64
+        L.llmt_b200_set_wait_limit_ns.argtypes = [ctypes.c_uint64, ctypes.c_uint64]
+        L.llmt_b200_set_wait_limit_ns.restype = ctypes.c_int
+        L.llmt_b200_tensor_map_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
+        L.llmt_b200_tensor_map_cache_stats.restype = None
         L.llmt_b200_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_char_p, ctypes.c_size_t]
         L.llmt_b200_gemm_plan.restype = ctypes.c_int
         L.llmt_b200_softmax_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -193,8 +200,23 @@ def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=N
     return d
 
 
-def workspace_bytes(desc: GemmDesc) -> int:
-    return int(lib().llmt_b200_gemm_workspace_bytes(ctypes.byref(desc)))
+def workspace_bytes(desc: GemmDesc, a=None, b=None) -> int:
+    """Scratch the problem needs; pass the operand tensors when their base address may be odd."""
+    if a is None or b is None:
+        return int(lib().llmt_b200_gemm_workspace_bytes(ctypes.byref(desc)))
+    return int(lib().llmt_b200_gemm_workspace_bytes_for(ctypes.byref(desc), a.data_ptr(), b.data_ptr()))
+
+
+def set_wait_limit_ns(gemm_ns: int = 0, exchange_ns: int = 0) -> None:
+    """Bound of the waits inside the kernels (0 = leave unchanged)."""
+    _check(lib().llmt_b200_set_wait_limit_ns(int(gemm_ns), int(exchange_ns)))
+
+
+def tensor_map_cache_stats():
+    """(hits, misses) of the host-side cache of encoded TMA descriptors."""
+    h, m = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    lib().llmt_b200_tensor_map_cache_stats(ctypes.byref(h), ctypes.byref(m))
+    return int(h.value), int(m.value)
 
 
 def plan(desc: GemmDesc) -> str:
@@ -269,7 +291,7 @@ def gemm(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, 
     d = make_desc(c, a, b, trans_a, trans_b, alpha, beta, bias, gelu, dbias, dbias_beta, workspace,
                   tile_n, splits, cta_pairs)
     if workspace is None:
-        need = workspace_bytes(d)
+        need = workspace_bytes(d, a, b)
         if need:
             ws = torch.empty(need, dtype=torch.uint8, device=c.device)
             d.workspace = ws.data_ptr()

@@ -33,8 +33,8 @@ void Linear::backward(const RunCtx& ctx, Tensor& dx, const Tensor& dy, const Ten
     calls[0].c = &dx; calls[0].a = &dy; calls[0].b = &weight_.weight;            // dx = dy W
     calls[1].c = &weight_.grad; calls[1].a = &dy; calls[1].b = &x;                // dW += dy^T x
     calls[1].trans_a = true; calls[1].beta = 1.0f;
-    // The fused dbias exists on the bf16 path; the bias gradient always accumulates.
-    if (bias_ != nullptr && dy.dtype == DType::BF16) calls[1].epi.dbias = &bias_->grad;
+    // The bias gradient accumulates like dW (beta = 1), on both paths.
+    if (bias_ != nullptr) calls[1].epi.dbias = &bias_->grad;
     kernels::matmul_grouped(ctx, calls, 2);
 }
 

@@ -90,12 +90,16 @@ int sm_count() {
     return g_sm_budget > 0 && g_sm_budget < cached ? g_sm_budget : cached;
 }
 
-// Cost of one 64-deep k-block of a 128 x bn tile in SM cycles: tensor time is 2*bn
-// cycles (128*bn*64*2 flop at 8192 flop/clk); below it sit a floor of ~420 cycles per
-// tcgen05.commit and the time to stream (128+bn) rows of operands from L2.
-int kblock_cost(int bn) {
-    const int mma = bn * 2, floor_cycles = 420 + bn / 2;
-    return mma > floor_cycles ? mma : floor_cycles;
+// Cost of one 64-deep k-block of a tile in SM cycles.  Two bounds: the tensor pipe (2*bn
+// cycles for the CTA's 128 rows, about 15 % more once the per-k-block commit is counted:
+// 590 measured for bn = 256) and the rate at which one SM pulls operand bytes out of L2
+// (about 76 bytes per cycle measured; a single CTA stages 128 + bn rows of 128 bytes, a CTA of a
+// pair 128 + bn/2).  A single CTA's 256-wide tile is load-bound (measured 610-665), a pair's
+// is not.
+int kblock_cost(int bn, bool pairs) {
+    const int mma = bn * 2 * 115 / 100;
+    const int load = (128 + (pairs ? bn / 2 : bn)) * 128 / 76;
+    return mma > load ? mma : load;
 }
 
 int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
@@ -104,6 +108,9 @@ void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, boo
                  bool pairs) {
     pl->bn = bn;
     pl->pairs = pairs ? 1 : 0;
+    // The fused dbias is carried out as tickets of its own: one per block of rows of op(A)
+    // (and per split) that a CTA, or the two CTAs of a pair, reduce.
+    pl->colsum_blocks = dbias ? ceil_div(m, static_cast<int64_t>(tc_dbias_rows_per_cta()) * (pairs ? 2 : 1)) : 0;
     pl->tiles_m = ceil_div(m, pairs ? 256 : 128);
     pl->tiles_n = ceil_div(n, bn);
     pl->kblocks_total = ceil_div(k, 64);
@@ -147,7 +154,6 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
     int best_bn = 0, best_splits = 1;
     int64_t best_cost = 0;
     for (int bn : cands) {
-        if (dbias && !pairs && bn > 192) continue;  // a single CTA needs 16 spare columns next to the tile
         if (force_bn != 0 && bn != force_bn) continue;
         if (pairs && (bn == 64 || (b_mn && bn % 128 != 0))) continue;
         // Never pick a tile wider than needed when a narrower one covers n in one column.
@@ -158,7 +164,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
         const int kps = ceil_div(kblocks_total, splits);
         const int64_t waves = (tiles * splits + sms - 1) / sms;
         // Estimated cycles: main loops, an epilogue per wave, one pass over the partials when split.
-        int64_t cost = waves * (static_cast<int64_t>(kblock_cost(bn)) * (kps > 0 ? kps : 1) + 8 * bn);
+        int64_t cost = waves * (static_cast<int64_t>(kblock_cost(bn, pairs)) * (kps > 0 ? kps : 1) + 4 * bn);
         if (splits > 1) cost += static_cast<int64_t>(splits) * 64 + 4000;
         if (best_bn == 0 || cost < best_cost) {
             best_bn = bn;
@@ -177,7 +183,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
 // and split only reductions that are longer than the average load of an SM.
 TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
                        int64_t group_kblock_tiles, int force_bn, int force_splits, bool pairs, bool b_mn) {
-    int bn = (dbias && !pairs) ? 192 : 256;
+    int bn = 256;
     if (n <= 64) bn = pairs ? 128 : 64;
     else if (n <= 128) bn = 128;
     else if (n <= 192) bn = (pairs && b_mn) ? 256 : 192;
@@ -212,7 +218,6 @@ bool pairs_enabled() {
     }
     return v == 1;
 }
-int pair_units_hint() { return sm_count() / 2; }
 // Whether a problem CAN run on CTA pairs, and whether the library chooses to.
 bool pair_capable(const llmt_b200_gemm_desc* d) {
     if (d->m <= 128 || d->plan_tile_n == 64) return false;
@@ -223,17 +228,24 @@ bool pair_capable(const llmt_b200_gemm_desc* d) {
 bool pair_eligible(const llmt_b200_gemm_desc* d) {
     if (!pair_capable(d) || d->plan_cta_pairs == 1) return false;
     if (d->plan_cta_pairs == 2) return true;
-    if (!pairs_enabled()) return false;
-    if (d->dbias == nullptr) return true;
-    // Fused-dbias products (the long dW reductions): their first tile column carries a second
-    // MMA per k-step in pair form, which makes those tiles a third longer.  With fewer tiles
-    // than pairs they set the launch's makespan (measured -10 % on 768x3072x8192), with
-    // several tiles per pair the dynamic queue absorbs them (+10 % on 6400x1600x8192).
-    const int64_t tiles = static_cast<int64_t>(ceil_div(d->m, 256)) * ceil_div(d->n, 256) * (d->batch > 0 ? d->batch : 1);
-    return tiles >= 2 * pair_units_hint();
+    return pairs_enabled();
+}
+// Debug hook, read once: LLMT_B200_STATIC=1 replaces the dynamic tile queue by a static order.
+bool static_schedule_forced() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LLMT_B200_STATIC");
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
 }
 int pair_units() {
-    { const char* e = getenv("LLMT_B200_PAIR_UNITS"); if (e != nullptr && atoi(e) > 0) return atoi(e); }
+    static int forced = -1;  // debug hook, read once
+    if (forced < 0) {
+        const char* e = getenv("LLMT_B200_PAIR_UNITS");
+        forced = (e != nullptr && atoi(e) > 0) ? atoi(e) : 0;
+    }
+    if (forced > 0) return forced;
     const int r = max_resident_pairs();
     const int by_sm = sm_count() / 2;
     return (r > 0 && r < by_sm) ? r : by_sm;
@@ -251,6 +263,7 @@ bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
 
 struct Checked {
     int64_t a_rows, a_cols, b_rows, b_cols;
+    size_t a_bytes, b_bytes, c_bytes;  // extent of each operand in memory (0 for an empty problem)
     bool bf16;
 };
 
@@ -262,6 +275,10 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
         return fail(LLMT_B200_ERR_INVALID, "matmul: invalid tensor (null data)");
     if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: negative dimension");
+    // Tile counts and TMA coordinates are 32-bit.
+    constexpr int64_t kMaxDim = 0x7fffffff;
+    if (d->m > kMaxDim || d->n > kMaxDim || d->k > kMaxDim || d->batch > kMaxDim)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dimension above 2^31 - 1");
     if (d->dtype_ab != LLMT_B200_FP32 && d->dtype_ab != LLMT_B200_BF16)
         return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dtype code %d not supported", d->dtype_ab);
     if (d->dtype_c != LLMT_B200_FP32 && d->dtype_c != LLMT_B200_BF16)
@@ -290,8 +307,6 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     if (d->plan_cta_pairs == 2 && (d->m <= 128 || d->plan_tile_n == 64 || (d->trans_b == 0 && d->plan_tile_n == 192)))
         return fail(LLMT_B200_ERR_INVALID, "matmul: CTA pairs need m > 128 and a tile width of 128 or 256 "
                     "(192 only when B is stored [n, k])");
-    if (d->plan_tile_n == 256 && d->dbias != nullptr && d->plan_cta_pairs != 2)
-        return fail(LLMT_B200_ERR_INVALID, "matmul: the fused dbias on single CTAs needs plan_tile_n <= 192");
     if (d->plan_splits < 0) return fail(LLMT_B200_ERR_INVALID, "matmul: negative plan_splits");
     if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU)) != 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: unknown epilogue flags 0x%x", d->epilogue);
@@ -301,8 +316,6 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
         d->bias_dtype != LLMT_B200_BF16)
         return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: bias dtype code %d not supported", d->bias_dtype);
     if (d->dbias != nullptr) {
-        if (!out->bf16)
-            return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dbias is fused only into the bf16 path");
         if (d->batch > 1)
             return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dbias with a batched product is not defined");
     }
@@ -316,8 +329,25 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
                                                    (out->b_rows - 1) * d->ldb + out->b_cols) * es_ab;
         const size_t c_bytes = static_cast<size_t>((nb - 1) * (nb > 1 ? d->stride_c : 0) +
                                                    (d->m - 1) * d->ldc + d->n) * es_c;
+        out->a_bytes = a_bytes; out->b_bytes = b_bytes; out->c_bytes = c_bytes;
         if (overlaps(c, c_bytes, a, a_bytes) || overlaps(c, c_bytes, b, b_bytes))
             return fail(LLMT_B200_ERR_INVALID, "matmul: C overlaps an input");
+        // Nothing the call writes (C, dbias, workspace) may overlap anything else it touches.
+        const size_t dbias_bytes = d->dbias != nullptr ? static_cast<size_t>(d->m) * 4 : 0;
+        const size_t bias_bytes = (d->epilogue & LLMT_B200_EPI_BIAS)
+                                      ? static_cast<size_t>(d->n) * (d->bias_dtype == LLMT_B200_BF16 ? 2 : 4) : 0;
+        const size_t ws_bytes = d->workspace != nullptr ? static_cast<size_t>(d->workspace_bytes) : 0;
+        struct Range { const void* p; size_t n; const char* what; };
+        const Range reads[4] = {{a, a_bytes, "A"}, {b, b_bytes, "B"}, {d->bias, bias_bytes, "bias"}, {c, c_bytes, "C"}};
+        const Range writes[2] = {{d->dbias, dbias_bytes, "dbias"}, {d->workspace, ws_bytes, "workspace"}};
+        for (const Range& w : writes) {
+            if (w.n == 0) continue;
+            for (const Range& r : reads)
+                if (r.n != 0 && overlaps(w.p, w.n, r.p, r.n))
+                    return fail(LLMT_B200_ERR_INVALID, "matmul: %s overlaps %s", w.what, r.what);
+        }
+        if (dbias_bytes != 0 && ws_bytes != 0 && overlaps(d->dbias, dbias_bytes, d->workspace, ws_bytes))
+            return fail(LLMT_B200_ERR_INVALID, "matmul: dbias overlaps workspace");
     }
     return LLMT_B200_OK;
 }
@@ -347,62 +377,110 @@ int encode_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows,
     return LLMT_B200_OK;
 }
 
+// Encoded tensor maps are kept: a map is a pure function of (address, element size, shape,
+// pitches, box, swizzle), a training step calls the same GEMMs on the same buffers over and
+// over, and cuTensorMapEncodeTiled is the most expensive thing the host does per call.  This
+// is the part of llmt's AlgoCache (include/llmt/kernels/algo_cache.h:18-42: resolve once per
+// problem, replay) that has a cost worth caching here; the plan itself is recomputed, being a
+// few integer operations.  Direct-mapped, per host thread, no device state.
+struct MapKey {
+    const void* base;
+    int64_t rows, cols, ld, batch, stride;
+    int32_t elem_bytes, box_cols, box_rows, swizzle;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && batch == o.batch &&
+               stride == o.stride && elem_bytes == o.elem_bytes && box_cols == o.box_cols &&
+               box_rows == o.box_rows && swizzle == o.swizzle;
+    }
+};
+struct MapCacheEntry {
+    MapKey key;
+    bool used;
+    CUtensorMap map;
+};
+constexpr int kMapCacheSlots = 1024;
+std::atomic<uint64_t> g_map_cache_hits{0}, g_map_cache_misses{0};
+
+int cached_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols, int64_t ld,
+               int64_t batch, int64_t stride, int box_cols, int box_rows, CUtensorMapSwizzle swizzle) {
+    thread_local MapCacheEntry* table = nullptr;
+    if (table == nullptr) table = new MapCacheEntry[kMapCacheSlots]();
+    const MapKey key{base, rows, cols, ld, batch > 1 ? batch : 1, batch > 1 ? stride : 0,
+                     elem_bytes, box_cols, box_rows, static_cast<int32_t>(swizzle)};
+    uint64_t h = 1469598103934665603ull;  // FNV-1a over the key's words, as llmt's AlgoKeyHash does
+    const uint64_t words[8] = {reinterpret_cast<uintptr_t>(base), static_cast<uint64_t>(rows),
+                               static_cast<uint64_t>(cols), static_cast<uint64_t>(ld),
+                               static_cast<uint64_t>(key.batch), static_cast<uint64_t>(key.stride),
+                               (static_cast<uint64_t>(elem_bytes) << 32) | static_cast<uint32_t>(box_cols),
+                               (static_cast<uint64_t>(box_rows) << 32) | static_cast<uint32_t>(swizzle)};
+    for (uint64_t w : words) { h ^= w; h *= 1099511628211ull; }
+    MapCacheEntry& e = table[(h ^ (h >> 29)) % kMapCacheSlots];
+    if (e.used && e.key == key) {
+        *map = e.map;
+        g_map_cache_hits.fetch_add(1, std::memory_order_relaxed);
+        return LLMT_B200_OK;
+    }
+    const int st = encode_map(map, base, elem_bytes, rows, cols, ld, batch, stride, box_cols, box_rows, swizzle);
+    if (st != LLMT_B200_OK) return st;
+    e.key = key; e.used = true; e.map = *map;
+    g_map_cache_misses.fetch_add(1, std::memory_order_relaxed);
+    return LLMT_B200_OK;
+}
+
 // bf16 operand map boxed for 128-byte-swizzled tiles (64 elements wide).
 int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
                        int64_t batch, int64_t stride, int box_rows) {
-    return encode_map(map, base, 2, rows, cols, ld, batch, stride, 64, box_rows,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+    return cached_map(map, base, 2, rows, cols, ld, batch, stride, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// bf16 1.0 block for the fused dbias, inside the library image; filled once per device.
-static __device__ __align__(1024) uint16_t g_ones[64 * 64];
 // Tile-queue counters: zero between launches (the kernel re-arms its counter); launches
 // take them round-robin so that kernels in flight at the same time do not share one.
 constexpr int kSchedSlots = 64;
 static __device__ int32_t g_sched_counters[kSchedSlots];
 
+// Per-device host state.  Several devices per process are supported as long as each device's
+// calls come from one host thread at a time (llmt's rule: one thread issues the launches,
+// src/kernels/matmul.cpp:23-27).
 struct DeviceGlobals {
     bool ready = false;
-    CUtensorMap map_ones;
     int32_t* counters = nullptr;
     unsigned next = 0;
 };
 
-int device_globals(DeviceGlobals** out) {
+DeviceGlobals* device_globals_slot() {
     static DeviceGlobals globals[64];
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
-        return fail(LLMT_B200_ERR_CUDA, "no current CUDA device");
-    DeviceGlobals& g = globals[dev];
-    if (!g.ready) {
-        static uint16_t host_ones[64 * 64];
-        for (uint16_t& v : host_ones) v = 0x3F80;  // bf16 1.0
-        void* ones = nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return &globals[dev];
+}
+
+// First use on a device: resolves and zeroes the tile-queue counters.  This is a synchronous
+// memset, so the first GEMM on a device must not be issued inside a stream capture.
+int device_globals(DeviceGlobals** out) {
+    DeviceGlobals* g = device_globals_slot();
+    if (g == nullptr) return fail(LLMT_B200_ERR_CUDA, "no current CUDA device");
+    if (!g->ready) {
         void* ctr = nullptr;
-        cudaError_t e = cudaMemcpyToSymbol(g_ones, host_ones, sizeof host_ones);
-        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ones, g_ones);
-        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ctr, g_sched_counters);
+        cudaError_t e = cudaGetSymbolAddress(&ctr, g_sched_counters);
         if (e == cudaSuccess) e = cudaMemset(ctr, 0, sizeof(int32_t) * kSchedSlots);
         if (e != cudaSuccess)
             return fail(LLMT_B200_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
-        const int st = encode_map(&g.map_ones, ones, 2, 64, 64, 64, 1, 0, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (st != LLMT_B200_OK) return st;
-        g.counters = static_cast<int32_t*>(ctr);
-        g.ready = true;
+        g->counters = static_cast<int32_t*>(ctr);
+        g->ready = true;
     }
-    *out = &g;
+    *out = g;
     return LLMT_B200_OK;
 }
 
-// TMA needs 16-byte aligned bases, pitches and batch strides.  An operand whose pitch (or
-// batch stride) is not a multiple of 8 elements - e.g. a contiguous [tokens, 50257] dLogits -
-// is first copied into the workspace with its pitch rounded up ("repacked"); an operand that
-// merely starts at an odd address is not supported.
-int check_tma_operands(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
-    (void)d;
-    if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u))
-        return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: bf16 operands must start on a 16-byte boundary");
-    return LLMT_B200_OK;
+// Bound of every wait inside the kernels (nanoseconds of %globaltimer).
+uint64_t g_wait_limit_ns = 2000000000ull;
+uint64_t g_comm_wait_limit_ns = 4000000000ull;
+
+// TMA needs 16-byte aligned bases, pitches and batch strides.  An operand that breaks one of
+// the rules - a contiguous [tokens, 50257] dLogits, a slice x[:, 1:] - is first copied into
+// the workspace with an aligned base and its pitch rounded up ("repacked").
+bool needs_repack(const void* base, int64_t ld, int64_t batch, int64_t stride) {
+    return (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld % 8) != 0 || (batch > 1 && (stride % 8) != 0);
 }
 
 struct Repack {
@@ -412,17 +490,19 @@ struct Repack {
     size_t total() const { return bytes_a + bytes_b; }
 };
 
-Repack repack_plan(const llmt_b200_gemm_desc* d, const Checked& ck) {
+// a, b: the operands' addresses, or null when only the size is wanted for operands that are
+// known to be 16-byte aligned.
+Repack repack_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* a, const void* b) {
     Repack r;
     const int64_t nb = d->batch > 1 ? d->batch : 1;
     auto round8 = [](int64_t v) { return (v + 7) / 8 * 8; };
-    if (d->k > 0 && ((d->lda % 8) != 0 || (d->batch > 1 && (d->stride_a % 8) != 0))) {
+    if (d->k > 0 && needs_repack(a, d->lda, d->batch, d->stride_a)) {
         r.a = true;
         r.lda = round8(ck.a_cols);
         r.stride_a = ck.a_rows * r.lda;
         r.bytes_a = (static_cast<size_t>(nb) * r.stride_a * 2 + 255) / 256 * 256;
     }
-    if (d->k > 0 && ((d->ldb % 8) != 0 || (d->batch > 1 && (d->stride_b % 8) != 0))) {
+    if (d->k > 0 && needs_repack(b, d->ldb, d->batch, d->stride_b)) {
         r.b = true;
         r.ldb = round8(ck.b_cols);
         r.stride_b = ck.b_rows * r.ldb;
@@ -488,6 +568,9 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->bias = d->bias; p->bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
     p->epi_flags = d->epilogue;
     p->dbias = d->dbias; p->dbias_beta = d->dbias_beta;
+    p->a_raw = a; p->lda = d->lda;
+    p->colsum_blocks = pl.colsum_blocks;
+    p->colsum_tiles = pl.colsum_blocks * pl.splits;
     if (pl.splits > 1) {
         p->ws = static_cast<float*>(d->workspace);
         size_t ws = static_cast<size_t>(d->batch) * pl.splits * d->m * d->n * sizeof(float);
@@ -501,13 +584,23 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     st = encode_operand_map(&p->map_b, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
                             p->b_mn ? 64 : (pl.pairs ? pl.bn / 2 : pl.bn));
     if (st != LLMT_B200_OK) return st;
-    // C leaves through shared memory and TMA stores when its layout allows a tensor map
-    // (16-byte aligned base, pitch and batch stride); otherwise straight from registers.
+    // Results leave through shared memory and TMA stores (boxes of 32 rows x 128 bytes) when
+    // their layout allows a tensor map (16-byte aligned base, pitch and batch stride);
+    // otherwise straight from registers.
+    if (pl.splits > 1) {
+        if (d->n % 4 == 0) {
+            st = cached_map(&p->map_ws, d->workspace, 4, d->m, d->n, d->n, d->batch * pl.splits, d->m * d->n, 32, 32,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+            if (st != LLMT_B200_OK) return st;
+            p->ws_tma = 1;
+        }
+        return LLMT_B200_OK;
+    }
     const int ces = p->c_is_bf16 ? 2 : 4;
     if ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
-        (d->batch <= 1 || (d->stride_c * ces) % 16 == 0) && pl.splits == 1) {
-        st = encode_map(&p->map_c, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, 32, 128,
-                        p->c_is_bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+        (d->batch <= 1 || (d->stride_c * ces) % 16 == 0)) {
+        st = cached_map(&p->map_c, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, p->c_is_bf16 ? 64 : 32, 32,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != LLMT_B200_OK) return st;
         p->c_tma = 1;
     }
@@ -520,7 +613,7 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
     DeviceGlobals* g = nullptr;
     int st = device_globals(&g);
     if (st != LLMT_B200_OK) return st;
-    static GroupParams gp;  // one host thread issues launches (as in llmt, matmul.cpp:23-27)
+    thread_local GroupParams gp;
     // Longest reductions first: with a dynamic queue this is longest-processing-time-first.
     int order[kMaxGroupProblems];
     for (int i = 0; i < count; ++i) order[i] = i;
@@ -528,22 +621,31 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         for (int j = i; j > 0 && probs[order[j]].kblocks_per_split > probs[order[j - 1]].kblocks_per_split; --j) {
             const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
         }
-    int64_t total = 0;
+    // Ticket layout: the dbias reductions of all problems first (they keep only the epilogue
+    // warps busy, so the CTAs that draw them go straight on to an MMA tile), then the MMA tiles.
+    int64_t colsum_total = 0;
     int n = 0;
     for (int i = 0; i < count; ++i) {
         GroupProblem& p = probs[order[i]];
         if (p.k == 0 || p.num_tiles == 0) continue;
-        p.tile_begin = static_cast<int32_t>(total);
-        total += p.num_tiles;
+        p.colsum_begin = static_cast<int32_t>(colsum_total);
+        colsum_total += p.colsum_tiles;
         gp.prob[n++] = p;
     }
-    if (total > 0x7fffff00) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: too many tiles in one launch");
+    int64_t total = colsum_total;
+    for (int i = 0; i < n; ++i) {
+        if (total + gp.prob[i].num_tiles > 0x7fffff00)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: too many tiles in one launch");
+        gp.prob[i].tile_begin = static_cast<int32_t>(total);
+        total += gp.prob[i].num_tiles;
+    }
     if (n > 0) {
-        gp.map_ones = g->map_ones;
         gp.num_problems = n;
         gp.total_tiles = static_cast<int32_t>(total);
+        gp.colsum_total = static_cast<int32_t>(colsum_total);
         gp.sched_counter = g->counters + (g->next++ % kSchedSlots);
-        { const char* e = getenv("LLMT_B200_STATIC"); gp.static_schedule = (e && e[0] == '1') ? 1 : 0; }
+        gp.static_schedule = static_schedule_forced() ? 1 : 0;
+        gp.wait_limit_ns = g_wait_limit_ns;
         gp.status = device_status_ptr();
         if (gp.status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
         const int units = pairs ? pair_units() : sm_count();
@@ -563,11 +665,9 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
 
 int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const void* a, const void* b,
              cudaStream_t stream) {
-    int st = check_tma_operands(d, a, b);
-    if (st != LLMT_B200_OK) return st;
     const TcPlan pl = plan_single(d);
-    const Repack rp = repack_plan(d, ck);
-    st = check_workspace(d, pl, rp.total());
+    const Repack rp = repack_plan(d, ck, a, b);
+    int st = check_workspace(d, pl, rp.total());
     if (st != LLMT_B200_OK) return st;
     llmt_b200_gemm_desc local = *d;
     if (rp.total() > 0) {
@@ -581,15 +681,14 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
 }
 
 // Group plans: every problem is planned knowing the total work of the launch.
-int plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
+bool plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
     bool pairs = true;  // a launch is either all pairs or all single CTAs
     for (int i = 0; i < count; ++i) pairs = pairs && pair_eligible(&descs[i]);
     const int sms = pairs ? pair_units() : sm_count();
     int64_t work = 0;
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
-        const int bn = (d.dbias && !pairs) ? 192 : 256;
-        work += static_cast<int64_t>(ceil_div(d.m, pairs ? 256 : 128)) * ceil_div(d.n, bn) *
+        work += static_cast<int64_t>(ceil_div(d.m, pairs ? 256 : 128)) * ceil_div(d.n, 256) *
                 (d.batch > 0 ? d.batch : 1) * ceil_div(d.k, 64);
     }
     for (int i = 0; i < count; ++i) {
@@ -598,7 +697,7 @@ int plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
                               : make_group_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, work,
                                                 d.plan_tile_n, d.plan_splits, pairs, d.trans_b == 0);
     }
-    return LLMT_B200_OK;
+    return count == 1 ? plans[0].pairs != 0 : pairs;
 }
 
 int run_fp32(const llmt_b200_gemm_desc* d, void* c, const void* a, const void* b, cudaStream_t stream) {
@@ -617,6 +716,8 @@ int run_fp32(const llmt_b200_gemm_desc* d, void* c, const void* a, const void* b
     p.epi_flags = d->epilogue;
     if (d->batch > 65535) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: fp32 path supports batch <= 65535");
     cudaError_t e = launch_fp32_gemm(p, stream);
+    // The strict-fp32 path has nothing to fuse the bias gradient into: a second small kernel.
+    if (e == cudaSuccess && d->dbias != nullptr) e = launch_fp32_rowsum(p, d->dbias, d->dbias_beta, stream);
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return LLMT_B200_OK;
 }
@@ -663,7 +764,7 @@ int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const v
     if (!ck.bf16) return run_fp32(d, c, a, b, s);  // the fp32 path uses no scratch at all
     // Size check first: a problem that does not fit is turned away before the scratch is
     // resolved and before anything is enqueued.
-    const size_t need = plan_single(d).workspace_bytes + repack_plan(d, ck).total();
+    const size_t need = plan_single(d).workspace_bytes + repack_plan(d, ck, a, b).total();
     if (need > kStaticScratchBytes)
         return fail(LLMT_B200_ERR_WORKSPACE,
                     "gemm_static_scratch: this problem's split-K plan needs %llu scratch bytes but the "
@@ -697,20 +798,45 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
         if (st != LLMT_B200_OK) return st;
         if (!ck[i].bf16)
             return fail(LLMT_B200_ERR_UNSUPPORTED, "gemm_grouped: problem %d is not a bf16 problem", i);
-        const int st2 = check_tma_operands(&descs[i], a[i], b[i]);
-        if (st2 != LLMT_B200_OK) return st2;
-        // A problem must not write what another problem of the same launch reads or writes.
-        for (int j = 0; j < i; ++j)
-            if (c[i] == c[j] || c[i] == a[j] || c[i] == b[j] || c[j] == a[i] || c[j] == b[i])
+        // A problem must not write (C, dbias, workspace) what another problem of the same launch
+        // reads or writes: the tiles of all problems run concurrently.
+        for (int j = 0; j < i; ++j) {
+            struct Range { const void* p; size_t n; };
+            auto writes_of = [&](int q, Range* out) {
+                out[0] = {c[q], ck[q].c_bytes};
+                out[1] = {descs[q].dbias, descs[q].dbias != nullptr ? static_cast<size_t>(descs[q].m) * 4 : 0};
+                out[2] = {descs[q].workspace, descs[q].workspace != nullptr ? static_cast<size_t>(descs[q].workspace_bytes) : 0};
+            };
+            auto touches_of = [&](int q, Range* out) {
+                writes_of(q, out);
+                out[3] = {a[q], ck[q].a_bytes};
+                out[4] = {b[q], ck[q].b_bytes};
+                out[5] = {descs[q].bias, (descs[q].epilogue & LLMT_B200_EPI_BIAS)
+                                             ? static_cast<size_t>(descs[q].n) * (descs[q].bias_dtype == LLMT_B200_BF16 ? 2 : 4) : 0};
+            };
+            Range wi[3], wj[3], ti[6], tj[6];
+            writes_of(i, wi); writes_of(j, wj); touches_of(i, ti); touches_of(j, tj);
+            bool clash = false;
+            for (const Range& w : wi)
+                for (const Range& t : tj) clash = clash || (w.n != 0 && t.n != 0 && overlaps(w.p, w.n, t.p, t.n));
+            for (const Range& w : wj)
+                for (const Range& t : ti) clash = clash || (w.n != 0 && t.n != 0 && overlaps(w.p, w.n, t.p, t.n));
+            if (clash)
                 return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: problems %d and %d are not independent", j, i);
+        }
     }
     TcPlan plans[kMaxGroupProblems];
-    plan_group(descs, count, plans);
+    const bool pairs = plan_group(descs, count, plans);
+    for (int i = 0; i < count; ++i)
+        if (descs[i].plan_cta_pairs == 2 && !pairs)
+            return fail(LLMT_B200_ERR_INVALID,
+                        "gemm_grouped: problem %d asks for CTA pairs, but another problem of the launch cannot run "
+                        "on pairs (a launch is all pairs or all single CTAs)", i);
     GroupProblem probs[kMaxGroupProblems];
     int n = 0;
     for (int i = 0; i < count; ++i) {
         if (descs[i].m == 0 || descs[i].n == 0 || descs[i].batch == 0) continue;
-        const Repack rp = repack_plan(&descs[i], ck[i]);
+        const Repack rp = repack_plan(&descs[i], ck[i], a[i], b[i]);
         int st = check_workspace(&descs[i], plans[i], rp.total());
         if (st != LLMT_B200_OK) return st;
         llmt_b200_gemm_desc local = descs[i];
@@ -726,8 +852,18 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
         ++n;
     }
     if (n == 0) return LLMT_B200_OK;
-    return launch_group(probs, n, plans[0].pairs != 0, static_cast<cudaStream_t>(stream));
+    return launch_group(probs, n, pairs, static_cast<cudaStream_t>(stream));
 }
+
+namespace {
+void shape_only(const llmt_b200_gemm_desc& d, Checked* ck) {
+    ck->a_rows = d.trans_a ? d.k : d.m; ck->a_cols = d.trans_a ? d.m : d.k;
+    ck->b_rows = d.trans_b ? d.n : d.k; ck->b_cols = d.trans_b ? d.k : d.n;
+}
+bool is_tc_problem(const llmt_b200_gemm_desc& d) {
+    return d.dtype_ab == LLMT_B200_BF16 && d.m > 0 && d.n > 0 && d.k > 0 && d.batch > 0;
+}
+}  // namespace
 
 int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int32_t count,
                                            uint64_t* bytes_per_problem) {
@@ -736,24 +872,23 @@ int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int
     TcPlan plans[kMaxGroupProblems];
     plan_group(descs, count, plans);
     for (int i = 0; i < count; ++i) {
-        const llmt_b200_gemm_desc& d = descs[i];
         Checked ck{};
-        ck.a_rows = d.trans_a ? d.k : d.m; ck.a_cols = d.trans_a ? d.m : d.k;
-        ck.b_rows = d.trans_b ? d.n : d.k; ck.b_cols = d.trans_b ? d.k : d.n;
-        bytes_per_problem[i] = (d.dtype_ab == LLMT_B200_BF16 && d.m > 0 && d.n > 0 && d.k > 0 && d.batch > 0)
-                                   ? plans[i].workspace_bytes + repack_plan(&d, ck).total() : 0;
+        shape_only(descs[i], &ck);
+        bytes_per_problem[i] = is_tc_problem(descs[i])
+                                   ? plans[i].workspace_bytes + repack_plan(&descs[i], ck, nullptr, nullptr).total() : 0;
     }
     return LLMT_B200_OK;
 }
 
 uint64_t llmt_b200_gemm_workspace_bytes(const llmt_b200_gemm_desc* d) {
-    if (d == nullptr || d->dtype_ab != LLMT_B200_BF16 || d->m <= 0 || d->n <= 0 || d->k <= 0 ||
-        d->batch <= 0)
-        return 0;
+    return llmt_b200_gemm_workspace_bytes_for(d, nullptr, nullptr);
+}
+
+uint64_t llmt_b200_gemm_workspace_bytes_for(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
+    if (d == nullptr || !is_tc_problem(*d)) return 0;
     Checked ck{};
-    ck.a_rows = d->trans_a ? d->k : d->m; ck.a_cols = d->trans_a ? d->m : d->k;
-    ck.b_rows = d->trans_b ? d->n : d->k; ck.b_cols = d->trans_b ? d->k : d->n;
-    return plan_single(d).workspace_bytes + repack_plan(d, ck).total();
+    shape_only(*d, &ck);
+    return plan_single(d).workspace_bytes + repack_plan(d, ck, a, b).total();
 }
 
 int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
@@ -765,10 +900,11 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
     }
     const TcPlan pl = plan_single(d);
     const int units = pl.pairs ? pair_units() : sm_count();
-    snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d grid=%d smem=%zu ws=%zu resident_pairs=%d",
-             pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? 6 : 4, pl.splits, pl.tiles_m,
-             pl.tiles_n, pl.kblocks_total,
-             static_cast<int>(pl.num_tiles < units ? pl.num_tiles : units) * (pl.pairs ? 2 : 1),
+    const int64_t tickets = pl.num_tiles + static_cast<int64_t>(pl.colsum_blocks) * pl.splits;
+    snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d dbias_tickets=%d grid=%d smem=%zu ws=%zu resident_pairs=%d",
+             pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? 5 : 4, pl.splits, pl.tiles_m,
+             pl.tiles_n, pl.kblocks_total, pl.colsum_blocks * pl.splits,
+             static_cast<int>(tickets < units ? tickets : units) * (pl.pairs ? 2 : 1),
              tc_grouped_smem_bytes(), pl.workspace_bytes, pl.pairs ? max_resident_pairs() : 0);
     return LLMT_B200_OK;
 }
@@ -816,6 +952,10 @@ int llmt_b200_device_status(int32_t* code, int32_t* detail) {
     if (h.code != 0) {
         DeviceStatus z{};
         cudaMemcpy(dp, &z, sizeof z, cudaMemcpyHostToDevice);
+        // A kernel that gave up may have left its tile-queue counter part-way; results of
+        // launches that were in flight are void, later launches start from clean counters.
+        DeviceGlobals* g = device_globals_slot();
+        if (g != nullptr && g->ready) cudaMemset(g->counters, 0, sizeof(int32_t) * kSchedSlots);
         return fail(LLMT_B200_ERR_DEVICE, "a kernel gave up on a bounded wait: code %d detail %d block %d",
                     h.code, h.detail, h.block);
     }
@@ -863,12 +1003,13 @@ int llmt_b200_grad_allreduce(const llmt_b200_comm_desc* comm, int64_t offset, in
     using namespace llmt_b200;
     if (ctas < 1 || ctas > kMaxCommCtas)
         return fail(LLMT_B200_ERR_INVALID, "allreduce: ctas must be 1..%d", kMaxCommCtas);
-    static AllreduceParams p;  // one host thread issues launches
+    thread_local AllreduceParams p;
     int st = fill_comm(&p.ctx[0], comm, offset, count);
     if (st != LLMT_B200_OK) return st;
     if (comm->world == 1 || count == 0) return LLMT_B200_OK;
     p.offset = offset;
     p.count = count;
+    p.wait_limit_ns = g_comm_wait_limit_ns;
     cudaError_t e = comm->grad_mc != nullptr ? launch_grad_allreduce_mc(p, ctas, static_cast<cudaStream_t>(stream))
                                              : launch_grad_allreduce(p, ctas, 0, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
@@ -882,7 +1023,7 @@ int llmt_b200_grad_allreduce_emulated(const llmt_b200_comm_desc* comms, int32_t 
         return fail(LLMT_B200_ERR_INVALID, "allreduce: world must be 1..%d", kMaxCommRanks);
     if (ctas < 1 || ctas > kMaxCommCtas)
         return fail(LLMT_B200_ERR_INVALID, "allreduce: ctas must be 1..%d", kMaxCommCtas);
-    static AllreduceParams p;
+    thread_local AllreduceParams p;
     for (int r = 0; r < world; ++r) {
         if (comms[r].world != world || comms[r].rank != r)
             return fail(LLMT_B200_ERR_INVALID, "allreduce: descriptor %d is not rank %d of %d", r, r, world);
@@ -892,6 +1033,7 @@ int llmt_b200_grad_allreduce_emulated(const llmt_b200_comm_desc* comms, int32_t 
     if (world == 1 || count == 0) return LLMT_B200_OK;
     p.offset = offset;
     p.count = count;
+    p.wait_limit_ns = g_comm_wait_limit_ns;
     cudaError_t e = launch_grad_allreduce(p, ctas, world, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return LLMT_B200_OK;
@@ -917,6 +1059,17 @@ int llmt_b200_set_sm_budget(int32_t sms) {
     const int prev = g_sm_budget;
     g_sm_budget = sms;
     return prev;
+}
+
+int llmt_b200_set_wait_limit_ns(uint64_t gemm_ns, uint64_t exchange_ns) {
+    if (gemm_ns != 0) g_wait_limit_ns = gemm_ns;
+    if (exchange_ns != 0) g_comm_wait_limit_ns = exchange_ns;
+    return LLMT_B200_OK;
+}
+
+void llmt_b200_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses) {
+    if (hits != nullptr) *hits = g_map_cache_hits.load(std::memory_order_relaxed);
+    if (misses != nullptr) *misses = g_map_cache_misses.load(std::memory_order_relaxed);
 }
 
 uint64_t llmt_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -33,24 +33,32 @@ constexpr int kMaxGroupProblems = 8;
 
 // One GEMM of a group as the tensor-core kernel sees it.
 struct alignas(64) GroupProblem {
-    CUtensorMap map_a, map_b, map_c;  // operand loads (128B swizzle), C store (32-column slabs)
+    CUtensorMap map_a, map_b;   // operand loads (128B swizzle)
+    CUtensorMap map_c;          // C store: boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+    CUtensorMap map_ws;         // split-K partial sums [batch*splits][m][n] fp32, same boxes
     int64_t m, n, k;
     int32_t batch;
     int32_t tiles_m, tiles_n, splits;
     int32_t kblocks_total;      // ceil(k / 64)
     int32_t kblocks_per_split;  // k-blocks handled by each split (the last one may be shorter)
-    int32_t bn;                 // tile width along N: 64, 128, 192 or 256 (tile height is 128)
+    int32_t bn;                 // tile width along N: 64, 128, 192 or 256 (tile height is 128 per CTA)
     int32_t a_mn, b_mn;         // operand stored with M / N contiguous (transposed use)
-    int32_t tile_begin;         // first tile of this problem in the group's queue
+    int32_t tile_begin;         // first MMA tile of this problem in the group's queue
     int32_t num_tiles;          // tiles_m * tiles_n * splits * batch
+    int32_t colsum_begin;       // first dbias ticket of this problem in the group's queue
+    int32_t colsum_tiles;       // colsum_blocks * splits (0 without a dbias)
+    int32_t colsum_blocks;      // ceil(m / (64 * CTAs per tile))
     void* c;
     int64_t ldc, stride_c;
     int32_t c_is_bf16;
     int32_t c_tma;              // map_c is valid: tiles leave through shared memory + TMA store
+    int32_t ws_tma;             // map_ws is valid
     float alpha, beta;
     const void* bias;
     int32_t bias_is_bf16;
     int32_t epi_flags;
+    const void* a_raw;          // A as the dbias reduction reads it (plain loads): base and row pitch
+    int64_t lda;
     float* ws;                  // split-K partial sums [batch][splits][m][n] fp32 (splits > 1)
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
@@ -58,13 +66,14 @@ struct alignas(64) GroupProblem {
 };
 
 struct GroupParams {
-    CUtensorMap map_ones;       // 64 x 64 block of bf16 1.0 (fused dbias)
     GroupProblem prob[kMaxGroupProblems];
     int32_t num_problems;
-    int32_t total_tiles;
-    int32_t static_schedule;    // 1 = tile i goes to CTA i % grid instead of the dynamic queue
+    int32_t total_tiles;        // tickets of the launch: the dbias tickets first, then the MMA tiles
+    int32_t colsum_total;       // tickets [0, colsum_total) are dbias reductions
+    int32_t static_schedule;    // 1 = ticket i goes to CTA i % grid instead of the dynamic queue
     int32_t* sched_counter;     // zero between launches; the kernel re-arms it
     DeviceStatus* status;
+    uint64_t wait_limit_ns;     // every wait inside the kernel gives up after this long
 };
 
 // ---- gradient all-reduce over peer memory -------------------------------------------------
@@ -88,6 +97,7 @@ struct CommRank {
 struct AllreduceParams {
     CommRank ctx[kMaxCommRanks];     // [0] on a real rank; one per rank when emulated on one device
     int64_t offset, count;           // range of the span, in floats (multiples of 4)
+    uint64_t wait_limit_ns;          // every cross-rank wait gives up after this long
 };
 
 cudaError_t launch_grad_allreduce(const AllreduceParams& p, int ctas, int emulated_ranks, cudaStream_t stream);
@@ -102,6 +112,7 @@ struct TcPlan {
     int tiles_m, tiles_n;
     int kblocks_total, kblocks_per_split;
     int64_t num_tiles;
+    int colsum_blocks;  // dbias tickets per split (0 without a dbias)
     size_t workspace_bytes;
 };
 
@@ -142,9 +153,11 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
 cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream);
 int max_resident_pairs(void);
+int tc_dbias_rows_per_cta(void);
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
 size_t tc_grouped_smem_bytes(void);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
+cudaError_t launch_fp32_rowsum(const Fp32GemmParams& p, float* dbias, float dbias_beta, cudaStream_t stream);
 cudaError_t launch_zero_f32(float* dst, int64_t n, cudaStream_t stream);
 cudaError_t launch_repack_bf16(void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld_src,
                                int64_t ld_dst, int64_t batch, int64_t stride_src, int64_t stride_dst,

@@ -91,61 +91,93 @@ fp32_gemm_kernel(const Fp32GemmParams p) {
     }
 }
 
-// ---- row softmax helpers (fp32 arithmetic; one warp per row) -----------------
-
-__device__ __forceinline__ float warp_reduce_max(float v) {
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+// dbias[i] = dbias_beta * dbias[i] + sum_p op(A)[i, p] on the strict-fp32 path: one thread per
+// i, p ascending, so the order of the additions is fixed.  A parity path, like the GEMM above.
+__global__ void fp32_rowsum_kernel(const Fp32GemmParams p, float* dbias, float dbias_beta) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= p.m) return;
+    float acc = 0.0f;
+    if (p.trans_a) {
+        for (int64_t q = 0; q < p.k; ++q) acc += p.a[q * p.lda + i];   // A stored [k, m]
+    } else {
+        for (int64_t q = 0; q < p.k; ++q) acc += p.a[i * p.lda + q];   // A stored [m, k]
+    }
+    dbias[i] = (dbias_beta != 0.0f ? dbias_beta * dbias[i] : 0.0f) + acc;
 }
-__device__ __forceinline__ float warp_reduce_sum(float v) {
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+
+// ---- masked row softmax and its backward (fp32 arithmetic; one warp per row) ------------------
+
+// Element access that converts at the edges: arithmetic is always fp32.
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float get(const float* p, int64_t i) { return p[i]; }
+    static __device__ __forceinline__ void put(float* p, int64_t i, float v) { p[i] = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float get(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+    static __device__ __forceinline__ void put(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+};
+
+// (running maximum, sum of exp(x - maximum)) of a set of scores; two such pairs merge exactly.
+struct MaxSum {
+    float mx, sum;
+};
+__device__ __forceinline__ MaxSum merge(MaxSum a, MaxSum b) {
+    const float mx = fmaxf(a.mx, b.mx);
+    if (mx == -INFINITY) return MaxSum{mx, 0.0f};
+    return MaxSum{mx, a.sum * expf(a.mx - mx) + b.sum * expf(b.mx - mx)};
 }
 
+// Row softmax with llmt's masking rule (src/kernels/softmax.cu:33-50: under the causal mask
+// only columns <= r % tq take part; the others are written as exact zeros; y may be x).
+// One warp per row, ONE pass over the scores to find (max, sum) - each lane keeps a running
+// pair that is rescaled whenever its maximum grows, the 32 pairs merge in a butterfly - and
+// one pass to write, instead of llmt's three passes.
 template <typename T>
-__device__ __forceinline__ float ldf(const T* p, int64_t i);
-template <>
-__device__ __forceinline__ float ldf<float>(const float* p, int64_t i) { return p[i]; }
-template <>
-__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
-    return __bfloat162float(p[i]);
-}
-__device__ __forceinline__ void stf(float* p, int64_t i, float v) { p[i] = v; }
-__device__ __forceinline__ void stf(__nv_bfloat16* p, int64_t i, float v) {
-    p[i] = __float2bfloat16_rn(v);
-}
-
-template <typename T>
-__global__ void softmax_fwd_kernel(T* y, const T* x, int64_t rows, int64_t tq, int64_t tk,
-                                   int causal) {
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
-    if (row >= rows) return;
-    const int lane = threadIdx.x % 32;
-    const int64_t limit = causal ? (row % tq) + 1 : tk;
-    const T* xr = x + row * tk;
-    T* yr = y + row * tk;
-    float mx = -INFINITY;
-    for (int64_t i = lane; i < limit; i += 32) mx = fmaxf(mx, ldf(xr, i));
-    mx = warp_reduce_max(mx);
-    float sum = 0.0f;
-    for (int64_t i = lane; i < limit; i += 32) sum += expf(ldf(xr, i) - mx);
-    sum = warp_reduce_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int64_t i = lane; i < tk; i += 32)
-        stf(yr, i, i < limit ? expf(ldf(xr, i) - mx) * inv : 0.0f);
+__global__ void softmax_rows_kernel(T* y, const T* x, int64_t rows, int64_t tq, int64_t tk, int causal) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (r >= rows) return;
+    const int64_t live = causal ? (r % tq) + 1 : tk;  // columns that take part
+    const T* in = x + r * tk;
+    T* out = y + r * tk;
+    MaxSum ms{-INFINITY, 0.0f};
+    for (int64_t c = lane; c < live; c += 32) {
+        const float v = Elem<T>::get(in, c);
+        if (v > ms.mx) {
+            ms.sum = ms.sum * expf(ms.mx - v) + 1.0f;  // exp(-inf) = 0 on the first element
+            ms.mx = v;
+        } else {
+            ms.sum += expf(v - ms.mx);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        MaxSum other;
+        other.mx = __shfl_xor_sync(0xffffffffu, ms.mx, o);
+        other.sum = __shfl_xor_sync(0xffffffffu, ms.sum, o);
+        ms = merge(ms, other);
+    }
+    const float scale = 1.0f / ms.sum;
+    for (int64_t c = lane; c < tk; c += 32)
+        Elem<T>::put(out, c, c < live ? expf(Elem<T>::get(in, c) - ms.mx) * scale : 0.0f);
 }
 
+// dS = P * (dP - sum_c dP[c] P[c]) per row (llmt docs/TODO.md:227).  ds may be dp.
 template <typename T>
-__global__ void softmax_bwd_kernel(T* ds, const T* p, const T* dp, int64_t rows, int64_t tk) {
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
-    if (row >= rows) return;
-    const int lane = threadIdx.x % 32;
-    const T* pr = p + row * tk;
-    const T* dr = dp + row * tk;
+__global__ void softmax_rows_bwd_kernel(T* ds, const T* p, const T* dp, int64_t rows, int64_t tk) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (r >= rows) return;
+    const T* pr = p + r * tk;
+    const T* gr = dp + r * tk;
+    T* out = ds + r * tk;
     float dot = 0.0f;
-    for (int64_t i = lane; i < tk; i += 32) dot += ldf(pr, i) * ldf(dr, i);
-    dot = warp_reduce_sum(dot);
-    for (int64_t i = lane; i < tk; i += 32) stf(ds + row * tk, i, ldf(pr, i) * (ldf(dr, i) - dot));
+    for (int64_t c = lane; c < tk; c += 32) dot = fmaf(Elem<T>::get(pr, c), Elem<T>::get(gr, c), dot);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    for (int64_t c = lane; c < tk; c += 32)
+        Elem<T>::put(out, c, Elem<T>::get(pr, c) * (Elem<T>::get(gr, c) - dot));
 }
 
 // Copies a row-major bf16 matrix (any pitch, any 2-byte alignment) into a buffer whose pitch
@@ -228,15 +260,22 @@ cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+cudaError_t launch_fp32_rowsum(const Fp32GemmParams& p, float* dbias, float dbias_beta, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>((p.m + 127) / 128);
+    fp32_rowsum_kernel<<<grid, 128, 0, stream>>>(p, dbias, dbias_beta);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq, int64_t tk,
                                int is_bf16, int causal, cudaStream_t stream) {
-    const int warps = 8;
-    const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+    constexpr int kRowsPerBlock = 4;  // one warp per row
+    const unsigned grid = static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock);
     if (is_bf16)
-        softmax_fwd_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        softmax_rows_kernel<__nv_bfloat16><<<grid, kRowsPerBlock * 32, 0, stream>>>(
             static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), rows, tq, tk, causal);
     else
-        softmax_fwd_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        softmax_rows_kernel<float><<<grid, kRowsPerBlock * 32, 0, stream>>>(
             static_cast<float*>(y), static_cast<const float*>(x), rows, tq, tk, causal);
     count_launch(1);
     return cudaGetLastError();
@@ -244,14 +283,14 @@ cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq,
 
 cudaError_t launch_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
                                int is_bf16, cudaStream_t stream) {
-    const int warps = 8;
-    const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+    constexpr int kRowsPerBlock = 4;
+    const unsigned grid = static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock);
     if (is_bf16)
-        softmax_bwd_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        softmax_rows_bwd_kernel<__nv_bfloat16><<<grid, kRowsPerBlock * 32, 0, stream>>>(
             static_cast<__nv_bfloat16*>(ds), static_cast<const __nv_bfloat16*>(p),
             static_cast<const __nv_bfloat16*>(dp), rows, tk);
     else
-        softmax_bwd_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        softmax_rows_bwd_kernel<float><<<grid, kRowsPerBlock * 32, 0, stream>>>(
             static_cast<float*>(ds), static_cast<const float*>(p), static_cast<const float*>(dp),
             rows, tk);
     count_launch(1);

@@ -1,17 +1,19 @@
 // bf16 x bf16 -> fp32-accumulate GEMM for sm_100a as ONE persistent kernel over
 // a list of problems ("group"): tcgen05 MMA with the accumulator in tensor
 // memory, operands staged in 128-byte-swizzled shared memory by TMA, results
-// leaving through swizzled shared-memory slabs and TMA stores.
+// leaving through swizzled shared-memory buffers and TMA stores.
 //
 // One CTA per SM, 352 threads, warp-specialised:
-//   warp 0      scheduler + TMA producer: draws the next tile from a global counter,
+//   warp 0      scheduler + TMA producer: draws the next ticket from a global counter,
 //               publishes it to the other roles through a small ring in shared memory,
 //               then streams the even k-blocks of that tile's operands
-//   warp 10     second TMA producer (the odd k-blocks)
+//   warp 10     second TMA producer (the odd k-blocks; CTA pairs only)
 //   warp 1      MMA issuer (one lane issues tcgen05.mma / tcgen05.commit; the warp
 //               owns the TMEM allocation)
-//   warps 2-9   epilogue: tcgen05.ld, alpha/beta/bias/GELU/cast, store C (two warps
-//               per TMEM lane quarter, each taking half of the tile's columns)
+//   warps 2-9   epilogue: tcgen05.ld, alpha/beta/bias/GELU/cast, store C.  Two warps per
+//               TMEM lane quarter; each warp drains every other 128-byte-wide column unit of
+//               its 32 rows through staging buffers of its own and issues its own TMA
+//               stores, so no epilogue warp ever waits for another one.
 //
 // Every problem of the group is llmt's row-major  C = alpha*op(A)*op(B) + beta*C
 // (llmt include/llmt/kernels/matmul.h:12-24) with its own shape, transposes, tile
@@ -20,12 +22,17 @@
 // products of Linear::backward (llmt src/layers/linear.cpp:22-30) run as one launch.
 //
 // A transposed operand is not copied: the tile is loaded as stored and described
-// to the tensor core as MN-major.  The fused bias gradient (row sums of op(A)) is
-// an extra 64-wide block of bf16 ones loaded behind the B tile of the tiles in
-// the first tile column, whose MMAs then run with N = bn + 16.
+// to the tensor core as MN-major.
 //
-// No wait is unbounded: every mbarrier wait gives up after kWaitLimitNs, records
-// why in the DeviceStatus word and makes the CTA drain and exit.
+// The fused bias gradient (dbias[i] = sum_p op(A)[i, p]; for the dW product of a linear
+// layer: the column sums of dy) is part of the same launch: its reductions are extra
+// tickets at the head of the queue that the epilogue warps of whichever CTA draws them
+// carry out with plain loads (dy is in L2: the dX and dW tiles of the launch stream it),
+// in a fixed order, while that CTA's producer and MMA warps already work on the next
+// tile.  The tensor pipe never sees them.
+//
+// No wait is unbounded: every mbarrier wait gives up after GroupParams::wait_limit_ns,
+// records why in the DeviceStatus word and makes the CTA drain and exit.
 #include <cuda_bf16.h>
 
 #include <type_traits>
@@ -48,22 +55,21 @@ constexpr int kProducerHelperWarp = 10;  // second TMA producer warp
 constexpr int kMaxStages = 6;
 constexpr int kRing = 4;                             // scheduler ring entries
 constexpr uint32_t kATileBytes = BM * BK * 2;        // 16 KB
-// Per CTA and stage: the A tile plus room for the widest B tile (or a narrower tile and the
-// ones block).  A CTA pair (CG = 2) splits B between its two CTAs, so a stage is smaller
-// and six of them fit where a single CTA has four.
+constexpr uint32_t kStoreBufBytes = 32 * 128;        // one staging buffer: 32 rows x 128 bytes
+// Per CTA and stage: the A tile plus room for the widest B tile.  A CTA pair (CG = 2)
+// splits B between its two CTAs, so a stage is smaller: five of them and two staging
+// buffers per epilogue warp fit where a single CTA has four stages and one buffer.
 template <int CG> struct Geo {
     static constexpr uint32_t kBRegionBytes = (256 / CG) * BK * 2;
     static constexpr uint32_t kStageBytes = kATileBytes + kBRegionBytes;
-    static constexpr int kStages = CG == 2 ? 6 : 4;
+    static constexpr int kStages = CG == 2 ? 5 : 4;
+    static constexpr int kStoreBufs = CG == 2 ? 2 : 1;
+    static constexpr uint32_t kStagingBytes = kEpilogueWarps * kStoreBufs * kStoreBufBytes;
 };
-constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block / the ones block
+constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block
 constexpr uint32_t kAccStride = 256;                 // TMEM columns per accumulator buffer
 constexpr uint32_t kTmemCols = 512;
-constexpr int kDbiasCols = 16;
-constexpr uint32_t kSlabBytes = 128 * 32 * 4;        // 128 rows x 32 columns of fp32
-constexpr uint32_t kStagingBytes = 2 * kSlabBytes;   // one slab per column half
-constexpr uint32_t kOnesRegionBytes = 1024;          // 8 rows x 128 B of bf16 1.0 (pair-mode dbias MMA)
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr int kDbiasColsPerCta = 128;                // columns (rows of op(A)) one CTA reduces per dbias ticket
 
 struct __align__(8) Control {
     uint64_t full[kMaxStages];
@@ -82,7 +88,7 @@ struct __align__(8) Control {
 // accumulators through tcgen05 fences), so the default CTA-scope acquire is enough.
 template <bool CLUSTER = false>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                             DeviceStatus* st, int code, int detail) {
+                                             DeviceStatus* st, int code, int detail, uint64_t limit_ns) {
     auto poll = [&]() { return mbar_try_wait(bar, parity); };
     if (poll()) return true;
     // The wall clock is slow to read: it is first looked at after 256 failed polls, so a wait
@@ -96,7 +102,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > limit_ns) {
                 if (atomicCAS(&st->code, 0, code) == 0) {
                     st->detail = detail;
                     st->block = static_cast<int32_t>(blockIdx.x);
@@ -146,19 +152,20 @@ __device__ __forceinline__ void store_chunk_f32(float* dst, const float* v, int 
     }
 }
 
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 __device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* dst, const float* v, int valid) {
     if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0u) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j + 0], v[j + 1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
             uint4 u;
-            u.x = *reinterpret_cast<uint32_t*>(&h0);
-            u.y = *reinterpret_cast<uint32_t*>(&h1);
-            u.z = *reinterpret_cast<uint32_t*>(&h2);
-            u.w = *reinterpret_cast<uint32_t*>(&h3);
+            u.x = pack_bf16(v[j + 0], v[j + 1]);
+            u.y = pack_bf16(v[j + 2], v[j + 3]);
+            u.z = pack_bf16(v[j + 4], v[j + 5]);
+            u.w = pack_bf16(v[j + 6], v[j + 7]);
             *reinterpret_cast<uint4*>(dst + j) = u;
         }
     } else {
@@ -199,10 +206,123 @@ __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float*
     }
 }
 
+// 16 bytes of an operand that this kernel only reads.
+__device__ __forceinline__ uint4 ld_operand16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void add_bf16x8(float* acc, const uint4& u) {
+    acc[0] += __uint_as_float(u.x << 16); acc[1] += __uint_as_float(u.x & 0xFFFF0000u);
+    acc[2] += __uint_as_float(u.y << 16); acc[3] += __uint_as_float(u.y & 0xFFFF0000u);
+    acc[4] += __uint_as_float(u.z << 16); acc[5] += __uint_as_float(u.z & 0xFFFF0000u);
+    acc[6] += __uint_as_float(u.w << 16); acc[7] += __uint_as_float(u.w & 0xFFFF0000u);
+}
+// Sum over the 32 lanes in a fixed tree (the same on every run and every machine).
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One dbias ticket as one of the eight epilogue warps (ew = 0..7) of a CTA sees it:
+// dbias[i] (+)= sum over p in this split's k range of op(A)[i, p] for the 16 values of i
+// that belong to this warp; the CTA covers kDbiasColsPerCta of them starting at i_cta.
+// Warps work independently (no shared memory, no barrier between warps); the order of the
+// additions depends only on the problem's shape.
+__device__ __noinline__ void dbias_ticket_warp(const GroupProblem& p, int64_t i_cta, int split, int ew, int lane) {
+    const int64_t i0 = i_cta + 16 * ew;
+    if (i0 >= p.m) return;
+    const int64_t kbeg = static_cast<int64_t>(split) * p.kblocks_per_split * BK;
+    int64_t kend = kbeg + static_cast<int64_t>(p.kblocks_per_split) * BK;
+    if (kend > p.k) kend = p.k;
+    const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a_raw);
+    float out = 0.0f;  // lane j < 16 ends with the sum for i0 + j
+    if (p.a_mn) {
+        // A is stored [k, m]: the sums run down columns i0 .. i0+15 (32 bytes of every row).
+        // Lane L takes rows kbeg + L, + 32, ...; eight rows (256 bytes) in flight per lane.
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+        const bool second = i0 + 8 < p.m;   // the row pitch covers whole groups of 8 columns
+        const __nv_bfloat16* col = A + i0;
+        int64_t r = kbeg + lane;
+        for (; r + 7 * 32 < kend; r += 8 * 32) {
+            uint4 q[16];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const __nv_bfloat16* src = col + (r + 32 * u) * p.lda;
+                q[2 * u] = ld_operand16(src);
+                q[2 * u + 1] = second ? ld_operand16(src + 8) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                add_bf16x8(acc, q[2 * u]);
+                add_bf16x8(acc + 8, q[2 * u + 1]);
+            }
+        }
+        for (; r < kend; r += 32) {
+            const __nv_bfloat16* src = col + r * p.lda;
+            add_bf16x8(acc, ld_operand16(src));
+            if (second) add_bf16x8(acc + 8, ld_operand16(src + 8));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float t = lanes_sum(acc[j]);
+            if (lane == j) out = t;
+        }
+    } else {
+        // A is stored [m, k]: the sums run along rows i0 .. i0+15.  Lane L takes the 8 elements
+        // at kbeg + 8 L, + 256, ... of each row; lane 0 also takes the ragged end of the range.
+        const int64_t span = kend - kbeg;
+        const int64_t vec_end = kbeg + span / 8 * 8;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+            const int64_t i = i0 + j;
+            if (i >= p.m) break;  // warp-uniform
+            const __nv_bfloat16* row = A + i * p.lda;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+            for (int64_t q = kbeg + 8 * lane; q < vec_end; q += 256) add_bf16x8(acc, ld_operand16(row + q));
+            float t = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+            if (lane == 0)
+                for (int64_t q = vec_end; q < kend; ++q) t += __bfloat162float(row[q]);
+            t = lanes_sum(t);
+            if (lane == j) out = t;
+        }
+    }
+    const int64_t i = i0 + lane;
+    if (lane < 16 && i < p.m) {
+        if (p.splits > 1) {
+            p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = out;
+        } else {
+            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+            p.dbias[i] = prev + out;
+        }
+    }
+}
+
+// tcgen05.ld fills its destination registers asynchronously until tcgen05.wait::ld.  The
+// compiler must not schedule a read of them ahead of the wait: this empty statement, placed
+// after the wait, makes every later use depend on it.
+__device__ __forceinline__ void after_tmem_ld_wait(uint32_t (&r)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+        asm volatile("" : "+r"(r[j]), "+r"(r[j + 1]), "+r"(r[j + 2]), "+r"(r[j + 3]), "+r"(r[j + 4]), "+r"(r[j + 5]),
+                          "+r"(r[j + 6]), "+r"(r[j + 7]) :: "memory");
+}
+
+template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 template <int CG>
 __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     constexpr int kStages = Geo<CG>::kStages;
     constexpr uint32_t kStageBytes = Geo<CG>::kStageBytes;
+    constexpr int kStoreBufs = Geo<CG>::kStoreBufs;
     constexpr bool kPair = CG == 2;
     constexpr int kTileRows = BM * CG;  // rows of C one scheduled tile covers
     // A pair's leader (cluster rank 0) runs the scheduler and issues the MMAs for both CTAs.
@@ -210,13 +330,13 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     const bool leader = rank == 0;
     const int n_sched = static_cast<int>(gridDim.x) / CG;  // CTAs (pairs) drawing tickets
     const int sched_id = static_cast<int>(blockIdx.x) / CG;
+    const uint64_t wait_ns = gp.wait_limit_ns;
 
     extern __shared__ uint8_t smem_raw[];
-    // Layout: control block, then (1024-byte aligned, as swizzled tiles need) a 1 KB block of
-    // bf16 ones, the operand stages and the epilogue staging slabs.
+    // Layout: control block, then (1024-byte aligned, as swizzled tiles need) the operand
+    // stages and the epilogue warps' staging buffers.
     Control* ctl = reinterpret_cast<Control*>(smem_raw);
-    const uint32_t ones_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
-    const uint32_t smem_base = ones_base + kOnesRegionBytes;
+    const uint32_t smem_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
     const uint32_t staging_base = smem_base + kStages * kStageBytes;
     volatile int* abort_flag = &ctl->abort_flag;
     DeviceStatus* status = gp.status;
@@ -240,12 +360,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
-    if (kPair) {
-        // bf16 1.0 everywhere: reads the same under any swizzle.
-        for (uint32_t i = threadIdx.x; i < kOnesRegionBytes / 4; i += kThreads)
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(ones_base + 4u * i), "r"(0x3F803F80u) : "memory");
-        fence_proxy_async_smem();
-    }
     if (warp == 1) {
         tmem_alloc_cg<CG>(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish_cg<CG>();
@@ -255,7 +369,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
-    // Still independent of the previous kernel in the stream: the first tile ticket (this
+    // Still independent of the previous kernel in the stream: the first ticket (this
     // launch's counter was re-armed by the launch that used it 64 launches ago) and the tensor
     // maps, which the host encoded.
     int first_ticket = 0;
@@ -289,7 +403,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         // warp): one iteration costs a few hundred cycles of barrier and issue latency, which
         // a single warp cannot hide and which would otherwise cap how far loads run ahead.
         // In each the whole warp walks the loop; lane 0 does the barrier bookkeeping and
-        // lane L issues the L-th box of a stage, so the up to seven TMA boxes of a k-block
+        // lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
         // (MN-major operands come in 64-wide blocks) leave in one issue slot.  Warp 0 of the
         // leader also runs the scheduler.
         const bool scheduler = warp == 0 && leader;
@@ -315,7 +429,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (lane == 0) {
                 if (scheduler) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
-                                             kDevWaitSched, slot);
+                                             kDevWaitSched, slot, wait_ns);
                     if (ok) {
                         t = it == 0 ? first_ticket
                                     : (dynamic ? atomicAdd(gp.sched_counter, 1) : prev_ticket + n_sched);
@@ -336,7 +450,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     // In the peer CTA warp 0 arms the ring barrier for the leader's 4-byte store.
                     if (kPair && warp == 0) mbar_arrive_expect_tx(smem_u32(&ctl->sched_full[slot]), 4u);
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
-                                             kDevWaitSched, 48 + slot);
+                                             kDevWaitSched, 48 + slot, wait_ns);
                     if (ok) {
                         t = ctl->ring[slot];
                         release_ring_slot(slot);
@@ -346,14 +460,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             t = __shfl_sync(0xffffffffu, t, 0);
             if (!ok || t < 0) break;
+            if (t < gp.colsum_total) continue;  // a dbias ticket: work for the epilogue warps only
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int bn = p.bn, a_mn = p.a_mn, b_mn = p.b_mn;
             const int bn_cta = bn / CG;                         // B columns this CTA stages
             const int m0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM;
             const int n0 = tc.n_tile * bn + static_cast<int>(rank) * bn_cta;
-            const bool ones = !kPair && p.dbias != nullptr && tc.n_tile == 0;
-            const uint32_t tx = kATileBytes + static_cast<uint32_t>(bn_cta) * (BK * 2) + (ones ? kBlock64Bytes : 0u);
+            const uint32_t tx = kATileBytes + static_cast<uint32_t>(bn_cta) * (BK * 2);
             // This lane's box: destination offset inside the stage, tensor map, and the
             // coordinates (the k coordinate advances with the k-block).
             const int n_a = a_mn ? 2 : 1, n_b = b_mn ? (bn_cta >> 6) : 1;
@@ -361,7 +475,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             uint32_t my_off = 0;
             int my_x = 0, my_y = 0;
             bool k_is_x = false, k_is_y = false;
-            int batch = tc.batch;
             if (lane < n_a) {
                 my_map = &p.map_a;
                 if (a_mn) { my_off = lane * kBlock64Bytes; my_x = m0 + 64 * lane; k_is_y = true; }
@@ -372,16 +485,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 my_off = kATileBytes;
                 if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
-            } else if (lane == n_a + n_b && ones) {
-                my_map = &gp.map_ones;
-                my_off = kATileBytes + static_cast<uint32_t>(bn) * (BK * 2);
-                batch = 0;
             }
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
                 if ((seq & parity_mask) == my_parity) {
                     if (lane == 0) {
                         ok = bounded_wait<kPair>(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, status,
-                                                 kDevWaitSmemEmpty, stage);
+                                                 kDevWaitSmemEmpty, stage, wait_ns);
                         // The leader's barrier counts the bytes of both CTAs of a pair.
                         if (ok && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
                     }
@@ -391,8 +500,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         const int k0 = kb * BK;
                         const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
                         const int x = my_x + (k_is_x ? k0 : 0), y = my_y + (k_is_y ? k0 : 0);
-                        if (kPair) tma_load_3d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, batch);
-                        else tma_load_3d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, batch);
+                        if (kPair) tma_load_3d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, tc.batch);
+                        else tma_load_3d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, tc.batch);
                     }
                 }
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -415,288 +524,242 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 const int slot = it % kRing;
                 const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
                 ok = bounded_wait(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
-                                  kDevWaitSched, 16 + slot);
+                                  kDevWaitSched, 16 + slot, wait_ns);
                 if (!ok) break;
                 const int t = ctl->ring[slot];
                 release_ring_slot(slot);
                 if (t < 0) break;
+                if (t < gp.colsum_total) continue;
                 const TileCoord tc = decode_tile(gp, t);
                 const GroupProblem& p = gp.prob[tc.prob];
-                const bool ones = !kPair && p.dbias != nullptr && tc.n_tile == 0;
-                const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn + (ones ? kDbiasCols : 0), p.a_mn, p.b_mn);
+                const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn, p.a_mn, p.b_mn);
                 const uint32_t step_a = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
                 const uint32_t step_b = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
                 const uint32_t a_lo_base = (smem_base >> 4) | (((p.a_mn ? kBlock64Bytes : 16u) >> 4) << 16);
                 const uint32_t b_lo_base = ((smem_base + kATileBytes) >> 4) |
                                            (((p.b_mn ? kBlock64Bytes : 16u) >> 4) << 16);
-                // In a pair the fused dbias is a second, 16-column MMA per k-step against the ones
-                // block; its accumulator takes the next slot (the other TMEM buffer).
-                const bool dbias2 = kPair && p.dbias != nullptr && tc.n_tile == 0;
                 const int acc = static_cast<int>(acc_seq & 1u);
                 ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc]), ((acc_seq >> 1) & 1u) ^ 1u, abort_flag,
-                                         status, kDevWaitTmemEmpty, acc);
-                if (ok && dbias2)
-                    ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc ^ 1]), (((acc_seq + 1) >> 1) & 1u) ^ 1u,
-                                             abort_flag, status, kDevWaitTmemEmpty, acc ^ 1);
+                                         status, kDevWaitTmemEmpty, acc, wait_ns);
                 if (!ok) break;
                 tc_fence_after_thread_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
-                const uint32_t d_dbias = tmem_base + static_cast<uint32_t>(acc ^ 1) * kAccStride;
-                const uint32_t idesc_dbias = make_idesc_bf16(kTileRows, kDbiasCols, p.a_mn, 0);
-                const uint64_t ones_desc = (static_cast<uint64_t>(kDescHi) << 32) |
-                                           static_cast<uint64_t>((ones_base >> 4) | (1u << 16));
-                // The k loop exists twice: the ordinary tile must not carry the fused-dbias MMA even
-                // as a not-taken branch (in pair form that alone costs a fifth of the MMA rate).
-                auto k_loop = [&](auto with_dbias) {
-                    for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
-                        ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
-                                                 kDevWaitSmemFull, stage);
-                        if (!ok) break;
-                        tc_fence_after_thread_sync();
-                        const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
-                        const uint32_t a_lo = a_lo_base + stage_off;
-                        const uint32_t b_lo = b_lo_base + stage_off;
+                for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+                    ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
+                                             kDevWaitSmemFull, stage, wait_ns);
+                    if (!ok) break;
+                    tc_fence_after_thread_sync();
+                    const uint32_t stage_off = static_cast<uint32_t>(stage) * (kStageBytes >> 4);
+                    const uint32_t a_lo = a_lo_base + stage_off;
+                    const uint32_t b_lo = b_lo_base + stage_off;
 #pragma unroll
-                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                            const uint64_t da = (static_cast<uint64_t>(kDescHi) << 32) |
-                                                static_cast<uint64_t>(a_lo + kk * step_a);
-                            const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
-                                                static_cast<uint64_t>(b_lo + kk * step_b);
-                            umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
-                            if constexpr (decltype(with_dbias)::value)
-                                umma_bf16_cg<CG>(d_dbias, da, ones_desc, idesc_dbias, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
-                        }
-                        umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
-                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t da = (static_cast<uint64_t>(kDescHi) << 32) |
+                                            static_cast<uint64_t>(a_lo + kk * step_a);
+                        const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
+                                            static_cast<uint64_t>(b_lo + kk * step_b);
+                        umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
                     }
-                };
-                if (dbias2) k_loop(std::true_type{});
-                else k_loop(std::false_type{});
+                    umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
                 if (!ok) break;
                 umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc]));
                 ++acc_seq;
-                if (dbias2) {
-                    umma_commit_cg<CG>(smem_u32(&ctl->tmem_full[acc ^ 1]));
-                    ++acc_seq;
-                }
             }
         }
     } else if (warp < 2 + kEpilogueWarps) {
         // ---------------------------------------------------------- epilogue
         const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-        const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp drains
-        const int tile_row = quarter * 32 + lane;
-        const uint32_t slab = staging_base + static_cast<uint32_t>(half) * kSlabBytes;
-        const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
-        uint32_t slab_toggle = 0;
-        bool after_fp32_slab = false;  // the last slab store of this half was an fp32 one
+        const int half = (warp - 2) >> 2;    // this warp takes the column units u with u % 2 == half
+        const int ew = warp - 2;             // 0..7
+        const uint32_t my_bufs = staging_base + static_cast<uint32_t>(ew * kStoreBufs) * kStoreBufBytes;
+        uint32_t buf_seq = 0;  // TMA stores this warp has issued so far
         uint32_t acc_seq = 0;  // accumulator slot counter, in step with the MMA issuer's
         bool ok = true;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
             ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
-                                     kDevWaitSched, 32 + slot);
+                                     kDevWaitSched, 32 + slot, wait_ns);
             if (!ok) break;
             const int t = ctl->ring[slot];
             __syncwarp();
             if (lane == 0) release_ring_slot(slot);
             if (t < 0) break;
+            if (t < gp.colsum_total) {
+                // A dbias ticket: (block of rows of op(A), split) of the problem that owns it.
+                int pi = 0;
+#pragma unroll 1
+                for (int i = 0; i < gp.num_problems; ++i)
+                    if (gp.prob[i].colsum_tiles > 0 && t >= gp.prob[i].colsum_begin) pi = i;
+                const GroupProblem& p = gp.prob[pi];
+                const int r = t - p.colsum_begin;
+                const int blk = r % p.colsum_blocks, split = r / p.colsum_blocks;
+                dbias_ticket_warp(p, (static_cast<int64_t>(blk) * CG + rank) * kDbiasColsPerCta, split, ew, lane);
+                continue;
+            }
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
-            ok = bounded_wait(smem_u32(&ctl->tmem_full[acc]), (acc_seq >> 1) & 1u, abort_flag, status,
-                              kDevWaitTmemFull, acc);
-            if (!ok) break;
-            tc_fence_after_thread_sync();
-            const int row0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM;  // first row of this CTA's half
-            const int64_t row = static_cast<int64_t>(row0) + tile_row;
+            const int row0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM + quarter * 32;  // this warp's first row
+            const int64_t row = static_cast<int64_t>(row0) + lane;
             const bool row_ok = row < p.m;
             const int64_t n0 = static_cast<int64_t>(tc.n_tile) * p.bn;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(acc) * kAccStride;
             const bool partial = p.splits > 1;
-            const bool via_tma = p.c_tma && !partial;
-            const int half_cols = p.bn >> 1;
+            const bool out_bf16 = !partial && p.c_is_bf16;
+            // A column unit is what one TMA store carries: 32 rows x 128 bytes.
+            const int unit_cols = out_bf16 ? 64 : 32;
+            const int spu = out_bf16 ? 2 : 1;  // 32-column steps (one tcgen05.ld each) per unit
+            const bool tma_ok = partial ? p.ws_tma != 0 : p.c_tma != 0;
+            const CUtensorMap* out_map = partial ? &p.map_ws : &p.map_c;
+            const int out_z = partial ? tc.batch * p.splits + tc.split : tc.batch;
+            // Column (inside the tile) of this warp's s-th step.
+            auto step_col = [&](int s) { return (half + 2 * (s / spu)) * unit_cols + (s % spu) * 32; };
+            int ns = ((p.bn / unit_cols + 1 - half) / 2) * spu;
+            while (ns > 0 && n0 + step_col(ns - 1) >= p.n) --ns;
+            if (row0 >= p.m) ns = 0;  // the whole warp lies below the matrix
             if (p.beta != 0.0f && !partial && row_ok) {
-                // beta * C_in is read row by row (one row per thread): ask L2 for this thread's whole
-                // stretch of the row now, so that the chunks below do not each wait for DRAM.  The dW
-                // tiles of a backward launch end last, which puts this read on the launch's tail.
+                // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
+                // lines now, while the tile's main loop is still running.
                 const int esz = p.c_is_bf16 ? 2 : 4;
                 const char* base = static_cast<const char*>(p.c) +
-                                   (static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0 + half * half_cols) * esz;
-                int64_t cols = p.n - (n0 + half * half_cols);
-                if (cols > half_cols) cols = half_cols;
-                for (int64_t off = 0; off < cols * esz; off += 128)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+                                   (static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0) * esz;
+                for (int s = 0; s < ns; s += spu)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<int64_t>(step_col(s)) * esz));
             }
-#pragma unroll 1
-            for (int c0 = half * half_cols; c0 < (half + 1) * half_cols; c0 += 32) {
-                if (n0 + c0 >= p.n) break;  // warp-uniform, and the same in all warps of a half
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + static_cast<uint32_t>(c0), r);
-                tmem_ld_wait();
+            ok = bounded_wait(smem_u32(&ctl->tmem_full[acc]), (acc_seq >> 1) & 1u, abort_flag, status,
+                              kDevWaitTmemFull, acc, wait_ns);
+            if (!ok) break;
+            tc_fence_after_thread_sync();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(acc) * kAccStride;
+            // The accumulator goes back to the MMA issuer (in the leader CTA) as soon as this
+            // warp's last tcgen05.ld has completed.
+            auto release_acc = [&]() {
+                tc_fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (kPair) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc]));
+                    else mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+                }
+            };
+            // One 32-column step: epilogue arithmetic on the values of this thread's row, then
+            // into the staging buffer (and out by TMA once the unit is complete) or, for a
+            // ragged unit or a C that TMA cannot address, straight to global memory.
+            auto emit = [&](const uint32_t (&r)[32], int s) {
+                const int c0 = step_col(s);
                 const int64_t col = n0 + c0;
                 const int valid = static_cast<int>(min(static_cast<int64_t>(32), p.n - col));
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (partial) {
-                    if (row_ok) {
-                        float* dst = p.ws +
-                                     ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + row) * p.n + col;
-                        store_chunk_f32(dst, v, valid);
-                    }
-                    continue;
-                }
-                if (p.alpha != 1.0f) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
-                }
                 const int64_t c_off = static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + col;
-                if (p.beta != 0.0f && row_ok) {
-                    float cin[32];
-                    if (p.c_is_bf16)
-                        load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.c) + c_off, cin, valid);
-                    else
-                        load_chunk_f32(static_cast<const float*>(p.c) + c_off, cin, valid);
+                if (!partial) {
+                    if (p.alpha != 1.0f) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cin[j], v[j]);
-                }
-                if (p.epi_flags & kEpiBias) {
-                    float bv[32];
-                    if (p.bias_is_bf16)
-                        load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.bias) + col, bv, valid);
-                    else
-                        load_chunk_f32(static_cast<const float*>(p.bias) + col, bv, valid);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += bv[j];
-                }
-                if (p.epi_flags & kEpiGelu) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
-                }
-                // TMA clips a box at 16-byte granularity, so a ragged last chunk goes out
-                // through registers instead.
-                if (via_tma && valid == 32) {
-                    // bf16 slabs are half the size of fp32 ones, so a half alternates between
-                    // two of them and only waits for the store before the previous one; an
-                    // fp32 slab is free once the previous TMA store has read it.
-                    // A bf16 chunk needs ONE barrier: the sub-slab it writes was read by the store
-                    // of two chunks ago, and the leader waited for that store before the previous
-                    // chunk's barrier.  After an fp32 chunk (whose store read the whole slab and was
-                    // issued after the last barrier) the half synchronises first.
-                    uint32_t slab_now = slab;
-                    if (p.c_is_bf16) {
-                        slab_now += (slab_toggle & 1u) * (kSlabBytes / 2);
-                        ++slab_toggle;
-                        if (after_fp32_slab) {
-                            if (store_leader) bulk_wait_group_read0();
-                            named_barrier_sync(1 + half, 128);
-                            after_fp32_slab = false;
-                        }
-                    } else {
-                        if (store_leader) bulk_wait_group_read0();
-                        named_barrier_sync(1 + half, 128);
-                        after_fp32_slab = true;
+                        for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
                     }
-                    if (p.c_is_bf16) {
-                        const uint32_t row_addr = slab_now + static_cast<uint32_t>(tile_row) * 64u;
-                        const uint32_t sw = static_cast<uint32_t>(tile_row >> 1) & 3u;
+                    if (p.beta != 0.0f && row_ok) {
+                        float cin[32];
+                        if (p.c_is_bf16)
+                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.c) + c_off, cin, valid);
+                        else
+                            load_chunk_f32(static_cast<const float*>(p.c) + c_off, cin, valid);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * q + 0], v[8 * q + 1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+                        for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cin[j], v[j]);
+                    }
+                    if (p.epi_flags & kEpiBias) {
+                        float bv[32];
+                        if (p.bias_is_bf16)
+                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.bias) + col, bv, valid);
+                        else
+                            load_chunk_f32(static_cast<const float*>(p.bias) + col, bv, valid);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] += bv[j];
+                    }
+                    if (p.epi_flags & kEpiGelu) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
+                    }
+                }
+                const int sub = s % spu;
+                const int64_t unit_col = col - sub * 32;
+                if (tma_ok && unit_col + unit_cols <= p.n) {
+                    const uint32_t buf = my_bufs + (buf_seq % kStoreBufs) * kStoreBufBytes;
+                    if (sub == 0) {
+                        // The buffer is free once the store that last read it has done so.
+                        if (lane == 0) bulk_wait_group_read_n<kStoreBufs - 1>();
+                        __syncwarp();
+                    }
+                    const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+                    const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+                    if (out_bf16) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
                             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
-                                           "r"(*reinterpret_cast<uint32_t*>(&h0)),
-                                           "r"(*reinterpret_cast<uint32_t*>(&h1)),
-                                           "r"(*reinterpret_cast<uint32_t*>(&h2)),
-                                           "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
-                        }
+                                         ::"r"(row_addr + ((static_cast<uint32_t>(sub * 4 + q) ^ sw) << 4)),
+                                           "r"(pack_bf16(v[8 * q + 0], v[8 * q + 1])),
+                                           "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])),
+                                           "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
+                                           "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7])) : "memory");
                     } else {
-                        const uint32_t row_addr = slab_now + static_cast<uint32_t>(tile_row) * 128u;
-                        const uint32_t sw = static_cast<uint32_t>(tile_row) & 7u;
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
+                        for (int q = 0; q < 8; ++q)
                             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
                                          ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
                                            "r"(__float_as_uint(v[4 * q + 0])), "r"(__float_as_uint(v[4 * q + 1])),
                                            "r"(__float_as_uint(v[4 * q + 2])), "r"(__float_as_uint(v[4 * q + 3]))
                                          : "memory");
-                        }
                     }
-                    fence_proxy_async_smem();
-                    // bf16: the store of the previous chunk (the other sub-slab) must have finished
-                    // reading before anybody passes this barrier and starts the next chunk.
-                    if (p.c_is_bf16 && store_leader) bulk_wait_group_read0();
-                    named_barrier_sync(1 + half, 128);
-                    if (store_leader) {
-                        tma_store_3d(&p.map_c, slab_now, static_cast<int32_t>(col), row0, tc.batch);
-                        bulk_commit_group();
+                    if (sub == spu - 1) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z);
+                            bulk_commit_group();
+                        }
+                        ++buf_seq;
                     }
                 } else if (row_ok) {
-                    if (p.c_is_bf16)
-                        store_chunk_bf16(static_cast<__nv_bfloat16*>(p.c) + c_off, v, valid);
-                    else
-                        store_chunk_f32(static_cast<float*>(p.c) + c_off, v, valid);
-                }
-            }
-            if (!kPair && p.dbias != nullptr && tc.n_tile == 0 && half == 0) {
-                // Accumulator column bn holds sum_k op(A)[row, k] (the ones block).
-                uint32_t r[16];
-                tmem_ld_32x16(t_row + static_cast<uint32_t>(p.bn), r);
-                tmem_ld_wait();
-                if (row_ok) {
-                    const float s = __uint_as_float(r[0]);
                     if (partial) {
-                        p.ws_dbias[static_cast<int64_t>(tc.split) * p.m + row] = s;
+                        float* dst = p.ws +
+                                     ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + row) * p.n + col;
+                        store_chunk_f32(dst, v, valid);
+                    } else if (p.c_is_bf16) {
+                        store_chunk_bf16(static_cast<__nv_bfloat16*>(p.c) + c_off, v, valid);
                     } else {
-                        const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[row] : 0.0f;
-                        p.dbias[row] = prev + s;
+                        store_chunk_f32(static_cast<float*>(p.c) + c_off, v, valid);
                     }
                 }
-            }
-            tc_fence_before_thread_sync();
-            __syncwarp();
-            if (lane == 0) {
-                // The accumulator buffer goes back to the MMA issuer (in the leader CTA).
-                if (kPair) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc]));
-                else mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+            };
+            // Software pipeline over the steps: the tcgen05.ld of step s+1 is in flight while
+            // step s is converted and staged.
+            if (ns == 0) {
+                release_acc();
+            } else {
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(0)), ra);
+#pragma unroll 1
+                for (int s = 0; s < ns; s += 2) {
+                    tmem_ld_wait();
+                    after_tmem_ld_wait(ra);
+                    if (s + 1 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 1)), rb);
+                    else release_acc();
+                    emit(ra, s);
+                    if (s + 1 < ns) {
+                        tmem_ld_wait();
+                        after_tmem_ld_wait(rb);
+                        if (s + 2 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 2)), ra);
+                        else release_acc();
+                        emit(rb, s + 1);
+                    }
+                }
             }
             ++acc_seq;
-            if (kPair && p.dbias != nullptr && tc.n_tile == 0) {
-                // The pair's dbias accumulator: column 0 of the next slot holds sum_k op(A)[row, k].
-                const int acc2 = static_cast<int>(acc_seq & 1u);
-                ok = bounded_wait(smem_u32(&ctl->tmem_full[acc2]), (acc_seq >> 1) & 1u, abort_flag, status,
-                                  kDevWaitTmemFull, acc2);
-                if (!ok) break;
-                tc_fence_after_thread_sync();
-                if (half == 0) {
-                    uint32_t r[16];
-                    tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                      static_cast<uint32_t>(acc2) * kAccStride, r);
-                    tmem_ld_wait();
-                    if (row_ok) {
-                        const float sum = __uint_as_float(r[0]);
-                        if (partial) {
-                            p.ws_dbias[static_cast<int64_t>(tc.split) * p.m + row] = sum;
-                        } else {
-                            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[row] : 0.0f;
-                            p.dbias[row] = prev + sum;
-                        }
-                    }
-                }
-                tc_fence_before_thread_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(on_leader(&ctl->tmem_empty[acc2]));
-                ++acc_seq;
-            }
         }
         // Outstanding TMA stores must complete before the shared memory goes away.
-        if (store_leader) bulk_wait_group0();
+        if (lane == 0) bulk_wait_group0();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -780,26 +843,34 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
 }  // namespace
 
 size_t tc_grouped_smem_bytes() {
-    // Both geometries use the same amount: 4 x 48 KB or 6 x 32 KB of operand stages.
-    static_assert(Geo<1>::kStages * Geo<1>::kStageBytes == Geo<2>::kStages * Geo<2>::kStageBytes, "stage budget");
+    // Both geometries use the same amount: 4 x 48 KB of operand stages + 32 KB of staging,
+    // or 5 x 32 KB + 64 KB.
+    static_assert(Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes ==
+                  Geo<2>::kStages * Geo<2>::kStageBytes + Geo<2>::kStagingBytes, "shared-memory budget");
     static_assert(sizeof(Control) <= 1024, "control block must fit below the first aligned KB");
-    return 1024 /* control block + alignment */ + kOnesRegionBytes + Geo<1>::kStages * Geo<1>::kStageBytes +
-           kStagingBytes;
+    return 1024 /* control block + alignment */ + Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes;
+}
+
+int tc_dbias_rows_per_cta() { return kDbiasColsPerCta; }
+
+// Per-device record of what has been configured (cudaFuncSetAttribute is per device).
+static bool g_configured[64];
+
+static cudaError_t configure_device(int dev) {
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (g_configured[dev]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(tc_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) g_configured[dev] = true;
+    return e;
 }
 
 cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream) {
-    static int configured_device = -1;
     int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(tc_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             227 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     227 * 1024);
-        if (e != cudaSuccess) return e;
-        configured_device = dev;
-    }
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = configure_device(dev);
+    if (e != cudaSuccess) return e;
     // Programmatic dependent launch: the kernel's prologue (barriers, TMEM) overlaps the tail
     // of the previous kernel in the stream; the kernel itself waits before touching memory.
     cudaLaunchAttribute attr[1];
@@ -812,26 +883,31 @@ cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaS
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_kernel, gp)
-                                : cudaLaunchKernelEx(&cfg, tc_grouped_kernel, gp);
+    e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_kernel, gp)
+              : cudaLaunchKernelEx(&cfg, tc_grouped_kernel, gp);
     count_launch(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-// How many CTA pairs can be resident at once (1 CTA per SM, pairs share a cluster).
+// How many CTA pairs can be resident at once on the current device (1 CTA per SM, pairs
+// share a cluster); -1 when the query fails.
 int max_resident_pairs() {
-    static int cached = 0;
-    if (cached == 0) {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (cached[dev] == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2, 1, 1);
         cfg.blockDim = dim3(kThreads, 1, 1);
         cfg.dynamicSmemBytes = tc_grouped_smem_bytes();
-        cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, tc_grouped_pair_kernel, &cfg) == cudaSuccess && n > 0) cached = n;
-        else cached = -1;
+        if (configure_device(dev) == cudaSuccess &&
+            cudaOccupancyMaxActiveClusters(&n, tc_grouped_pair_kernel, &cfg) == cudaSuccess && n > 0)
+            cached[dev] = n;
+        else
+            cached[dev] = -1;
     }
-    return cached;
+    return cached[dev];
 }
 
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream) {

@@ -20,7 +20,8 @@
 // with the same bits and reruns reproduce them.  Flags are call counters (kept per CTA in the
 // rank's own memory), so a captured launch can be replayed; staging slots are free again when
 // the call returns because the join of a rank follows every peer's reduce.
-// Every wait gives up after kCommWaitNs, records kDevWaitPeer and lets the kernel finish.
+// Every wait gives up after AllreduceParams::wait_limit_ns, records kDevWaitPeer and lets the
+// kernel finish.
 //
 // Data movement: one thread per CTA drives the copy engine.  Push is a ring of 16 KB buffers
 // (bulk load from the own span, bulk store into the peer's staging slot, eight loads in
@@ -35,8 +36,6 @@ namespace llmt_b200 {
 namespace {
 
 using namespace ptx;
-
-constexpr uint64_t kCommWaitNs = 4000000000ull;
 
 constexpr uint32_t kPushChunk = 16384;                 // bytes per ring buffer
 constexpr int kPushBufs = 12, kPushAhead = 8;          // ring size, loads in flight
@@ -86,7 +85,8 @@ __device__ __forceinline__ void record_failure(const CommRank& c, int detail, in
 }
 
 // Bounded wait on a local mbarrier (bulk loads from this GPU's own memory land on it).
-__device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity, const CommRank& c, int g, int* s_ok) {
+__device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity, const CommRank& c, int g, int* s_ok,
+                                          uint64_t limit_ns) {
     // the wall clock is slow to read: it is first looked at after 256 failed polls
     uint64_t t0 = 0;
     uint32_t spins = 0;
@@ -96,7 +96,7 @@ __device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity, const C
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kCommWaitNs) {
+            } else if (now - t0 > limit_ns) {
                 record_failure(c, 1024, g, s_ok);
                 return false;
             }
@@ -106,7 +106,8 @@ __device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity, const C
 }
 
 // Thread `tid` < world (tid != me) waits until the flag written by rank tid reaches `e`.
-__device__ __forceinline__ void wait_peers(const CommRank& c, int phase, int g, uint32_t e, int* s_ok) {
+__device__ __forceinline__ void wait_peers(const CommRank& c, int phase, int g, uint32_t e, int* s_ok,
+                                           uint64_t limit_ns) {
     const int tid = threadIdx.x;
     if (tid < c.world && tid != c.rank) {
         const uint32_t* f = c.flags[c.rank] + (phase * kMaxCommRanks + tid) * kMaxCommCtas + g;
@@ -117,7 +118,7 @@ __device__ __forceinline__ void wait_peers(const CommRank& c, int phase, int g, 
                 const uint64_t now = globaltimer_ns();
                 if (t0 == 0) {
                     t0 = now;
-                } else if (now - t0 > kCommWaitNs) {
+                } else if (now - t0 > limit_ns) {
                     record_failure(c, phase * 256 + tid, g, s_ok);
                     break;
                 }
@@ -202,7 +203,8 @@ grad_allreduce_kernel(const AllreduceParams P) {
             const int64_t hi = hi_of(sc.d);
             const int64_t len4 = hi - sc.pos < kChunk4 ? hi - sc.pos : kChunk4;
             const int b = static_cast<int>(n_stored % kPushBufs);
-            ok = wait_full(smem_u32(&full_bar[b]), static_cast<uint32_t>((n_stored / kPushBufs) & 1), c, g, &s_ok);
+            ok = wait_full(smem_u32(&full_bar[b]), static_cast<uint32_t>((n_stored / kPushBufs) & 1), c, g, &s_ok,
+                           P.wait_limit_ns);
             if (!ok) break;
             bulk_store(reinterpret_cast<float4*>(c.stage[s]) + me * slot4 + sc.pos, smem_base + b * kPushChunk,
                        static_cast<uint32_t>(len4 * 16));
@@ -219,7 +221,7 @@ grad_allreduce_kernel(const AllreduceParams P) {
         raise_flags(c, 0, g, e);
     }
     // ---- 2. sum my own shard in rank order and hand the result to everybody ------------------
-    wait_peers(c, 0, g, e, &s_ok);
+    wait_peers(c, 0, g, e, &s_ok, P.wait_limit_ns);
     {
         const int64_t base = me * shard4;
         int64_t hi = n4 - base;
@@ -274,7 +276,7 @@ grad_allreduce_kernel(const AllreduceParams P) {
     }
 
     // ---- 3. my span is complete once every peer has delivered its shard ----------------------
-    wait_peers(c, 1, g, e, &s_ok);
+    wait_peers(c, 1, g, e, &s_ok, P.wait_limit_ns);
     if (tid == 0) c.epoch[g] = e;
 }
 
@@ -318,7 +320,7 @@ grad_allreduce_mc_kernel(const AllreduceParams P) {
 
     // 0. every rank's partial sums are in place (they were written by earlier kernels)
     if (tid < W && tid != me) st_release_sys(c.flags[tid] + (0 * kMaxCommRanks + me) * kMaxCommCtas + g, e);
-    wait_peers(c, 0, g, e, &s_ok);
+    wait_peers(c, 0, g, e, &s_ok, P.wait_limit_ns);
 
     // 1. my shard: sum in the switch, broadcast to everybody
     float4* mc = reinterpret_cast<float4*>(c.grad_mc + P.offset) + me * shard4;
@@ -337,7 +339,7 @@ grad_allreduce_mc_kernel(const AllreduceParams P) {
     __threadfence_system();
     __syncthreads();
     if (tid < W && tid != me) st_release_sys(c.flags[tid] + (1 * kMaxCommRanks + me) * kMaxCommCtas + g, e);
-    wait_peers(c, 1, g, e, &s_ok);
+    wait_peers(c, 1, g, e, &s_ok, P.wait_limit_ns);
     if (tid == 0) c.epoch[g] = e;
 }
 
@@ -350,12 +352,16 @@ cudaError_t launch_grad_allreduce_mc(const AllreduceParams& p, int ctas, cudaStr
 }
 
 cudaError_t launch_grad_allreduce(const AllreduceParams& p, int ctas, int emulated_ranks, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64];  // the attribute is per device
+    int dev = 0;
+    cudaError_t e0 = cudaGetDevice(&dev);
+    if (e0 != cudaSuccess) return e0;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(grad_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(kCommSmemBytes));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured[dev] = true;
     }
     cudaError_t e;
     if (emulated_ranks > 0) {

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(set(declared_symbols())) == sorted(set(L.EXPORTS) | set(declared_symbols()))
-    assert lib.llmt_b200_abi_version() == 1
+    assert lib.llmt_b200_abi_version() == 2
 
 
 def test_descriptor_layout_matches_the_header():
@@ -85,16 +85,67 @@ def test_null_and_overlapping_pointers_are_rejected():
     assert _call(d, c=A + 64) == L.ERR_INVALID and "overlaps" in L.last_error()
 
 
-def test_unaligned_bf16_base_is_reported_not_run():
-    assert _call(_desc(), a=A + 2) == L.ERR_UNSUPPORTED
-    assert "16-byte" in L.last_error()
+def test_unaligned_bf16_base_needs_scratch_for_an_aligned_copy():
+    # a slice such as x[:, 1:] starts at an odd address: TMA cannot read it in place
+    d = _desc()
+    assert _call(d, a=A + 2) == L.ERR_WORKSPACE and "repacked operands" in L.last_error()
+    lib = L.lib()
+    assert lib.llmt_b200_gemm_workspace_bytes(ctypes.byref(d)) == 0
+    need = lib.llmt_b200_gemm_workspace_bytes_for(ctypes.byref(d), ctypes.c_void_p(A + 2), ctypes.c_void_p(B))
+    assert need == 128 * 64 * 2  # one aligned copy of A
 
 
 def test_dbias_contract():
-    d = _desc(dbias=0x80000, dtype_ab=L.FP32)
-    assert _call(d) == L.ERR_UNSUPPORTED and "dbias" in L.last_error()
-    d = _desc(dbias=0x80000, plan_tile_n=256)
-    assert _call(d) == L.ERR_INVALID and "single CTAs" in L.last_error()
+    d = _desc(dbias=0x80000, batch=2, stride_a=128 * 64, stride_b=128 * 64, stride_c=128 * 128)
+    assert _call(d) == L.ERR_UNSUPPORTED and "batched" in L.last_error()
+
+
+def test_dimensions_above_int32_are_refused():
+    big = 1 << 31
+    d = _desc(m=big, ldc=128)
+    assert _call(d) == L.ERR_UNSUPPORTED and "2^31" in L.last_error()
+    d = _desc(k=big, lda=big, ldb=big)
+    assert _call(d) == L.ERR_UNSUPPORTED and "2^31" in L.last_error()
+
+
+def test_written_ranges_must_not_overlap_anything_else():
+    # C is 128 x 128 fp32 at C; A and B are 128 x 64 bf16
+    assert _call(_desc(dbias=C + 256)) == L.ERR_INVALID and "dbias overlaps C" in L.last_error()
+    assert _call(_desc(dbias=A + 16)) == L.ERR_INVALID and "dbias overlaps A" in L.last_error()
+    d = _desc(workspace=B + 1024, workspace_bytes=4096)
+    assert _call(d) == L.ERR_INVALID and "workspace overlaps B" in L.last_error()
+    d = _desc(epilogue=L.EPI_BIAS, bias=0x90000, bias_dtype=L.FP32, workspace=0x90000 + 256, workspace_bytes=4096)
+    assert _call(d) == L.ERR_INVALID and "workspace overlaps bias" in L.last_error()
+    d = _desc(dbias=0x90000, workspace=0x90000, workspace_bytes=4096)
+    assert _call(d) == L.ERR_INVALID and "dbias overlaps workspace" in L.last_error()
+
+
+def _grouped(descs, cs, as_, bs):
+    n = len(descs)
+    arr = (L.GemmDesc * n)(*descs)
+    vp = lambda xs: (ctypes.c_void_p * n)(*xs)
+    return L.lib().llmt_b200_gemm_grouped(arr, vp(cs), vp(as_), vp(bs), n, None)
+
+
+def test_grouped_problems_are_checked_by_address_range():
+    d0, d1 = _desc(), _desc()
+    # problem 1 reads, as its A, a view into the middle of what problem 0 writes
+    assert _grouped([d0, d1], [C, 0x80000], [A, C + 4096], [B, B]) == L.ERR_INVALID
+    assert "not independent" in L.last_error()
+    # two C views into one buffer at different offsets
+    assert _grouped([d0, d1], [C, C + 512], [A, A], [B, B]) == L.ERR_INVALID
+    assert "not independent" in L.last_error()
+    # a dbias of one problem inside the C of the other
+    assert _grouped([_desc(dbias=0x80000 + 64), d1], [C, 0x80000], [A, A], [B, B]) == L.ERR_INVALID
+
+
+def test_forced_pairs_are_refused_in_a_launch_that_cannot_pair():
+    # plan_cta_pairs = 2 on a problem that shares its launch with one that has m <= 128: the launch
+    # would fall back to single CTAs; that is reported, not done silently
+    wide = _desc(m=512, n=256, k=64, ldc=256, plan_cta_pairs=2, plan_tile_n=256, dbias=0x5000000)
+    small = _desc()
+    assert _grouped([wide, small], [0x1000000, 0x2000000], [A, A], [B, B]) == L.ERR_INVALID
+    assert "asks for CTA pairs" in L.last_error()
 
 
 def test_empty_output_is_a_no_op():
@@ -194,14 +245,14 @@ def test_exchange_layout_is_aligned_and_large_enough():
         exchange_layout(6, 2)
 
 
-def test_fused_dbias_products_take_pairs_only_when_tiles_outnumber_them():
-    # dW + dbias of GPT-2-XL's MLP (6400 x 1600 over 8192 tokens): 25 x 7 pair tiles >= 2 x 74 pairs
-    big = _desc(m=6400, n=1600, k=8192, trans_a=1, trans_b=0, lda=6400, ldb=1600, ldc=1600,
-                dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
-    assert "cta-pair" in L.plan(big)
-    # the same product of GPT-2-small's QKV layer has 9 x 3 pair tiles: single CTAs
-    small = _desc(m=2304, n=768, k=8192, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
-                  dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
-    assert "1-cta" in L.plan(small)
-    small.plan_cta_pairs = 2  # still available on request
-    assert "cta-pair" in L.plan(small)
+def test_fused_dbias_products_run_on_pairs_with_full_width_tiles():
+    # dW + dbias: the bias gradient is reduced by tickets of its own, so the product may use
+    # any tile width, on CTA pairs too (the QKV layer of GPT-2-small: 2304 x 768 over 8192 tokens)
+    d = _desc(m=2304, n=768, k=8192, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
+              dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
+    plan = L.plan(d)
+    assert "cta-pair tile=256x" in plan and "dbias_tickets=9 " in plan  # 2304 / (2 x 128) row blocks
+    d.plan_tile_n = 256
+    assert "cta-pair tile=256x256x64" in L.plan(d)
+    d.plan_cta_pairs = 1
+    assert "1-cta tile=128x256x64" in L.plan(d) and "splits=2 " in L.plan(d) and "dbias_tickets=36 " in L.plan(d)
