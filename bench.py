@@ -2,18 +2,24 @@
 """Benchmark of the GEMM path: one "step" = the linear-layer GEMMs of a training
 step (forward, dX, dW+dbias for every layer) on synthetic seeded inputs.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3c|c4|c5] [--impl reference]
 
 Workloads (shapes of the reference's benchmark configurations):
   c2  GPT-2-small, M = 8192 tokens per GPU, C = 768: QKV 768->2304, attention
       out-proj 768->768, MLP fc 768->3072 (bias+GELU fused), MLP proj 3072->768;
       bf16 operands, fp32 accumulation, bf16 activations, fp32 dW/dbias.
   c5  GPT-2-XL MLP, C = 1600, 4C = 6400, M = 8192 tokens per GPU.
-  c3  LM head 768->50257 (row pitch 50264, fp32 logits); c4 the six attention products.
-With N > 1 every GPU runs the same per-GPU workload on its own token shard
-(weak scaling) and the fp32 dW/dbias span is summed layer by layer on a side stream
-(--exchange: the library's kernel through NVSwitch multicast or peer copies, or NCCL),
-overlapped with the backward launches of the remaining layers.
+  c3  LM head 768->50257, fp32 logits, row pitch 50264; c3c the same with contiguous
+      [tokens, 50257] logits and dLogits; c4 the six attention products.
+The headline (`value`) is c2.  At N = 1 the default run also times the other workloads
+(`workloads`), every GEMM of c2 on its own next to cuBLASLt called the way llmt calls it but
+with bf16 operands (`comparators`), a two-second replay of the step (`sustained`) and the CPU
+baselines.  With N > 1 every GPU runs the same per-GPU workload on its own token shard (weak
+scaling) and the fp32 dW/dbias span is summed layer by layer on a side stream (--exchange:
+the library's kernel through NVSwitch multicast or peer copies, or NCCL), overlapped with
+the backward launches of the remaining layers; the sum is checked against NCCL's
+(`exchange_check`) and config 5's literal form, M = 65536 split N ways, is timed too
+(`config.c5_strong`).
 
 Prints ONE JSON line. `value` is device-timed throughput with inputs resident in
 HBM; `e2e` is the same step called with HOST (pinned) buffers, copies included.
@@ -39,11 +45,16 @@ LAYERS = {
                        ("mlp_fc", 768, 3072, True), ("mlp_proj", 3072, 768, False)]),
     "c5": dict(name="gpt2-xl MLP", C=1600,
                layers=[("mlp_fc", 1600, 6400, True), ("mlp_proj", 6400, 1600, False)]),
-    # tied-embedding LM head: fp32 logits, no bias, vocabulary 50257 in a row pitch of 50264
+    # tied-embedding LM head: fp32 logits, no bias, vocabulary 50257 in a row pitch of 50264 ...
     "c3": dict(name="LM head, vocab 50257 (row pitch 50264), fp32 logits", C=768, bias=False, y_fp32=True,
                ld_out=50264, layers=[("lm_head", 768, 50257, False)]),
+    # ... or contiguous (row pitch 50257: TMA cannot address it; logits leave through registers,
+    # dLogits is first copied to an aligned pitch)
+    "c3c": dict(name="LM head, vocab 50257 (contiguous), fp32 logits", C=768, bias=False, y_fp32=True,
+                ld_out=50257, layers=[("lm_head", 768, 50257, False)]),
 }
 M_PER_GPU = 8192
+L2_BYTES = 126 << 20
 
 
 def step_flops(workload: str, m: int) -> float:
@@ -54,12 +65,23 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
-    return 1590.0, 6650.0, "fallback"
+        return {"tf": float(d["bf16_tflops"]), "tf_sustained": float(d.get("bf16_tflops_sustained", 1400.0)),
+                "bw": float(d["hbm_gbs"]), "which": "measured"}
+    return {"tf": 1590.0, "tf_sustained": 1400.0, "bw": 6650.0, "which": "fallback"}
+
+
+def recorded_traffic(workload: str):
+    """DRAM bytes per step from the ncu capture recorded under profiles/ (null when none is
+    recorded for this workload)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        return json.load(open(path)).get(workload)
+    except (OSError, ValueError):
+        return None
 
 
 class ClockSampler:
-    """Samples SM clock, power and clock-event reasons of one GPU while the timed region runs:
+    """Samples SM clock, power and clock-event reasons of one GPU while a timed region runs:
     NVML polled every 2 ms from a thread (read-only queries), nvidia-smi at 100 ms as fallback."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -84,7 +106,7 @@ class ClockSampler:
             self.nvml = (pynvml, h)
             self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
-            return
+            return self
         except Exception:
             self.nvml = None
         try:
@@ -95,6 +117,7 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _poll(self):
         pynvml, h = self.nvml
@@ -119,6 +142,7 @@ class ClockSampler:
             self.stop_flag = True
             self.thread.join(timeout=1.0)
             pynvml, _ = self.nvml
+
             def bit(event_name, throttle_name, default):
                 return getattr(pynvml, event_name, getattr(pynvml, throttle_name, default))
             bits = {"hw_slowdown": bit("nvmlClocksEventReasonHwSlowdown", "nvmlClocksThrottleReasonHwSlowdown", 0x8),
@@ -154,24 +178,42 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms period"}
 
 
+def make_sampler(torch, dev):
+    props = torch.cuda.get_device_properties(dev)
+    try:
+        pci = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+    except AttributeError:
+        pci = None
+    return ClockSampler(dev.index or 0, pci)
+
+
 # --------------------------------------------------------------------- own arm ---
 
 class LinearStep:
-    """Device tensors and prebuilt C-ABI descriptors of one training step's GEMMs."""
+    """Device tensors and prebuilt C-ABI descriptors of one training step's GEMMs.
 
-    def __init__(self, workload, m, dev, seed, world=1, exchange="peer", comm_ctas=8, split_last=False):
+    Launch order (what a network's data dependencies allow): the forward of every layer, then,
+    walking the layers backwards, one launch per layer that holds its dX and dW + dbias
+    (llmt's Linear::backward, src/layers/linear.cpp:22-30, as one grouped launch).  With
+    `defer` = {layer: later layer}, the dW + dbias of `layer` is not launched with its own dX
+    but rides in the backward launch of `later layer`, which runs after it: dW depends on
+    nothing but dy and x of its own layer, so it may run any time after them, and a short
+    layer's few long dW tiles balance better inside a larger launch."""
+
+    def __init__(self, workload, m, dev, seed, world=1, exchange="peer", comm_ctas=8, defer=None):
         import torch
         import llmt_b200 as L
         from llmt_b200.dp import GradBucket, PeerExchange
-        self.L, self.torch, self.m = L, torch, m
+        self.L, self.torch, self.m, self.workload = L, torch, m, workload
         g = torch.Generator(device=dev).manual_seed(seed)
         bf = torch.bfloat16
         cfg = LAYERS[workload]
         spec = cfg["layers"]
         has_bias = cfg.get("bias", True)
+        self.has_bias = has_bias
         shapes = {k: v for n, i, o, _ in spec for k, v in ((n + ".dW", (o, i)), (n + ".dbias", (o,)))}
         # N > 1: the span lives in peer-mapped memory and is summed by the library's own kernel
-        # over NVLink ("peer"), or stays private and goes through NCCL ("nccl")
+        # over NVLink ("peer" / "nvls"), or stays private and goes through NCCL ("nccl")
         self.exchange = None
         if world > 1 and exchange in ("peer", "nvls"):
             try:
@@ -188,90 +230,102 @@ class LinearStep:
                 self.exchange.ctas = 16
                 L.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - 16)
         self.bucket = GradBucket(shapes, dev, storage=self.exchange.attach if self.exchange else None)
-        self.layers, self.calls = [], []
+        self.layers = []
         for n, i, o, gelu in spec:
             t = dict(name=n, gelu=gelu, i=i, o=o)
             ld = cfg.get("ld_out", o)  # row pitch of the [m, out] tensors (padded vocabulary)
             t["x"] = torch.randn(m, i, device=dev, generator=g).to(bf)
             t["w"] = (torch.randn(o, i, device=dev, generator=g) * 0.02).to(bf)
             t["b"] = torch.randn(o, device=dev, generator=g) * 0.02 if has_bias else None
-            t["dy"] = (torch.randn(m, ld, device=dev, generator=g) * 0.01).to(bf)[:, :o]
+            scale = 1e-4 if workload.startswith("c3") else 0.01
+            t["dy"] = (torch.randn(m, ld, device=dev, generator=g) * scale).to(bf)[:, :o]
             t["y"] = torch.empty(m, ld, device=dev, dtype=torch.float32 if cfg.get("y_fp32") else bf)[:, :o]
             t["dx"] = torch.empty(m, i, device=dev, dtype=bf)
             t["dw"], t["db"] = self.bucket.view(n + ".dW"), self.bucket.view(n + ".dbias")
             self.layers.append(t)
-        for t in self.layers:
-            t["d_fwd"] = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
-            # Linear::backward as one launch: dx = dy W and dW += dy^T x (+ dbias) share a tile queue
-            dx = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
-            dw = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0,
-                             dbias=t["db"] if has_bias else None, dbias_beta=1.0)
-            t["bwd"] = L.Group([(dx, t["dx"], t["dy"], t["w"]), (dw, t["dw"], t["dy"], t["x"])])
-            # N > 1: the layer whose backward runs last launches dW on its own, ahead of dX, so that
-            # the exchange of its gradients overlaps its dX instead of trailing the step
-            if world > 1 and split_last and t is self.layers[0]:
-                dx2 = L.make_desc(t["dx"], t["dy"], t["w"], False, False)
-                dw2 = L.make_desc(t["dw"], t["dy"], t["x"], True, False, beta=1.0,
-                                  dbias=t["db"] if has_bias else None, dbias_beta=1.0)
-                t["bwd_dw"] = L.Group([(dw2, t["dw"], t["dy"], t["x"])])
-                t["bwd_dx"] = L.Group([(dx2, t["dx"], t["dy"], t["w"])])
-        # one scratch buffer per problem that needs one (split-K partial sums)
+        by_name = {t["name"]: t for t in self.layers}
+        defer = {k: v for k, v in (defer or {}).items() if k in by_name and v in by_name}
+        riders = {}
+        for src, dst in defer.items():
+            riders.setdefault(dst, []).append(by_name[src])
         self.ws = []
         for t in self.layers:
-            need = L.workspace_bytes(t["d_fwd"])
+            t["d_fwd"] = L.make_desc(t["y"], t["x"], t["w"], False, True, bias=t["b"], gelu=t["gelu"])
+            need = L.workspace_bytes(t["d_fwd"], t["x"], t["w"])
             buf = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
             t["d_fwd"].workspace, t["d_fwd"].workspace_bytes = buf.data_ptr(), buf.numel()
             self.ws.append(buf)
-            for key in ("bwd", "bwd_dw", "bwd_dx"):
-                if key in t:
-                    bufs = [torch.empty(max(b, 256), dtype=torch.uint8, device=dev) for b in t[key].workspace_bytes()]
-                    t[key].set_workspaces(bufs)
-                    self.ws += bufs
+
+            def dw_problem(u):
+                return (L.make_desc(u["dw"], u["dy"], u["x"], True, False, beta=1.0,
+                                    dbias=u["db"] if has_bias else None, dbias_beta=1.0), u["dw"], u["dy"], u["x"])
+            probs = [(L.make_desc(t["dx"], t["dy"], t["w"], False, False), t["dx"], t["dy"], t["w"])]
+            t["carries"] = []
+            if t["name"] not in defer:
+                probs.append(dw_problem(t))
+                t["carries"].append(t)
+            for u in riders.get(t["name"], []):
+                probs.append(dw_problem(u))
+                t["carries"].append(u)
+            t["bwd"] = L.Group(probs)
+            bufs = [torch.empty(max(b, 256), dtype=torch.uint8, device=dev) for b in t["bwd"].workspace_bytes()]
+            t["bwd"].set_workspaces(bufs)
+            self.ws += bufs
+            t["bwd_flops"] = 2.0 * m * t["i"] * t["o"] + sum(2.0 * m * u["i"] * u["o"] for u in t["carries"])
         self.comm_stream = torch.cuda.Stream(device=dev)
+        self.flops = step_flops(workload, m)
 
     def launches(self):
-        """(label, flops, callable) in launch order: forwards, then the backward of every layer."""
+        """(label, flops, callable, layers whose gradients are complete after it) in launch order."""
         out = []
         for t in self.layers:
             f = 2.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), None))
+            out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), []))
         for t in reversed(self.layers):
-            f = 4.0 * self.m * t["i"] * t["o"]
-            if "bwd_dw" in t:
-                out.append((t["name"] + ".bwd(dW)", f / 2, t["bwd_dw"].run, t))
-                out.append((t["name"] + ".bwd(dX)", f / 2, t["bwd_dx"].run, None))
-            else:
-                out.append((t["name"] + ".bwd(dX+dW)", f, t["bwd"].run, t))
+            label = t["name"] + ".bwd(dX" + "".join("+dW_" + u["name"] for u in t["carries"]) + ")"
+            out.append((label, t["bwd_flops"], t["bwd"].run, t["carries"]))
         return out
 
-    def grad_slice(self, t):
-        """The layer's dW and dbias are adjacent in the flat span: one view covers both."""
-        lo = self.bucket.offsets[t["name"] + ".dW"][0]
-        off, n, _ = self.bucket.offsets[t["name"] + ".dbias"]
-        return self.bucket.flat[lo:off + n]
+    def exchange_layers(self, layers):
+        """Sums the dW + dbias slices of `layers` over the ranks, on the side stream.  A layer's dW
+        and dbias are adjacent in the flat span, and so are the slices of neighbouring layers: one
+        call covers every run of neighbours."""
+        torch = self.torch
+        order = [t["name"] for t in self.layers]
+        idx = sorted(order.index(t["name"]) for t in layers)
+        runs, start = [], None
+        for j, i in enumerate(idx):
+            if start is None:
+                start = i
+            if j + 1 == len(idx) or idx[j + 1] != i + 1:
+                runs.append((start, i))
+                start = None
+        for lo_i, hi_i in runs:
+            names = [order[i] + sfx for i in range(lo_i, hi_i + 1) for sfx in (".dW", ".dbias")]
+            off, cnt = self.bucket.span_of(names)
+            if self.exchange is not None:
+                self.exchange.allreduce(off, cnt, stream=self.comm_stream)
+            else:
+                with torch.cuda.stream(self.comm_stream):
+                    torch.distributed.all_reduce(self.bucket.flat[off:off + cnt])
 
-    def run(self, world, events=None):
+    def run(self, world=1, events=None):
         """Enqueues one step on the current stream. With world > 1 every layer's gradient
-        slice is all-reduced on a side stream as soon as that layer's backward is enqueued,
-        so the exchange overlaps the backward of the remaining layers."""
+        slice is all-reduced on a side stream as soon as the launch that completes it is
+        enqueued, so the exchange overlaps the backward of the remaining layers."""
         torch = self.torch
         self.bucket.zero_()
-        for label, _, fn, layer in self.launches():
+        for label, _, fn, done in self.launches():
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record()
             fn()
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record()
                 events.append((label, e0, e1))
-            if world > 1 and layer is not None:
+            if world > 1 and done:
                 ready = torch.cuda.Event(); ready.record()
                 self.comm_stream.wait_event(ready)
-                if self.exchange is not None:
-                    off, cnt = self.bucket.span_of([layer["name"] + ".dW", layer["name"] + ".dbias"])
-                    self.exchange.allreduce(off, cnt, stream=self.comm_stream)
-                else:
-                    with torch.cuda.stream(self.comm_stream):
-                        torch.distributed.all_reduce(self.grad_slice(layer))
+                self.exchange_layers(done)
         if world > 1:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
@@ -313,11 +367,12 @@ class AttentionStep:
             ("dK=adS^TQ", md(self.dk, self.ds, self.q, True, False, alpha=a), self.dk, self.ds, self.q),
         ]
         self.flops_each = 2.0 * BH * T * T * HD
+        self.flops = 6 * self.flops_each
         # minimum bytes of one product: the [BH,T,T] matrix once plus three [BH,T,hd] tensors
         self.bytes_each = 2.0 * (BH * T * T + 3 * BH * T * HD)
 
     def launches(self):
-        return [(lab, self.flops_each, (lambda d=d, c=c, a=a, b=b: self.L.gemm_desc(d, c, a, b)), None)
+        return [(lab, self.flops_each, (lambda d=d, c=c, a=a, b=b: self.L.gemm_desc(d, c, a, b)), [])
                 for lab, d, c, a, b in self.calls]
 
     def run(self, world=1, events=None):
@@ -329,6 +384,79 @@ class AttentionStep:
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record()
                 events.append((label, e0, e1))
+
+
+def make_step(workload, m, dev, seed, world=1, args=None):
+    if workload == "c4":
+        return AttentionStep(dev, seed)
+    defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) else None
+    return LinearStep(workload, m, dev, seed, world=world, exchange=args.exchange if args else "nccl",
+                      comm_ctas=(args.comm_ctas if args and args.comm_ctas else 8), defer=defer)
+
+
+def timed_steps(torch, L, step, world, steps, warmup, use_graph, barrier):
+    """W untimed steps, then exactly K steps between CUDA events.  One step (its GEMM launches
+    and, for N > 1, the gradient exchanges on the side stream) is captured into a CUDA graph and
+    replayed, so the host enqueues one graph per step instead of a dozen launches."""
+    for _ in range(warmup):
+        step.run(world)
+    barrier()
+    graph, per_step = None, None
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            n0 = L.launch_count()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step.run(world)
+            per_step = L.launch_count() - n0
+            for _ in range(warmup):
+                graph.replay()
+        except Exception as exc:  # capture refused: fall back to direct launches and say so
+            print(f"[bench] graph capture failed ({exc}); launching directly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    barrier()
+    n0 = L.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            step.run(world)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    launches = per_step * steps if graph is not None else L.launch_count() - n0
+    return ms, int(launches), graph
+
+
+def sustained_replay(torch, graph, step, dev, seconds, flops, peaks):
+    """The same step replayed for `seconds`: long enough for the power governor to settle."""
+    sampler = make_sampler(torch, dev).start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_end = time.perf_counter() + seconds
+    n = 0
+    e0.record()
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            if graph is not None:
+                graph.replay()
+            else:
+                step.run(1)
+        n += 50
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    clocks = sampler.stop()
+    tf = flops / ms / 1e9
+    return {"tflops": round(tf, 1), "ms_per_step": round(ms, 4), "steps": n, "seconds": round(ms * n / 1e3, 2),
+            "sm_mhz_median": clocks.get("sm_mhz"), "power_w_max": clocks.get("power_w_max"),
+            "reasons": clocks.get("reasons"), "clock_samples": clocks.get("samples"),
+            "frac_of_sustained_peak": round(tf / peaks["tf_sustained"], 4),
+            "ms_x_ghz": round(ms * (clocks.get("sm_mhz") or 0) / 1e3, 4)}
 
 
 class HostPipeline:
@@ -384,50 +512,213 @@ class HostStep(HostPipeline):
         super().__init__(torch, inputs, outputs, lambda: step.run(world))
 
 
-def cpu_baseline(workload, budget_s=12.0):
-    """The C port of the path (oracle/oracle.c, fp32 arithmetic, OpenMP) timed on this
-    host's cores on a bounded sample: the first 256 token rows of every GEMM of the step."""
+# ------------------------------------------------------------- per-GEMM comparisons ---
+
+def gemm_list(workload, m):
+    """Every GEMM of the step: (label, kind, m, n, k, trans_a, trans_b, layer index)."""
+    out = []
+    for li, (n_, i, o, gelu) in enumerate(LAYERS[workload]["layers"]):
+        out.append((n_ + ".fwd", "fwd", m, o, i, False, True, li))
+        out.append((n_ + ".dX", "dx", m, i, o, False, False, li))
+        out.append((n_ + ".dW", "dw", o, i, m, True, False, li))
+    return out
+
+
+def _loop_ms(torch, fns, iters=20, warm=3):
+    """Mean time of one call when the calls in `fns` (the same GEMM on rotating buffer sets, so
+    that no iteration finds its operands in L2) run back to back."""
+    for w in range(warm):
+        fns[w % len(fns)]()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for it in range(iters):
+        fns[it % len(fns)]()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def per_gemm_comparison(torch, L, workload, m, dev, want_cublaslt=True):
+    """Each GEMM of the step timed on its own, back to back on rotating buffer sets (> 2 x L2
+    in total), for this library and for cuBLASLt called the way llmt calls it (operand swap,
+    32 MiB workspace, cached top-1 heuristic; llmt src/kernels/matmul.cpp:99-170) but with
+    bf16 operands and fp32 accumulation.  Fused cases are timed for cuBLASLt both with its own
+    epilogues (BIAS, GELU_BIAS, bias gradient) and as the unfused composition (plain GEMM, then
+    torch element-wise kernels / a torch column sum)."""
+    cfg = LAYERS[workload]
+    has_bias = cfg.get("bias", True)
+    lt = None
+    notes = {}
+    if want_cublaslt:
+        try:
+            from oracle import cublaslt_ref
+            if cublaslt_ref.available():
+                lt = cublaslt_ref.CublasLtBf16()
+            else:
+                notes["cublaslt_bf16"] = "comparator library not built (make -C oracle cmp)"
+        except Exception as exc:
+            notes["cublaslt_bf16"] = f"unavailable: {exc}"
+    g = torch.Generator(device=dev).manual_seed(1234)
+    bf = torch.bfloat16
+    own, lib_fused, lib_unfused = {}, {}, {}
+    for label, kind, gm, gn, gk, ta, tb, li in gemm_list(workload, m):
+        _, i, o, gelu = cfg["layers"][li]
+        cdt = torch.float32 if kind == "dw" or (kind == "fwd" and cfg.get("y_fp32")) else bf
+        set_bytes = 2 * (gm * gk + gk * gn) + gm * gn * (4 if cdt == torch.float32 else 2)
+        n_sets = max(2, min(8, -(-2 * L2_BYTES // set_bytes)))
+        sets = []
+        for _ in range(n_sets):
+            a = torch.randn((gk, gm) if ta else (gm, gk), device=dev, generator=g).mul_(0.01 if kind != "fwd" else 1.0).to(bf)
+            b = torch.randn((gn, gk) if tb else (gk, gn), device=dev, generator=g).mul_(0.02).to(bf)
+            c = torch.zeros(gm, gn, device=dev, dtype=cdt)
+            bias = (torch.randn(gn, device=dev, generator=g) * 0.02) if (kind == "fwd" and has_bias) else None
+            db = torch.zeros(gm, device=dev) if (kind == "dw" and has_bias) else None
+            sets.append((a, b, c, bias, db))
+        flops = 2.0 * gm * gn * gk
+        # this library
+        fns, keep = [], []
+        for a, b, c, bias, db in sets:
+            d = L.make_desc(c, a, b, ta, tb, beta=1.0 if kind == "dw" else 0.0, bias=bias,
+                            gelu=(kind == "fwd" and gelu), dbias=db, dbias_beta=1.0)
+            need = L.workspace_bytes(d, a, b)
+            ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+            d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
+            keep.append((d, ws))
+            fns.append(lambda d=d, c=c, a=a, b=b: L.gemm_desc(d, c, a, b))
+        own[label] = round(flops / _loop_ms(torch, fns) / 1e9, 1)
+        if lt is None:
+            continue
+        # cuBLASLt, fused epilogues (bias in C's type, as Lt requires)
+        try:
+            fns = []
+            for a, b, c, bias, db in sets:
+                lb = bias.to(c.dtype) if bias is not None else None
+                fns.append(lambda a=a, b=b, c=c, lb=lb, db=db: lt.matmul(
+                    c, a, b, ta, tb, beta=1.0 if kind == "dw" else 0.0, bias=lb,
+                    gelu=(kind == "fwd" and gelu and lb is not None), dbias=db))
+            lib_fused[label] = round(flops / _loop_ms(torch, fns) / 1e9, 1)
+        except Exception as exc:
+            lib_fused[label] = None
+            notes["fused:" + label] = str(exc)
+        # cuBLASLt, unfused composition
+        try:
+            fns = []
+            for a, b, c, bias, db in sets:
+                tmp = torch.empty(gm, device=dev) if db is not None else None
+                c2 = torch.empty_like(c) if (kind == "fwd" and gelu) else None
+
+                def unfused(a=a, b=b, c=c, bias=bias, db=db, tmp=tmp, c2=c2):
+                    lt.matmul(c, a, b, ta, tb, beta=1.0 if kind == "dw" else 0.0)
+                    if bias is not None:
+                        c.add_(bias.to(c.dtype))
+                    if c2 is not None:
+                        torch.ops.aten.gelu.out(c, approximate="tanh", out=c2)
+                    if db is not None:
+                        torch.sum(a, dim=0, dtype=torch.float32, out=tmp)
+                        db.add_(tmp)
+                fns.append(unfused)
+            lib_unfused[label] = round(flops / _loop_ms(torch, fns) / 1e9, 1)
+        except Exception as exc:
+            lib_unfused[label] = None
+            notes["unfused:" + label] = str(exc)
+        del sets, fns
+    if lt is not None:
+        lt.close()
+    glist = gemm_list(workload, m)
+    total = sum(2.0 * gm * gn * gk for _, _, gm, gn, gk, *_ in glist)
+
+    def step_rate(table):
+        if not table or any(table.get(lab) in (None, 0) for lab, *_ in glist):
+            return None
+        t = sum(2.0 * gm * gn * gk / (table[lab] * 1e9) for lab, _, gm, gn, gk, *_ in glist)
+        return round(total / t / 1e9, 1)
+    out = {"own_per_gemm_tflops": own, "own_step_tflops_sum_of_gemms": step_rate(own),
+           "method": "each GEMM alone, 20 calls back to back after 3 warm-up calls, CUDA events, operands "
+                     "rotating over buffer sets larger than twice L2"}
+    if lt is not None or lib_fused:
+        best = {lab: max(v for v in (lib_fused.get(lab), lib_unfused.get(lab)) if v) if
+                (lib_fused.get(lab) or lib_unfused.get(lab)) else None for lab, *_ in glist}
+        out["cublaslt_bf16"] = {
+            "per_gemm_tflops_lt_epilogues": lib_fused, "per_gemm_tflops_unfused": lib_unfused,
+            "step_tflops_lt_epilogues": step_rate(lib_fused), "step_tflops_unfused": step_rate(lib_unfused),
+            "step_tflops": step_rate(best),
+            "own_over_cublaslt": {lab: (round(own[lab] / best[lab], 3) if best.get(lab) else None) for lab, *_ in glist},
+            "call_pattern": "llmt src/kernels/matmul.cpp:99-170 (operand swap, 32 MiB workspace, cached top-1 "
+                            "heuristic) with CUDA_R_16BF operands and CUBLAS_COMPUTE_32F"}
+    if notes:
+        out["notes"] = notes
+    return out
+
+
+# -------------------------------------------------------------------- CPU baselines ---
+
+def _best_median(fn, reps):
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter(); fn(); ts.append(time.perf_counter() - t0)
+    ts.sort()
+    return ts[0], ts[len(ts) // 2]
+
+
+def cpu_baseline(workload):
+    """Config 1 of the reference's benchmark set on this host's cores: the single fp32 linear
+    forward Y = X W^T + b, X [256,768] ~ N(0,1), W [3072,768] ~ N(0,0.02), b ~ N(0,0.02), seed 0.
+    Timed for the C port of the path (oracle/oracle.c, fp32, OpenMP) and for PyTorch on CPU,
+    which is what llmt's own known-answer files were computed with (tools/gen_golden.py:94-98).
+    `value` is the C port's best; a sample of the headline workload's shapes is timed beside it."""
     import numpy as np
     from oracle import oracle
-    rows = 256
     rng = np.random.default_rng(0)
-    spec = LAYERS[workload]["layers"]
-    data = []
-    for _, i, o, _g in spec:
-        data.append((rng.standard_normal((rows, i)).astype(np.float32),
-                     (rng.standard_normal((o, i)) * 0.02).astype(np.float32),
-                     (rng.standard_normal((rows, o)) * 0.01).astype(np.float32)))
-    flops = step_flops(workload, rows)
+    x = rng.standard_normal((256, 768)).astype(np.float32)
+    w = (rng.standard_normal((3072, 768)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(3072) * 0.02).astype(np.float32)
+    flops1 = 2.0 * 256 * 3072 * 768
 
-    def one_pass():
-        for x, w, dy in data:
-            oracle.gemm_f32(x, w, False, True)          # fwd
-            oracle.gemm_f32(dy, w, False, False)        # dX
-            oracle.gemm_f32(dy, x, True, False)         # dW
-    one_pass()
-    best, t_total, n = 1e30, 0.0, 0
-    while t_total < budget_s and n < 50:
-        t0 = time.perf_counter(); one_pass(); dt = time.perf_counter() - t0
-        best = min(best, dt); t_total += dt; n += 1
-    out = {"value": round(flops / best / 1e12, 4), "unit": "TFLOP/s", "cores": oracle.num_threads(),
-           "kind": "port",
-           "sample": f"first {rows} token rows of every GEMM of the step ({flops / 1e9:.1f} GFLOP), "
-                     f"best of {n} passes, fp32 OpenMP C port"}
-    try:  # PyTorch on CPU is the oracle llmt's own golden files were made with (tools/gen_golden.py)
+    def port():
+        y = oracle.gemm_f32(x, w, False, True)
+        y += b
+        return y
+    port()
+    best, med = _best_median(port, 25)
+    out = {"value": round(flops1 / best / 1e12, 4), "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+           "sample": "config 1 itself: Y = X W^T + b, [256,768] x [3072,768]^T, fp32, seed 0 (1.208 GFLOP), "
+                     "best of 25 runs of the OpenMP C port",
+           "config1": {"port_best_ms": round(best * 1e3, 3), "port_median_ms": round(med * 1e3, 3),
+                       "port_best_tflops": round(flops1 / best / 1e12, 4)}}
+    try:
         import torch
-        tx = [(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(dy)) for x, w, dy in data]
-
-        def torch_pass():
-            for x, w, dy in tx:
-                x @ w.T; dy @ w; dy.T @ x
-        torch_pass()
-        tb = 1e30
-        for _ in range(10):
-            t0 = time.perf_counter(); torch_pass(); tb = min(tb, time.perf_counter() - t0)
-        out["torch_cpu_tflops"] = round(flops / tb / 1e12, 4)
-        out["torch_cpu_threads"] = torch.get_num_threads()
+        torch.manual_seed(0)
+        tx, tw, tb = torch.randn(256, 768), torch.randn(3072, 768) * 0.02, torch.randn(3072) * 0.02
+        fn = lambda: tx @ tw.T + tb
+        fn()
+        tbest, tmed = _best_median(fn, 25)
+        out["config1"].update({"torch_cpu_best_ms": round(tbest * 1e3, 3), "torch_cpu_median_ms": round(tmed * 1e3, 3),
+                               "torch_cpu_best_tflops": round(flops1 / tbest / 1e12, 4),
+                               "torch_cpu_threads": torch.get_num_threads()})
     except Exception:
         pass
+    # a bounded sample of the headline workload: the first 256 token rows of every GEMM of the step
+    rows = 256
+    spec = LAYERS[workload if workload in LAYERS else "c2"]["layers"]
+    data = [(rng.standard_normal((rows, i)).astype(np.float32),
+             (rng.standard_normal((o, i)) * 0.02).astype(np.float32),
+             (rng.standard_normal((rows, o)) * 0.01).astype(np.float32)) for _, i, o, _g in spec]
+    flops = sum(3 * 2.0 * rows * i * o for _, i, o, _ in spec)
+
+    def one_pass():
+        for xx, ww, dy in data:
+            oracle.gemm_f32(xx, ww, False, True)
+            oracle.gemm_f32(dy, ww, False, False)
+            oracle.gemm_f32(dy, xx, True, False)
+    one_pass()
+    t_best, t_total, n = 1e30, 0.0, 0
+    while t_total < 6.0 and n < 20:
+        t0 = time.perf_counter(); one_pass(); dt = time.perf_counter() - t0
+        t_best = min(t_best, dt); t_total += dt; n += 1
+    out["step_sample"] = {"tflops": round(flops / t_best / 1e12, 4),
+                          "sample": f"first {rows} token rows of every GEMM of the step ({flops / 1e9:.1f} GFLOP), "
+                                    f"best of {n} passes of the C port"}
     return out
 
 
@@ -472,11 +763,12 @@ def run_reference(args):
     if rank != 0:
         return 0
     from oracle import llmt_ref
-    flops = step_flops(args.workload, M_PER_GPU)
+    workload = args.workload if args.workload in LAYERS else "c2"
+    flops = step_flops(workload, M_PER_GPU)
     base = {"impl": "reference", "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job",
             "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {LAYERS[args.workload]['name']}, "
+            "config": {"workload": f"{workload}: {LAYERS[workload]['name']}, "
                                    f"M={M_PER_GPU} tokens, fwd+dX+dW per layer",
                        "l2": "working set larger than L2"}}
     try:
@@ -487,20 +779,22 @@ def run_reference(args):
     if not (have_gpu and llmt_ref.available()):
         # llmt's matmul path is a GPU library call; without its build (or a GPU) the
         # C port on the host cores stands in.
-        cb = cpu_baseline(args.workload)
-        base.update({"value": cb["value"], "dtype": "f32", "ms_per_step": None, "cpu_baseline": cb,
-                     "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+        cb = cpu_baseline(workload)
+        v = cb["step_sample"]["tflops"]
+        cb["value"], cb["sample"] = v, cb["step_sample"]["sample"]
+        base.update({"value": v, "dtype": "f32", "ms_per_step": None, "cpu_baseline": cb,
+                     "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                              "d2h_bytes_per_step": 0},
                      "note": "llmt build or GPU unavailable: CPU port of the path timed instead"})
         print(json.dumps(base))
         return 0
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    step = ReferenceStep(args.workload, M_PER_GPU, dev, seed=0)
+    step = ReferenceStep(workload, M_PER_GPU, dev, seed=0)
     for _ in range(max(args.warmup, 3)):
         step.run()
     torch.cuda.synchronize()
-    sampler = ClockSampler(0); sampler.start()
+    sampler = ClockSampler(0).start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -534,6 +828,93 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------ main ---
 
+def workload_text(workload, m):
+    if workload == "c4":
+        return ("c4: strided-batched attention products, B*H=96, T=1024, hd=64: S, O, dV, dP, dQ, dK "
+                "(dense FLOP count); P and dS from the softmax helpers outside the timed set")
+    cfg = LAYERS[workload]
+    return (f"{workload}: {cfg['name']}, M={m} tokens per GPU, fwd+dX+dW(+dbias) per layer"
+            + (", bias+GELU fused in mlp_fc" if cfg.get("bias", True) else ""))
+
+
+def roofline_of(step, workload, ms, peaks):
+    """Roofline entry of a workload from the CUDA-event time of its timed loop (the loop is the
+    GEMM kernel back to back)."""
+    if workload == "c4":
+        gbs = 6 * step.bytes_each / ms / 1e6
+        return {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["bw"], "unit": "GB/s",
+                "frac": round(gbs / peaks["bw"], 4), "traffic": recorded_traffic(workload),
+                "algorithmic_bytes": int(6 * step.bytes_each), "peak_source": f"of {peaks['which']}",
+                "tflops": round(step.flops / ms / 1e9, 1),
+                "kernel": "tc_grouped_pair_kernel (six batched launches; algorithmic bytes = one [96,T,T] "
+                          "bf16 matrix + three [96,T,64] tensors per product)"}
+    tf = step.flops / ms / 1e9
+    return {"bound": "tensor", "achieved": round(tf, 1), "peak": peaks["tf"], "unit": "TFLOP/s",
+            "frac": round(tf / peaks["tf"], 4), "traffic": recorded_traffic(workload),
+            "peak_source": f"of {peaks['which']}",
+            "kernel": "tc_grouped_pair_kernel (all GEMM launches of the step; step FLOP / CUDA-event time "
+                      "of the timed loop per step, per GPU)"}
+
+
+def exchange_check(torch, step, world, rank, dev):
+    """The exchange of the timed step on fresh per-rank partial sums, against two references:
+    NCCL's all-reduce of the same partial sums and their sum in rank order.  Two ranks: bitwise
+    equal to both.  Peer-copy form: bitwise equal to the rank-order sum.  Sum formed inside the
+    switch with more than two ranks: within 1e-6 of NCCL's (the order of the additions is the
+    switch's).  In every case a rerun must reproduce its own bits and all ranks must hold the
+    same bits."""
+    import torch.distributed as dist
+    flat = step.bucket.flat
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    part = torch.randn(flat.numel(), device=dev, generator=g)
+    want_nccl = part.clone()
+    dist.all_reduce(want_nccl)
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    want_order = parts[0].clone()
+    for p_ in parts[1:]:
+        want_order += p_
+    del parts
+    results = []
+    for _ in range(2):
+        flat.copy_(part)
+        torch.cuda.synchronize(); dist.barrier()
+        # the calls the timed step makes, in its order
+        for _label, _f, _fn, done in step.launches():
+            if done:
+                step.exchange_layers(done)
+        torch.cuda.current_stream().wait_stream(step.comm_stream)
+        torch.cuda.synchronize(); dist.barrier()
+        results.append(flat.clone())
+    # only what the exchange covers (the padding between slices is covered too: it is inside the ranges)
+    mask = torch.zeros(flat.numel(), dtype=torch.bool, device=dev)
+    for layer in step.layers:
+        off, cnt = step.bucket.span_of([layer["name"] + ".dW", layer["name"] + ".dbias"])
+        mask[off:off + cnt] = True
+    got, again = results[0][mask], results[1][mask]
+    eq_nccl = bool(torch.equal(got, want_nccl[mask]))
+    eq_order = bool(torch.equal(got, want_order[mask]))
+    close_nccl = bool(torch.allclose(got, want_nccl[mask], rtol=1e-6, atol=1e-6))
+    in_switch = step.exchange is not None and step.exchange.multicast
+    if world == 2:
+        ok_value = eq_nccl and eq_order
+    elif step.exchange is not None and not in_switch:
+        ok_value = eq_order
+    else:
+        ok_value = close_nccl
+    ok_rerun = bool(torch.equal(got, again))
+    same = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(same, got.contiguous())
+    ok_ranks = all(torch.equal(same[0], t) for t in same)
+    flag = torch.tensor([1 if (ok_value and ok_rerun and ok_ranks) else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    detail = {"bitwise_equal_to_nccl": eq_nccl, "bitwise_equal_to_rank_order_sum": eq_order,
+              "within_1e-6_of_nccl": close_nccl, "rerun_bitwise_equal": ok_rerun,
+              "ranks_bitwise_equal": ok_ranks,
+              "max_abs_err_vs_nccl": float((got - want_nccl[mask]).abs().max())}
+    return ("ok" if int(flag.item()) == 1 else "FAILED"), detail
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -542,6 +923,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4"], default="c2")
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="N = 1: skip the other workloads, the per-GEMM comparison and the sustained replay")
     ap.add_argument("--exchange", choices=["nvls", "peer", "nccl"], default="nvls",
                     help="N > 1: how the gradient span is summed: the library's kernel through NVSwitch "
                          "multicast (falls back to peer copies where no multicast mapping is offered), "
@@ -552,8 +935,8 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 0 for nvls, "
                          "--comm-ctas for peer, 0 for nccl)")
-    ap.add_argument("--split-last", action="store_true",
-                    help="N > 1: launch dW of the last backward on its own, ahead of dX")
+    ap.add_argument("--no-defer", action="store_true",
+                    help="c2: launch every layer's dW with its own dX (no deferred dW)")
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue every launch from the host instead of replaying one captured step")
     args = ap.parse_args()
@@ -594,68 +977,30 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    peaks = measured_peaks()
     attention = args.workload == "c4"
-    step = AttentionStep(dev, seed=rank) if attention else LinearStep(args.workload, M_PER_GPU, dev, seed=rank, world=world, exchange=args.exchange, comm_ctas=args.comm_ctas or 8, split_last=args.split_last)
-    flops = 6 * step.flops_each if attention else step_flops(args.workload, M_PER_GPU)
-    for _ in range(args.warmup):
-        step.run(world)
-    barrier()
-    # One step (its GEMM launches and, for N > 1, the gradient all-reduces on the side stream)
-    # captured into a CUDA graph: the timed loop replays it, so the host enqueues one graph
-    # per step instead of a dozen launches.
-    graph, per_step_launches = None, None
-    if not args.no_graph:
-        try:
-            graph = torch.cuda.CUDAGraph()
-            n0 = L.launch_count()
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                step.run(world)
-            per_step_launches = L.launch_count() - n0
-            for _ in range(args.warmup):
-                graph.replay()
-        except Exception as exc:  # capture refused: fall back to direct launches and say so
-            print(f"[bench] graph capture failed ({exc}); launching directly", file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize()
-    barrier()
-    props = torch.cuda.get_device_properties(dev)
-    try:
-        pci = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
-    except AttributeError:
-        pci = None
-    sampler = ClockSampler(local, pci)
+    step = make_step(args.workload, M_PER_GPU, dev, seed=rank, world=world, args=args)
+    flops = step.flops
+    sampler = make_sampler(torch, dev)
     if rank == 0:
         sampler.start()
-    launches0 = L.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
-            step.run(world)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = per_step_launches * args.steps if graph is not None else L.launch_count() - launches0
-    # The same K steps again with an event pair around every launch: the per-launch device
-    # times behind roofline.achieved (kept out of the loop above, where events between
-    # kernels would defeat the overlap of one kernel's prologue with the previous one's tail).
-    events = []
-    for _ in range(args.steps):
-        step.run(world, events)
-    barrier()
+    ms, launches, graph = timed_steps(torch, L, step, world, args.steps, args.warmup, not args.no_graph, barrier)
     clocks = sampler.stop() if rank == 0 else None
     L.device_status()
 
-    # per-launch device time
+    # The same steps again with an event pair around every launch: per-launch device times
+    # (kept out of the loop above, where events between kernels would defeat the overlap of
+    # one kernel's prologue with the previous one's tail).
+    events = []
+    for _ in range(min(args.steps, 20)):
+        step.run(world, events)
+    barrier()
     per = {}
     for label, a, b in events:
         per.setdefault(label, []).append(a.elapsed_time(b))
     gemm_ms = sum(sum(v) / len(v) for v in per.values())
     gl = {lab: f for lab, f, *_ in step.launches()}
-    per_gemm = {lab: round(gl[lab] / (sum(v) / len(v)) / 1e9, 1) for lab, v in per.items()}
+    per_launch = {lab: round(gl[lab] / (sum(v) / len(v)) / 1e9, 1) for lab, v in per.items()}
 
     # end to end from host buffers
     if attention:
@@ -664,95 +1009,140 @@ def main():
         hs = HostStep(step, world)
         hs.run(1); barrier()
         n_e2e = max(2, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         hs.run(n_e2e)
         e1.record(); barrier()
         ms_e2e = e0.elapsed_time(e1) / n_e2e
         h2d, d2h = hs.h2d_bytes, hs.d2h_bytes
+        del hs
+
+    extras = {}
+    xcheck, xdetail, c5_strong = None, None, None
+    if world > 1 and not attention:
+        xcheck, xdetail = exchange_check(torch, step, world, rank, dev)
+    if world == 1 and not args.no_extras:
+        extras["sustained"] = sustained_replay(torch, graph, step, dev, 2.0, flops, peaks)
+        L.device_status()
 
     t = torch.tensor([ms, 0.0 if attention else ms_e2e, gemm_ms], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms, ms_e2e, gemm_ms = (float(x) for x in t.cpu())
+
+    ar_bytes = step.bucket.nbytes() if (world > 1 and not attention) else 0
+    exchange_name = (None if world == 1 or attention else "nccl" if step.exchange is None else
+                     "llmt_b200_grad_allreduce, " + ("NVSwitch multicast" if step.exchange.multicast else "peer copies"))
+
+    # release the headline step before the other workloads are built
+    if graph is not None:
+        graph.reset()
+    graph = None
+    main_roof = roofline_of(step, args.workload, ms, peaks)
+    main_roof["achieved_per_launch_events"] = round(flops / gemm_ms / 1e9, 1)
+    del step
+    torch.cuda.empty_cache()
+
+    if world > 1 and args.workload == "c2":
+        # config 5 as it is written: M = 65536 tokens split over the N GPUs, gradients exchanged
+        try:
+            m5 = 65536 // world
+            s5 = make_step("c5", m5, dev, seed=100 + rank, world=world, args=args)
+            ms5, _, g5 = timed_steps(torch, L, s5, world, 10, 3, not args.no_graph, barrier)
+            t5 = torch.tensor([ms5], device=dev, dtype=torch.float64)
+            torch.distributed.all_reduce(t5, op=torch.distributed.ReduceOp.MAX)
+            ms5 = float(t5.item())
+            c5_strong = {"m_per_gpu": m5, "ms_per_step": round(ms5, 4),
+                         "per_gpu_tflops": round(s5.flops / ms5 / 1e9, 1),
+                         "whole_job_tflops": round(world * s5.flops / ms5 / 1e9, 1),
+                         "allreduce_bytes": s5.bucket.nbytes(), "steps": 10}
+            if g5 is not None:
+                g5.reset()
+            del s5, g5
+            torch.cuda.empty_cache()
+        except Exception as exc:  # never lose the headline line to the extra measurement
+            c5_strong = {"error": str(exc)}
+
+    if world == 1 and not args.no_extras:
+        others = {}
+        for wl in ("c3", "c3c", "c4", "c5"):
+            if wl == args.workload:
+                continue
+            try:
+                s2 = make_step(wl, M_PER_GPU, dev, seed=7, world=1, args=args)
+                smp = make_sampler(torch, dev).start()
+                ms2, n2, g2 = timed_steps(torch, L, s2, 1, 20, 3, not args.no_graph, barrier)
+                ck = smp.stop()
+                L.device_status()
+                roof = roofline_of(s2, wl, ms2, peaks)
+                others[wl] = {"workload": workload_text(wl, M_PER_GPU), "ms_per_step": round(ms2, 4),
+                              "tflops": round(s2.flops / ms2 / 1e9, 1), "steps": 20, "gpu_launches": n2,
+                              "roofline": roof, "clocks": ck}
+                if g2 is not None:
+                    g2.reset()
+                del s2, g2
+            except Exception as exc:
+                others[wl] = {"error": str(exc)}
+            torch.cuda.empty_cache()
+        extras["workloads"] = others
+        if not attention:
+            try:
+                extras["comparators"] = per_gemm_comparison(torch, L, args.workload, M_PER_GPU, dev)
+            except Exception as exc:
+                extras["comparators"] = {"error": str(exc)}
+            torch.cuda.empty_cache()
+        h, mi = L.tensor_map_cache_stats()
+        extras["tensor_map_cache"] = {"hits": h, "misses": mi}
+
     if rank == 0:
-        peak_tf, peak_bw, which = measured_peaks()
-        achieved = flops / gemm_ms / 1e9
-        if attention:
-            wl = ("c4: strided-batched attention products, B*H=96, T=1024, hd=64: S, O, dV, dP, dQ, dK "
-                  "(dense FLOP count); P and dS from the softmax helpers outside the timed set")
-            launches_txt = "6 batched GEMM launches"
-            gbs = 6 * step.bytes_each / gemm_ms / 1e6
-            roof = {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak_bw, "unit": "GB/s",
-                    "frac": round(gbs / peak_bw, 4), "traffic": None, "peak_source": f"of {which}",
-                    "kernel": "tc_grouped_kernel (six batched launches; algorithmic bytes = one [96,T,T] "
-                              "bf16 matrix + three [96,T,64] tensors per product)"}
-            ar_bytes = 0
-        else:
-            cfg = LAYERS[args.workload]
-            wl = (f"{args.workload}: {cfg['name']}, M={M_PER_GPU} tokens per GPU, fwd+dX+dW(+dbias) per layer"
-                  + (", bias+GELU fused in mlp_fc" if cfg.get("bias", True) else ""))
-            nl = len(cfg["layers"])
-            launches_txt = (f"{nl} forward GEMMs + {nl} grouped backward launches (dX and dW+dbias of a layer "
-                            "in one kernel) + split-K reductions")
-            # DRAM bytes of one step's launches (dram__bytes_read.sum + dram__bytes_write.sum over the
-            # 8 GEMM launches + 1 split-K reduction, one ncu capture of this workload at the default
-            # settings; writes of a replayed launch partly stay in L2): 380.1 MB + 25.4 MB against
-            # 343.6 MB of algorithmic operand reads.
-            traffic = 405.5e6 if args.workload == "c2" and world == 1 else None
-            # The timed loop is the GEMM kernel back to back (98.6 % of its kernel time, see profiles/):
-            # its CUDA-event duration is the kernel's duration.  The per-launch sum of the second,
-            # instrumented pass is reported beside it; it is longer because an event between two
-            # launches keeps one launch's prologue from overlapping the previous launch's tail.
-            in_loop = flops / ms / 1e9
-            roof = {"bound": "tensor", "achieved": round(in_loop, 1), "peak": peak_tf,
-                    "unit": "TFLOP/s", "frac": round(in_loop / peak_tf, 4), "traffic": traffic,
-                    "peak_source": f"of {which}",
-                    "achieved_per_launch_events": round(achieved, 1),
-                    "kernel": "tc_grouped_kernel (all GEMM launches of the step; step FLOP / CUDA-event time "
-                              "of the timed loop per step, per GPU)"}
-            ar_bytes = step.bucket.nbytes() if world > 1 else 0
+        nl = 0 if attention else len(LAYERS[args.workload]["layers"])
+        launches_txt = ("6 batched GEMM launches" if attention else
+                        f"{nl} forward GEMMs + {nl} grouped backward launches (dX of a layer with dW+dbias of that "
+                        "layer or of one whose backward ran earlier) + split-K reductions + 1 zero-fill of the span")
         line = {
             "metric": "GEMM TFLOP/s (fwd+dX+dW), whole job", "value": round(world * flops / ms / 1e9, 2),
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl, "launches_per_step": launches_txt,
+            "config": {"workload": workload_text(args.workload, M_PER_GPU), "launches_per_step": launches_txt,
                        "per_gpu_gflop_per_step": round(flops / 1e9, 1),
                        "allreduce_bytes_per_step": ar_bytes,
-                       "exchange": (None if world == 1 else "nccl" if step.exchange is None else
-                                    "llmt_b200_grad_allreduce, " + ("NVSwitch multicast" if step.exchange.multicast
-                                                                    else "peer copies")),
+                       "exchange": exchange_name,
                        "comm_ctas": args.comm_ctas if world > 1 else 0,
                        "comm_sms": args.comm_sms if world > 1 else 0,
                        "l2": "working set of a step larger than L2 (operands stream from HBM)"},
             "per_gpu_tflops": round(flops / ms / 1e9, 2),
-            "pct_of_bf16_peak": round(100.0 * flops / ms / 1e9 / peak_tf, 1),
-            "roofline": roof,
-            "per_gemm_tflops": per_gemm,
+            "pct_of_bf16_peak": round(100.0 * flops / ms / 1e9 / peaks["tf"], 1),
+            "roofline": main_roof,
+            "per_launch_tflops": per_launch,
             "e2e": {"value": None if attention else round(world * flops / ms_e2e / 1e9, 2), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
-            "cuda_graph": graph is not None,
+            "cuda_graph": not args.no_graph,
             "clocks": clocks,
         }
+        if c5_strong is not None:
+            line["config"]["c5_strong"] = c5_strong
+        if xcheck is not None:
+            line["exchange_check"] = xcheck
+            line["exchange_check_detail"] = xdetail
+        line.update(extras)
         if world == 1 and not args.no_cpu_baseline and not attention:
             line["cpu_baseline"] = cpu_baseline(args.workload)
         print(json.dumps(line))
+    rc = 0
     if world > 1:
-        # The captured step holds NCCL work: release it before the communicator goes, and
-        # never let a stuck teardown outlive the measurement.
-        import threading
+        if xcheck is not None and xcheck != "ok":
+            rc = 3
+        # Never let a stuck teardown outlive the measurement.
         sys.stdout.flush()
-        guard = threading.Timer(60.0, os._exit, (0,))
+        guard = threading.Timer(60.0, os._exit, (rc,))
         guard.daemon = True
         guard.start()
-        if graph is not None:
-            graph.reset()
-            del graph
         torch.cuda.synchronize()
         torch.distributed.destroy_process_group()
         guard.cancel()
-    return 0
+    return rc
 
 
 if __name__ == "__main__":

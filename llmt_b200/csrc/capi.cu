@@ -792,7 +792,7 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
         return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: null argument");
     if (count < 1 || count > kMaxGroupProblems)
         return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: count must be 1..%d", kMaxGroupProblems);
-    Checked ck[kMaxGroupProblems];
+    Checked ck[kMaxGroupProblems] = {};
     for (int i = 0; i < count; ++i) {
         const int st = validate(&descs[i], c[i], a[i], b[i], &ck[i]);
         if (st != LLMT_B200_OK) return st;

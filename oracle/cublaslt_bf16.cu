@@ -46,7 +46,9 @@ CMP_API void cmp_destroy(void* h) {
 }
 
 // C[M,N] = alpha*op(A)*op(B) + beta*C (row-major, contiguous), bf16 A/B, C bf16 (c_fp32 = 0)
-// or fp32.  epilogue: 0 none, 1 bias (fp32 or bf16 per Lt's rule = C's type), 3 bias + tanh-GELU.
+// or fp32.  epilogue: 0 none, 1 bias (fp32 or bf16 per Lt's rule = C's type), 3 bias + tanh-GELU,
+// 4 bias gradient: `bias` receives sum_p op(A)[i, p] for i < M (after the operand swap our A
+// sits in Lt's B slot, so this is Lt's BGRADB; Lt overwrites, it does not accumulate).
 // Returns 0 on success, otherwise the failing cublasStatus_t (or -1 when no algorithm exists).
 CMP_API int cmp_matmul_bf16(void* h, void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k,
                             int64_t batch, int trans_a, int trans_b, float alpha, float beta, int c_fp32,
@@ -63,7 +65,8 @@ CMP_API int cmp_matmul_bf16(void* h, void* c, const void* a, const void* b, int6
     cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSA, &slot_a, sizeof slot_a);
     cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSB, &slot_b, sizeof slot_b);
     if (epilogue != 0) {
-        const cublasLtEpilogue_t epi = epilogue == 3 ? CUBLASLT_EPILOGUE_GELU_BIAS : CUBLASLT_EPILOGUE_BIAS;
+        const cublasLtEpilogue_t epi = epilogue == 3 ? CUBLASLT_EPILOGUE_GELU_BIAS
+                                     : epilogue == 4 ? CUBLASLT_EPILOGUE_BGRADB : CUBLASLT_EPILOGUE_BIAS;
         cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_EPILOGUE, &epi, sizeof epi);
         cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof bias);
     }

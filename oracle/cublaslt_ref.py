@@ -57,8 +57,9 @@ class CublasLtBf16:
             self.h = None
 
     def matmul(self, c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
-               stream=None):
-        """C = alpha*op(A)*op(B) + beta*C on contiguous bf16 A/B and bf16-or-fp32 C (rank 2 or 3)."""
+               stream=None, dbias=None):
+        """C = alpha*op(A)*op(B) + beta*C on contiguous bf16 A/B and bf16-or-fp32 C (rank 2 or 3).
+        dbias (fp32 [M] for fp32 C): Lt's bias-gradient epilogue writes sum_p op(A)[i, p] into it."""
         import torch
         assert a.is_contiguous() and b.is_contiguous() and c.is_contiguous()
         assert a.dtype == b.dtype == torch.bfloat16
@@ -68,7 +69,10 @@ class CublasLtBf16:
         m, k = (ac, ar) if trans_a else (ar, ac)
         n = br if trans_b else bc
         epi = 0
-        if bias is not None:
+        if dbias is not None:
+            assert bias is None and not gelu
+            epi, bias = 4, dbias
+        elif bias is not None:
             epi = 3 if gelu else 1
         elif gelu:
             raise ValueError("GELU without bias is not an Lt epilogue used here")

@@ -232,7 +232,7 @@ void test_bf16_linear(Device& dev) {
     make(OUT, IN, 0.05f, &w32, &w16, nullptr);
 
     ParamStore ps32(StateDtypes::uniform(DType::FP32));
-    const Linear l32(ps32, "w", IN, OUT, Role::Matrix);
+    const Linear l32(ps32, "w", IN, OUT, Role::Matrix, /*bias=*/true);  // fp32 layer with a bias too
     ps32.finalize();
     ParamStore ps16(StateDtypes{DType::BF16, DType::FP32});
     const Linear l16(ps16, "w", IN, OUT, Role::Matrix, /*bias=*/true);
@@ -269,6 +269,14 @@ void test_bf16_linear(Device& dev) {
     for (int64_t r = 0; r < M; ++r)
         for (int64_t c = 0; c < OUT; ++c) db[static_cast<size_t>(c)] += dy_host[static_cast<size_t>(r * OUT + c)];
     expect(rel_fro(download(l16.bias_param()->grad), db), 1e-3, "bf16 Linear dbias (fused) vs host column sum");
+    expect(rel_fro(download(l32.bias_param()->grad), db), 1e-5, "fp32 Linear dbias vs host column sum");
+    // gradients accumulate (llmt tests/unit/test_linear.cu:49-56): a second backward doubles them
+    l32.backward(c32, dx32, dy32, x32);
+    l16.backward(c16, dx16, dy16, x16);
+    dev.synchronize();
+    for (float& v : db) v *= 2.0f;
+    expect(rel_fro(download(l16.bias_param()->grad), db), 1e-3, "bf16 Linear dbias accumulates");
+    expect(rel_fro(download(l32.bias_param()->grad), db), 1e-5, "fp32 Linear dbias accumulates");
 }
 
 }  // namespace

@@ -1,0 +1,193 @@
+"""Edges of the tensor-core path, through the C ABI: every extent at 1, tile-1, tile and
+tile+1 in each of M, N and K, on every transpose combination, on single CTAs and CTA pairs,
+with and without split-K, with guard words around everything the call may write (C, dbias,
+the workspace); operands that TMA cannot address in place; the host-side tensor-map cache.
+
+Tolerances are those of test_gemm_gpu.py: fp32 output of bf16 operands vs the fp64 product of
+the same bf16-rounded inputs, relative Frobenius <= 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+import llmt_b200 as L
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = 1e-3
+GUARD = 12345.0
+
+
+@pytest.fixture(autouse=True)
+def _healthy_device():
+    yield
+    assert L.device_status() == (0, 0)
+
+
+def _bf16_dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(DEV).to(torch.bfloat16)
+
+
+class Guarded:
+    """A [rows, cols] fp32 view in the middle of a larger buffer filled with a sentinel."""
+
+    def __init__(self, rows, cols, pad_rows=2, pad_cols=8, init=None):
+        self.full = torch.full((rows + 2 * pad_rows, cols + 2 * pad_cols), GUARD, device=DEV)
+        self.view = self.full[pad_rows:pad_rows + rows, pad_cols:pad_cols + cols]
+        self.view.copy_(init if init is not None else torch.zeros(rows, cols, device=DEV))
+        self.mask = torch.ones_like(self.full, dtype=torch.bool)
+        self.mask[pad_rows:pad_rows + rows, pad_cols:pad_cols + cols] = False
+
+    def intact(self):
+        return bool((self.full[self.mask] == GUARD).all())
+
+
+def _padded_operand(x):
+    """bf16 copy of x with a row pitch that TMA accepts (multiple of 8) but that is larger than the row."""
+    rows, cols = x.shape
+    ld = (cols + 7) // 8 * 8 + 8
+    buf = torch.zeros(rows, ld, device=DEV, dtype=torch.bfloat16)
+    buf[:, :cols] = _bf16_dev(x)
+    return buf[:, :cols]
+
+
+def _extents(tile):
+    return [1, tile - 1, tile, tile + 1]
+
+
+@pytest.mark.parametrize("pairs", [1, 2])
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+def test_ragged_grid_with_guard_words(ta, tb, pairs):
+    tile_m = 128 * pairs
+    rng = np.random.default_rng(1000 + 10 * pairs + 2 * ta + tb)
+    cases = 0
+    for tile_n in ([128, 256] if pairs == 2 else [64, 192, 256]):
+        for m in _extents(tile_m):
+            if pairs == 2 and m <= 128:
+                continue  # CTA pairs need more than one 128-row block
+            for n in _extents(tile_n):
+                for k in [1, 63, 64, 65, 200]:
+                    for splits in ([1, 2] if k > 64 else [1]):
+                        a = oracle.round_bf16(rng.standard_normal((k, m) if ta else (m, k)))
+                        b = oracle.round_bf16(rng.standard_normal((n, k) if tb else (k, n)) * 0.5)
+                        c0 = rng.standard_normal((m, n)).astype(np.float32)
+                        ad, bd = _padded_operand(a), _padded_operand(b)
+                        c = Guarded(m, n, init=torch.from_numpy(c0).to(DEV))
+                        want_dbias = ta == 1
+                        db = Guarded(1, m) if want_dbias else None
+                        d = L.make_desc(c.view, ad, bd, bool(ta), bool(tb), alpha=0.5, beta=1.0,
+                                        dbias=db.view[0] if want_dbias else None, dbias_beta=0.0,
+                                        tile_n=tile_n, splits=splits, cta_pairs=pairs)
+                        need = L.workspace_bytes(d, ad, bd)
+                        ws = torch.full((need // 4 + 64,), GUARD, device=DEV)
+                        if need:
+                            d.workspace, d.workspace_bytes = ws.data_ptr(), need
+                        L.gemm_desc(d, c.view, ad, bd)
+                        what = (m, n, k, tile_n, splits)
+                        ref = oracle.gemm(a, b, bool(ta), bool(tb), 0.5, 1.0, c0)
+                        assert oracle.rel_fro(c.view.cpu().numpy(), ref) <= TOL, what
+                        assert c.intact(), ("C guard", what)
+                        assert bool((ws[need // 4:] == GUARD).all()), ("workspace guard", what)
+                        if want_dbias:
+                            got = db.view[0].cpu().numpy()
+                            assert oracle.rel_fro(got, oracle.rowsum(a, trans_a=True)) <= TOL, ("dbias", what)
+                            assert db.intact(), ("dbias guard", what)
+                        cases += 1
+    assert cases >= 100
+
+
+@pytest.mark.parametrize("pairs", [1, 2])
+def test_pair_and_single_split_ragged_mn_major_b_with_dbias_accumulation(pairs):
+    """dW-shaped product (both operands MN-major), ragged in every extent, split-K, dbias with
+    beta = 1 onto a prior value, twice in a row: the second call doubles the increment."""
+    m, n, k = 520, 392, 1000
+    rng = np.random.default_rng(77 + pairs)
+    dy = oracle.round_bf16(rng.standard_normal((k, m)) * 0.01)
+    x = oracle.round_bf16(rng.standard_normal((k, n)))
+    dw0 = rng.standard_normal((m, n)).astype(np.float32)
+    db0 = rng.standard_normal(m).astype(np.float32)
+    dyd, xd = _padded_operand(dy), _padded_operand(x)
+    dw = Guarded(m, n, init=torch.from_numpy(dw0).to(DEV))
+    db = Guarded(1, m, init=torch.from_numpy(db0).to(DEV)[None, :])
+    for rep in (1, 2):
+        L.gemm(dw.view, dyd, xd, True, False, beta=1.0, dbias=db.view[0], dbias_beta=1.0, splits=3,
+               tile_n=256 if pairs == 2 else 192, cta_pairs=pairs)
+        inc_w = oracle.gemm(dy, x, trans_a=True)
+        inc_b = oracle.rowsum(dy, trans_a=True)
+        assert oracle.rel_fro(dw.view.cpu().numpy() - dw0, rep * inc_w) <= 5e-3  # difference of close numbers
+        assert oracle.rel_fro(db.view[0].cpu().numpy() - db0, rep * inc_b) <= 5e-3
+        assert dw.intact() and db.intact()
+
+
+@pytest.mark.parametrize("ta", [0, 1])
+def test_dbias_without_transposition_and_with(ta):
+    """dbias[i] = sum_p op(A)[i, p] for both storage orders of A (row sums of an [m, k] matrix,
+    column sums of a [k, m] one), ragged k, on the default plan."""
+    m, n, k = 333, 264, 1234
+    rng = np.random.default_rng(88 + ta)
+    a = oracle.round_bf16(rng.standard_normal((k, m) if ta else (m, k)))
+    b = oracle.round_bf16(rng.standard_normal((k, n)))
+    ad, bd = _padded_operand(a), _padded_operand(b)
+    c = torch.empty(m, n, device=DEV)
+    db = torch.full((m,), 7.0, device=DEV)
+    L.gemm(c, ad, bd, bool(ta), False, dbias=db, dbias_beta=0.0)
+    assert oracle.rel_fro(c.cpu().numpy(), oracle.gemm(a, b, bool(ta), False)) <= TOL
+    assert oracle.rel_fro(db.cpu().numpy(), oracle.rowsum(a, trans_a=bool(ta))) <= TOL
+
+
+def test_fp32_path_bias_gradient():
+    """Strict-fp32 Linear backward with a bias: dbias += column sums of dy (fixed order)."""
+    rng = np.random.default_rng(91)
+    dy = rng.standard_normal((300, 70)).astype(np.float32)
+    x = rng.standard_normal((300, 50)).astype(np.float32)
+    db0 = rng.standard_normal(70).astype(np.float32)
+    dw = torch.zeros(70, 50, device=DEV)
+    db = torch.from_numpy(db0).to(DEV)
+    L.gemm(dw, torch.from_numpy(dy).to(DEV), torch.from_numpy(x).to(DEV), True, False, beta=1.0,
+           dbias=db, dbias_beta=1.0)
+    assert oracle.rel_fro(dw.cpu().numpy(), oracle.gemm(dy, x, trans_a=True)) <= 1e-5
+    assert oracle.rel_fro(db.cpu().numpy(), db0 + dy.astype(np.float64).sum(axis=0)) <= 1e-5
+
+
+def test_operands_that_start_at_odd_addresses_are_repacked():
+    """Slices such as x[:, 1:] start 2 bytes off a 16-byte boundary (and have an odd pitch view):
+    they are copied into the workspace first; the result is that of the aligned operands."""
+    m, n, k = 200, 136, 264
+    rng = np.random.default_rng(93)
+    a = oracle.round_bf16(rng.standard_normal((m, k)))
+    b = oracle.round_bf16(rng.standard_normal((n, k)))
+    abuf = torch.zeros(m, k + 8, device=DEV, dtype=torch.bfloat16)
+    bbuf = torch.zeros(n, k + 8, device=DEV, dtype=torch.bfloat16)
+    abuf[:, 1:k + 1] = _bf16_dev(a)
+    bbuf[:, 3:k + 3] = _bf16_dev(b)
+    av, bv = abuf[:, 1:k + 1], bbuf[:, 3:k + 3]
+    assert av.data_ptr() % 16 != 0 and bv.data_ptr() % 16 != 0
+    c = torch.empty(m, n, device=DEV)
+    d = L.make_desc(c, av, bv, False, True)
+    assert L.workspace_bytes(d) == 0 and L.workspace_bytes(d, av, bv) >= 2 * (m + n) * k
+    L.gemm(c, av, bv, False, True)
+    assert oracle.rel_fro(c.cpu().numpy(), oracle.gemm(a, b, False, True)) <= TOL
+
+
+def test_tensor_map_cache_replays_descriptors():
+    """The second call on the same buffers encodes nothing and gives the same bits."""
+    m, n, k = 512, 384, 256
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn(m, k, device=DEV, generator=g).to(torch.bfloat16)
+    b = torch.randn(n, k, device=DEV, generator=g).to(torch.bfloat16)
+    c1 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    d = L.make_desc(c1, a, b, False, True)
+    L.gemm_desc(d, c1, a, b)
+    h0, m0 = L.tensor_map_cache_stats()
+    first = c1.clone()
+    c1.zero_()
+    L.gemm_desc(d, c1, a, b)
+    h1, m1 = L.tensor_map_cache_stats()
+    assert m1 == m0 and h1 >= h0 + 3   # A, B and C maps all came from the cache
+    assert torch.equal(c1, first)
+    # a different shape on the same base addresses must not be answered from the cache
+    c2 = torch.empty(m // 2, n, device=DEV, dtype=torch.bfloat16)
+    L.gemm(c2, a[: m // 2], b, False, True)
+    assert torch.equal(c2, first[: m // 2])

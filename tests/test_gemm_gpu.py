@@ -299,8 +299,8 @@ def test_bf16_strided_batched(ta, tb):
 @pytest.mark.parametrize("splits", [0, 1, 3])
 @pytest.mark.parametrize("tile_n", [128, 256])
 def test_bf16_dw_with_fused_dbias_on_cta_pairs(tile_n, splits):
-    """The same product on CTA pairs (256-row tiles): dbias comes from a second 16-column MMA
-    per k-step against a block of ones, in an accumulator slot of its own."""
+    """The same product on CTA pairs (256-row tiles); each CTA of the pair that draws a dbias
+    ticket reduces half of its rows."""
     tokens, out_f, in_f = 1024, 520, 2 * tile_n + 40
     rng = np.random.default_rng(53 + tile_n + splits)
     dy = oracle.round_bf16(rng.standard_normal((tokens, out_f)) * 0.01)
@@ -327,7 +327,7 @@ def test_bf16_single_cta_and_pair_kernels_agree(ta, tb, cta_pairs):
 
 
 @pytest.mark.parametrize("splits", [0, 1, 3, 8])
-@pytest.mark.parametrize("tile_n", [64, 128, 192])
+@pytest.mark.parametrize("tile_n", [64, 128, 192, 256])
 def test_bf16_dw_with_fused_dbias_and_splitk(tile_n, splits):
     # Linear backward: dW += dy^T x, dbias += sum_rows dy (llmt linear.cpp:27-29 + bias extension)
     tokens, out_f, in_f = 1024, 200, 2 * tile_n + 40

@@ -92,6 +92,39 @@ def test_rejects_bad_arguments():
         L.grad_allreduce_emulated(descs, 0, 8, 4)
 
 
+def test_a_peer_that_never_arrives_ends_the_wait_with_a_status_not_a_hang():
+    """The plain (one rank per launch) kernel as rank 0 of a world of 2 whose 'peer' buffers are
+    local and whose peer never runs: rank 1's flags are never raised.  With the wait limit
+    lowered to 50 ms the kernel gives up, finishes, and the host reads ERR_DEVICE with
+    DEV_WAIT_PEER; nothing faults, nothing waits for ever, and the context stays usable."""
+    dev = torch.device("cuda", 0)
+    descs, spans, keep = _emulated(2, 4096, dev)
+    assert descs[0].grad_mc is None  # peer-copy form: no multicast object is involved
+    L.set_wait_limit_ns(exchange_ns=50_000_000)
+    try:
+        L.grad_allreduce(descs[0], 0, 4096, 2)
+        with pytest.raises(L.LlmtB200Error) as ei:
+            L.device_status()
+    finally:
+        L.set_wait_limit_ns(exchange_ns=4_000_000_000)
+    assert ei.value.status == L.ERR_DEVICE
+    assert f"code {L.DEV_WAIT_PEER} " in str(ei.value)
+    assert L.device_status() == (0, 0)  # reading the word cleared it
+    # the same context afterwards: a complete exchange on fresh buffers, and an ordinary GEMM
+    descs2, spans2, keep2 = _emulated(2, 4096, dev)
+    parts = [torch.full((4096,), float(r + 1), device=dev) for r in range(2)]
+    for s_, p_ in zip(spans2, parts):
+        s_.copy_(p_)
+    L.grad_allreduce_emulated(descs2, 0, 4096, 2)
+    assert L.device_status() == (0, 0)
+    assert torch.equal(spans2[0], parts[0] + parts[1]) and torch.equal(spans2[1], spans2[0])
+    a = torch.ones(256, 64, device=dev, dtype=torch.bfloat16)
+    c = torch.empty(256, 256, device=dev)
+    L.gemm(c, a, torch.ones(256, 64, device=dev, dtype=torch.bfloat16), False, True)
+    assert L.device_status() == (0, 0)
+    assert torch.equal(c, torch.full_like(c, 64.0))
+
+
 # ---- the real path: one process per GPU --------------------------------------------------
 
 def _free_port():
@@ -133,6 +166,16 @@ def _peer_worker(rank, world, port, out_dir, multicast=False):
                 torch.allclose(bucket.flat, want, rtol=1e-6, atol=1e-6)  # the switch's order of additions
             if not same:
                 msg = f"call {call}: mismatch, max abs err {float((bucket.flat - want).abs().max())}"
+                break
+            # the same partial sums again: the exchange must reproduce its own bits
+            first = bucket.flat.clone()
+            bucket.flat.copy_(parts[rank])
+            dist.barrier()
+            ex.allreduce(off, cnt)
+            ex.allreduce(off2, cnt2)
+            L.device_status()
+            if not torch.equal(bucket.flat, first):
+                msg = f"call {call}: rerun differs"
                 break
         gathered = [torch.empty_like(bucket.flat) for _ in range(world)]
         dist.all_gather(gathered, bucket.flat)

@@ -5,9 +5,7 @@ GEMM (a frozen memory plan where cudaMalloc would stall the device, a plugin
 that receives tensors but no allocator). Its split-K scratch is a fixed array
 inside the library. The test drives it through the C ABI on a split-K problem
 (a Linear dW + dbias shape), twice in a row, and requires the same output as the
-ordinary entry point gives with a caller-supplied workspace. The file name keeps
-it last in pytest's collection order, so a run that stops at the first failure
-has already run everything else.
+ordinary entry point gives with a caller-supplied workspace.
 """
 import ctypes
 
