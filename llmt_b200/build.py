@@ -82,11 +82,13 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 CPP_DIR = os.path.join(HERE, "cpp")
-CPP_SOURCES = ["runtime.cpp", "matmul.cpp", "layers.cpp", "attention.cpp"]
+CPP_SOURCES = ["runtime.cpp", "matmul.cpp", "layers.cpp", "attention.cpp", "peer_exchange.cpp"]
 HOST_LIB = os.path.join(LIB_DIR, "libllmt_b200_host.so")
 ROOT = os.path.dirname(HERE)
 CPP_TEST_SRC = os.path.join(ROOT, "tests", "cpp", "test_llmt_goldens.cpp")
 CPP_TEST_BIN = os.path.join(ROOT, "tests", "cpp", "_build", "test_llmt_goldens")
+CPP_TESTS = {"test_llmt_goldens": CPP_TEST_BIN,
+             "test_peer_exchange": os.path.join(ROOT, "tests", "cpp", "_build", "test_peer_exchange")}
 
 
 def build_cpp(force: bool = False) -> str:
@@ -107,14 +109,16 @@ def build_cpp(force: bool = False) -> str:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("C++ interface library failed to build")
     os.makedirs(os.path.dirname(CPP_TEST_BIN), exist_ok=True)
-    if force or _stale(CPP_TEST_BIN, [CPP_TEST_SRC, HOST_LIB]):
-        cmd = [nvcc(), *flags, "-o", CPP_TEST_BIN, CPP_TEST_SRC, f"-L{LIB_DIR}", "-lllmt_b200_host",
-               "-lllmt_b200", "-Xlinker", "-rpath", "-Xlinker", LIB_DIR,
-               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../llmt_b200/lib"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("C++ golden test failed to build")
+    for name, binary in CPP_TESTS.items():
+        src = os.path.join(ROOT, "tests", "cpp", name + ".cpp")
+        if force or _stale(binary, [src, HOST_LIB]):
+            cmd = [nvcc(), *flags, "-o", binary, src, f"-L{LIB_DIR}", "-lllmt_b200_host",
+                   "-lllmt_b200", "-Xlinker", "-rpath", "-Xlinker", LIB_DIR,
+                   "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../llmt_b200/lib"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                sys.stderr.write(r.stdout + r.stderr)
+                raise RuntimeError(f"C++ test {name} failed to build")
     return CPP_TEST_BIN
 
 

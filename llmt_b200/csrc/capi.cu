@@ -93,12 +93,19 @@ int sm_count() {
 // Cost of one 64-deep k-block of a tile in SM cycles.  Two bounds: the tensor pipe (2*bn
 // cycles for the CTA's 128 rows, about 15 % more once the per-k-block commit is counted:
 // 590 measured for bn = 256) and the rate at which one SM pulls operand bytes out of L2
-// (about 76 bytes per cycle measured; a single CTA stages 128 + bn rows of 128 bytes, a CTA of a
-// pair 128 + bn/2).  A single CTA's 256-wide tile is load-bound (measured 610-665), a pair's
-// is not.
+// (about 76 bytes per cycle measured; a single CTA stages 128 + bn rows of 128 bytes).  A single
+// CTA's 256-wide tile is load-bound (measured 610-665), a pair's is not; a pair's narrower
+// tiles cost more per column than the model of either bound says (measured: 128-wide tiles
+// take three quarters of the time of 256-wide ones), so they only pay against wave
+// quantisation.
 int kblock_cost(int bn, bool pairs) {
+    if (pairs) {
+        // measured: 590 for a 256-wide tile, the same per column at 192, and no less than 445
+        const int c = 590 * bn / 256;
+        return c > 445 ? c : 445;
+    }
     const int mma = bn * 2 * 115 / 100;
-    const int load = (128 + (pairs ? bn / 2 : bn)) * 128 / 76;
+    const int load = (128 + bn) * 128 / 76;
     return mma > load ? mma : load;
 }
 

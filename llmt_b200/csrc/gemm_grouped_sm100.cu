@@ -26,10 +26,11 @@
 //
 // The fused bias gradient (dbias[i] = sum_p op(A)[i, p]; for the dW product of a linear
 // layer: the column sums of dy) is part of the same launch: its reductions are extra
-// tickets at the head of the queue that the epilogue warps of whichever CTA draws them
-// carry out with plain loads (dy is in L2: the dX and dW tiles of the launch stream it),
-// in a fixed order, while that CTA's producer and MMA warps already work on the next
-// tile.  The tensor pipe never sees them.
+// tickets at the head of the queue, each 16 values of i per CTA, that the epilogue warps of
+// whichever CTA draws them carry out with plain loads (dy is in L2: the dX and dW tiles of the
+// launch stream it), in a fixed order, while that CTA's producer and MMA warps already work
+// on the next tile.  Narrow tickets put every SM to work on them: the reduction is bound by
+// the bytes one SM can keep in flight, not by arithmetic.  The tensor pipe never sees them.
 //
 // No wait is unbounded: every mbarrier wait gives up after GroupParams::wait_limit_ns,
 // records why in the DeviceStatus word and makes the CTA drain and exit.
@@ -69,7 +70,8 @@ template <int CG> struct Geo {
 constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block
 constexpr uint32_t kAccStride = 256;                 // TMEM columns per accumulator buffer
 constexpr uint32_t kTmemCols = 512;
-constexpr int kDbiasColsPerCta = 128;                // columns (rows of op(A)) one CTA reduces per dbias ticket
+constexpr int kDbiasColsPerCta = 16;                 // rows of op(A) whose sums one CTA forms per dbias ticket
+constexpr uint32_t kDbiasScratchBytes = kRing * kEpilogueWarps * kDbiasColsPerCta * 4;  // 2 KB
 
 struct __align__(8) Control {
     uint64_t full[kMaxStages];
@@ -79,6 +81,7 @@ struct __align__(8) Control {
     uint64_t sched_full[kRing];
     uint64_t sched_empty[kRing];
     int32_t ring[kRing];
+    int32_t dbias_arrivals[kRing];  // epilogue warps that have delivered their part of a dbias ticket, per ring slot
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -227,79 +230,104 @@ __device__ __forceinline__ float lanes_sum(float v) {
 }
 
 // One dbias ticket as one of the eight epilogue warps (ew = 0..7) of a CTA sees it:
-// dbias[i] (+)= sum over p in this split's k range of op(A)[i, p] for the 16 values of i
-// that belong to this warp; the CTA covers kDbiasColsPerCta of them starting at i_cta.
-// Warps work independently (no shared memory, no barrier between warps); the order of the
-// additions depends only on the problem's shape.
-__device__ __noinline__ void dbias_ticket_warp(const GroupProblem& p, int64_t i_cta, int split, int ew, int lane) {
-    const int64_t i0 = i_cta + 16 * ew;
-    if (i0 >= p.m) return;
+// dbias[i] (+)= sum over p in this split's k range of op(A)[i, p] for the kDbiasColsPerCta
+// values of i starting at i0.  The order of the additions depends only on the problem's
+// shape.  `scratch` (8 x 16 floats) and `arrivals` belong to the ring slot the ticket came in.
+__device__ __noinline__ void dbias_ticket_warp(const GroupProblem& p, int64_t i0, int split, int ew, int lane,
+                                               float* scratch, int32_t* arrivals) {
+    if (i0 >= p.m) return;  // CTA-uniform: all eight warps skip together
     const int64_t kbeg = static_cast<int64_t>(split) * p.kblocks_per_split * BK;
     int64_t kend = kbeg + static_cast<int64_t>(p.kblocks_per_split) * BK;
     if (kend > p.k) kend = p.k;
     const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a_raw);
-    float out = 0.0f;  // lane j < 16 ends with the sum for i0 + j
     if (p.a_mn) {
         // A is stored [k, m]: the sums run down columns i0 .. i0+15 (32 bytes of every row).
-        // Lane L takes rows kbeg + L, + 32, ...; eight rows (256 bytes) in flight per lane.
-        float acc[16];
+        // The eight warps share the rows: warp w, lane L reads 16 bytes (columns i0 + 8 (L & 1) ..)
+        // of rows kbeg + 16 w + L / 2, + 128, ...; sixteen rows in flight per lane.  A warp then
+        // folds its sixteen row-lanes in a fixed tree and leaves 16 partial sums in shared memory;
+        // the warp that arrives last adds the eight partial sums of every column in warp order.
+        float acc[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
-        const bool second = i0 + 8 < p.m;   // the row pitch covers whole groups of 8 columns
-        const __nv_bfloat16* col = A + i0;
-        int64_t r = kbeg + lane;
-        for (; r + 7 * 32 < kend; r += 8 * 32) {
-            uint4 q[16];
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        const int64_t c = i0 + 8 * (lane & 1);
+        if (c < p.m) {  // the row pitch covers whole groups of 8 columns
+            const __nv_bfloat16* col = A + c;
+            int64_t r = kbeg + 16 * ew + (lane >> 1);
+            for (; r + 15 * 128 < kend; r += 16 * 128) {
+                uint4 q[16];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const __nv_bfloat16* src = col + (r + 32 * u) * p.lda;
-                q[2 * u] = ld_operand16(src);
-                q[2 * u + 1] = second ? ld_operand16(src + 8) : make_uint4(0u, 0u, 0u, 0u);
+                for (int u = 0; u < 16; ++u) q[u] = ld_operand16(col + (r + 128 * u) * p.lda);
+#pragma unroll
+                for (int u = 0; u < 16; ++u) add_bf16x8(acc, q[u]);
             }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                add_bf16x8(acc, q[2 * u]);
-                add_bf16x8(acc + 8, q[2 * u + 1]);
-            }
-        }
-        for (; r < kend; r += 32) {
-            const __nv_bfloat16* src = col + r * p.lda;
-            add_bf16x8(acc, ld_operand16(src));
-            if (second) add_bf16x8(acc + 8, ld_operand16(src + 8));
+            for (; r < kend; r += 128) add_bf16x8(acc, ld_operand16(col + r * p.lda));
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float t = lanes_sum(acc[j]);
-            if (lane == j) out = t;
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int o = 16; o > 1; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+        }
+        if (lane < 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) scratch[ew * kDbiasColsPerCta + 8 * lane + j] = acc[j];
+        }
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            last = (atomicAdd(arrivals, 1) & (kEpilogueWarps - 1)) == kEpilogueWarps - 1;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence_block();
+        const int64_t i = i0 + lane;
+        if (lane < kDbiasColsPerCta && i < p.m) {
+            const volatile float* sc = scratch;
+            float out = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kEpilogueWarps; ++w) out += sc[w * kDbiasColsPerCta + lane];
+            if (p.splits > 1) {
+                p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = out;
+            } else {
+                const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+                p.dbias[i] = prev + out;
+            }
         }
     } else {
-        // A is stored [m, k]: the sums run along rows i0 .. i0+15.  Lane L takes the 8 elements
-        // at kbeg + 8 L, + 256, ... of each row; lane 0 also takes the ragged end of the range.
+        // A is stored [m, k]: the sums run along rows; warp w takes rows i0 + 2 w and i0 + 2 w + 1.
+        // Lane L takes the 8 elements at kbeg + 8 L, + 256, ... of a row; lane 0 also takes the
+        // ragged end of the range.
         const int64_t span = kend - kbeg;
         const int64_t vec_end = kbeg + span / 8 * 8;
 #pragma unroll 1
-        for (int j = 0; j < 16; ++j) {
-            const int64_t i = i0 + j;
+        for (int j = 0; j < 2; ++j) {
+            const int64_t i = i0 + 2 * ew + j;
             if (i >= p.m) break;  // warp-uniform
             const __nv_bfloat16* row = A + i * p.lda;
             float acc[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-            for (int64_t q = kbeg + 8 * lane; q < vec_end; q += 256) add_bf16x8(acc, ld_operand16(row + q));
+            int64_t q = kbeg + 8 * lane;
+            for (; q + 3 * 256 < vec_end; q += 4 * 256) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = ld_operand16(row + q + 256 * u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) add_bf16x8(acc, v[u]);
+            }
+            for (; q < vec_end; q += 256) add_bf16x8(acc, ld_operand16(row + q));
             float t = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
             if (lane == 0)
-                for (int64_t q = vec_end; q < kend; ++q) t += __bfloat162float(row[q]);
+                for (int64_t e = vec_end; e < kend; ++e) t += __bfloat162float(row[e]);
             t = lanes_sum(t);
-            if (lane == j) out = t;
-        }
-    }
-    const int64_t i = i0 + lane;
-    if (lane < 16 && i < p.m) {
-        if (p.splits > 1) {
-            p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = out;
-        } else {
-            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
-            p.dbias[i] = prev + out;
+            if (lane == 0) {
+                if (p.splits > 1) {
+                    p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = t;
+                } else {
+                    const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+                    p.dbias[i] = prev + t;
+                }
+            }
         }
     }
 }
@@ -338,6 +366,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     Control* ctl = reinterpret_cast<Control*>(smem_raw);
     const uint32_t smem_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
     const uint32_t staging_base = smem_base + kStages * kStageBytes;
+    float* dbias_scratch = reinterpret_cast<float*>(smem_raw + (staging_base - smem_u32(smem_raw)) + Geo<CG>::kStagingBytes);
     volatile int* abort_flag = &ctl->abort_flag;
     DeviceStatus* status = gp.status;
 
@@ -357,6 +386,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             mbar_init(smem_u32(&ctl->sched_full[r]), 1);
             mbar_init(smem_u32(&ctl->sched_empty[r]), kPair ? 2 * (2 + kEpilogueWarps) : 1 + kEpilogueWarps);  // every ring reader
         }
+        for (int r = 0; r < kRing; ++r) ctl->dbias_arrivals[r] = 0;
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
@@ -585,10 +615,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (!ok) break;
             const int t = ctl->ring[slot];
             __syncwarp();
-            if (lane == 0) release_ring_slot(slot);
-            if (t < 0) break;
-            if (t < gp.colsum_total) {
-                // A dbias ticket: (block of rows of op(A), split) of the problem that owns it.
+            if (t >= 0 && t < gp.colsum_total) {
+                // A dbias ticket: (block of rows of op(A), split) of the problem that owns it.  The
+                // ring slot is released only afterwards: its scratch area is in use until then.
                 int pi = 0;
 #pragma unroll 1
                 for (int i = 0; i < gp.num_problems; ++i)
@@ -596,9 +625,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 const GroupProblem& p = gp.prob[pi];
                 const int r = t - p.colsum_begin;
                 const int blk = r % p.colsum_blocks, split = r / p.colsum_blocks;
-                dbias_ticket_warp(p, (static_cast<int64_t>(blk) * CG + rank) * kDbiasColsPerCta, split, ew, lane);
+                dbias_ticket_warp(p, (static_cast<int64_t>(blk) * CG + rank) * kDbiasColsPerCta, split, ew, lane,
+                                  dbias_scratch + slot * (kEpilogueWarps * kDbiasColsPerCta), &ctl->dbias_arrivals[slot]);
+                __syncwarp();
+                if (lane == 0) release_ring_slot(slot);
                 continue;
             }
+            if (lane == 0) release_ring_slot(slot);
+            if (t < 0) break;
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
@@ -844,11 +878,12 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
 
 size_t tc_grouped_smem_bytes() {
     // Both geometries use the same amount: 4 x 48 KB of operand stages + 32 KB of staging,
-    // or 5 x 32 KB + 64 KB.
+    // or 5 x 32 KB + 64 KB; then 2 KB for the dbias tickets.  227 KB in all.
     static_assert(Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes ==
                   Geo<2>::kStages * Geo<2>::kStageBytes + Geo<2>::kStagingBytes, "shared-memory budget");
     static_assert(sizeof(Control) <= 1024, "control block must fit below the first aligned KB");
-    return 1024 /* control block + alignment */ + Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes;
+    return 1024 /* control block + alignment */ + Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes +
+           kDbiasScratchBytes;
 }
 
 int tc_dbias_rows_per_cta() { return kDbiasColsPerCta; }

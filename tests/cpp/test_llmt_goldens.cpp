@@ -234,7 +234,7 @@ void test_bf16_linear(Device& dev) {
     ParamStore ps32(StateDtypes::uniform(DType::FP32));
     const Linear l32(ps32, "w", IN, OUT, Role::Matrix, /*bias=*/true);  // fp32 layer with a bias too
     ps32.finalize();
-    ParamStore ps16(StateDtypes{DType::BF16, DType::FP32});
+    ParamStore ps16(StateDtypes::mixed(DType::BF16));
     const Linear l16(ps16, "w", IN, OUT, Role::Matrix, /*bias=*/true);
     ps16.finalize();
     CUDA_CHECK(cudaMemcpy(l32.param().weight.data, w32.data, w32.bytes(), cudaMemcpyDeviceToDevice));

@@ -20,6 +20,22 @@ def test_llmt_cpp_interface_goldens():
     assert "0 failures" in r.stdout
 
 
+@pytest.mark.gpu
+def test_cpp_param_store_allreduce_over_cuda_ipc_two_processes():
+    """The C++ host side of the exchange: ParamStore (aliases, four spans, gradient span placed in
+    a dist::PeerExchange allocation) + allreduce_grads over CUDA IPC, two processes on two GPUs."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    binary = os.path.join(ROOT, "tests", "cpp", "_build", "test_peer_exchange")
+    assert os.path.exists(binary), "run `python -m llmt_b200.build` (or __graft_entry__.build()) first"
+    r = subprocess.run([binary, "2"], capture_output=True, text=True, timeout=300)
+    if r.returncode == 77:
+        pytest.skip("fewer GPUs than ranks")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "0 failures" in r.stdout
+
+
 def test_cpp_interface_is_built_and_links_the_c_abi():
     """CPU check: the interface library exists and resolves against the C-ABI library."""
     host = os.path.join(ROOT, "llmt_b200", "lib", "libllmt_b200_host.so")
