@@ -246,13 +246,13 @@ def test_exchange_layout_is_aligned_and_large_enough():
 
 
 def test_fused_dbias_products_run_on_pairs_with_full_width_tiles():
-    # dW + dbias: the bias gradient is reduced by tickets of its own, so the product may use
-    # any tile width, on CTA pairs too (the QKV layer of GPT-2-small: 2304 x 768 over 8192 tokens)
+    # dW + dbias: the bias gradient is reduced by tickets of its own (16 rows of op(A) per CTA),
+    # so the product keeps 256-wide tiles on CTA pairs (the QKV layer of GPT-2-small: 2304 x 768
+    # over 8192 tokens, split in two so that its 27 tiles fill the 74 pairs)
     d = _desc(m=2304, n=768, k=8192, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
               dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
     plan = L.plan(d)
-    assert "cta-pair tile=256x" in plan and "dbias_tickets=9 " in plan  # 2304 / (2 x 128) row blocks
-    d.plan_tile_n = 256
-    assert "cta-pair tile=256x256x64" in L.plan(d)
+    assert "cta-pair tile=256x256x64" in plan and "splits=2 " in plan
+    assert "dbias_tickets=144 " in plan  # 2304 / (2 x 16) row blocks x 2 splits
     d.plan_cta_pairs = 1
-    assert "1-cta tile=128x256x64" in L.plan(d) and "splits=2 " in L.plan(d) and "dbias_tickets=36 " in L.plan(d)
+    assert "1-cta tile=128x256x64" in L.plan(d) and "dbias_tickets=288 " in L.plan(d)
