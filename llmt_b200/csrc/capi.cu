@@ -111,13 +111,11 @@ int kblock_cost(int bn, bool pairs) {
 
 int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
-void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int bn, int splits,
+// dbias_mode: 0 none, 1 column sums of A stored [k, m] (two phases), 2 row sums of A stored [m, k].
+void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode, int bn, int splits,
                  bool pairs) {
     pl->bn = bn;
     pl->pairs = pairs ? 1 : 0;
-    // The fused dbias is carried out as tickets of its own: one per block of rows of op(A)
-    // (and per split) that a CTA, or the two CTAs of a pair, reduce.
-    pl->colsum_blocks = dbias ? ceil_div(m, static_cast<int64_t>(tc_dbias_rows_per_cta()) * (pairs ? 2 : 1)) : 0;
     pl->tiles_m = ceil_div(m, pairs ? 256 : 128);
     pl->tiles_n = ceil_div(n, bn);
     pl->kblocks_total = ceil_div(k, 64);
@@ -129,9 +127,23 @@ void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, boo
     pl->workspace_bytes = 0;
     if (pl->splits > 1) {
         size_t ws = static_cast<size_t>(batch) * pl->splits * m * n * sizeof(float);
-        ws = (ws + 255) / 256 * 256;
-        if (dbias) ws += (static_cast<size_t>(pl->splits) * m * sizeof(float) + 255) / 256 * 256;
-        pl->workspace_bytes = ws;
+        pl->workspace_bytes = (ws + 255) / 256 * 256;
+    }
+    // The fused dbias runs as tickets of its own, independent of the product's tiling.
+    const int cg = pairs ? 2 : 1;
+    pl->dbias_mode = k > 0 ? dbias_mode : 0;
+    pl->colsum_tiles = pl->dbias_rows = pl->fin_tiles = 0;
+    pl->ws_dbias_off = 0;
+    if (pl->dbias_mode == 1) {
+        // chunks of at least 64 rows of A, at most 512 chunks
+        const int64_t rows = ceil_div(k, 512) > 64 ? ceil_div(k, 512) : 64;
+        pl->dbias_rows = static_cast<int>(rows);
+        pl->colsum_tiles = ceil_div(k, rows);
+        pl->fin_tiles = ceil_div(m, static_cast<int64_t>(tc_dbias_finish_per_cta()) * cg);
+        pl->ws_dbias_off = pl->workspace_bytes;
+        pl->workspace_bytes += (static_cast<size_t>(pl->colsum_tiles) * m * sizeof(float) + 255) / 256 * 256;
+    } else if (pl->dbias_mode == 2) {
+        pl->colsum_tiles = ceil_div(m, static_cast<int64_t>(tc_dbias_rows_per_cta()) * cg);
     }
 }
 
@@ -152,7 +164,7 @@ int choose_splits(int64_t tiles, int kblocks_total, int sms) {
 // of waves of equal tiles.  A pure function of its arguments.
 // `pairs`: the launch uses CTA pairs (256-row tiles, `units` = number of pairs); with
 // MN-major B a pair needs a tile width that is a multiple of 128.
-TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int units,
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode, int units,
                  int force_bn, int force_splits, bool pairs, bool b_mn) {
     const int sms = units;
     const int cands[4] = {256, 192, 128, 64};
@@ -181,14 +193,14 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int
     }
     TcPlan pl{};
     if (best_bn == 0) best_bn = pairs ? 128 : 64;
-    finish_plan(&pl, m, n, k, batch, dbias, best_bn, best_splits, pairs);
+    finish_plan(&pl, m, n, k, batch, dbias_mode, best_bn, best_splits, pairs);
     return pl;
 }
 
 // Plan of a problem that shares its launch with others: the queue is dynamic, so wave
 // quantisation of one problem does not matter; take the widest tile that wastes nothing
 // and split only reductions that are longer than the average load of an SM.
-TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbias, int sms,
+TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode, int sms,
                        int64_t group_kblock_tiles, int force_bn, int force_splits, bool pairs, bool b_mn) {
     int bn = 256;
     if (n <= 64) bn = pairs ? 128 : 64;
@@ -207,7 +219,7 @@ TcPlan make_group_plan(int64_t m, int64_t n, int64_t k, int64_t batch, bool dbia
         if (splits > max_by_k) splits = max_by_k;
     }
     TcPlan pl{};
-    finish_plan(&pl, m, n, k, batch, dbias, bn, splits, pairs);
+    finish_plan(&pl, m, n, k, batch, dbias_mode, bn, splits, pairs);
     return pl;
 }
 
@@ -257,9 +269,10 @@ int pair_units() {
     const int by_sm = sm_count() / 2;
     return (r > 0 && r < by_sm) ? r : by_sm;
 }
+int dbias_mode_of(const llmt_b200_gemm_desc* d) { return d->dbias == nullptr ? 0 : (d->trans_a ? 1 : 2); }
 TcPlan plan_single(const llmt_b200_gemm_desc* d) {
     const bool pairs = pair_eligible(d);
-    return make_plan(d->m, d->n, d->k, d->batch, d->dbias != nullptr, pairs ? pair_units() : sm_count(),
+    return make_plan(d->m, d->n, d->k, d->batch, dbias_mode_of(d), pairs ? pair_units() : sm_count(),
                      d->plan_tile_n, d->plan_splits, pairs, d->trans_b == 0);
 }
 
@@ -444,6 +457,9 @@ int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t
 // take them round-robin so that kernels in flight at the same time do not share one.
 constexpr int kSchedSlots = 64;
 static __device__ int32_t g_sched_counters[kSchedSlots];
+// Arrival counters of the two-phase dbias reduction, one pair per launch slot; the kernel
+// re-arms them too.
+static __device__ int32_t g_dbias_sync[kSchedSlots][2];
 
 // Per-device host state.  Several devices per process are supported as long as each device's
 // calls come from one host thread at a time (llmt's rule: one thread issues the launches,
@@ -451,6 +467,7 @@ static __device__ int32_t g_sched_counters[kSchedSlots];
 struct DeviceGlobals {
     bool ready = false;
     int32_t* counters = nullptr;
+    int32_t* dbias_sync = nullptr;
     unsigned next = 0;
 };
 
@@ -468,11 +485,15 @@ int device_globals(DeviceGlobals** out) {
     if (g == nullptr) return fail(LLMT_B200_ERR_CUDA, "no current CUDA device");
     if (!g->ready) {
         void* ctr = nullptr;
+        void* sync = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ctr, g_sched_counters);
         if (e == cudaSuccess) e = cudaMemset(ctr, 0, sizeof(int32_t) * kSchedSlots);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&sync, g_dbias_sync);
+        if (e == cudaSuccess) e = cudaMemset(sync, 0, sizeof(int32_t) * kSchedSlots * 2);
         if (e != cudaSuccess)
             return fail(LLMT_B200_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
         g->counters = static_cast<int32_t*>(ctr);
+        g->dbias_sync = static_cast<int32_t*>(sync);
         g->ready = true;
     }
     *out = g;
@@ -576,14 +597,12 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->epi_flags = d->epilogue;
     p->dbias = d->dbias; p->dbias_beta = d->dbias_beta;
     p->a_raw = a; p->lda = d->lda;
-    p->colsum_blocks = pl.colsum_blocks;
-    p->colsum_tiles = pl.colsum_blocks * pl.splits;
-    if (pl.splits > 1) {
-        p->ws = static_cast<float*>(d->workspace);
-        size_t ws = static_cast<size_t>(d->batch) * pl.splits * d->m * d->n * sizeof(float);
-        ws = (ws + 255) / 256 * 256;
-        p->ws_dbias = d->dbias ? reinterpret_cast<float*>(static_cast<char*>(d->workspace) + ws) : nullptr;
-    }
+    p->dbias_mode = pl.dbias_mode;
+    p->colsum_tiles = pl.colsum_tiles;
+    p->dbias_rows = pl.dbias_rows;
+    p->fin_tiles = pl.fin_tiles;
+    if (pl.splits > 1) p->ws = static_cast<float*>(d->workspace);
+    if (pl.dbias_mode == 1) p->ws_dbias = reinterpret_cast<float*>(static_cast<char*>(d->workspace) + pl.ws_dbias_off);
     if (d->k == 0) return LLMT_B200_OK;  // no operand is read
     int st = encode_operand_map(&p->map_a, a, ck.a_rows, ck.a_cols, d->lda, d->batch, d->stride_a,
                                 p->a_mn ? 64 : 128);
@@ -629,28 +648,35 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
             const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
         }
     // Ticket layout: the dbias reductions of all problems first (they keep only the epilogue
-    // warps busy, so the CTAs that draw them go straight on to an MMA tile), then the MMA tiles.
-    int64_t colsum_total = 0;
+    // warps busy, so the CTAs that draw them go straight on to an MMA tile), then the MMA tiles,
+    // then the tickets that finish the two-phase dbias reductions.
+    int64_t colsum_total = 0, fin_total = 0;
     int n = 0;
     for (int i = 0; i < count; ++i) {
         GroupProblem& p = probs[order[i]];
         if (p.k == 0 || p.num_tiles == 0) continue;
         p.colsum_begin = static_cast<int32_t>(colsum_total);
         colsum_total += p.colsum_tiles;
+        p.fin_begin = static_cast<int32_t>(fin_total);
+        fin_total += p.fin_tiles;
         gp.prob[n++] = p;
     }
     int64_t total = colsum_total;
     for (int i = 0; i < n; ++i) {
-        if (total + gp.prob[i].num_tiles > 0x7fffff00)
+        if (total + gp.prob[i].num_tiles + fin_total > 0x7fffff00)
             return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: too many tiles in one launch");
         gp.prob[i].tile_begin = static_cast<int32_t>(total);
         total += gp.prob[i].num_tiles;
     }
     if (n > 0) {
+        const unsigned slot = g->next++ % kSchedSlots;
         gp.num_problems = n;
-        gp.total_tiles = static_cast<int32_t>(total);
         gp.colsum_total = static_cast<int32_t>(colsum_total);
-        gp.sched_counter = g->counters + (g->next++ % kSchedSlots);
+        gp.fin_begin = static_cast<int32_t>(total);
+        total += fin_total;
+        gp.total_tiles = static_cast<int32_t>(total);
+        gp.sched_counter = g->counters + slot;
+        gp.dbias_sync = g->dbias_sync + 2 * slot;
         gp.static_schedule = static_schedule_forced() ? 1 : 0;
         gp.wait_limit_ns = g_wait_limit_ns;
         gp.status = device_status_ptr();
@@ -701,7 +727,7 @@ bool plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
     for (int i = 0; i < count; ++i) {
         const llmt_b200_gemm_desc& d = descs[i];
         plans[i] = count == 1 ? plan_single(&d)
-                              : make_group_plan(d.m, d.n, d.k, d.batch, d.dbias != nullptr, sms, work,
+                              : make_group_plan(d.m, d.n, d.k, d.batch, dbias_mode_of(&d), sms, work,
                                                 d.plan_tile_n, d.plan_splits, pairs, d.trans_b == 0);
     }
     return count == 1 ? plans[0].pairs != 0 : pairs;
@@ -907,10 +933,10 @@ int llmt_b200_gemm_plan(const llmt_b200_gemm_desc* d, char* buf, size_t n) {
     }
     const TcPlan pl = plan_single(d);
     const int units = pl.pairs ? pair_units() : sm_count();
-    const int64_t tickets = pl.num_tiles + static_cast<int64_t>(pl.colsum_blocks) * pl.splits;
+    const int64_t tickets = pl.num_tiles + pl.colsum_tiles + pl.fin_tiles;
     snprintf(buf, n, "tcgen05 %s tile=%dx%dx64 stages=%d splits=%d tiles=%dx%d kblocks=%d dbias_tickets=%d grid=%d smem=%zu ws=%zu resident_pairs=%d",
-             pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? 5 : 4, pl.splits, pl.tiles_m,
-             pl.tiles_n, pl.kblocks_total, pl.colsum_blocks * pl.splits,
+             pl.pairs ? "cta-pair" : "1-cta", pl.pairs ? 256 : 128, pl.bn, pl.pairs ? tc_pair_stages() : 4, pl.splits, pl.tiles_m,
+             pl.tiles_n, pl.kblocks_total, pl.colsum_tiles + pl.fin_tiles,
              static_cast<int>(tickets < units ? tickets : units) * (pl.pairs ? 2 : 1),
              tc_grouped_smem_bytes(), pl.workspace_bytes, pl.pairs ? max_resident_pairs() : 0);
     return LLMT_B200_OK;
@@ -962,7 +988,10 @@ int llmt_b200_device_status(int32_t* code, int32_t* detail) {
         // A kernel that gave up may have left its tile-queue counter part-way; results of
         // launches that were in flight are void, later launches start from clean counters.
         DeviceGlobals* g = device_globals_slot();
-        if (g != nullptr && g->ready) cudaMemset(g->counters, 0, sizeof(int32_t) * kSchedSlots);
+        if (g != nullptr && g->ready) {
+            cudaMemset(g->counters, 0, sizeof(int32_t) * kSchedSlots);
+            cudaMemset(g->dbias_sync, 0, sizeof(int32_t) * kSchedSlots * 2);
+        }
         return fail(LLMT_B200_ERR_DEVICE, "a kernel gave up on a bounded wait: code %d detail %d block %d",
                     h.code, h.detail, h.block);
     }

@@ -45,9 +45,12 @@ struct alignas(64) GroupProblem {
     int32_t a_mn, b_mn;         // operand stored with M / N contiguous (transposed use)
     int32_t tile_begin;         // first MMA tile of this problem in the group's queue
     int32_t num_tiles;          // tiles_m * tiles_n * splits * batch
+    int32_t dbias_mode;         // 0 none; 1 column sums of A stored [k, m] (two phases); 2 row sums of A stored [m, k]
     int32_t colsum_begin;       // first dbias ticket of this problem in the group's queue
-    int32_t colsum_tiles;       // colsum_blocks * splits (0 without a dbias)
-    int32_t colsum_blocks;      // ceil(m / (64 * CTAs per tile))
+    int32_t colsum_tiles;       // mode 1: chunks of rows of A; mode 2: blocks of rows of op(A)
+    int32_t dbias_rows;         // mode 1: rows of A per ticket
+    int32_t fin_begin;          // first finishing ticket of this problem (mode 1), relative to the group's first
+    int32_t fin_tiles;          // finishing tickets: blocks of 256 values of i per CTA
     void* c;
     int64_t ldc, stride_c;
     int32_t c_is_bf16;
@@ -62,14 +65,16 @@ struct alignas(64) GroupProblem {
     float* ws;                  // split-K partial sums [batch][splits][m][n] fp32 (splits > 1)
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
-    float* ws_dbias;            // [splits][m] fp32 (splits > 1 and dbias wanted)
+    float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums
 };
 
 struct GroupParams {
     GroupProblem prob[kMaxGroupProblems];
     int32_t num_problems;
-    int32_t total_tiles;        // tickets of the launch: the dbias tickets first, then the MMA tiles
+    int32_t total_tiles;        // tickets of the launch: dbias reductions, MMA tiles, dbias finishing tickets
     int32_t colsum_total;       // tickets [0, colsum_total) are dbias reductions
+    int32_t fin_begin;          // tickets [fin_begin, total_tiles) finish the two-phase dbias reductions
+    int32_t* dbias_sync;        // [2] arrival counters of the two phases; zero between launches
     int32_t static_schedule;    // 1 = ticket i goes to CTA i % grid instead of the dynamic queue
     int32_t* sched_counter;     // zero between launches; the kernel re-arms it
     DeviceStatus* status;
@@ -112,7 +117,11 @@ struct TcPlan {
     int tiles_m, tiles_n;
     int kblocks_total, kblocks_per_split;
     int64_t num_tiles;
-    int colsum_blocks;  // dbias tickets per split (0 without a dbias)
+    int dbias_mode;     // 0 none, 1 column sums in two phases, 2 row sums
+    int colsum_tiles;   // dbias reduction tickets
+    int dbias_rows;     // mode 1: rows of A per ticket
+    int fin_tiles;      // mode 1: finishing tickets
+    size_t ws_dbias_off;  // mode 1: offset of the partial sums inside the workspace
     size_t workspace_bytes;
 };
 
@@ -153,9 +162,11 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
 cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream);
 int max_resident_pairs(void);
-int tc_dbias_rows_per_cta(void);
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
 size_t tc_grouped_smem_bytes(void);
+int tc_pair_stages(void);
+int tc_dbias_rows_per_cta(void);
+int tc_dbias_finish_per_cta(void);
 cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream);
 cudaError_t launch_fp32_rowsum(const Fp32GemmParams& p, float* dbias, float dbias_beta, cudaStream_t stream);
 cudaError_t launch_zero_f32(float* dst, int64_t n, cudaStream_t stream);

@@ -180,18 +180,46 @@ __global__ void softmax_rows_bwd_kernel(T* ds, const T* p, const T* dp, int64_t 
         Elem<T>::put(out, c, Elem<T>::get(pr, c) * (Elem<T>::get(gr, c) - dot));
 }
 
-// Copies a row-major bf16 matrix (any pitch, any 2-byte alignment) into a buffer whose pitch
-// is a multiple of 8 elements, so that TMA can address it.  One thread per element pair.
+// Copies a row-major bf16 matrix (any pitch, any 2-byte alignment) into a buffer whose base is
+// 16-byte aligned and whose pitch is a multiple of 8 elements, so that TMA can address it.
+// One thread per 8 output elements (one 16-byte store): the source elements come from the
+// five aligned 32-bit words that cover them, shifted by 16 bits when the source row starts on
+// an odd element.  Columns beyond `cols` are written as zeros.
 __global__ void repack_bf16_kernel(uint16_t* __restrict__ dst, const uint16_t* __restrict__ src, int64_t rows,
                                    int64_t cols, int64_t ld_src, int64_t ld_dst, int64_t batch,
                                    int64_t stride_src, int64_t stride_dst) {
-    const int64_t total = batch * rows * ld_dst;
+    const int64_t groups_per_row = ld_dst / 8;
+    const int64_t total = batch * rows * groups_per_row;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t c = i % ld_dst;
-        const int64_t r = (i / ld_dst) % rows;
-        const int64_t b = i / (ld_dst * rows);
-        dst[b * stride_dst + r * ld_dst + c] = c < cols ? src[b * stride_src + r * ld_src + c] : uint16_t(0);
+        const int64_t g = i % groups_per_row;
+        const int64_t r = (i / groups_per_row) % rows;
+        const int64_t b = i / (groups_per_row * rows);
+        const int64_t c0 = g * 8;
+        const uint16_t* s = src + b * stride_src + r * ld_src + c0;
+        uint32_t out[4];
+        if (c0 + 8 <= cols) {
+            const uintptr_t addr = reinterpret_cast<uintptr_t>(s);
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(addr & ~static_cast<uintptr_t>(3));
+            if ((addr & 2u) == 0u) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) out[j] = w[j];
+            } else {
+                uint32_t v[5];
+#pragma unroll
+                for (int j = 0; j < 5; ++j) v[j] = w[j];   // the first and last halves belong to neighbours
+#pragma unroll
+                for (int j = 0; j < 4; ++j) out[j] = __funnelshift_r(v[j], v[j + 1], 16);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lo = c0 + 2 * j < cols ? s[2 * j] : 0u;
+                const uint32_t hi = c0 + 2 * j + 1 < cols ? s[2 * j + 1] : 0u;
+                out[j] = lo | (hi << 16);
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + b * stride_dst + r * ld_dst + c0) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -242,9 +270,10 @@ cudaError_t launch_zero_f32(float* dst, int64_t n, cudaStream_t stream) {
 cudaError_t launch_repack_bf16(void* dst, const void* src, int64_t rows, int64_t cols, int64_t ld_src,
                                int64_t ld_dst, int64_t batch, int64_t stride_src, int64_t stride_dst,
                                cudaStream_t stream) {
-    const int64_t total = batch * rows * ld_dst;
+    const int64_t total = batch * rows * (ld_dst / 8);   // ld_dst is a multiple of 8
     int64_t grid = (total + 255) / 256;
     if (grid > 148 * 32) grid = 148 * 32;
+    if (grid < 1) grid = 1;
     repack_bf16_kernel<<<static_cast<unsigned>(grid), 256, 0, stream>>>(
         static_cast<uint16_t*>(dst), static_cast<const uint16_t*>(src), rows, cols, ld_src, ld_dst, batch,
         stride_src, stride_dst);

@@ -25,12 +25,16 @@
 // to the tensor core as MN-major.
 //
 // The fused bias gradient (dbias[i] = sum_p op(A)[i, p]; for the dW product of a linear
-// layer: the column sums of dy) is part of the same launch: its reductions are extra
-// tickets at the head of the queue, each 16 values of i per CTA, that the epilogue warps of
-// whichever CTA draws them carry out with plain loads (dy is in L2: the dX and dW tiles of the
-// launch stream it), in a fixed order, while that CTA's producer and MMA warps already work
-// on the next tile.  Narrow tickets put every SM to work on them: the reduction is bound by
-// the bytes one SM can keep in flight, not by arithmetic.  The tensor pipe never sees them.
+// layer: the column sums of dy) is part of the same launch, as extra tickets that only the
+// epilogue warps of whichever CTA draws them work on, with plain loads, while that CTA's
+// producer and MMA warps go straight on to the next tile; the tensor pipe never sees them.
+// For A stored [k, m] (the dW case) the reduction runs in two phases, both in a fixed order:
+// tickets at the head of the queue each sum a chunk of rows of A over ALL columns (whole rows,
+// so every load instruction reads 512 contiguous bytes and every byte of dy is read once) into
+// a row of partial sums in the workspace; tickets at the tail of the queue, drawn by the CTAs
+// that run out of tiles first, add the partial sums in chunk order.  The tail tickets wait
+// (bounded) on a counter of finished head tickets; the wait can never block progress, since
+// head tickets are drawn first and wait for nothing.
 //
 // No wait is unbounded: every mbarrier wait gives up after GroupParams::wait_limit_ns,
 // records why in the DeviceStatus word and makes the CTA drain and exit.
@@ -58,20 +62,31 @@ constexpr int kRing = 4;                             // scheduler ring entries
 constexpr uint32_t kATileBytes = BM * BK * 2;        // 16 KB
 constexpr uint32_t kStoreBufBytes = 32 * 128;        // one staging buffer: 32 rows x 128 bytes
 // Per CTA and stage: the A tile plus room for the widest B tile.  A CTA pair (CG = 2)
-// splits B between its two CTAs, so a stage is smaller: five of them and two staging
-// buffers per epilogue warp fit where a single CTA has four stages and one buffer.
+// splits B between its two CTAs, so a stage is smaller: six of them fit where a single CTA
+// has four.  The main loop is bound by the bytes in flight: a stage is refilled about 1.7 us
+// after its MMAs retire (commit -> producer -> TMA -> L2 -> shared memory -> MMA issuer), and a
+// pair consumes 32 KB per CTA every 0.3 us, so anything below ~180 KB of stages starves the
+// tensor pipe (measured with five stages: 0.34-0.43 us per k-block).
+#ifndef LLMT_B200_PAIR_STAGES
+#define LLMT_B200_PAIR_STAGES 6
+#endif
+#ifndef LLMT_B200_PAIR_STORE_BUFS
+#define LLMT_B200_PAIR_STORE_BUFS 1
+#endif
 template <int CG> struct Geo {
     static constexpr uint32_t kBRegionBytes = (256 / CG) * BK * 2;
     static constexpr uint32_t kStageBytes = kATileBytes + kBRegionBytes;
-    static constexpr int kStages = CG == 2 ? 5 : 4;
-    static constexpr int kStoreBufs = CG == 2 ? 2 : 1;
+    static constexpr int kStages = CG == 2 ? LLMT_B200_PAIR_STAGES : 4;
+    static constexpr int kStoreBufs = CG == 2 ? LLMT_B200_PAIR_STORE_BUFS : 1;   // staging buffers per epilogue warp
     static constexpr uint32_t kStagingBytes = kEpilogueWarps * kStoreBufs * kStoreBufBytes;
+    static constexpr uint32_t kSmemBytes = 1024 /* control block + alignment */ + kStages * kStageBytes + kStagingBytes;
 };
+static_assert(Geo<1>::kSmemBytes <= 227 * 1024 && Geo<2>::kSmemBytes <= 227 * 1024, "shared-memory budget");
 constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block
 constexpr uint32_t kAccStride = 256;                 // TMEM columns per accumulator buffer
 constexpr uint32_t kTmemCols = 512;
-constexpr int kDbiasColsPerCta = 16;                 // rows of op(A) whose sums one CTA forms per dbias ticket
-constexpr uint32_t kDbiasScratchBytes = kRing * kEpilogueWarps * kDbiasColsPerCta * 4;  // 2 KB
+constexpr int kDbiasRowsPerCta = 16;                 // mode 2: rows of op(A) one CTA sums per dbias ticket
+constexpr int kDbiasFinishPerCta = 256;              // mode 1: values of i one CTA finishes per ticket
 
 struct __align__(8) Control {
     uint64_t full[kMaxStages];
@@ -81,7 +96,6 @@ struct __align__(8) Control {
     uint64_t sched_full[kRing];
     uint64_t sched_empty[kRing];
     int32_t ring[kRing];
-    int32_t dbias_arrivals[kRing];  // epilogue warps that have delivered their part of a dbias ticket, per ring slot
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -131,51 +145,30 @@ __device__ __forceinline__ TileCoord decode_tile(const GroupParams& gp, int t) {
         if (t >= gp.prob[i].tile_begin) pi = i;
     const GroupProblem& p = gp.prob[pi];
     tc.prob = pi;
-    int r = t - p.tile_begin;
-    tc.m_tile = r % p.tiles_m;
-    r /= p.tiles_m;
-    tc.n_tile = r % p.tiles_n;
-    r /= p.tiles_n;
-    tc.split = r % p.splits;
-    tc.batch = r / p.splits;
+    // One thread of the MMA warp runs this between two tiles: integer divisions are slow
+    // there, so the common cases (one split, one batch item) avoid all but one.
+    const uint32_t r = static_cast<uint32_t>(t - p.tile_begin);
+    const uint32_t q1 = r / static_cast<uint32_t>(p.tiles_m);
+    tc.m_tile = static_cast<int>(r - q1 * static_cast<uint32_t>(p.tiles_m));
+    if (p.splits == 1 && p.batch <= 1) {
+        tc.n_tile = static_cast<int>(q1);
+        tc.split = 0;
+        tc.batch = 0;
+    } else {
+        const uint32_t q2 = q1 / static_cast<uint32_t>(p.tiles_n);
+        tc.n_tile = static_cast<int>(q1 - q2 * static_cast<uint32_t>(p.tiles_n));
+        const uint32_t q3 = q2 / static_cast<uint32_t>(p.splits);
+        tc.split = static_cast<int>(q2 - q3 * static_cast<uint32_t>(p.splits));
+        tc.batch = static_cast<int>(q3);
+    }
     tc.kb0 = tc.split * p.kblocks_per_split;
     tc.kb1 = min(tc.kb0 + p.kblocks_per_split, p.kblocks_total);
     return tc;
 }
 
-__device__ __forceinline__ void store_chunk_f32(float* dst, const float* v, int valid) {
-    if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0u) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < valid) dst[j] = v[j];
-    }
-}
-
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* dst, const float* v, int valid) {
-    if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0u) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-            uint4 u;
-            u.x = pack_bf16(v[j + 0], v[j + 1]);
-            u.y = pack_bf16(v[j + 2], v[j + 3]);
-            u.z = pack_bf16(v[j + 4], v[j + 5]);
-            u.w = pack_bf16(v[j + 6], v[j + 7]);
-            *reinterpret_cast<uint4*>(dst + j) = u;
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (j < valid) dst[j] = __float2bfloat16_rn(v[j]);
-    }
 }
 
 __device__ __forceinline__ void load_chunk_f32(const float* src, float* dst, int valid) {
@@ -229,105 +222,87 @@ __device__ __forceinline__ float lanes_sum(float v) {
     return v;
 }
 
-// One dbias ticket as one of the eight epilogue warps (ew = 0..7) of a CTA sees it:
-// dbias[i] (+)= sum over p in this split's k range of op(A)[i, p] for the kDbiasColsPerCta
-// values of i starting at i0.  The order of the additions depends only on the problem's
-// shape.  `scratch` (8 x 16 floats) and `arrivals` belong to the ring slot the ticket came in.
-__device__ __noinline__ void dbias_ticket_warp(const GroupProblem& p, int64_t i0, int split, int ew, int lane,
-                                               float* scratch, int32_t* arrivals) {
-    if (i0 >= p.m) return;  // CTA-uniform: all eight warps skip together
-    const int64_t kbeg = static_cast<int64_t>(split) * p.kblocks_per_split * BK;
-    int64_t kend = kbeg + static_cast<int64_t>(p.kblocks_per_split) * BK;
-    if (kend > p.k) kend = p.k;
+// dbias, A stored [k, m], first phase.  Ticket j covers rows [j R, (j+1) R) of A and every
+// column: warp `wid` of the `nw` warps that share the ticket takes the 256-column chunks wid,
+// wid + nw, ...; lane L sums columns c + 8 L .. + 7 of the chunk down the rows (sixteen rows in
+// flight) and leaves eight partial sums in row j of the workspace.
+__device__ __noinline__ void dbias_partial_warp(const GroupProblem& p, int j, int wid, int nw, int lane) {
+    const int64_t r0 = static_cast<int64_t>(j) * p.dbias_rows;
+    int64_t r1 = r0 + p.dbias_rows;
+    if (r1 > p.k) r1 = p.k;
     const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a_raw);
-    if (p.a_mn) {
-        // A is stored [k, m]: the sums run down columns i0 .. i0+15 (32 bytes of every row).
-        // The eight warps share the rows: warp w, lane L reads 16 bytes (columns i0 + 8 (L & 1) ..)
-        // of rows kbeg + 16 w + L / 2, + 128, ...; sixteen rows in flight per lane.  A warp then
-        // folds its sixteen row-lanes in a fixed tree and leaves 16 partial sums in shared memory;
-        // the warp that arrives last adds the eight partial sums of every column in warp order.
+    float* out = p.ws_dbias + static_cast<int64_t>(j) * p.m;
+    for (int64_t c = static_cast<int64_t>(wid) * 256 + 8 * lane; c - 8 * lane < p.m; c += static_cast<int64_t>(nw) * 256) {
+        if (c >= p.m) continue;  // the row pitch covers whole groups of 8 columns
         float acc[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-        const int64_t c = i0 + 8 * (lane & 1);
-        if (c < p.m) {  // the row pitch covers whole groups of 8 columns
-            const __nv_bfloat16* col = A + c;
-            int64_t r = kbeg + 16 * ew + (lane >> 1);
-            for (; r + 15 * 128 < kend; r += 16 * 128) {
-                uint4 q[16];
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        const __nv_bfloat16* col = A + c;
+        int64_t r = r0;
+        for (; r + 16 <= r1; r += 16) {
+            uint4 q[16];
 #pragma unroll
-                for (int u = 0; u < 16; ++u) q[u] = ld_operand16(col + (r + 128 * u) * p.lda);
+            for (int u = 0; u < 16; ++u) q[u] = ld_operand16(col + (r + u) * p.lda);
 #pragma unroll
-                for (int u = 0; u < 16; ++u) add_bf16x8(acc, q[u]);
-            }
-            for (; r < kend; r += 128) add_bf16x8(acc, ld_operand16(col + r * p.lda));
+            for (int u = 0; u < 16; ++u) add_bf16x8(acc, q[u]);
         }
+        for (; r < r1; ++r) add_bf16x8(acc, ld_operand16(col + r * p.lda));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int e = 0; e < 8; ++e)
+            if (c + e < p.m) out[c + e] = acc[e];
+    }
+}
+
+// dbias, A stored [k, m], second phase: dbias[i] = dbias_beta * dbias[i] + sum_j partial[j][i],
+// j ascending, for the 32 values of i starting at i0 (one per lane).
+__device__ __noinline__ void dbias_finish_warp(const GroupProblem& p, int64_t i0, int lane) {
+    const int64_t i = i0 + lane;
+    if (i >= p.m) return;
+    const float* src = p.ws_dbias + i;
+    float acc = 0.0f;
+    int j = 0;
+    for (; j + 8 <= p.colsum_tiles; j += 8) {
+        float v[8];
 #pragma unroll
-            for (int o = 16; o > 1; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-        }
-        if (lane < 2) {
+        for (int u = 0; u < 8; ++u) v[u] = src[static_cast<int64_t>(j + u) * p.m];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) scratch[ew * kDbiasColsPerCta + 8 * lane + j] = acc[j];
-        }
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            last = (atomicAdd(arrivals, 1) & (kEpilogueWarps - 1)) == kEpilogueWarps - 1;
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) return;
-        __threadfence_block();
-        const int64_t i = i0 + lane;
-        if (lane < kDbiasColsPerCta && i < p.m) {
-            const volatile float* sc = scratch;
-            float out = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kEpilogueWarps; ++w) out += sc[w * kDbiasColsPerCta + lane];
-            if (p.splits > 1) {
-                p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = out;
-            } else {
-                const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
-                p.dbias[i] = prev + out;
-            }
-        }
-    } else {
-        // A is stored [m, k]: the sums run along rows; warp w takes rows i0 + 2 w and i0 + 2 w + 1.
-        // Lane L takes the 8 elements at kbeg + 8 L, + 256, ... of a row; lane 0 also takes the
-        // ragged end of the range.
-        const int64_t span = kend - kbeg;
-        const int64_t vec_end = kbeg + span / 8 * 8;
+        for (int u = 0; u < 8; ++u) acc += v[u];
+    }
+    for (; j < p.colsum_tiles; ++j) acc += src[static_cast<int64_t>(j) * p.m];
+    const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+    p.dbias[i] = prev + acc;
+}
+
+// dbias, A stored [m, k]: the sums run along rows, nothing to combine.  The warp takes rows
+// i0 and i0 + 1; lane L takes the 8 elements at 8 L, + 256, ... of a row; lane 0 also takes
+// the ragged end.
+__device__ __noinline__ void dbias_rows_warp(const GroupProblem& p, int64_t i0, int lane) {
+    const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a_raw);
+    const int64_t vec_end = p.k / 8 * 8;
 #pragma unroll 1
-        for (int j = 0; j < 2; ++j) {
-            const int64_t i = i0 + 2 * ew + j;
-            if (i >= p.m) break;  // warp-uniform
-            const __nv_bfloat16* row = A + i * p.lda;
-            float acc[8];
+    for (int j = 0; j < 2; ++j) {
+        const int64_t i = i0 + j;
+        if (i >= p.m) break;  // warp-uniform
+        const __nv_bfloat16* row = A + i * p.lda;
+        float acc[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-            int64_t q = kbeg + 8 * lane;
-            for (; q + 3 * 256 < vec_end; q += 4 * 256) {
-                uint4 v[4];
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        int64_t q = 8 * lane;
+        for (; q + 3 * 256 < vec_end; q += 4 * 256) {
+            uint4 v[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = ld_operand16(row + q + 256 * u);
+            for (int u = 0; u < 4; ++u) v[u] = ld_operand16(row + q + 256 * u);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) add_bf16x8(acc, v[u]);
-            }
-            for (; q < vec_end; q += 256) add_bf16x8(acc, ld_operand16(row + q));
-            float t = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
-            if (lane == 0)
-                for (int64_t e = vec_end; e < kend; ++e) t += __bfloat162float(row[e]);
-            t = lanes_sum(t);
-            if (lane == 0) {
-                if (p.splits > 1) {
-                    p.ws_dbias[static_cast<int64_t>(split) * p.m + i] = t;
-                } else {
-                    const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
-                    p.dbias[i] = prev + t;
-                }
-            }
+            for (int u = 0; u < 4; ++u) add_bf16x8(acc, v[u]);
+        }
+        for (; q < vec_end; q += 256) add_bf16x8(acc, ld_operand16(row + q));
+        float t = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+        if (lane == 0)
+            for (int64_t e = vec_end; e < p.k; ++e) t += __bfloat162float(row[e]);
+        t = lanes_sum(t);
+        if (lane == 0) {
+            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+            p.dbias[i] = prev + t;
         }
     }
 }
@@ -366,7 +341,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     Control* ctl = reinterpret_cast<Control*>(smem_raw);
     const uint32_t smem_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
     const uint32_t staging_base = smem_base + kStages * kStageBytes;
-    float* dbias_scratch = reinterpret_cast<float*>(smem_raw + (staging_base - smem_u32(smem_raw)) + Geo<CG>::kStagingBytes);
     volatile int* abort_flag = &ctl->abort_flag;
     DeviceStatus* status = gp.status;
 
@@ -386,7 +360,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             mbar_init(smem_u32(&ctl->sched_full[r]), 1);
             mbar_init(smem_u32(&ctl->sched_empty[r]), kPair ? 2 * (2 + kEpilogueWarps) : 1 + kEpilogueWarps);  // every ring reader
         }
-        for (int r = 0; r < kRing; ++r) ctl->dbias_arrivals[r] = 0;
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
@@ -490,7 +463,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             t = __shfl_sync(0xffffffffu, t, 0);
             if (!ok || t < 0) break;
-            if (t < gp.colsum_total) continue;  // a dbias ticket: work for the epilogue warps only
+            if (t < gp.colsum_total || t >= gp.fin_begin) continue;  // a dbias ticket: work for the epilogue warps only
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int bn = p.bn, a_mn = p.a_mn, b_mn = p.b_mn;
@@ -559,7 +532,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 const int t = ctl->ring[slot];
                 release_ring_slot(slot);
                 if (t < 0) break;
-                if (t < gp.colsum_total) continue;
+                if (t < gp.colsum_total || t >= gp.fin_begin) continue;
                 const TileCoord tc = decode_tile(gp, t);
                 const GroupProblem& p = gp.prob[tc.prob];
                 const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn, p.a_mn, p.b_mn);
@@ -615,24 +588,79 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (!ok) break;
             const int t = ctl->ring[slot];
             __syncwarp();
-            if (t >= 0 && t < gp.colsum_total) {
-                // A dbias ticket: (block of rows of op(A), split) of the problem that owns it.  The
-                // ring slot is released only afterwards: its scratch area is in use until then.
+            if (lane == 0) release_ring_slot(slot);
+            if (t < 0) break;
+            if (t < gp.colsum_total) {
+                // A dbias reduction ticket of the problem that owns it.
                 int pi = 0;
 #pragma unroll 1
                 for (int i = 0; i < gp.num_problems; ++i)
                     if (gp.prob[i].colsum_tiles > 0 && t >= gp.prob[i].colsum_begin) pi = i;
                 const GroupProblem& p = gp.prob[pi];
                 const int r = t - p.colsum_begin;
-                const int blk = r % p.colsum_blocks, split = r / p.colsum_blocks;
-                dbias_ticket_warp(p, (static_cast<int64_t>(blk) * CG + rank) * kDbiasColsPerCta, split, ew, lane,
-                                  dbias_scratch + slot * (kEpilogueWarps * kDbiasColsPerCta), &ctl->dbias_arrivals[slot]);
-                __syncwarp();
-                if (lane == 0) release_ring_slot(slot);
+                if (p.dbias_mode == 1) {
+                    dbias_partial_warp(p, r, static_cast<int>(rank) * kEpilogueWarps + ew, CG * kEpilogueWarps, lane);
+                    if (gp.fin_begin < gp.total_tiles) {
+                        // this warp's partial sums are written: count it for the finishing tickets
+                        __syncwarp();
+                        if (lane == 0) {
+                            __threadfence();
+                            atomicAdd(gp.dbias_sync, 1);
+                        }
+                    }
+                } else {
+                    dbias_rows_warp(p, (static_cast<int64_t>(r) * CG + rank) * kDbiasRowsPerCta + 2 * ew, lane);
+                }
                 continue;
             }
-            if (lane == 0) release_ring_slot(slot);
-            if (t < 0) break;
+            if (t >= gp.fin_begin) {
+                // A finishing ticket: every first-phase warp of the launch must have delivered.
+                const int f = t - gp.fin_begin;
+                int pi = 0;
+#pragma unroll 1
+                for (int i = 0; i < gp.num_problems; ++i)
+                    if (gp.prob[i].fin_tiles > 0 && f >= gp.prob[i].fin_begin) pi = i;
+                const GroupProblem& p = gp.prob[pi];
+                int expected = 0;
+#pragma unroll 1
+                for (int i = 0; i < gp.num_problems; ++i)
+                    if (gp.prob[i].dbias_mode == 1) expected += gp.prob[i].colsum_tiles;
+                expected *= CG * kEpilogueWarps;
+                int ready = 1;
+                if (lane == 0) {
+                    uint64_t t0 = 0;
+                    uint32_t spins = 0;
+                    while (*reinterpret_cast<volatile int32_t*>(gp.dbias_sync) < expected) {
+                        if ((++spins & 63u) == 0u) {
+                            const uint64_t now = globaltimer_ns();
+                            if (t0 == 0) {
+                                t0 = now;
+                            } else if (now - t0 > wait_ns || *abort_flag) {
+                                if (atomicCAS(&status->code, 0, kDevWaitSched) == 0) {
+                                    status->detail = 99;
+                                    status->block = static_cast<int32_t>(blockIdx.x);
+                                }
+                                ready = 0;
+                                break;
+                            }
+                        }
+                    }
+                    __threadfence();
+                }
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (ready)
+                    dbias_finish_warp(p, (static_cast<int64_t>(f - p.fin_begin) * CG + rank) * kDbiasFinishPerCta + 32 * ew, lane);
+                __syncwarp();
+                if (lane == 0) {
+                    // the last finishing warp of the launch re-arms both counters
+                    const int fin_warps = (gp.total_tiles - gp.fin_begin) * CG * kEpilogueWarps;
+                    if (atomicAdd(gp.dbias_sync + 1, 1) == fin_warps - 1) {
+                        gp.dbias_sync[0] = 0;
+                        gp.dbias_sync[1] = 0;
+                    }
+                }
+                continue;
+            }
             const TileCoord tc = decode_tile(gp, t);
             const GroupProblem& p = gp.prob[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
@@ -679,8 +707,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 }
             };
             // One 32-column step: epilogue arithmetic on the values of this thread's row, then
-            // into the staging buffer (and out by TMA once the unit is complete) or, for a
-            // ragged unit or a C that TMA cannot address, straight to global memory.
+            // into the staging buffer; once the unit is complete it leaves by TMA or, for a
+            // ragged unit or a C that TMA cannot address, by the warp's own row-wise stores.
             auto emit = [&](const uint32_t (&r)[32], int s) {
                 const int c0 = step_col(s);
                 const int64_t col = n0 + c0;
@@ -719,53 +747,74 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 }
                 const int sub = s % spu;
                 const int64_t unit_col = col - sub * 32;
-                if (tma_ok && unit_col + unit_cols <= p.n) {
-                    const uint32_t buf = my_bufs + (buf_seq % kStoreBufs) * kStoreBufBytes;
-                    if (sub == 0) {
-                        // The buffer is free once the store that last read it has done so.
-                        if (lane == 0) bulk_wait_group_read_n<kStoreBufs - 1>();
-                        __syncwarp();
+                const bool by_tma = tma_ok && unit_col + unit_cols <= p.n;
+                const uint32_t buf = my_bufs + (buf_seq % kStoreBufs) * kStoreBufBytes;
+                if (sub == 0) {
+                    // The buffer is free once the TMA store that last read it has done so.
+                    if (lane == 0) bulk_wait_group_read_n<kStoreBufs - 1>();
+                    __syncwarp();
+                }
+                const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+                const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+                if (out_bf16) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(row_addr + ((static_cast<uint32_t>(sub * 4 + q) ^ sw) << 4)),
+                                       "r"(pack_bf16(v[8 * q + 0], v[8 * q + 1])),
+                                       "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])),
+                                       "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
+                                       "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7])) : "memory");
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
+                                       "r"(__float_as_uint(v[4 * q + 0])), "r"(__float_as_uint(v[4 * q + 1])),
+                                       "r"(__float_as_uint(v[4 * q + 2])), "r"(__float_as_uint(v[4 * q + 3]))
+                                     : "memory");
+                }
+                if (sub != spu - 1 && s != ns - 1) return;  // the unit's other half follows
+                if (by_tma) {
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z);
+                        bulk_commit_group();
                     }
-                    const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
-                    const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+                    ++buf_seq;
+                    return;
+                }
+                // A ragged unit, or a destination TMA cannot address (odd pitch or base): the warp
+                // copies the staged rows out itself, one row per instruction, so that every store
+                // instruction writes up to 128 contiguous bytes.
+                __syncwarp();
+                const int unit_valid = static_cast<int>(min(static_cast<int64_t>(unit_cols), p.n - unit_col));
+                const uint32_t word = ((static_cast<uint32_t>(lane) >> 2) << 4) | ((static_cast<uint32_t>(lane) & 3u) << 2);
+#pragma unroll 4
+                for (int rr = 0; rr < 32; ++rr) {
+                    const int64_t grow = static_cast<int64_t>(row0) + rr;
+                    if (grow >= p.m) break;
+                    uint32_t w;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w)
+                                 : "r"(buf + static_cast<uint32_t>(rr) * 128u + (word ^ ((static_cast<uint32_t>(rr) & 7u) << 4))));
                     if (out_bf16) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(row_addr + ((static_cast<uint32_t>(sub * 4 + q) ^ sw) << 4)),
-                                           "r"(pack_bf16(v[8 * q + 0], v[8 * q + 1])),
-                                           "r"(pack_bf16(v[8 * q + 2], v[8 * q + 3])),
-                                           "r"(pack_bf16(v[8 * q + 4], v[8 * q + 5])),
-                                           "r"(pack_bf16(v[8 * q + 6], v[8 * q + 7])) : "memory");
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                         ::"r"(row_addr + ((static_cast<uint32_t>(q) ^ sw) << 4)),
-                                           "r"(__float_as_uint(v[4 * q + 0])), "r"(__float_as_uint(v[4 * q + 1])),
-                                           "r"(__float_as_uint(v[4 * q + 2])), "r"(__float_as_uint(v[4 * q + 3]))
-                                         : "memory");
-                    }
-                    if (sub == spu - 1) {
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_store_3d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z);
-                            bulk_commit_group();
+                        uint16_t* dst = static_cast<uint16_t*>(p.c) + static_cast<int64_t>(tc.batch) * p.stride_c +
+                                        grow * p.ldc + unit_col + 2 * lane;
+                        if (2 * lane + 1 < unit_valid && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0u) {
+                            *reinterpret_cast<uint32_t*>(dst) = w;
+                        } else {
+                            if (2 * lane < unit_valid) dst[0] = static_cast<uint16_t>(w & 0xFFFFu);
+                            if (2 * lane + 1 < unit_valid) dst[1] = static_cast<uint16_t>(w >> 16);
                         }
-                        ++buf_seq;
-                    }
-                } else if (row_ok) {
-                    if (partial) {
-                        float* dst = p.ws +
-                                     ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + row) * p.n + col;
-                        store_chunk_f32(dst, v, valid);
-                    } else if (p.c_is_bf16) {
-                        store_chunk_bf16(static_cast<__nv_bfloat16*>(p.c) + c_off, v, valid);
-                    } else {
-                        store_chunk_f32(static_cast<float*>(p.c) + c_off, v, valid);
+                    } else if (lane < unit_valid) {
+                        float* dst = partial
+                            ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + grow) * p.n + unit_col + lane
+                            : static_cast<float*>(p.c) + static_cast<int64_t>(tc.batch) * p.stride_c + grow * p.ldc + unit_col + lane;
+                        *dst = __uint_as_float(w);
                     }
                 }
+                __syncwarp();  // the buffer may be rewritten once every lane has read its words
             };
             // Software pipeline over the steps: the tcgen05.ld of step s+1 is in flight while
             // step s is converted and staged.
@@ -792,8 +841,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             }
             ++acc_seq;
         }
-        // Outstanding TMA stores must complete before the shared memory goes away.
-        if (lane == 0) bulk_wait_group0();
+        // Outstanding TMA stores must have read their staging buffers before the shared memory goes
+        // away; their writes complete with the grid.
+        if (lane == 0) bulk_wait_group_read_n<0>();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -866,27 +916,21 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
                 static_cast<float*>(p.c)[c_off + j] = v;
         }
     }
-    if (p.dbias != nullptr && i < p.m) {
-        float acc = 0.0f;
-        for (int s = 0; s < p.splits; ++s) acc += p.ws_dbias[static_cast<int64_t>(s) * p.m + i];
-        const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
-        p.dbias[i] = prev + acc;
-    }
+    // An empty reduction (k == 0) sums nothing into the bias gradient either.
+    if (p.splits == 0 && p.dbias != nullptr && i < p.m)
+        p.dbias[i] = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
 }
 
 }  // namespace
 
 size_t tc_grouped_smem_bytes() {
-    // Both geometries use the same amount: 4 x 48 KB of operand stages + 32 KB of staging,
-    // or 5 x 32 KB + 64 KB; then 2 KB for the dbias tickets.  227 KB in all.
-    static_assert(Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes ==
-                  Geo<2>::kStages * Geo<2>::kStageBytes + Geo<2>::kStagingBytes, "shared-memory budget");
     static_assert(sizeof(Control) <= 1024, "control block must fit below the first aligned KB");
-    return 1024 /* control block + alignment */ + Geo<1>::kStages * Geo<1>::kStageBytes + Geo<1>::kStagingBytes +
-           kDbiasScratchBytes;
+    return Geo<1>::kSmemBytes > Geo<2>::kSmemBytes ? Geo<1>::kSmemBytes : Geo<2>::kSmemBytes;
 }
 
-int tc_dbias_rows_per_cta() { return kDbiasColsPerCta; }
+int tc_pair_stages() { return Geo<2>::kStages; }
+int tc_dbias_rows_per_cta() { return kDbiasRowsPerCta; }
+int tc_dbias_finish_per_cta() { return kDbiasFinishPerCta; }
 
 // Per-device record of what has been configured (cudaFuncSetAttribute is per device).
 static bool g_configured[64];
