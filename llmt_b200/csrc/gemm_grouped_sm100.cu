@@ -264,11 +264,11 @@ __device__ __noinline__ void dbias_finish_warp(const GroupProblem& p, int64_t i0
     for (; j + 8 <= p.colsum_tiles; j += 8) {
         float v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = src[static_cast<int64_t>(j + u) * p.m];
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + static_cast<int64_t>(j + u) * p.m);  // written by other SMs: read from L2
 #pragma unroll
         for (int u = 0; u < 8; ++u) acc += v[u];
     }
-    for (; j < p.colsum_tiles; ++j) acc += src[static_cast<int64_t>(j) * p.m];
+    for (; j < p.colsum_tiles; ++j) acc += __ldcg(src + static_cast<int64_t>(j) * p.m);
     const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
     p.dbias[i] = prev + acc;
 }
