@@ -191,6 +191,18 @@ LLMT_B200_API int llmt_b200_softmax_fwd(void* y, const void* x, int64_t rows, in
 LLMT_B200_API int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
                           int32_t dtype, void* stream);
 
+/* Head split and merge as copies (llmt include/llmt/kernels/permute.h:21-46, kernels in
+ * src/kernels/permute.cu:18-46):
+ *   merge: y[b, t, h*hd + d] = x[b, h, t, d]                       x [B,H,T,hd] -> y [B,T,H*hd]
+ *   split: q|k|v[b, h, t, d] = qkv[b, t, part*H*hd + h*hd + d]     qkv [B,T,3*H*hd] -> 3 x [B,H,T,hd]
+ * Outputs must not alias inputs.  The GEMM entry points can read and write the per-head layout
+ * in place through batch_inner / stride_*_outer, which makes these copies unnecessary on the
+ * attention path; they exist for callers that want the re-shelved tensors themselves. */
+LLMT_B200_API int llmt_b200_head_merge(void* y, const void* x, int64_t b, int64_t h, int64_t t, int64_t hd,
+                                       int32_t dtype, void* stream);
+LLMT_B200_API int llmt_b200_head_split(void* q, void* k, void* v, const void* qkv, int64_t b, int64_t h, int64_t t,
+                                       int64_t hd, int32_t dtype, void* stream);
+
 /* Device-side health word.  Kernels never spin without bound: a wait that runs
  * out records (code, detail) here and the kernel drains and returns.  This call
  * synchronises the device, copies the word back and clears it.  code == 0 means

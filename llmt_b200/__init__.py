@@ -26,7 +26,7 @@ EXPORTS = [
     "llmt_b200_launch_count", "llmt_b200_last_error", "llmt_b200_abi_version",
     "llmt_b200_set_sm_budget", "llmt_b200_grad_allreduce", "llmt_b200_grad_allreduce_emulated",
     "llmt_b200_zero_grads", "llmt_b200_gemm_workspace_bytes_for", "llmt_b200_set_wait_limit_ns",
-    "llmt_b200_tensor_map_cache_stats",
+    "llmt_b200_tensor_map_cache_stats", "llmt_b200_head_merge", "llmt_b200_head_split",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
@@ -98,6 +98,13 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_set_wait_limit_ns.restype = ctypes.c_int
         L.llmt_b200_tensor_map_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
         L.llmt_b200_tensor_map_cache_stats.restype = None
+        L.llmt_b200_head_merge.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_head_merge.restype = ctypes.c_int
+        L.llmt_b200_head_split.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                           ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_head_split.restype = ctypes.c_int
         L.llmt_b200_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_char_p, ctypes.c_size_t]
         L.llmt_b200_gemm_plan.restype = ctypes.c_int
         L.llmt_b200_softmax_fwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -314,6 +321,19 @@ def softmax_bwd(ds, p, dp, stream=None) -> None:
     tk = p.shape[-1]
     _check(lib().llmt_b200_softmax_bwd(ds.data_ptr(), p.data_ptr(), dp.data_ptr(), p.numel() // tk, tk,
                                        _dtype_code(p), ctypes.c_void_p(s.cuda_stream)))
+
+
+def head_merge(y, x, stream=None) -> None:
+    """y[b, t, h*hd + d] = x[b, h, t, d] (llmt permute_merge): x [B,H,T,hd] -> y [B,T,H*hd]."""
+    b, h, t, hd = x.shape
+    _check(lib().llmt_b200_head_merge(y.data_ptr(), x.data_ptr(), b, h, t, hd, _dtype_code(x), _stream(stream)))
+
+
+def head_split(q, k, v, qkv, stream=None) -> None:
+    """q|k|v[b, h, t, d] = qkv[b, t, part*A + h*hd + d] (llmt permute_split): qkv [B,T,3A] -> 3 x [B,H,T,hd]."""
+    b, h, t, hd = q.shape
+    _check(lib().llmt_b200_head_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), qkv.data_ptr(), b, h, t, hd,
+                                      _dtype_code(qkv), _stream(stream)))
 
 
 def device_status():

@@ -7,6 +7,7 @@
 #include "llmt/core/error.h"
 #include "llmt/kernels/attention.h"
 #include "llmt/kernels/matmul.h"
+#include "llmt/kernels/permute.h"
 #include "llmt_b200.h"
 
 namespace llmt::kernels {
@@ -49,16 +50,30 @@ void attention_fwd(const RunCtx& ctx, Tensor& y, Tensor& scores, Tensor& y_heads
     matmul(ctx, o3, s3, v3, false, false, 1.0f, 0.0f);
     if (y.data != nullptr) {
         if (y.shape != Shape{b, t, h * hd}) detail::fatal("attention_fwd", "y must be [B, T, H·hd]");
-        // Head merge [B,H,T,hd] -> [B,T,H*hd]: a strided copy per (batch, head).
-        const size_t es = dtype_size(y.dtype);
-        for (int64_t bi = 0; bi < b; ++bi)
-            for (int64_t hi = 0; hi < h; ++hi) {
-                const char* src = static_cast<const char*>(y_heads.data) + ((bi * h + hi) * t * hd) * es;
-                char* dst = static_cast<char*>(y.data) + (bi * t * h * hd + hi * hd) * es;
-                CUDA_CHECK(cudaMemcpy2DAsync(dst, h * hd * es, src, hd * es, hd * es, t,
-                                             cudaMemcpyDeviceToDevice, ctx.stream));
-            }
+        permute_merge(ctx.stream, y, y_heads);  // [B,H,T,hd] -> [B,T,H*hd], one launch
     }
+}
+
+void permute_split(cudaStream_t s, Tensor& q, Tensor& k, Tensor& v, const Tensor& qkv, int64_t n_head) noexcept {
+    for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &k, &v, &qkv})
+        if (!t->valid()) detail::fatal("permute_split", "invalid tensor (null data)");
+    if (qkv.shape.rank != 3 || q.shape.rank != 4) detail::fatal("permute_split", "expected qkv [B,T,3A] and q/k/v [B,H,T,hd]");
+    if (k.shape != q.shape || v.shape != q.shape) detail::fatal("permute_split", "q/k/v must share one [B,H,T,hd] shape");
+    if (q.dtype != qkv.dtype || k.dtype != qkv.dtype || v.dtype != qkv.dtype) detail::fatal("permute_split", "dtype mismatch");
+    const int64_t b = q.shape[0], h = q.shape[1], t = q.shape[2], hd = q.shape[3];
+    if (h != n_head || qkv.shape != Shape{b, t, 3 * h * hd}) detail::fatal("permute_split", "qkv must be [B, T, 3·H·hd]");
+    const int st = llmt_b200_head_split(q.data, k.data, v.data, qkv.data, b, h, t, hd, static_cast<int32_t>(qkv.dtype), s);
+    if (st != LLMT_B200_OK) detail::fatal("permute_split", "%s", llmt_b200_last_error());
+}
+
+void permute_merge(cudaStream_t s, Tensor& y, const Tensor& x) noexcept {
+    if (!y.valid() || !x.valid()) detail::fatal("permute_merge", "invalid tensor (null data)");
+    if (x.shape.rank != 4 || y.shape.rank != 3) detail::fatal("permute_merge", "expected x [B,H,T,hd] and y [B,T,A]");
+    const int64_t b = x.shape[0], h = x.shape[1], t = x.shape[2], hd = x.shape[3];
+    if (y.shape != Shape{b, t, h * hd}) detail::fatal("permute_merge", "y must be [B, T, H·hd]");
+    if (y.dtype != x.dtype) detail::fatal("permute_merge", "dtype mismatch");
+    const int st = llmt_b200_head_merge(y.data, x.data, b, h, t, hd, static_cast<int32_t>(x.dtype), s);
+    if (st != LLMT_B200_OK) detail::fatal("permute_merge", "%s", llmt_b200_last_error());
 }
 
 void attention_bwd(const RunCtx& ctx, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dscores,

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cstdlib>
+#include <initializer_list>
 
 #include "../../include/llmt_b200.h"
 #include "common.h"
@@ -968,6 +969,38 @@ int llmt_b200_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows,
     if (rows == 0) return LLMT_B200_OK;
     cudaError_t e = launch_softmax_bwd(ds, p, dp, rows, tk, dtype == LLMT_B200_BF16,
                                        static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_head_merge(void* y, const void* x, int64_t b, int64_t h, int64_t t, int64_t hd, int32_t dtype,
+                         void* stream) {
+    if (y == nullptr || x == nullptr) return fail(LLMT_B200_ERR_INVALID, "permute_merge: invalid tensor (null data)");
+    if (b < 0 || h <= 0 || t < 0 || hd <= 0) return fail(LLMT_B200_ERR_INVALID, "permute_merge: bad shape");
+    if (dtype != LLMT_B200_FP32 && dtype != LLMT_B200_BF16)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "permute_merge: no kernel for dtype code %d", dtype);
+    const int es = dtype == LLMT_B200_BF16 ? 2 : 4;
+    const size_t bytes = static_cast<size_t>(b) * h * t * hd * es;
+    if (bytes == 0) return LLMT_B200_OK;
+    if (overlaps(y, bytes, x, bytes)) return fail(LLMT_B200_ERR_INVALID, "permute_merge: y must not alias x");
+    cudaError_t e = launch_head_merge(y, x, b, h, t, hd, es, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_head_split(void* q, void* k, void* v, const void* qkv, int64_t b, int64_t h, int64_t t, int64_t hd,
+                         int32_t dtype, void* stream) {
+    if (q == nullptr || k == nullptr || v == nullptr || qkv == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "permute_split: invalid tensor (null data)");
+    if (b < 0 || h <= 0 || t < 0 || hd <= 0) return fail(LLMT_B200_ERR_INVALID, "permute_split: bad shape");
+    if (dtype != LLMT_B200_FP32 && dtype != LLMT_B200_BF16)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "permute_split: no kernel for dtype code %d", dtype);
+    const int es = dtype == LLMT_B200_BF16 ? 2 : 4;
+    const size_t part = static_cast<size_t>(b) * h * t * hd * es;
+    if (part == 0) return LLMT_B200_OK;
+    for (const void* out : {q, k, v})
+        if (overlaps(out, part, qkv, 3 * part)) return fail(LLMT_B200_ERR_INVALID, "permute_split: outputs must not alias qkv");
+    cudaError_t e = launch_head_split(q, k, v, qkv, b, h, t, hd, es, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return LLMT_B200_OK;
 }

@@ -149,7 +149,7 @@ __device__ __forceinline__ float gelu_tanh_precise(float v) {
 // u = k0*(v + k1*v^3): algebraically identical to 0.5*v*(1+tanh(u)), no cancellation
 // for negative v, and five FP32 operations plus one exp2 and one reciprocal on the
 // special-function unit per element (relative error of the result ~1e-6).
-__device__ __forceinline__ float gelu_tanh_fast(float v) {
+__device__ __forceinline__ float gelu_tanh_sigmoid(float v) {
     const float a0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2*k0*log2(e)
     const float a1 = a0 * 0.044715f;
     const float w = v * fmaf(a1, v * v, a0);  // -2u * log2(e)
@@ -157,6 +157,25 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));         // exp(-2u); +inf for very negative v
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));  // sigmoid(2u); 0 when e = +inf
     return v * r;
+}
+
+// The epilogue's GELU.  The special-function unit issues 16 operations per clock and SM, and
+// a 128 x 256 tile has 32768 elements, so the two-operation form above costs a CTA 4096 clocks
+// per tile - more than half of a 768-deep main loop.  llmt's own form, 0.5*v*(1 + tanh(u)),
+// needs one operation with the hardware tanh (relative error 2^-11): its absolute error,
+// below 2.5e-4 * |v|, is far inside the resolution of a bf16 result (2^-8) and of the stated
+// fp32 tolerance wherever 1 + tanh(u) is not small; where it is small (v < -1.5: 1 + tanh(u)
+// < 0.14, a few elements in a thousand for pre-activations of a GPT-2 MLP) the sum cancels
+// and the sigmoid form is used instead.
+__device__ __forceinline__ float gelu_tanh_fast(float v) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f * 0.7978845608028654f;
+    const float u = v * fmaf(k1, v * v, k0);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    const float h = 0.5f * v;
+    float out = fmaf(h, t, h);
+    if (v < -1.5f) out = gelu_tanh_sigmoid(v);
+    return out;
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
@@ -177,6 +196,10 @@ cudaError_t launch_softmax_fwd(void* y, const void* x, int64_t rows, int64_t tq,
                                int is_bf16, int causal, cudaStream_t stream);
 cudaError_t launch_softmax_bwd(void* ds, const void* p, const void* dp, int64_t rows, int64_t tk,
                                int is_bf16, cudaStream_t stream);
+cudaError_t launch_head_merge(void* y, const void* x, int64_t B, int64_t H, int64_t T, int64_t hd, int elem_bytes,
+                              cudaStream_t stream);
+cudaError_t launch_head_split(void* q, void* k, void* v, const void* qkv, int64_t B, int64_t H, int64_t T, int64_t hd,
+                              int elem_bytes, cudaStream_t stream);
 DeviceStatus* device_status_ptr(void);
 
 void count_launch(int n);

@@ -8,6 +8,8 @@
 // bitwise reproducible.
 #include <cuda_bf16.h>
 
+#include <initializer_list>
+
 #include "common.h"
 
 namespace llmt_b200 {
@@ -223,6 +225,39 @@ __global__ void repack_bf16_kernel(uint16_t* __restrict__ dst, const uint16_t* _
     }
 }
 
+// Head split / merge as copies (llmt include/llmt/kernels/permute.h:21-46).  The GEMMs can read
+// and write the per-head layout through strides, so these are only needed where a caller wants
+// the re-shelved tensor itself.  One thread moves `vec` consecutive elements of one head's row
+// (hd is a multiple of vec): 16 bytes when the pointers and hd allow it, else one element.
+//   merge: y[b, t, h*hd + d] = x[b, h, t, d]
+//   split: out[part][b, h, t, d] = qkv[b, t, part*A + h*hd + d],  A = H*hd, part = 0..parts-1
+template <typename V>
+__global__ void head_merge_kernel(V* __restrict__ y, const V* __restrict__ x, int64_t B, int64_t H, int64_t T,
+                                  int64_t hdv) {
+    const int64_t total = B * H * T * hdv;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        // i runs over the OUTPUT [B, T, H, hdv]: consecutive threads write consecutive vectors
+        const int64_t d = i % hdv, h = (i / hdv) % H, t = (i / (hdv * H)) % T, b = i / (hdv * H * T);
+        y[i] = x[((b * H + h) * T + t) * hdv + d];
+    }
+}
+
+template <typename V>
+__global__ void head_split_kernel(V* __restrict__ q, V* __restrict__ k, V* __restrict__ v, const V* __restrict__ qkv,
+                                  int64_t B, int64_t H, int64_t T, int64_t hdv) {
+    const int64_t per_part = B * T * H * hdv;
+    const int64_t total = 3 * per_part;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        // i runs over the INPUT [B, T, 3, H, hdv]: consecutive threads read consecutive vectors
+        const int64_t d = i % hdv, h = (i / hdv) % H, part = (i / (hdv * H)) % 3, t = (i / (hdv * H * 3)) % T,
+                      b = i / (hdv * H * 3 * T);
+        V* out = part == 0 ? q : part == 1 ? k : v;
+        out[((b * H + h) * T + t) * hdv + d] = qkv[i];
+    }
+}
+
 // Zeroes the flat gradient span between steps (the zero_grad of llmt's ParamStore contract,
 // include/llmt/model/param_store.h:142-148).  Written here rather than left to a memset so that it
 // joins the stream's programmatic dependent launches: the first GEMM of the step starts its
@@ -285,6 +320,57 @@ cudaError_t launch_fp32_gemm(const Fp32GemmParams& p, cudaStream_t stream) {
     dim3 grid(static_cast<unsigned>((p.n + TN - 1) / TN), static_cast<unsigned>((p.m + TM - 1) / TM),
               static_cast<unsigned>(p.batch));
     fp32_gemm_kernel<<<grid, 256, 0, stream>>>(p);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+namespace {
+int64_t copy_grid(int64_t total) {
+    int64_t grid = (total + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    return grid < 1 ? 1 : grid;
+}
+bool vec16_ok(std::initializer_list<const void*> ptrs, int64_t hd, int elem_bytes) {
+    if ((hd * elem_bytes) % 16 != 0) return false;
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return false;
+    return true;
+}
+}  // namespace
+
+cudaError_t launch_head_merge(void* y, const void* x, int64_t B, int64_t H, int64_t T, int64_t hd, int elem_bytes,
+                              cudaStream_t stream) {
+    if (vec16_ok({y, x}, hd, elem_bytes)) {
+        const int64_t hdv = hd * elem_bytes / 16;
+        head_merge_kernel<uint4><<<static_cast<unsigned>(copy_grid(B * H * T * hdv)), 256, 0, stream>>>(
+            static_cast<uint4*>(y), static_cast<const uint4*>(x), B, H, T, hdv);
+    } else if (elem_bytes == 4) {
+        head_merge_kernel<uint32_t><<<static_cast<unsigned>(copy_grid(B * H * T * hd)), 256, 0, stream>>>(
+            static_cast<uint32_t*>(y), static_cast<const uint32_t*>(x), B, H, T, hd);
+    } else {
+        head_merge_kernel<uint16_t><<<static_cast<unsigned>(copy_grid(B * H * T * hd)), 256, 0, stream>>>(
+            static_cast<uint16_t*>(y), static_cast<const uint16_t*>(x), B, H, T, hd);
+    }
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_head_split(void* q, void* k, void* v, const void* qkv, int64_t B, int64_t H, int64_t T, int64_t hd,
+                              int elem_bytes, cudaStream_t stream) {
+    if (vec16_ok({q, k, v, qkv}, hd, elem_bytes)) {
+        const int64_t hdv = hd * elem_bytes / 16;
+        head_split_kernel<uint4><<<static_cast<unsigned>(copy_grid(3 * B * H * T * hdv)), 256, 0, stream>>>(
+            static_cast<uint4*>(q), static_cast<uint4*>(k), static_cast<uint4*>(v), static_cast<const uint4*>(qkv), B, H,
+            T, hdv);
+    } else if (elem_bytes == 4) {
+        head_split_kernel<uint32_t><<<static_cast<unsigned>(copy_grid(3 * B * H * T * hd)), 256, 0, stream>>>(
+            static_cast<uint32_t*>(q), static_cast<uint32_t*>(k), static_cast<uint32_t*>(v),
+            static_cast<const uint32_t*>(qkv), B, H, T, hd);
+    } else {
+        head_split_kernel<uint16_t><<<static_cast<unsigned>(copy_grid(3 * B * H * T * hd)), 256, 0, stream>>>(
+            static_cast<uint16_t*>(q), static_cast<uint16_t*>(k), static_cast<uint16_t*>(v),
+            static_cast<const uint16_t*>(qkv), B, H, T, hd);
+    }
     count_launch(1);
     return cudaGetLastError();
 }

@@ -418,13 +418,18 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        // A ticket is drawn only when the producer is ready to stream that tile (the first one
-        // before the dependency wait).  Drawing one tile ahead would hide the atomic's round trip,
-        // but every CTA busy with a long tile would then sit on a short one that idle CTAs could
-        // have taken (measured on the QKV backward: the dX CTAs idle from 35 us of an 84 us launch).
-        // The operand stages already in shared memory cover the round trip instead.
+        // A ticket is drawn when the producer is nearly ready to stream that tile: a few k-blocks
+        // before it has issued the last loads of the current one (the first ticket before the
+        // dependency wait), so that the atomic's round trip (about a microsecond) overlaps those
+        // loads instead of opening a bubble between two tiles.  Drawing a whole tile ahead would hide
+        // it too, but every CTA busy with a long tile would then sit on a short one that idle
+        // CTAs could have taken (measured on the QKV backward: the dX CTAs idle from 35 us of an
+        // 84 us launch).
         const bool dynamic = gp.static_schedule == 0;
         int prev_ticket = 0;
+        constexpr int kDrawAhead = 6;   // k-blocks before the end of a tile at which the next ticket is drawn
+        constexpr int kNotDrawn = -2;
+        int next_ticket = kNotDrawn;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
@@ -435,7 +440,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                              kDevWaitSched, slot, wait_ns);
                     if (ok) {
                         t = it == 0 ? first_ticket
-                                    : (dynamic ? atomicAdd(gp.sched_counter, 1) : prev_ticket + n_sched);
+                                    : !dynamic ? prev_ticket + n_sched
+                                    : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1);
+                        next_ticket = kNotDrawn;
                         prev_ticket = t;
                         if (t >= gp.total_tiles) {
                             // Every drawer takes exactly one out-of-range ticket; the last re-arms the counter.
@@ -489,7 +496,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
             }
+            const int draw_kb = tc.kb1 - kDrawAhead > tc.kb0 ? tc.kb1 - kDrawAhead : tc.kb0;
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
+                if (scheduler && dynamic && lane == 0 && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
                 if ((seq & parity_mask) == my_parity) {
                     if (lane == 0) {
                         ok = bounded_wait<kPair>(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, status,

@@ -20,6 +20,7 @@
 #include "llmt/kernels/algo_cache.h"
 #include "llmt/kernels/attention.h"
 #include "llmt/kernels/matmul.h"
+#include "llmt/kernels/permute.h"
 #include "llmt/layers/linear.h"
 #include "llmt/layers/mlp.h"
 
@@ -70,13 +71,14 @@ std::vector<float> download(const Tensor& t) {
     return v;
 }
 
-void check_close(const Tensor& got, const HostTensor& want, const char* what, double scale = 1.0) {
+void check_close(const Tensor& got, const HostTensor& want, const char* what, double scale = 1.0,
+                 double rtol = 1e-5, double atol = 1e-6) {
     ++g_checks;
     const std::vector<float> g = download(got);
     if (g.size() != want.v.size()) { ++g_failures; std::fprintf(stderr, "FAIL %s: size\n", what); return; }
     for (size_t i = 0; i < g.size(); ++i) {
         const double e = scale * want.v[i];
-        if (!(std::fabs(g[i] - e) <= 1e-6 + 1e-5 * std::fabs(e))) {
+        if (!(std::fabs(g[i] - e) <= atol + rtol * std::fabs(e))) {
             ++g_failures;
             std::fprintf(stderr, "FAIL %s: [%zu] got %.9g want %.9g\n", what, i, g[i], e);
             return;
@@ -186,6 +188,24 @@ void test_attention(Device& dev, const RunCtx& ctx) {
     check_close(yh, load("attention", "out"), "attention_fwd y_heads");
 }
 
+// llmt tests/unit/test_attention.cu:23-43: head split and merge against the `permute` case.
+void test_permute(Device& dev) {
+    Arena arena(1 << 20, "perm-test");
+    const Tensor qkv = upload(arena, load("permute", "qkv"), dev.stream());
+    Tensor q = arena.alloc({2, 2, 3, 4}, DType::FP32), k = arena.alloc({2, 2, 3, 4}, DType::FP32),
+           v = arena.alloc({2, 2, 3, 4}, DType::FP32);
+    kernels::permute_split(dev.stream(), q, k, v, qkv, /*n_head=*/2);
+    dev.synchronize();
+    check_close(q, load("permute", "q"), "permute_split q", 1.0, 1e-6, 1e-7);
+    check_close(k, load("permute", "k"), "permute_split k", 1.0, 1e-6, 1e-7);
+    check_close(v, load("permute", "v"), "permute_split v", 1.0, 1e-6, 1e-7);
+    const Tensor x = upload(arena, load("permute", "x"), dev.stream());
+    Tensor y = arena.alloc({2, 3, 8}, DType::FP32);
+    kernels::permute_merge(dev.stream(), y, x);
+    dev.synchronize();
+    check_close(y, load("permute", "y"), "permute_merge y", 1.0, 1e-6, 1e-7);
+}
+
 // bf16 Linear with bias through the same C++ interface: forward with the fused bias,
 // backward as ONE grouped launch (dx, dW and dbias).  Checked against the strict-fp32
 // path of the same layer run on the same bf16-rounded values (relative Frobenius:
@@ -291,6 +311,7 @@ int main(int argc, char** argv) {
     test_linear(dev, ctx);
     test_mlp(dev, ctx);
     test_attention(dev, ctx);
+    test_permute(dev);
     test_bf16_linear(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());

@@ -191,3 +191,35 @@ def test_tensor_map_cache_replays_descriptors():
     c2 = torch.empty(m // 2, n, device=DEV, dtype=torch.bfloat16)
     L.gemm(c2, a[: m // 2], b, False, True)
     assert torch.equal(c2, first[: m // 2])
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_head_split_and_merge_match_llmt_goldens(dt):
+    """llmt tests/unit/test_attention.cu:23-43 (golden case `permute`, exact data movement)."""
+    from tests.support import GoldenCase
+    g = GoldenCase("permute")
+    dev = lambda n: torch.from_numpy(g.tensor(n)).to(DEV).to(dt)
+    qkv = dev("qkv")
+    q, k, v = (torch.empty(2, 2, 3, 4, device=DEV, dtype=dt) for _ in range(3))
+    L.head_split(q, k, v, qkv)
+    for got, name in ((q, "q"), (k, "k"), (v, "v")):
+        assert torch.equal(got, dev(name)), name
+    y = torch.empty(2, 3, 8, device=DEV, dtype=dt)
+    L.head_merge(y, dev("x"))
+    assert torch.equal(y, dev("y"))
+    with pytest.raises(L.LlmtB200Error):
+        L.head_merge(qkv.view(-1)[: 2 * 3 * 8].view(2, 3, 8), qkv.view(-1)[: 2 * 2 * 3 * 4].view(2, 2, 3, 4))  # aliasing
+
+
+def test_head_split_and_merge_at_model_size_vectorised():
+    """GPT-2-small attention shapes (B = 8, H = 12, T = 1024, hd = 64), bf16: the 16-byte path."""
+    B, H, T, hd = 8, 12, 1024, 64
+    g = torch.Generator(device=DEV).manual_seed(9)
+    qkv = torch.randn(B, T, 3 * H * hd, device=DEV, generator=g).to(torch.bfloat16)
+    q, k, v = (torch.empty(B, H, T, hd, device=DEV, dtype=torch.bfloat16) for _ in range(3))
+    L.head_split(q, k, v, qkv)
+    want = qkv.view(B, T, 3, H, hd).permute(2, 0, 3, 1, 4)
+    assert torch.equal(q, want[0]) and torch.equal(k, want[1]) and torch.equal(v, want[2])
+    y = torch.empty(B, T, H * hd, device=DEV, dtype=torch.bfloat16)
+    L.head_merge(y, q)
+    assert torch.equal(y, q.permute(0, 2, 1, 3).reshape(B, T, H * hd))
