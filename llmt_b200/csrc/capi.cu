@@ -585,6 +585,9 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->m = d->m; p->n = d->n; p->k = d->k;
     p->batch = static_cast<int32_t>(d->batch);
     p->tiles_m = pl.tiles_m; p->tiles_n = pl.tiles_n; p->splits = pl.splits;
+    p->inv_tiles_m = 1.0f / static_cast<float>(pl.tiles_m);
+    p->inv_tiles_n = 1.0f / static_cast<float>(pl.tiles_n);
+    p->inv_splits = 1.0f / static_cast<float>(pl.splits);
     p->kblocks_total = pl.kblocks_total;
     p->kblocks_per_split = pl.kblocks_per_split;
     p->bn = pl.bn;

@@ -39,6 +39,7 @@ struct alignas(64) GroupProblem {
     int64_t m, n, k;
     int32_t batch;
     int32_t tiles_m, tiles_n, splits;
+    float inv_tiles_m, inv_tiles_n, inv_splits;  // reciprocals, for the kernel's ticket decoding
     int32_t kblocks_total;      // ceil(k / 64)
     int32_t kblocks_per_split;  // k-blocks handled by each split (the last one may be shorter)
     int32_t bn;                 // tile width along N: 64, 128, 192 or 256 (tile height is 128 per CTA)
@@ -159,23 +160,27 @@ __device__ __forceinline__ float gelu_tanh_sigmoid(float v) {
     return v * r;
 }
 
-// The epilogue's GELU.  The special-function unit issues 16 operations per clock and SM, and
-// a 128 x 256 tile has 32768 elements, so the two-operation form above costs a CTA 4096 clocks
-// per tile - more than half of a 768-deep main loop.  llmt's own form, 0.5*v*(1 + tanh(u)),
-// needs one operation with the hardware tanh (relative error 2^-11): its absolute error,
-// below 2.5e-4 * |v|, is far inside the resolution of a bf16 result (2^-8) and of the stated
-// fp32 tolerance wherever 1 + tanh(u) is not small; where it is small (v < -1.5: 1 + tanh(u)
-// < 0.14, a few elements in a thousand for pre-activations of a GPT-2 MLP) the sum cancels
-// and the sigmoid form is used instead.
+// The epilogue's GELU: the same sigmoid form with ONE operation on the special-function unit.
+// That unit issues 16 operations per clock and SM, a 128 x 256 tile has 32768 elements, so
+// the two-operation form costs a CTA 4096 clocks per tile - more than half of a 768-deep main
+// loop - and the epilogue warps (two per scheduler) have little else to hide it behind.  Here
+// exp2 stays on the unit and the reciprocal of d = 1 + exp(-2u), d in [1, 2^127], is computed
+// on the FMA pipe: a starting value from the exponent/mantissa bits (relative error below 13 %)
+// and three Newton steps r <- r (2 - d r), which square the error each time (below 1e-7 after
+// the third).  No branches, so the 32 elements a thread holds overlap; no cancellation for
+// negative v, unlike 0.5 v (1 + tanh u) with the hardware tanh.
 __device__ __forceinline__ float gelu_tanh_fast(float v) {
-    const float k0 = 0.7978845608028654f, k1 = 0.044715f * 0.7978845608028654f;
-    const float u = v * fmaf(k1, v * v, k0);
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-    const float h = 0.5f * v;
-    float out = fmaf(h, t, h);
-    if (v < -1.5f) out = gelu_tanh_sigmoid(v);
-    return out;
+    const float a0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;  // -2*k0*log2(e)
+    const float a1 = a0 * 0.044715f;
+    const float w = fminf(v * fmaf(a1, v * v, a0), 126.0f);  // -2u * log2(e); the clamp keeps d finite
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(w));
+    const float d = 1.0f + e;
+    float r = __uint_as_float(0x7EF311C7u - __float_as_uint(d));
+    r = r * fmaf(-d, r, 2.0f);
+    r = r * fmaf(-d, r, 2.0f);
+    r = r * fmaf(-d, r, 2.0f);
+    return v * r;
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.

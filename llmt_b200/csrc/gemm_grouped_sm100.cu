@@ -137,6 +137,18 @@ struct TileCoord {
     int kb0, kb1;
 };
 
+// n / d with the reciprocal of d at hand.  One thread of the MMA warp decodes a ticket between
+// two tiles, where a hardware-emulated integer division (a long dependent chain) is exposed:
+// below 2^24 the float product is within one of the quotient and two compares fix it.
+__device__ __forceinline__ uint32_t div_by(uint32_t n, uint32_t d, float inv_d) {
+    if (n >= (1u << 24)) return n / d;
+    uint32_t q = static_cast<uint32_t>(__uint2float_rz(n) * inv_d);
+    const uint32_t prod = q * d;
+    if (prod > n) --q;
+    else if (n - prod >= d) ++q;
+    return q;
+}
+
 __device__ __forceinline__ TileCoord decode_tile(const GroupParams& gp, int t) {
     TileCoord tc;
     int pi = 0;
@@ -145,19 +157,18 @@ __device__ __forceinline__ TileCoord decode_tile(const GroupParams& gp, int t) {
         if (t >= gp.prob[i].tile_begin) pi = i;
     const GroupProblem& p = gp.prob[pi];
     tc.prob = pi;
-    // One thread of the MMA warp runs this between two tiles: integer divisions are slow
-    // there, so the common cases (one split, one batch item) avoid all but one.
+    // The common cases (one split, one batch item) need one quotient only.
     const uint32_t r = static_cast<uint32_t>(t - p.tile_begin);
-    const uint32_t q1 = r / static_cast<uint32_t>(p.tiles_m);
+    const uint32_t q1 = div_by(r, static_cast<uint32_t>(p.tiles_m), p.inv_tiles_m);
     tc.m_tile = static_cast<int>(r - q1 * static_cast<uint32_t>(p.tiles_m));
     if (p.splits == 1 && p.batch <= 1) {
         tc.n_tile = static_cast<int>(q1);
         tc.split = 0;
         tc.batch = 0;
     } else {
-        const uint32_t q2 = q1 / static_cast<uint32_t>(p.tiles_n);
+        const uint32_t q2 = div_by(q1, static_cast<uint32_t>(p.tiles_n), p.inv_tiles_n);
         tc.n_tile = static_cast<int>(q1 - q2 * static_cast<uint32_t>(p.tiles_n));
-        const uint32_t q3 = q2 / static_cast<uint32_t>(p.splits);
+        const uint32_t q3 = div_by(q2, static_cast<uint32_t>(p.splits), p.inv_splits);
         tc.split = static_cast<int>(q2 - q3 * static_cast<uint32_t>(p.splits));
         tc.batch = static_cast<int>(q3);
     }
@@ -679,23 +690,27 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const int64_t n0 = static_cast<int64_t>(tc.n_tile) * p.bn;
             const bool partial = p.splits > 1;
             const bool out_bf16 = !partial && p.c_is_bf16;
-            // A column unit is what one TMA store carries: 32 rows x 128 bytes.
-            const int unit_cols = out_bf16 ? 64 : 32;
-            const int spu = out_bf16 ? 2 : 1;  // 32-column steps (one tcgen05.ld each) per unit
+            // A column unit is what one TMA store carries: 32 rows x 128 bytes.  Everything per step
+            // is shifts and adds: an integer division on this path costs a warp hundreds of cycles.
+            const int unit_shift = out_bf16 ? 6 : 5;
+            const int unit_cols = 1 << unit_shift;
+            const int spu_shift = out_bf16 ? 1 : 0;
+            const int spu = 1 << spu_shift;  // 32-column steps (one tcgen05.ld each) per unit
             const bool tma_ok = partial ? p.ws_tma != 0 : p.c_tma != 0;
             const CUtensorMap* out_map = partial ? &p.map_ws : &p.map_c;
             const int out_z = partial ? tc.batch * p.splits + tc.split : tc.batch;
             // Column (inside the tile) of this warp's s-th step.
-            auto step_col = [&](int s) { return (half + 2 * (s / spu)) * unit_cols + (s % spu) * 32; };
-            int ns = ((p.bn / unit_cols + 1 - half) / 2) * spu;
+            auto step_col = [&](int s) { return ((half + 2 * (s >> spu_shift)) << unit_shift) + ((s & (spu - 1)) << 5); };
+            int ns = (((p.bn >> unit_shift) + 1 - half) >> 1) << spu_shift;
             while (ns > 0 && n0 + step_col(ns - 1) >= p.n) --ns;
             if (row0 >= p.m) ns = 0;  // the whole warp lies below the matrix
+            // Offset of this thread's row of the tile inside C, in elements.
+            const int64_t c_row_off = static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0;
             if (p.beta != 0.0f && !partial && row_ok) {
                 // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
                 // lines now, while the tile's main loop is still running.
                 const int esz = p.c_is_bf16 ? 2 : 4;
-                const char* base = static_cast<const char*>(p.c) +
-                                   (static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0) * esz;
+                const char* base = static_cast<const char*>(p.c) + c_row_off * esz;
                 for (int s = 0; s < ns; s += spu)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<int64_t>(step_col(s)) * esz));
             }
@@ -725,7 +740,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                const int64_t c_off = static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + col;
+                const int64_t c_off = c_row_off + c0;
                 if (!partial) {
                     if (p.alpha != 1.0f) {
 #pragma unroll
@@ -754,7 +769,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
                     }
                 }
-                const int sub = s % spu;
+                const int sub = s & (spu - 1);
                 const int64_t unit_col = col - sub * 32;
                 const bool by_tma = tma_ok && unit_col + unit_cols <= p.n;
                 const uint32_t buf = my_bufs + (buf_seq % kStoreBufs) * kStoreBufBytes;
