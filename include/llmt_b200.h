@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LLMT_B200_ABI_VERSION 2
+#define LLMT_B200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define LLMT_B200_API __attribute__((visibility("default")))
@@ -112,6 +112,17 @@ typedef struct llmt_b200_gemm_desc {
     int32_t plan_cta_pairs; /* 0 = choose; 1 = single CTAs (128-row tiles); 2 = CTA pairs (256-row tiles) */
     void* workspace;
     uint64_t workspace_bytes;
+    /* Two-level batch layout (0 = plain: item b sits b * stride_x past the base).  With
+     * batch_inner = I > 0 (I divides batch) item b sits (b % I) * stride_x + (b / I) * stride_x_outer
+     * past the base, and stride_x may be smaller than one matrix.  This is how the per-head
+     * products of an attention layer read Q, K, V straight out of the [B, T, 3*H*hd] output of
+     * the QKV projection (ld = 3*H*hd, stride = hd, stride_outer = T*3*H*hd, batch = B*H,
+     * batch_inner = H) and write their result straight into [B, T, H*hd]: the head split and
+     * merge that llmt runs as copy kernels (src/kernels/permute.cu:18-46) become strides.  bf16
+     * operands in such a layout must be addressable by TMA as they are (16-byte aligned base,
+     * pitches and strides multiples of 8 elements). */
+    int64_t batch_inner;
+    int64_t stride_a_outer, stride_b_outer, stride_c_outer;
 } llmt_b200_gemm_desc;
 
 /* Replaces llmt's kernels::matmul body (src/kernels/matmul.cpp:218-222 ->

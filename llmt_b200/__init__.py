@@ -57,6 +57,8 @@ class GemmDesc(ctypes.Structure):
         ("dbias_beta", ctypes.c_float), ("plan_tile_n", ctypes.c_int32),
         ("plan_splits", ctypes.c_int32), ("plan_cta_pairs", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+        ("batch_inner", ctypes.c_int64), ("stride_a_outer", ctypes.c_int64),
+        ("stride_b_outer", ctypes.c_int64), ("stride_c_outer", ctypes.c_int64),
     ]
 
 

@@ -23,4 +23,16 @@ void attention_bwd(const RunCtx& ctx, Tensor& dq, Tensor& dk, Tensor& dv, Tensor
 
 void softmax_fwd(const RunCtx& ctx, Tensor& y, const Tensor& x, MaskSpec mask) noexcept;
 
+// The same forward pass with the head split and merge folded into the GEMMs' strides:
+//   qkv [B, T, 3*H*hd]  the output of the fused QKV projection (per token: Q | K | V parts)
+//   scores [B, H, T, T] holds the probabilities on return, as in attention_fwd
+//   y [B, T, H*hd]      token rows, ready for the output projection
+// S = alpha Q K^T reads Q and K straight out of qkv (row pitch 3*H*hd, one head every hd
+// elements), O = P V reads V the same way and writes each head's [T, hd] block into its
+// columns of y.  Replaces permute_split -> attention_fwd -> permute_merge of llmt
+// (include/llmt/kernels/permute.h:13-46, src/kernels/attention.cpp:54-63): no q/k/v/y_heads
+// tensors, no copy kernels.  hd * sizeof(element) must be a multiple of 16 bytes.
+void attention_fwd_packed(const RunCtx& ctx, Tensor& y, Tensor& scores, const Tensor& qkv, int64_t n_head,
+                          MaskSpec mask) noexcept;
+
 }  // namespace llmt::kernels

@@ -54,6 +54,50 @@ void attention_fwd(const RunCtx& ctx, Tensor& y, Tensor& scores, Tensor& y_heads
     }
 }
 
+void attention_fwd_packed(const RunCtx& ctx, Tensor& y, Tensor& scores, const Tensor& qkv, int64_t n_head,
+                          MaskSpec mask) noexcept {
+    if (ctx.backend != KernelBackend::Naive) detail::fatal("attention_fwd", "no fused variant implemented yet");
+    for (const Tensor* t : std::initializer_list<const Tensor*>{&y, &scores, &qkv})
+        if (!t->valid()) detail::fatal("attention_fwd_packed", "invalid tensor (null data)");
+    if (qkv.shape.rank != 3 || y.shape.rank != 3 || scores.shape.rank != 4)
+        detail::fatal("attention_fwd_packed", "expected qkv [B,T,3A], y [B,T,A], scores [B,H,T,T]");
+    const int64_t b = qkv.shape[0], t = qkv.shape[1], a3 = qkv.shape[2], h = n_head;
+    if (h <= 0 || a3 % (3 * h) != 0) detail::fatal("attention_fwd_packed", "qkv must be [B, T, 3·H·hd]");
+    const int64_t a = a3 / 3, hd = a / h;
+    if (y.shape != Shape{b, t, a}) detail::fatal("attention_fwd_packed", "y must be [B, T, H·hd]");
+    if (scores.shape != Shape{b, h, t, t}) detail::fatal("attention_fwd_packed", "scores must be [B, H, T, T]");
+    if (y.dtype != qkv.dtype || scores.dtype != qkv.dtype) detail::fatal("attention_fwd_packed", "dtype mismatch");
+    const size_t es = dtype_size(qkv.dtype);
+    const char* base = static_cast<const char*>(qkv.data);
+    // S[b,h] = alpha Q[b,h] K[b,h]^T: operands are [T, hd] views with row pitch 3A inside qkv
+    llmt_b200_gemm_desc d{};
+    d.m = t; d.n = t; d.k = hd; d.batch = b * h; d.batch_inner = h;
+    d.lda = a3; d.ldb = a3; d.ldc = t;
+    d.stride_a = hd; d.stride_b = hd; d.stride_c = t * t;
+    d.stride_a_outer = t * a3; d.stride_b_outer = t * a3; d.stride_c_outer = h * t * t;
+    d.trans_a = 0; d.trans_b = 1;
+    d.dtype_ab = d.dtype_c = static_cast<int32_t>(qkv.dtype);
+    d.alpha = 1.0f / std::sqrt(static_cast<float>(hd)); d.beta = 0.0f;
+    d.workspace = ctx.blas_workspace; d.workspace_bytes = ctx.blas_workspace_bytes;
+    if (llmt_b200_gemm(&d, scores.data, base, base + a * es, ctx.stream) != LLMT_B200_OK)
+        detail::fatal("attention_fwd_packed", "%s", llmt_b200_last_error());
+    Tensor s3 = scores;
+    s3.shape = Shape{b * h, t, t};
+    softmax_fwd(ctx, s3, s3, mask);
+    // O[b,h] = P[b,h] V[b,h], written into columns h*hd .. of y's token rows
+    llmt_b200_gemm_desc o{};
+    o.m = t; o.n = hd; o.k = t; o.batch = b * h; o.batch_inner = h;
+    o.lda = t; o.ldb = a3; o.ldc = a;
+    o.stride_a = t * t; o.stride_b = hd; o.stride_c = hd;
+    o.stride_a_outer = h * t * t; o.stride_b_outer = t * a3; o.stride_c_outer = t * a;
+    o.trans_a = 0; o.trans_b = 0;
+    o.dtype_ab = o.dtype_c = static_cast<int32_t>(qkv.dtype);
+    o.alpha = 1.0f; o.beta = 0.0f;
+    o.workspace = ctx.blas_workspace; o.workspace_bytes = ctx.blas_workspace_bytes;
+    if (llmt_b200_gemm(&o, y.data, scores.data, base + 2 * a * es, ctx.stream) != LLMT_B200_OK)
+        detail::fatal("attention_fwd_packed", "%s", llmt_b200_last_error());
+}
+
 void permute_split(cudaStream_t s, Tensor& q, Tensor& k, Tensor& v, const Tensor& qkv, int64_t n_head) noexcept {
     for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &k, &v, &qkv})
         if (!t->valid()) detail::fatal("permute_split", "invalid tensor (null data)");

@@ -314,7 +314,15 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     if (d->lda < out->a_cols || d->ldb < out->b_cols || d->ldc < d->n)
         return fail(LLMT_B200_ERR_INVALID, "matmul: row pitch smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                     (long long)d->lda, (long long)d->ldb, (long long)d->ldc);
-    if (d->batch > 1) {
+    const bool two_level = d->batch_inner > 0;
+    if (two_level) {
+        if (d->batch_inner > d->batch || d->batch % d->batch_inner != 0)
+            return fail(LLMT_B200_ERR_INVALID, "matmul: batch_inner must divide batch");
+        if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0 || d->stride_a_outer < 0 ||
+            d->stride_b_outer < 0 || d->stride_c_outer < 0)
+            return fail(LLMT_B200_ERR_INVALID, "matmul: negative batch stride");
+        if (d->dbias != nullptr) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dbias with a batched product is not defined");
+    } else if (d->batch > 1) {
         if (d->stride_a < (out->a_rows - 1) * d->lda + out->a_cols ||
             d->stride_b < (out->b_rows - 1) * d->ldb + out->b_cols ||
             d->stride_c < (d->m - 1) * d->ldc + d->n)
@@ -344,11 +352,16 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     const size_t es_ab = out->bf16 ? 2 : 4, es_c = d->dtype_c == LLMT_B200_BF16 ? 2 : 4;
     const int64_t nb = d->batch > 0 ? d->batch : 1;
     if (d->m > 0 && d->n > 0 && d->k > 0) {
-        const size_t a_bytes = static_cast<size_t>((nb - 1) * (nb > 1 ? d->stride_a : 0) +
+        // extent of the batch: last item's offset (for a two-level layout: last of the last group)
+        auto batch_span = [&](int64_t stride, int64_t stride_outer) -> int64_t {
+            if (two_level) return (d->batch_inner - 1) * stride + (nb / d->batch_inner - 1) * stride_outer;
+            return (nb - 1) * (nb > 1 ? stride : 0);
+        };
+        const size_t a_bytes = static_cast<size_t>(batch_span(d->stride_a, d->stride_a_outer) +
                                                    (out->a_rows - 1) * d->lda + out->a_cols) * es_ab;
-        const size_t b_bytes = static_cast<size_t>((nb - 1) * (nb > 1 ? d->stride_b : 0) +
+        const size_t b_bytes = static_cast<size_t>(batch_span(d->stride_b, d->stride_b_outer) +
                                                    (out->b_rows - 1) * d->ldb + out->b_cols) * es_ab;
-        const size_t c_bytes = static_cast<size_t>((nb - 1) * (nb > 1 ? d->stride_c : 0) +
+        const size_t c_bytes = static_cast<size_t>(batch_span(d->stride_c, d->stride_c_outer) +
                                                    (d->m - 1) * d->ldc + d->n) * es_c;
         out->a_bytes = a_bytes; out->b_bytes = b_bytes; out->c_bytes = c_bytes;
         if (overlaps(c, c_bytes, a, a_bytes) || overlaps(c, c_bytes, b, b_bytes))
@@ -373,28 +386,45 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
     return LLMT_B200_OK;
 }
 
-// Tensor map over one row-major matrix [rows, cols] (pitch ld, `batch` items `stride`
-// elements apart) with a box of box_cols x box_rows elements.  elem_bytes 2 = bf16, 4 = fp32.
+// Tensor map over row-major matrices [rows, cols] (pitch ld) in a batch laid out on two levels:
+// `inner` items `stride` elements apart form a group, `outer` groups are `stride_outer` elements
+// apart (a plain batch is one group).  Box of box_cols x box_rows elements of one matrix.
+// elem_bytes 2 = bf16, 4 = fp32.
+struct BatchLayout {
+    int64_t inner = 1, stride = 0, outer = 1, stride_outer = 0;
+};
+
+BatchLayout batch_layout(int64_t batch, int64_t batch_inner, int64_t stride, int64_t stride_outer) {
+    BatchLayout bl;
+    if (batch_inner > 0) {
+        bl.inner = batch_inner; bl.stride = stride; bl.outer = batch / batch_inner; bl.stride_outer = stride_outer;
+    } else if (batch > 1) {
+        bl.inner = batch; bl.stride = stride;
+    }
+    return bl;
+}
+
 int encode_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols,
-               int64_t ld, int64_t batch, int64_t stride, int box_cols, int box_rows,
-               CUtensorMapSwizzle swizzle) {
+               int64_t ld, const BatchLayout& bl, int box_cols, int box_rows, CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail(LLMT_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-    const cuuint64_t stride_elems = batch > 1 ? static_cast<cuuint64_t>(stride)
-                                              : static_cast<cuuint64_t>(rows) * ld;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
-                          static_cast<cuuint64_t>(batch > 1 ? batch : 1)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elem_bytes, stride_elems * elem_bytes};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
+    // a dimension of extent 1 still needs a stride that passes the encoder's checks
+    const cuuint64_t one_matrix = static_cast<cuuint64_t>(rows) * ld;
+    const cuuint64_t s1 = bl.inner > 1 ? static_cast<cuuint64_t>(bl.stride) : one_matrix;
+    const cuuint64_t s2 = bl.outer > 1 ? static_cast<cuuint64_t>(bl.stride_outer) : s1 * static_cast<cuuint64_t>(bl.inner);
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(bl.inner), static_cast<cuuint64_t>(bl.outer)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * elem_bytes, s1 * elem_bytes, s2 * elem_bytes};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
-                          3, const_cast<void*>(base), dims, strides, box, estr,
+                          4, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(LLMT_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d "
-                    "(rows=%lld cols=%lld ld=%lld batch=%lld)", static_cast<int>(r),
-                    (long long)rows, (long long)cols, (long long)ld, (long long)batch);
+                    "(rows=%lld cols=%lld ld=%lld batch=%lld x %lld)", static_cast<int>(r),
+                    (long long)rows, (long long)cols, (long long)ld, (long long)bl.inner, (long long)bl.outer);
     return LLMT_B200_OK;
 }
 
@@ -406,12 +436,13 @@ int encode_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows,
 // few integer operations.  Direct-mapped, per host thread, no device state.
 struct MapKey {
     const void* base;
-    int64_t rows, cols, ld, batch, stride;
+    int64_t rows, cols, ld, inner, stride, outer, stride_outer;
     int32_t elem_bytes, box_cols, box_rows, swizzle;
     bool operator==(const MapKey& o) const {
-        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && batch == o.batch &&
-               stride == o.stride && elem_bytes == o.elem_bytes && box_cols == o.box_cols &&
-               box_rows == o.box_rows && swizzle == o.swizzle;
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && inner == o.inner &&
+               stride == o.stride && outer == o.outer && stride_outer == o.stride_outer &&
+               elem_bytes == o.elem_bytes && box_cols == o.box_cols && box_rows == o.box_rows &&
+               swizzle == o.swizzle;
     }
 };
 struct MapCacheEntry {
@@ -423,17 +454,18 @@ constexpr int kMapCacheSlots = 1024;
 std::atomic<uint64_t> g_map_cache_hits{0}, g_map_cache_misses{0};
 
 int cached_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t cols, int64_t ld,
-               int64_t batch, int64_t stride, int box_cols, int box_rows, CUtensorMapSwizzle swizzle) {
+               const BatchLayout& bl, int box_cols, int box_rows, CUtensorMapSwizzle swizzle) {
     thread_local MapCacheEntry* table = nullptr;
     if (table == nullptr) table = new MapCacheEntry[kMapCacheSlots]();
-    const MapKey key{base, rows, cols, ld, batch > 1 ? batch : 1, batch > 1 ? stride : 0,
-                     elem_bytes, box_cols, box_rows, static_cast<int32_t>(swizzle)};
+    const MapKey key{base, rows, cols, ld, bl.inner, bl.inner > 1 ? bl.stride : 0, bl.outer,
+                     bl.outer > 1 ? bl.stride_outer : 0, elem_bytes, box_cols, box_rows, static_cast<int32_t>(swizzle)};
     uint64_t h = 1469598103934665603ull;  // FNV-1a over the key's words, as llmt's AlgoKeyHash does
-    const uint64_t words[8] = {reinterpret_cast<uintptr_t>(base), static_cast<uint64_t>(rows),
-                               static_cast<uint64_t>(cols), static_cast<uint64_t>(ld),
-                               static_cast<uint64_t>(key.batch), static_cast<uint64_t>(key.stride),
-                               (static_cast<uint64_t>(elem_bytes) << 32) | static_cast<uint32_t>(box_cols),
-                               (static_cast<uint64_t>(box_rows) << 32) | static_cast<uint32_t>(swizzle)};
+    const uint64_t words[10] = {reinterpret_cast<uintptr_t>(base), static_cast<uint64_t>(rows),
+                                static_cast<uint64_t>(cols), static_cast<uint64_t>(ld),
+                                static_cast<uint64_t>(key.inner), static_cast<uint64_t>(key.stride),
+                                static_cast<uint64_t>(key.outer), static_cast<uint64_t>(key.stride_outer),
+                                (static_cast<uint64_t>(elem_bytes) << 32) | static_cast<uint32_t>(box_cols),
+                                (static_cast<uint64_t>(box_rows) << 32) | static_cast<uint32_t>(swizzle)};
     for (uint64_t w : words) { h ^= w; h *= 1099511628211ull; }
     MapCacheEntry& e = table[(h ^ (h >> 29)) % kMapCacheSlots];
     if (e.used && e.key == key) {
@@ -441,7 +473,7 @@ int cached_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows,
         g_map_cache_hits.fetch_add(1, std::memory_order_relaxed);
         return LLMT_B200_OK;
     }
-    const int st = encode_map(map, base, elem_bytes, rows, cols, ld, batch, stride, box_cols, box_rows, swizzle);
+    const int st = encode_map(map, base, elem_bytes, rows, cols, ld, bl, box_cols, box_rows, swizzle);
     if (st != LLMT_B200_OK) return st;
     e.key = key; e.used = true; e.map = *map;
     g_map_cache_misses.fetch_add(1, std::memory_order_relaxed);
@@ -450,8 +482,8 @@ int cached_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows,
 
 // bf16 operand map boxed for 128-byte-swizzled tiles (64 elements wide).
 int encode_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld,
-                       int64_t batch, int64_t stride, int box_rows) {
-    return cached_map(map, base, 2, rows, cols, ld, batch, stride, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+                       const BatchLayout& bl, int box_rows) {
+    return cached_map(map, base, 2, rows, cols, ld, bl, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 // Tile-queue counters: zero between launches (the kernel re-arms its counter); launches
@@ -508,8 +540,10 @@ uint64_t g_comm_wait_limit_ns = 4000000000ull;
 // TMA needs 16-byte aligned bases, pitches and batch strides.  An operand that breaks one of
 // the rules - a contiguous [tokens, 50257] dLogits, a slice x[:, 1:] - is first copied into
 // the workspace with an aligned base and its pitch rounded up ("repacked").
-bool needs_repack(const void* base, int64_t ld, int64_t batch, int64_t stride) {
-    return (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld % 8) != 0 || (batch > 1 && (stride % 8) != 0);
+bool needs_repack(const void* base, int64_t ld, int64_t batch, int64_t stride, int64_t batch_inner = 0,
+                  int64_t stride_outer = 0) {
+    return (reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ld % 8) != 0 || (batch > 1 && (stride % 8) != 0) ||
+           (batch_inner > 0 && (stride_outer % 8) != 0);
 }
 
 struct Repack {
@@ -525,13 +559,13 @@ Repack repack_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* 
     Repack r;
     const int64_t nb = d->batch > 1 ? d->batch : 1;
     auto round8 = [](int64_t v) { return (v + 7) / 8 * 8; };
-    if (d->k > 0 && needs_repack(a, d->lda, d->batch, d->stride_a)) {
+    if (d->k > 0 && needs_repack(a, d->lda, d->batch, d->stride_a, d->batch_inner, d->stride_a_outer)) {
         r.a = true;
         r.lda = round8(ck.a_cols);
         r.stride_a = ck.a_rows * r.lda;
         r.bytes_a = (static_cast<size_t>(nb) * r.stride_a * 2 + 255) / 256 * 256;
     }
-    if (d->k > 0 && needs_repack(b, d->ldb, d->batch, d->stride_b)) {
+    if (d->k > 0 && needs_repack(b, d->ldb, d->batch, d->stride_b, d->batch_inner, d->stride_b_outer)) {
         r.b = true;
         r.ldb = round8(ck.b_cols);
         r.stride_b = ck.b_rows * r.ldb;
@@ -581,7 +615,7 @@ int check_workspace(const llmt_b200_gemm_desc* d, const TcPlan& pl, size_t repac
 // Fills the kernel-side description of one problem (tensor maps included).
 int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& ck, const TcPlan& pl,
                  void* c, const void* a, const void* b) {
-    memset(p, 0, sizeof *p);
+    memset(static_cast<void*>(p), 0, sizeof *p);
     p->m = d->m; p->n = d->n; p->k = d->k;
     p->batch = static_cast<int32_t>(d->batch);
     p->tiles_m = pl.tiles_m; p->tiles_n = pl.tiles_n; p->splits = pl.splits;
@@ -594,7 +628,10 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->a_mn = d->trans_a ? 1 : 0;  // A stored [k, m]: m contiguous
     p->b_mn = d->trans_b ? 0 : 1;  // B stored [k, n]: n contiguous
     p->num_tiles = static_cast<int32_t>(pl.num_tiles);
+    p->batch_inner = static_cast<int32_t>(d->batch_inner);
+    p->inv_batch_inner = d->batch_inner > 0 ? 1.0f / static_cast<float>(d->batch_inner) : 0.0f;
     p->c = c; p->ldc = d->ldc; p->stride_c = d->batch > 1 ? d->stride_c : 0;
+    p->stride_c_outer = d->batch_inner > 0 ? d->stride_c_outer : 0;
     p->c_is_bf16 = d->dtype_c == LLMT_B200_BF16;
     p->alpha = d->alpha; p->beta = d->beta;
     p->bias = d->bias; p->bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
@@ -608,10 +645,11 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     if (pl.splits > 1) p->ws = static_cast<float*>(d->workspace);
     if (pl.dbias_mode == 1) p->ws_dbias = reinterpret_cast<float*>(static_cast<char*>(d->workspace) + pl.ws_dbias_off);
     if (d->k == 0) return LLMT_B200_OK;  // no operand is read
-    int st = encode_operand_map(&p->map_a, a, ck.a_rows, ck.a_cols, d->lda, d->batch, d->stride_a,
-                                p->a_mn ? 64 : 128);
+    int st = encode_operand_map(&p->map_a, a, ck.a_rows, ck.a_cols, d->lda,
+                                batch_layout(d->batch, d->batch_inner, d->stride_a, d->stride_a_outer), p->a_mn ? 64 : 128);
     if (st != LLMT_B200_OK) return st;
-    st = encode_operand_map(&p->map_b, b, ck.b_rows, ck.b_cols, d->ldb, d->batch, d->stride_b,
+    st = encode_operand_map(&p->map_b, b, ck.b_rows, ck.b_cols, d->ldb,
+                            batch_layout(d->batch, d->batch_inner, d->stride_b, d->stride_b_outer),
                             p->b_mn ? 64 : (pl.pairs ? pl.bn / 2 : pl.bn));
     if (st != LLMT_B200_OK) return st;
     // Results leave through shared memory and TMA stores (boxes of 32 rows x 128 bytes) when
@@ -619,8 +657,8 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     // otherwise straight from registers.
     if (pl.splits > 1) {
         if (d->n % 4 == 0) {
-            st = cached_map(&p->map_ws, d->workspace, 4, d->m, d->n, d->n, d->batch * pl.splits, d->m * d->n, 32, 32,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
+            st = cached_map(&p->map_ws, d->workspace, 4, d->m, d->n, d->n,
+                            batch_layout(d->batch * pl.splits, 0, d->m * d->n, 0), 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
             if (st != LLMT_B200_OK) return st;
             p->ws_tma = 1;
         }
@@ -628,8 +666,10 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     }
     const int ces = p->c_is_bf16 ? 2 : 4;
     if ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
-        (d->batch <= 1 || (d->stride_c * ces) % 16 == 0)) {
-        st = cached_map(&p->map_c, c, ces, d->m, d->n, d->ldc, d->batch, d->stride_c, p->c_is_bf16 ? 64 : 32, 32,
+        (d->batch <= 1 || (d->stride_c * ces) % 16 == 0) &&
+        (d->batch_inner <= 0 || (d->stride_c_outer * ces) % 16 == 0)) {
+        st = cached_map(&p->map_c, c, ces, d->m, d->n, d->ldc,
+                        batch_layout(d->batch, d->batch_inner, d->stride_c, d->stride_c_outer), p->c_is_bf16 ? 64 : 32, 32,
                         CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != LLMT_B200_OK) return st;
         p->c_tma = 1;
@@ -704,6 +744,9 @@ int run_bf16(const llmt_b200_gemm_desc* d, const Checked& ck, void* c, const voi
              cudaStream_t stream) {
     const TcPlan pl = plan_single(d);
     const Repack rp = repack_plan(d, ck, a, b);
+    if (rp.total() > 0 && d->batch_inner > 0)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: operands of a two-level batch layout must start on 16-byte "
+                    "boundaries with pitches and strides that are multiples of 8 elements");
     int st = check_workspace(d, pl, rp.total());
     if (st != LLMT_B200_OK) return st;
     llmt_b200_gemm_desc local = *d;
@@ -747,6 +790,8 @@ int run_fp32(const llmt_b200_gemm_desc* d, void* c, const void* a, const void* b
     p.stride_a = d->batch > 1 ? d->stride_a : 0;
     p.stride_b = d->batch > 1 ? d->stride_b : 0;
     p.stride_c = d->batch > 1 ? d->stride_c : 0;
+    p.batch_inner = d->batch_inner > 0 ? d->batch_inner : 0;
+    p.stride_a_outer = d->stride_a_outer; p.stride_b_outer = d->stride_b_outer; p.stride_c_outer = d->stride_c_outer;
     p.trans_a = d->trans_a; p.trans_b = d->trans_b;
     p.alpha = d->alpha; p.beta = d->beta;
     p.bias = d->bias; p.bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
@@ -874,6 +919,9 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
     for (int i = 0; i < count; ++i) {
         if (descs[i].m == 0 || descs[i].n == 0 || descs[i].batch == 0) continue;
         const Repack rp = repack_plan(&descs[i], ck[i], a[i], b[i]);
+        if (rp.total() > 0 && descs[i].batch_inner > 0)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "gemm_grouped: operands of a two-level batch layout must be "
+                        "addressable by TMA as they are");
         int st = check_workspace(&descs[i], plans[i], rp.total());
         if (st != LLMT_B200_OK) return st;
         llmt_b200_gemm_desc local = descs[i];

@@ -31,13 +31,14 @@ constexpr int kEpiGelu = 2;
 
 constexpr int kMaxGroupProblems = 8;
 
-// One GEMM of a group as the tensor-core kernel sees it.
-struct alignas(64) GroupProblem {
-    CUtensorMap map_a, map_b;   // operand loads (128B swizzle)
-    CUtensorMap map_c;          // C store: boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns)
-    CUtensorMap map_ws;         // split-K partial sums [batch*splits][m][n] fp32, same boxes
+// One GEMM of a group as the tensor-core kernel sees it: the scalars, which the kernel copies
+// into shared memory once (a problem is picked per tile at run time, and reading kernel
+// parameters through a run-time index is slow), and the tensor maps, which TMA reads in place.
+struct ProblemScalars {
     int64_t m, n, k;
     int32_t batch;
+    int32_t batch_inner;        // > 0: batch item b is item b % batch_inner of group b / batch_inner (two-level layout)
+    float inv_batch_inner;
     int32_t tiles_m, tiles_n, splits;
     float inv_tiles_m, inv_tiles_n, inv_splits;  // reciprocals, for the kernel's ticket decoding
     int32_t kblocks_total;      // ceil(k / 64)
@@ -54,6 +55,7 @@ struct alignas(64) GroupProblem {
     int32_t fin_tiles;          // finishing tickets: blocks of 256 values of i per CTA
     void* c;
     int64_t ldc, stride_c;
+    int64_t stride_c_outer;     // two-level layout: elements between groups of batch items of C
     int32_t c_is_bf16;
     int32_t c_tma;              // map_c is valid: tiles leave through shared memory + TMA store
     int32_t ws_tma;             // map_ws is valid
@@ -67,6 +69,13 @@ struct alignas(64) GroupProblem {
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
     float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums
+};
+static_assert(sizeof(ProblemScalars) % 8 == 0 && sizeof(ProblemScalars) <= 256, "ProblemScalars is copied to shared memory");
+
+struct alignas(64) GroupProblem : ProblemScalars {
+    CUtensorMap map_a, map_b;   // operand loads (128B swizzle)
+    CUtensorMap map_c;          // C store: boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+    CUtensorMap map_ws;         // split-K partial sums [batch*splits][m][n] fp32, same boxes
 };
 
 struct GroupParams {
@@ -133,6 +142,7 @@ struct Fp32GemmParams {
     float* c;
     int64_t lda, ldb, ldc;
     int64_t stride_a, stride_b, stride_c;
+    int64_t batch_inner, stride_a_outer, stride_b_outer, stride_c_outer;  // two-level batch layout (batch_inner 0 = plain)
     int32_t trans_a, trans_b;
     float alpha, beta;
     const void* bias;

@@ -24,9 +24,12 @@ fp32_gemm_kernel(const Fp32GemmParams p) {
     __shared__ float Bs[TK][TN + 4];
 
     const int64_t b = blockIdx.z;
-    const float* A = p.a + b * p.stride_a;
-    const float* B = p.b + b * p.stride_b;
-    float* C = p.c + b * p.stride_c;
+    // batch item b of a plain batch, or item (b % inner) of group (b / inner) of a two-level one
+    const int64_t bi = p.batch_inner > 0 ? b % p.batch_inner : b;
+    const int64_t bo = p.batch_inner > 0 ? b / p.batch_inner : 0;
+    const float* A = p.a + bi * p.stride_a + bo * p.stride_a_outer;
+    const float* B = p.b + bi * p.stride_b + bo * p.stride_b_outer;
+    float* C = p.c + bi * p.stride_c + bo * p.stride_c_outer;
     const int64_t m0 = static_cast<int64_t>(blockIdx.y) * TM;
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * TN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;

@@ -79,7 +79,8 @@ template <int CG> struct Geo {
     static constexpr int kStages = CG == 2 ? LLMT_B200_PAIR_STAGES : 4;
     static constexpr int kStoreBufs = CG == 2 ? LLMT_B200_PAIR_STORE_BUFS : 1;   // staging buffers per epilogue warp
     static constexpr uint32_t kStagingBytes = kEpilogueWarps * kStoreBufs * kStoreBufBytes;
-    static constexpr uint32_t kSmemBytes = 1024 /* control block + alignment */ + kStages * kStageBytes + kStagingBytes;
+    static constexpr uint32_t kScalarBytes = kMaxGroupProblems * static_cast<uint32_t>(sizeof(ProblemScalars));
+    static constexpr uint32_t kSmemBytes = 1024 /* control block + alignment */ + kStages * kStageBytes + kStagingBytes + kScalarBytes;
 };
 static_assert(Geo<1>::kSmemBytes <= 227 * 1024 && Geo<2>::kSmemBytes <= 227 * 1024, "shared-memory budget");
 constexpr uint32_t kBlock64Bytes = 64 * BK * 2;      // one 64-wide MN-major block
@@ -134,6 +135,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
 struct TileCoord {
     int prob;
     int m_tile, n_tile, split, batch;
+    int bz, bw;   // the batch item as (index inside its group, group): (batch, 0) for a plain batch
     int kb0, kb1;
 };
 
@@ -149,13 +151,13 @@ __device__ __forceinline__ uint32_t div_by(uint32_t n, uint32_t d, float inv_d) 
     return q;
 }
 
-__device__ __forceinline__ TileCoord decode_tile(const GroupParams& gp, int t) {
+__device__ __forceinline__ TileCoord decode_tile(const ProblemScalars* sp, int num_problems, int t) {
     TileCoord tc;
     int pi = 0;
 #pragma unroll 1
-    for (int i = 1; i < gp.num_problems; ++i)
-        if (t >= gp.prob[i].tile_begin) pi = i;
-    const GroupProblem& p = gp.prob[pi];
+    for (int i = 1; i < num_problems; ++i)
+        if (t >= sp[i].tile_begin) pi = i;
+    const ProblemScalars& p = sp[pi];
     tc.prob = pi;
     // The common cases (one split, one batch item) need one quotient only.
     const uint32_t r = static_cast<uint32_t>(t - p.tile_begin);
@@ -171,6 +173,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GroupParams& gp, int t) {
         const uint32_t q3 = div_by(q2, static_cast<uint32_t>(p.splits), p.inv_splits);
         tc.split = static_cast<int>(q2 - q3 * static_cast<uint32_t>(p.splits));
         tc.batch = static_cast<int>(q3);
+    }
+    tc.bz = tc.batch;
+    tc.bw = 0;
+    if (p.batch_inner > 0) {
+        tc.bw = static_cast<int>(div_by(static_cast<uint32_t>(tc.batch), static_cast<uint32_t>(p.batch_inner), p.inv_batch_inner));
+        tc.bz = tc.batch - tc.bw * p.batch_inner;
     }
     tc.kb0 = tc.split * p.kblocks_per_split;
     tc.kb1 = min(tc.kb0 + p.kblocks_per_split, p.kblocks_total);
@@ -237,7 +245,7 @@ __device__ __forceinline__ float lanes_sum(float v) {
 // column: warp `wid` of the `nw` warps that share the ticket takes the 256-column chunks wid,
 // wid + nw, ...; lane L sums columns c + 8 L .. + 7 of the chunk down the rows (sixteen rows in
 // flight) and leaves eight partial sums in row j of the workspace.
-__device__ __noinline__ void dbias_partial_warp(const GroupProblem& p, int j, int wid, int nw, int lane) {
+__device__ __noinline__ void dbias_partial_warp(const ProblemScalars& p, int j, int wid, int nw, int lane) {
     const int64_t r0 = static_cast<int64_t>(j) * p.dbias_rows;
     int64_t r1 = r0 + p.dbias_rows;
     if (r1 > p.k) r1 = p.k;
@@ -266,7 +274,7 @@ __device__ __noinline__ void dbias_partial_warp(const GroupProblem& p, int j, in
 
 // dbias, A stored [k, m], second phase: dbias[i] = dbias_beta * dbias[i] + sum_j partial[j][i],
 // j ascending, for the 32 values of i starting at i0 (one per lane).
-__device__ __noinline__ void dbias_finish_warp(const GroupProblem& p, int64_t i0, int lane) {
+__device__ __noinline__ void dbias_finish_warp(const ProblemScalars& p, int64_t i0, int lane) {
     const int64_t i = i0 + lane;
     if (i >= p.m) return;
     const float* src = p.ws_dbias + i;
@@ -287,7 +295,7 @@ __device__ __noinline__ void dbias_finish_warp(const GroupProblem& p, int64_t i0
 // dbias, A stored [m, k]: the sums run along rows, nothing to combine.  The warp takes rows
 // i0 and i0 + 1; lane L takes the 8 elements at 8 L, + 256, ... of a row; lane 0 also takes
 // the ragged end.
-__device__ __noinline__ void dbias_rows_warp(const GroupProblem& p, int64_t i0, int lane) {
+__device__ __noinline__ void dbias_rows_warp(const ProblemScalars& p, int64_t i0, int lane) {
     const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a_raw);
     const int64_t vec_end = p.k / 8 * 8;
 #pragma unroll 1
@@ -352,6 +360,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     Control* ctl = reinterpret_cast<Control*>(smem_raw);
     const uint32_t smem_base = (smem_u32(smem_raw) + static_cast<uint32_t>(sizeof(Control)) + 1023u) & ~1023u;
     const uint32_t staging_base = smem_base + kStages * kStageBytes;
+    // The problems' scalars, copied from the kernel parameters (see ProblemScalars).
+    ProblemScalars* sp = reinterpret_cast<ProblemScalars*>(smem_raw + (staging_base - smem_u32(smem_raw)) + Geo<CG>::kStagingBytes);
     volatile int* abort_flag = &ctl->abort_flag;
     DeviceStatus* status = gp.status;
 
@@ -373,6 +383,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         }
         ctl->abort_flag = 0;
         fence_barrier_init();
+    }
+    {
+        constexpr int kWords = static_cast<int>(sizeof(ProblemScalars) / 4);
+        for (int i = threadIdx.x; i < gp.num_problems * kWords; i += kThreads) {
+            const int pi = i / kWords, wi = i - pi * kWords;
+            reinterpret_cast<uint32_t*>(&sp[pi])[wi] =
+                reinterpret_cast<const uint32_t*>(static_cast<const ProblemScalars*>(&gp.prob[pi]))[wi];
+        }
     }
     if (warp == 1) {
         tmem_alloc_cg<CG>(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -482,8 +500,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             t = __shfl_sync(0xffffffffu, t, 0);
             if (!ok || t < 0) break;
             if (t < gp.colsum_total || t >= gp.fin_begin) continue;  // a dbias ticket: work for the epilogue warps only
-            const TileCoord tc = decode_tile(gp, t);
-            const GroupProblem& p = gp.prob[tc.prob];
+            const TileCoord tc = decode_tile(sp, gp.num_problems, t);
+            const ProblemScalars& p = sp[tc.prob];
+            const GroupProblem& pm = gp.prob[tc.prob];  // for the addresses of its tensor maps only
             const int bn = p.bn, a_mn = p.a_mn, b_mn = p.b_mn;
             const int bn_cta = bn / CG;                         // B columns this CTA stages
             const int m0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM;
@@ -497,12 +516,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             int my_x = 0, my_y = 0;
             bool k_is_x = false, k_is_y = false;
             if (lane < n_a) {
-                my_map = &p.map_a;
+                my_map = &pm.map_a;
                 if (a_mn) { my_off = lane * kBlock64Bytes; my_x = m0 + 64 * lane; k_is_y = true; }
                 else      { my_y = m0; k_is_x = true; }
             } else if (lane < n_a + n_b) {
                 const int j = lane - n_a;
-                my_map = &p.map_b;
+                my_map = &pm.map_b;
                 my_off = kATileBytes;
                 if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
@@ -523,8 +542,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         const int k0 = kb * BK;
                         const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
                         const int x = my_x + (k_is_x ? k0 : 0), y = my_y + (k_is_y ? k0 : 0);
-                        if (kPair) tma_load_3d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, tc.batch);
-                        else tma_load_3d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, tc.batch);
+                        if (kPair) tma_load_4d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, tc.bz, tc.bw);
+                        else tma_load_4d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, tc.bz, tc.bw);
                     }
                 }
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -553,8 +572,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 release_ring_slot(slot);
                 if (t < 0) break;
                 if (t < gp.colsum_total || t >= gp.fin_begin) continue;
-                const TileCoord tc = decode_tile(gp, t);
-                const GroupProblem& p = gp.prob[tc.prob];
+                const TileCoord tc = decode_tile(sp, gp.num_problems, t);
+                const ProblemScalars& p = sp[tc.prob];
                 const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn, p.a_mn, p.b_mn);
                 const uint32_t step_a = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
                 const uint32_t step_b = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
@@ -615,8 +634,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 int pi = 0;
 #pragma unroll 1
                 for (int i = 0; i < gp.num_problems; ++i)
-                    if (gp.prob[i].colsum_tiles > 0 && t >= gp.prob[i].colsum_begin) pi = i;
-                const GroupProblem& p = gp.prob[pi];
+                    if (sp[i].colsum_tiles > 0 && t >= sp[i].colsum_begin) pi = i;
+                const ProblemScalars& p = sp[pi];
                 const int r = t - p.colsum_begin;
                 if (p.dbias_mode == 1) {
                     dbias_partial_warp(p, r, static_cast<int>(rank) * kEpilogueWarps + ew, CG * kEpilogueWarps, lane);
@@ -639,12 +658,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 int pi = 0;
 #pragma unroll 1
                 for (int i = 0; i < gp.num_problems; ++i)
-                    if (gp.prob[i].fin_tiles > 0 && f >= gp.prob[i].fin_begin) pi = i;
-                const GroupProblem& p = gp.prob[pi];
+                    if (sp[i].fin_tiles > 0 && f >= sp[i].fin_begin) pi = i;
+                const ProblemScalars& p = sp[pi];
                 int expected = 0;
 #pragma unroll 1
                 for (int i = 0; i < gp.num_problems; ++i)
-                    if (gp.prob[i].dbias_mode == 1) expected += gp.prob[i].colsum_tiles;
+                    if (sp[i].dbias_mode == 1) expected += sp[i].colsum_tiles;
                 expected *= CG * kEpilogueWarps;
                 int ready = 1;
                 if (lane == 0) {
@@ -681,8 +700,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 }
                 continue;
             }
-            const TileCoord tc = decode_tile(gp, t);
-            const GroupProblem& p = gp.prob[tc.prob];
+            const TileCoord tc = decode_tile(sp, gp.num_problems, t);
+            const ProblemScalars& p = sp[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
             const int row0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM + quarter * 32;  // this warp's first row
             const int64_t row = static_cast<int64_t>(row0) + lane;
@@ -697,15 +716,18 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const int spu_shift = out_bf16 ? 1 : 0;
             const int spu = 1 << spu_shift;  // 32-column steps (one tcgen05.ld each) per unit
             const bool tma_ok = partial ? p.ws_tma != 0 : p.c_tma != 0;
-            const CUtensorMap* out_map = partial ? &p.map_ws : &p.map_c;
-            const int out_z = partial ? tc.batch * p.splits + tc.split : tc.batch;
+            const CUtensorMap* out_map = partial ? &gp.prob[tc.prob].map_ws : &gp.prob[tc.prob].map_c;
+            const int out_z = partial ? tc.batch * p.splits + tc.split : tc.bz;
+            const int out_w = partial ? 0 : tc.bw;
+            // Offset of this tile's batch item inside C, in elements.
+            const int64_t c_item_off = static_cast<int64_t>(tc.bz) * p.stride_c + static_cast<int64_t>(tc.bw) * p.stride_c_outer;
             // Column (inside the tile) of this warp's s-th step.
             auto step_col = [&](int s) { return ((half + 2 * (s >> spu_shift)) << unit_shift) + ((s & (spu - 1)) << 5); };
             int ns = (((p.bn >> unit_shift) + 1 - half) >> 1) << spu_shift;
             while (ns > 0 && n0 + step_col(ns - 1) >= p.n) --ns;
             if (row0 >= p.m) ns = 0;  // the whole warp lies below the matrix
             // Offset of this thread's row of the tile inside C, in elements.
-            const int64_t c_row_off = static_cast<int64_t>(tc.batch) * p.stride_c + row * p.ldc + n0;
+            const int64_t c_row_off = c_item_off + row * p.ldc + n0;
             if (p.beta != 0.0f && !partial && row_ok) {
                 // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
                 // lines now, while the tile's main loop is still running.
@@ -803,7 +825,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_3d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z);
+                        tma_store_4d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z, out_w);
                         bulk_commit_group();
                     }
                     ++buf_seq;
@@ -823,8 +845,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w)
                                  : "r"(buf + static_cast<uint32_t>(rr) * 128u + (word ^ ((static_cast<uint32_t>(rr) & 7u) << 4))));
                     if (out_bf16) {
-                        uint16_t* dst = static_cast<uint16_t*>(p.c) + static_cast<int64_t>(tc.batch) * p.stride_c +
-                                        grow * p.ldc + unit_col + 2 * lane;
+                        uint16_t* dst = static_cast<uint16_t*>(p.c) + c_item_off + grow * p.ldc + unit_col + 2 * lane;
                         if (2 * lane + 1 < unit_valid && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0u) {
                             *reinterpret_cast<uint32_t*>(dst) = w;
                         } else {
@@ -834,7 +855,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     } else if (lane < unit_valid) {
                         float* dst = partial
                             ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + grow) * p.n + unit_col + lane
-                            : static_cast<float*>(p.c) + static_cast<int64_t>(tc.batch) * p.stride_c + grow * p.ldc + unit_col + lane;
+                            : static_cast<float*>(p.c) + c_item_off + grow * p.ldc + unit_col + lane;
                         *dst = __uint_as_float(w);
                     }
                 }
@@ -924,7 +945,9 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
             for (int s = 0; s < p.splits; ++s)
                 for (int j = 0; j < cnt; ++j) acc[j] += src[s * sstride + j];
         }
-        const int64_t c_off = b * p.stride_c + row * p.ldc + col;
+        int64_t item_off = b * p.stride_c;
+        if (p.batch_inner > 0) item_off = (b % p.batch_inner) * p.stride_c + (b / p.batch_inner) * p.stride_c_outer;
+        const int64_t c_off = item_off + row * p.ldc + col;
         for (int j = 0; j < cnt; ++j) {
             float v = p.alpha * acc[j];
             if (p.beta != 0.0f)

@@ -92,6 +92,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// The same with four coordinates (innermost, row, batch item inside its group, group): the
+// maps of the GEMM operands are 4-D so that a batch may be laid out on two levels, e.g. the heads
+// of an attention layer interleaved inside token rows.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int32_t x,
+                                            int32_t y, int32_t z, int32_t w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src_smem, int32_t x, int32_t y,
+                                             int32_t z, int32_t w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
 // 3-D tiled store from this CTA's shared memory to global (bulk async-group
 // completion).  Elements of the box that fall outside the tensor are not written.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src_smem, int32_t x,
@@ -244,6 +263,15 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const CUtens
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst_smem, const CUtensorMap* map, uint32_t leader_bar,
+                                                 int32_t x, int32_t y, int32_t z, int32_t w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
 

@@ -188,6 +188,34 @@ void test_attention(Device& dev, const RunCtx& ctx) {
     check_close(yh, load("attention", "out"), "attention_fwd y_heads");
 }
 
+// The attention golden case through the packed path: qkv [B,T,3A] assembled on the host from the
+// golden q, k, v (the inverse of llmt's head split), then S/P/O with the split and the merge
+// folded into the GEMMs' strides; pinned by probs.bin and merged.bin
+// (llmt tests/unit/test_attention.cu:58-99).
+void test_attention_packed(Device& dev, const RunCtx& ctx) {
+    Arena arena(1 << 20, "attn-packed");
+    const HostTensor q = load("attention", "q"), k = load("attention", "k"), v = load("attention", "v");
+    const int64_t B = 2, H = 2, T = 4, hd = 6, A = H * hd;
+    HostTensor packed;
+    packed.shape = Shape{B, T, 3 * A};
+    packed.v.assign(static_cast<size_t>(B * T * 3 * A), 0.0f);
+    const HostTensor* parts[3] = {&q, &k, &v};
+    for (int64_t b = 0; b < B; ++b)
+        for (int64_t h = 0; h < H; ++h)
+            for (int64_t t = 0; t < T; ++t)
+                for (int64_t d = 0; d < hd; ++d)
+                    for (int part = 0; part < 3; ++part)
+                        packed.v[static_cast<size_t>((b * T + t) * 3 * A + part * A + h * hd + d)] =
+                            parts[part]->v[static_cast<size_t>(((b * H + h) * T + t) * hd + d)];
+    const Tensor qkv = upload(arena, packed, dev.stream());
+    Tensor scores = arena.alloc({B, H, T, T}, DType::FP32);
+    Tensor y = arena.alloc({B, T, A}, DType::FP32);
+    kernels::attention_fwd_packed(ctx, y, scores, qkv, H, kernels::MaskSpec{kernels::MaskKind::Causal});
+    dev.synchronize();
+    check_close(scores, load("attention", "probs"), "attention_fwd_packed leaves probs in scores");
+    check_close(y, load("attention", "merged"), "attention_fwd_packed merged output");
+}
+
 // llmt tests/unit/test_attention.cu:23-43: head split and merge against the `permute` case.
 void test_permute(Device& dev) {
     Arena arena(1 << 20, "perm-test");
@@ -312,6 +340,7 @@ int main(int argc, char** argv) {
     test_mlp(dev, ctx);
     test_attention(dev, ctx);
     test_permute(dev);
+    test_attention_packed(dev, ctx);
     test_bf16_linear(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());

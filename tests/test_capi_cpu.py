@@ -29,12 +29,13 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(set(declared_symbols())) == sorted(set(L.EXPORTS) | set(declared_symbols()))
-    assert lib.llmt_b200_abi_version() == 2
+    assert lib.llmt_b200_abi_version() == 3
 
 
 def test_descriptor_layout_matches_the_header():
     # field order and sizes of struct llmt_b200_gemm_desc as the C compiler lays them out
-    assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8
+    assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8 + 4 * 8
+    assert L.GemmDesc.batch_inner.offset == L.GemmDesc.workspace_bytes.offset + 8
     assert L.GemmDesc.plan_cta_pairs.offset == L.GemmDesc.plan_splits.offset + 4
     assert L.GemmDesc.workspace.offset % 8 == 0
 
@@ -146,6 +147,25 @@ def test_forced_pairs_are_refused_in_a_launch_that_cannot_pair():
     small = _desc()
     assert _grouped([wide, small], [0x1000000, 0x2000000], [A, A], [B, B]) == L.ERR_INVALID
     assert "asks for CTA pairs" in L.last_error()
+
+
+def test_two_level_batch_layout_contract():
+    # the per-head products of attention on the packed QKV buffer: B = 2, H = 3, T = 128, hd = 64
+    H, T, hd, B = 3, 128, 64, 2
+    A3 = 3 * H * hd
+    d = _desc(m=T, n=T, k=hd, batch=B * H, batch_inner=H, lda=A3, ldb=A3, ldc=T, trans_b=1,
+              stride_a=hd, stride_b=hd, stride_c=T * T, stride_a_outer=T * A3, stride_b_outer=T * A3,
+              stride_c_outer=H * T * T, dtype_c=L.BF16)
+    qkv, scores = 0x1000000, 0x3000000
+    # (strides between heads smaller than a matrix are what this layout is for; the valid case runs
+    # in the GPU tests - nothing here may reach a launch)
+    assert L.plan(d).startswith("tcgen05")
+    bad = _desc(m=T, n=T, k=hd, batch=B * H, batch_inner=4, lda=A3, ldb=A3, ldc=T, trans_b=1)
+    assert _call(bad, c=scores, a=qkv, b=qkv + 2 * H * hd) == L.ERR_INVALID and "batch_inner" in L.last_error()
+    odd = _desc(m=T, n=T, k=hd, batch=B * H, batch_inner=H, lda=A3, ldb=A3, ldc=T, trans_b=1,
+                stride_a=hd + 1, stride_b=hd, stride_c=T * T, stride_a_outer=T * A3, stride_b_outer=T * A3,
+                stride_c_outer=H * T * T)
+    assert _call(odd, c=scores, a=qkv, b=qkv + 2 * H * hd) == L.ERR_UNSUPPORTED and "two-level" in L.last_error()
 
 
 def test_empty_output_is_a_no_op():

@@ -223,3 +223,65 @@ def test_head_split_and_merge_at_model_size_vectorised():
     y = torch.empty(B, T, H * hd, device=DEV, dtype=torch.bfloat16)
     L.head_merge(y, q)
     assert torch.equal(y, q.permute(0, 2, 1, 3).reshape(B, T, H * hd))
+
+
+def _packed_desc(c, a, b, m, n, k, batch, inner, ld, st, st_outer, trans_b, alpha=1.0):
+    """Descriptor of a batch laid out on two levels: (lda, ldb, ldc), (stride_a, stride_b, stride_c) and
+    (stride_a_outer, ...) in elements; c, a, b are the tensors that own the memory."""
+    d = L.GemmDesc()
+    d.m, d.n, d.k, d.batch, d.batch_inner = m, n, k, batch, inner
+    d.lda, d.ldb, d.ldc = ld
+    d.stride_a, d.stride_b, d.stride_c = st
+    d.stride_a_outer, d.stride_b_outer, d.stride_c_outer = st_outer
+    d.trans_a, d.trans_b = 0, int(trans_b)
+    d.dtype_ab, d.dtype_c = L._dtype_code(a), L._dtype_code(c)
+    d.alpha, d.beta = alpha, 0.0
+    return d
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_attention_products_on_the_packed_qkv_layout(dt):
+    """S = Q K^T / sqrt(hd) and O = P V with Q, K, V read straight out of the [B, T, 3*H*hd] output of the
+    QKV projection and O written straight into [B, T, H*hd] token rows (batch_inner / stride_*_outer):
+    the same bits as head split -> per-head products -> head merge."""
+    import ctypes
+    B, H, T, hd = (2, 12, 256, 64) if dt == torch.bfloat16 else (2, 3, 40, 8)
+    A = H * hd
+    g = torch.Generator(device=DEV).manual_seed(21)
+    qkv = torch.randn(B, T, 3 * A, device=DEV, generator=g).to(dt)
+    alpha = 1.0 / float(np.sqrt(hd))
+    # reference route: explicit split, batched products on contiguous [B*H, T, hd] tensors, explicit merge
+    q, k, v = (torch.empty(B, H, T, hd, device=DEV, dtype=dt) for _ in range(3))
+    L.head_split(q, k, v, qkv)
+    s_ref = torch.empty(B * H, T, T, device=DEV, dtype=dt)
+    L.gemm(s_ref, q.view(B * H, T, hd), k.view(B * H, T, hd), False, True, alpha=alpha)
+    L.softmax_fwd(s_ref, s_ref, causal=True)
+    o_heads = torch.empty(B * H, T, hd, device=DEV, dtype=dt)
+    L.gemm(o_heads, s_ref, v.view(B * H, T, hd), False, False)
+    y_ref = torch.empty(B, T, A, device=DEV, dtype=dt)
+    L.head_merge(y_ref, o_heads.view(B, H, T, hd))
+    # packed route
+    es = qkv.element_size()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    scores = torch.empty(B, H, T, T, device=DEV, dtype=dt)
+    d = _packed_desc(scores, qkv, qkv, T, T, hd, B * H, H, (3 * A, 3 * A, T), (hd, hd, T * T),
+                     (T * 3 * A, T * 3 * A, H * T * T), True, alpha)
+    st = L.lib().llmt_b200_gemm(ctypes.byref(d), scores.data_ptr(), qkv.data_ptr(), qkv.data_ptr() + A * es, stream)
+    assert st == L.OK, L.last_error()
+    L.softmax_fwd(scores.view(B * H, T, T), scores.view(B * H, T, T), causal=True)
+    y = torch.full((B, T, A), 7.0, device=DEV, dtype=dt)
+    d2 = _packed_desc(y, scores, qkv, T, hd, T, B * H, H, (T, 3 * A, A), (T * T, hd, hd),
+                      (H * T * T, T * 3 * A, T * A), False)
+    st = L.lib().llmt_b200_gemm(ctypes.byref(d2), y.data_ptr(), scores.data_ptr(), qkv.data_ptr() + 2 * A * es, stream)
+    assert st == L.OK, L.last_error()
+    assert torch.equal(scores.view(B * H, T, T), s_ref)
+    assert torch.equal(y, y_ref)
+    # and against the oracle, one (batch, head) item
+    b_, h_ = 1, H - 1
+    qh, kh, vh = (qkv[b_, :, part * A + h_ * hd: part * A + (h_ + 1) * hd].float().cpu().numpy() for part in range(3))
+    p_ref = oracle.softmax(oracle.gemm(oracle.round_bf16(qh) if dt == torch.bfloat16 else qh, kh, False, True, alpha)[None],
+                           causal=True)[0]
+    tol = 4e-3 if dt == torch.bfloat16 else 1e-5
+    assert oracle.rel_fro(scores[b_, h_].float().cpu().numpy(), p_ref) <= 2 * tol
+    o_ref = oracle.gemm(scores[b_, h_].float().cpu().numpy(), vh)
+    assert oracle.rel_fro(y[b_, :, h_ * hd:(h_ + 1) * hd].float().cpu().numpy(), o_ref) <= tol
