@@ -191,7 +191,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 __device__ __forceinline__ void load_chunk_f32(const float* src, float* dst, int valid) {
-    if (valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u) {
+    if (__builtin_expect(valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u, 1)) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
             const float4 t = *reinterpret_cast<const float4*>(src + j);
@@ -204,7 +204,7 @@ __device__ __forceinline__ void load_chunk_f32(const float* src, float* dst, int
 }
 
 __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float* dst, int valid) {
-    if (valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u) {
+    if (__builtin_expect(valid >= 32 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u, 1)) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
             const uint4 u = *reinterpret_cast<const uint4*>(src + j);
@@ -778,13 +778,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cin[j], v[j]);
                     }
                     if (p.epi_flags & kEpiBias) {
-                        float bv[32];
-                        if (p.bias_is_bf16)
-                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.bias) + col, bv, valid);
-                        else
-                            load_chunk_f32(static_cast<const float*>(p.bias) + col, bv, valid);
+                        // every row of the step needs the same 32 bias values: lane j fetches the
+                        // j-th, the warp passes them round
+                        float mine = 0.0f;
+                        if (lane < valid)
+                            mine = p.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + lane])
+                                                  : static_cast<const float*>(p.bias)[col + lane];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] += bv[j];
+                        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
                     }
                     if (p.epi_flags & kEpiGelu) {
 #pragma unroll
@@ -837,7 +838,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 __syncwarp();
                 const int unit_valid = static_cast<int>(min(static_cast<int64_t>(unit_cols), p.n - unit_col));
                 const uint32_t word = ((static_cast<uint32_t>(lane) >> 2) << 4) | ((static_cast<uint32_t>(lane) & 3u) << 2);
-#pragma unroll 4
+#pragma unroll 1
                 for (int rr = 0; rr < 32; ++rr) {
                     const int64_t grow = static_cast<int64_t>(row0) + rr;
                     if (grow >= p.m) break;
@@ -862,26 +863,23 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 __syncwarp();  // the buffer may be rewritten once every lane has read its words
             };
             // Software pipeline over the steps: the tcgen05.ld of step s+1 is in flight while
-            // step s is converted and staged.
+            // step s is converted and staged.  One instance of the step's code (it is long, and the
+            // instruction cache is shared with the other roles): the prefetched values are moved
+            // into `cur` after their wait.
             if (ns == 0) {
                 release_acc();
             } else {
-                uint32_t ra[32], rb[32];
-                tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(0)), ra);
+                uint32_t cur[32], nxt[32];
+                tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(0)), nxt);
 #pragma unroll 1
-                for (int s = 0; s < ns; s += 2) {
+                for (int s = 0; s < ns; ++s) {
                     tmem_ld_wait();
-                    after_tmem_ld_wait(ra);
-                    if (s + 1 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 1)), rb);
+                    after_tmem_ld_wait(nxt);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
+                    if (s + 1 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 1)), nxt);
                     else release_acc();
-                    emit(ra, s);
-                    if (s + 1 < ns) {
-                        tmem_ld_wait();
-                        after_tmem_ld_wait(rb);
-                        if (s + 2 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 2)), ra);
-                        else release_acc();
-                        emit(rb, s + 1);
-                    }
+                    emit(cur, s);
                 }
             }
             ++acc_seq;
