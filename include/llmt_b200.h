@@ -75,7 +75,7 @@ enum llmt_b200_status {
  *                are read in place; others (a contiguous [tokens, 50257] matrix, a slice
  *                x[:, 1:]) are first copied to such a layout inside the workspace (one extra
  *                pass over that operand; llmt_b200_gemm_workspace_bytes_for counts it).
- *                m, n, k and batch must be below 2^31.
+ *                m, n, k and batch must be below 2^31 - 1024.
  *   stride_*     elements between consecutive batch items; ignored when batch == 1.
  *   dtype_ab     element type of A and B; dtype_c of C.  Supported pairs:
  *                (fp32, fp32) strict fp32 FMA path; (bf16, bf16) and (bf16, fp32)

@@ -12,40 +12,49 @@ namespace llmt::kernels {
 
 namespace {
 
+// The last two dimensions of a rank-2/3 tensor as a matrix, plus how many of them there are.
+struct MatrixView {
+    int64_t rows, cols, items, item_stride;
+    static MatrixView of(const Tensor& t) noexcept {
+        const int last = t.shape.rank - 1;
+        MatrixView v{t.shape[last - 1], t.shape[last], 1, 0};
+        if (t.shape.rank == 3) {
+            v.items = t.shape[0];
+            v.item_stride = v.rows * v.cols;
+        }
+        return v;
+    }
+    // op(X): the same storage read as its transpose
+    MatrixView op(bool transposed) const noexcept {
+        return transposed ? MatrixView{cols, rows, items, item_stride} : *this;
+    }
+};
+
 struct Problem {
     int64_t m, n, k, batch, stride_a, stride_b, stride_c;
 };
 
+bool supported(DType t) noexcept { return t == DType::FP32 || t == DType::BF16; }
+
+// The checks llmt makes, in llmt's order and with llmt's messages, so that a caller that trips
+// one sees the same abort.
 Problem check(const Tensor& c, const Tensor& a, const Tensor& b, bool trans_a, bool trans_b) noexcept {
     const int rank = c.shape.rank;
     if (rank != 2 && rank != 3) detail::fatal("matmul", "expected rank-2 or rank-3 tensors (got %d)", rank);
     if (a.shape.rank != rank || b.shape.rank != rank) detail::fatal("matmul", "mixed ranks in one matmul");
     if (a.dtype != b.dtype) detail::fatal("matmul", "mixed dtypes in one matmul");
     if (!c.valid() || !a.valid() || !b.valid()) detail::fatal("matmul", "invalid tensor (null data)");
-    if (a.dtype != DType::FP32 && a.dtype != DType::BF16)
-        detail::fatal("matmul", "dtype %s not yet supported", dtype_name(a.dtype));
+    if (!supported(a.dtype)) detail::fatal("matmul", "dtype %s not yet supported", dtype_name(a.dtype));
     if (a.dtype == DType::FP32 && c.dtype != DType::FP32) detail::fatal("matmul", "mixed dtypes in one matmul");
-    if (c.dtype != DType::FP32 && c.dtype != DType::BF16)
-        detail::fatal("matmul", "dtype %s not yet supported", dtype_name(c.dtype));
-    const int r = rank - 2;
-    Problem p{};
-    p.m = trans_a ? a.shape[r + 1] : a.shape[r];
-    p.k = trans_a ? a.shape[r] : a.shape[r + 1];
-    const int64_t kb = trans_b ? b.shape[r + 1] : b.shape[r];
-    p.n = trans_b ? b.shape[r] : b.shape[r + 1];
-    if (p.k != kb)
-        detail::fatal("matmul", "inner dims disagree: %lld vs %lld", static_cast<long long>(p.k),
-                      static_cast<long long>(kb));
-    if (c.shape[r] != p.m || c.shape[r + 1] != p.n) detail::fatal("matmul", "C shape mismatch");
-    p.batch = 1;
-    if (rank == 3) {
-        p.batch = a.shape[0];
-        if (b.shape[0] != p.batch || c.shape[0] != p.batch) detail::fatal("matmul", "batch sizes disagree");
-        p.stride_a = a.shape[1] * a.shape[2];
-        p.stride_b = b.shape[1] * b.shape[2];
-        p.stride_c = c.shape[1] * c.shape[2];
-    }
-    return p;
+    if (!supported(c.dtype)) detail::fatal("matmul", "dtype %s not yet supported", dtype_name(c.dtype));
+    const MatrixView va = MatrixView::of(a), vb = MatrixView::of(b), vc = MatrixView::of(c);
+    const MatrixView oa = va.op(trans_a), ob = vb.op(trans_b);  // [m, k] and [k, n]
+    if (oa.cols != ob.rows)
+        detail::fatal("matmul", "inner dims disagree: %lld vs %lld", static_cast<long long>(oa.cols),
+                      static_cast<long long>(ob.rows));
+    if (vc.rows != oa.rows || vc.cols != ob.cols) detail::fatal("matmul", "C shape mismatch");
+    if (vb.items != va.items || vc.items != va.items) detail::fatal("matmul", "batch sizes disagree");
+    return Problem{oa.rows, ob.cols, oa.cols, va.items, va.item_stride, vb.item_stride, vc.item_stride};
 }
 
 // The precision policy must name the arithmetic the operand dtype implies

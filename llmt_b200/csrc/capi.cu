@@ -296,10 +296,10 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
         return fail(LLMT_B200_ERR_INVALID, "matmul: invalid tensor (null data)");
     if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: negative dimension");
-    // Tile counts and TMA coordinates are 32-bit.
-    constexpr int64_t kMaxDim = 0x7fffffff;
+    // Tile counts and TMA coordinates are 32-bit, and a coordinate may point up to a tile past the end.
+    constexpr int64_t kMaxDim = 0x7fffffff - 1024;
     if (d->m > kMaxDim || d->n > kMaxDim || d->k > kMaxDim || d->batch > kMaxDim)
-        return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dimension above 2^31 - 1");
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dimension above 2^31 - 1025");
     if (d->dtype_ab != LLMT_B200_FP32 && d->dtype_ab != LLMT_B200_BF16)
         return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: dtype code %d not supported", d->dtype_ab);
     if (d->dtype_c != LLMT_B200_FP32 && d->dtype_c != LLMT_B200_BF16)

@@ -173,6 +173,22 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
     return v * r;
 }
 
+// The same function with the hardware tanh: five FP32 operations and ONE special-function
+// operation per element.  tanh.approx is good to 2^-11 relative, so the result carries an
+// absolute error of up to 0.5 |v| 2^-11 (2.4e-4 |v|): below the rounding of a bf16 result
+// (2^-9 relative) wherever |gelu(v)| > |v| / 8, and at most one bf16 unit of the largest
+// negative values (-0.17) on the tail v < -1, where gelu(v) itself tends to zero.  For bf16
+// results only.
+__device__ __forceinline__ float gelu_tanh_hw(float v) {
+    const float k0 = 0.7978845608028654f;  // sqrt(2/pi)
+    const float k1 = k0 * 0.044715f;
+    const float u = v * fmaf(k1, v * v, k0);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    const float h = 0.5f * v;
+    return fmaf(h, t, h);
+}
+
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
 cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream);
 int max_resident_pairs(void);

@@ -3,11 +3,12 @@
 // memory, operands staged in 128-byte-swizzled shared memory by TMA, results
 // leaving through swizzled shared-memory buffers and TMA stores.
 //
-// One CTA per SM, 352 threads, warp-specialised:
+// One CTA per SM, 384 threads, warp-specialised:
 //   warp 0      scheduler + TMA producer: draws the next ticket from a global counter,
 //               publishes it to the other roles through a small ring in shared memory,
 //               then streams the even k-blocks of that tile's operands
-//   warp 10     second TMA producer (the odd k-blocks; CTA pairs only)
+//   warps 10-11 helper TMA producers (CTA pairs only): the three producer warps take the
+//               k-blocks round robin
 //   warp 1      MMA issuer (one lane issues tcgen05.mma / tcgen05.commit; the warp
 //               owns the TMEM allocation)
 //   warps 2-9   epilogue: tcgen05.ld, alpha/beta/bias/GELU/cast, store C.  Two warps per
@@ -54,9 +55,10 @@ namespace {
 constexpr int BM = 128;  // UMMA M (cta_group::1)
 constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 352;
+constexpr int kThreads = 384;
 constexpr int kEpilogueWarps = 8;
-constexpr int kProducerHelperWarp = 10;  // second TMA producer warp
+constexpr int kProducerHelperWarp = 10;  // first of the helper TMA producer warps (CTA pairs only)
+constexpr int kProducerHelpers = 2;
 constexpr int kMaxStages = 6;
 constexpr int kRing = 4;                             // scheduler ring entries
 constexpr uint32_t kATileBytes = BM * BK * 2;        // 16 KB
@@ -274,22 +276,26 @@ __device__ __noinline__ void dbias_partial_warp(const ProblemScalars& p, int j, 
 
 // dbias, A stored [k, m], second phase: dbias[i] = dbias_beta * dbias[i] + sum_j partial[j][i],
 // j ascending, for the 32 values of i starting at i0 (one per lane).
-__device__ __noinline__ void dbias_finish_warp(const ProblemScalars& p, int64_t i0, int lane) {
-    const int64_t i = i0 + lane;
-    if (i >= p.m) return;
+// One value: partial sums j = 0 .. colsum_tiles-1 in that order, many loads in flight (the
+// loop is a chain of L2 round trips otherwise).
+__device__ __forceinline__ void dbias_finish_one(const ProblemScalars& p, int64_t i) {
     const float* src = p.ws_dbias + i;
     float acc = 0.0f;
     int j = 0;
-    for (; j + 8 <= p.colsum_tiles; j += 8) {
-        float v[8];
+    for (; j + 16 <= p.colsum_tiles; j += 16) {
+        float v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + static_cast<int64_t>(j + u) * p.m);  // written by other SMs: read from L2
+        for (int u = 0; u < 16; ++u) v[u] = __ldcg(src + static_cast<int64_t>(j + u) * p.m);  // written by other SMs: read from L2
 #pragma unroll
-        for (int u = 0; u < 8; ++u) acc += v[u];
+        for (int u = 0; u < 16; ++u) acc += v[u];
     }
     for (; j < p.colsum_tiles; ++j) acc += __ldcg(src + static_cast<int64_t>(j) * p.m);
     const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
     p.dbias[i] = prev + acc;
+}
+__device__ __noinline__ void dbias_finish_warp(const ProblemScalars& p, int64_t i0, int lane) {
+    const int64_t i = i0 + lane;
+    if (i < p.m) dbias_finish_one(p, i);
 }
 
 // dbias, A stored [m, k]: the sums run along rows, nothing to combine.  The warp takes rows
@@ -379,7 +385,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         }
         for (int r = 0; r < kRing; ++r) {
             mbar_init(smem_u32(&ctl->sched_full[r]), 1);
-            mbar_init(smem_u32(&ctl->sched_empty[r]), kPair ? 2 * (2 + kEpilogueWarps) : 1 + kEpilogueWarps);  // every ring reader
+            mbar_init(smem_u32(&ctl->sched_empty[r]), kPair ? 2 * (1 + kProducerHelpers + kEpilogueWarps) : 1 + kEpilogueWarps);  // every ring reader
         }
         ctl->abort_flag = 0;
         fence_barrier_init();
@@ -429,20 +435,24 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         else mbar_arrive(smem_u32(&ctl->sched_empty[slot]));
     };
 
-    if (warp == 0 || (kPair && warp == kProducerHelperWarp)) {
+    if (warp == 0 || (kPair && warp >= kProducerHelperWarp)) {
         // ------------------------------------------- scheduler + TMA producers
-        // Two producer warps share the k-blocks (even ones to warp 0, odd ones to the helper
-        // warp): one iteration costs a few hundred cycles of barrier and issue latency, which
-        // a single warp cannot hide and which would otherwise cap how far loads run ahead.
-        // In each the whole warp walks the loop; lane 0 does the barrier bookkeeping and
+        // Three producer warps take the k-blocks round robin.  The operand pipeline is bound by
+        // bytes in flight (six stages against a load latency of about six k-block times), so a
+        // load that is issued late is a bubble in the tensor pipe later: a producer must be
+        // waiting at a stage's barrier when the stage frees, and the work between two tiles
+        // (reading the ticket, decoding it: ~1000 cycles) must fit into the time until that warp's
+        // next k-block is due.  With two warps it did not (measured: the first load of a tile left
+        // ~1500 cycles after its stage was free).  In each warp the whole warp walks the loop; lane 0 does the barrier bookkeeping and
         // lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
         // (MN-major operands come in 64-wide blocks) leave in one issue slot.  Warp 0 of the
         // leader also runs the scheduler.
         const bool scheduler = warp == 0 && leader;
         // A single CTA streams 48 KB per k-block and is bound by that, not by issue latency:
         // there the helper stays idle and warp 0 takes every k-block.
-        const uint32_t my_parity = warp == 0 ? 0u : 1u;
-        const uint32_t parity_mask = kPair ? 1u : 0u;
+        const int n_turns = kPair ? 1 + kProducerHelpers : 1;
+        const int my_turn = warp == 0 ? 0 : warp - kProducerHelperWarp + 1;
+        int turn = 0;      // whose k-block `seq` is: producers take them round robin, across tiles
         uint32_t seq = 0;  // k-blocks streamed so far by this CTA; k-block `seq` uses stage seq % kStages
         int stage = 0;
         uint32_t phase = 0;
@@ -459,31 +469,50 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         constexpr int kDrawAhead = 6;   // k-blocks before the end of a tile at which the next ticket is drawn
         constexpr int kNotDrawn = -2;
         int next_ticket = kNotDrawn;
+        // The other producer warps (this CTA's helper, both of the peer's) can stream a tile only
+        // once they have read its ticket from the ring, and the operand pipeline has no slack to
+        // absorb a late one (a stage is refilled about as fast as it is consumed): publishing a
+        // ticket one ticket-decode later than possible measured 5 % slower on the GPT-2 GEMMs.  So
+        // on long tiles the drawn ticket is published a few k-blocks before the current tile's
+        // last loads, as soon as its ring slot is free; otherwise at the top of the next iteration.
+        constexpr int kPublishAhead = 3;     // k-blocks before the end of a tile
+        constexpr int kMinEarlyKblocks = 8;  // shorter tiles publish at the top (the draw has not returned yet)
+        bool early = false;                  // the next iteration's ticket is already in the ring
+        int early_t = -1;
+        // Ring entry `slot` <- ticket `raw` (out-of-range: the end marker).  Returns what was published.
+        auto publish = [&](int slot, int raw) {
+            int t = raw;
+            prev_ticket = raw;
+            if (t >= gp.total_tiles) {
+                // Every drawer takes exactly one out-of-range ticket; the last re-arms the counter.
+                if (dynamic && t == gp.total_tiles + n_sched - 1) *gp.sched_counter = 0;
+                t = -1;
+            }
+            ctl->ring[slot] = t;
+            mbar_arrive(smem_u32(&ctl->sched_full[slot]));
+            // The peer's copy travels as an async store that completes its barrier.
+            if (kPair)
+                st_async_cluster_u32(mapa_shared(smem_u32(&ctl->ring[slot]), 1u), static_cast<uint32_t>(t),
+                                     mapa_shared(smem_u32(&ctl->sched_full[slot]), 1u));
+            return t;
+        };
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
             int t = -1;
             if (lane == 0) {
-                if (scheduler) {
+                if (scheduler && early) {
+                    t = early_t;
+                    early = false;
+                } else if (scheduler) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
                                              kDevWaitSched, slot, wait_ns);
                     if (ok) {
-                        t = it == 0 ? first_ticket
-                                    : !dynamic ? prev_ticket + n_sched
-                                    : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1);
+                        const int raw = it == 0 ? first_ticket
+                                      : !dynamic ? prev_ticket + n_sched
+                                      : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1);
                         next_ticket = kNotDrawn;
-                        prev_ticket = t;
-                        if (t >= gp.total_tiles) {
-                            // Every drawer takes exactly one out-of-range ticket; the last re-arms the counter.
-                            if (dynamic && t == gp.total_tiles + n_sched - 1) *gp.sched_counter = 0;
-                            t = -1;
-                        }
-                        ctl->ring[slot] = t;
-                        mbar_arrive(smem_u32(&ctl->sched_full[slot]));
-                        // The peer's copy travels as an async store that completes its barrier.
-                        if (kPair)
-                            st_async_cluster_u32(mapa_shared(smem_u32(&ctl->ring[slot]), 1u), static_cast<uint32_t>(t),
-                                                 mapa_shared(smem_u32(&ctl->sched_full[slot]), 1u));
+                        t = publish(slot, raw);
                     }
                 } else {
                     // In the peer CTA warp 0 arms the ring barrier for the leader's 4-byte store.
@@ -527,17 +556,30 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 else      { my_y = n0; k_is_x = true; }
             }
             const int draw_kb = tc.kb1 - kDrawAhead > tc.kb0 ? tc.kb1 - kDrawAhead : tc.kb0;
+            const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : -1;
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
-                if (scheduler && dynamic && lane == 0 && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
-                if ((seq & parity_mask) == my_parity) {
-                    if (lane == 0) {
+                if (scheduler && lane == 0) {
+                    if (dynamic && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
+                    if (kb == publish_kb) {
+                        const int nslot = (it + 1) % kRing;
+                        const uint32_t nphase = static_cast<uint32_t>((it + 1) / kRing) & 1u;
+                        // one poll: a ring that is still full is waited for at the top, as before
+                        if (mbar_try_wait(smem_u32(&ctl->sched_empty[nslot]), nphase ^ 1u)) {
+                            early_t = publish(nslot, dynamic ? next_ticket : prev_ticket + n_sched);
+                            next_ticket = kNotDrawn;
+                            early = true;
+                        }
+                    }
+                }
+                if (turn == my_turn) {
+                    if (lane == 0)
                         ok = bounded_wait<kPair>(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, status,
                                                  kDevWaitSmemEmpty, stage, wait_ns);
-                        // The leader's barrier counts the bytes of both CTAs of a pair.
-                        if (ok && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
-                    }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (!ok) break;
+                    // The leader's barrier counts the bytes of both CTAs of a pair.  Bytes that land
+                    // before this arrival are counted all the same; the phase cannot complete without it.
+                    if (lane == 0 && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
                     if (my_map != nullptr) {
                         const int k0 = kb * BK;
                         const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
@@ -546,6 +588,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         else tma_load_4d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, tc.bz, tc.bw);
                     }
                 }
+                if (++turn == n_turns) turn = 0;
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -703,10 +746,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const TileCoord tc = decode_tile(sp, gp.num_problems, t);
             const ProblemScalars& p = sp[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
+            // Everything a step needs is read from the problem's scalars ONCE per tile, into
+            // registers: a step is a chain of dependent instructions executed by a warp that has
+            // one other warp to share its scheduler with, so every shared-memory read and every
+            // branch inside it costs its full latency, four times per tile.
+            const int pm = p.m, pn = p.n;
             const int row0 = tc.m_tile * kTileRows + static_cast<int>(rank) * BM + quarter * 32;  // this warp's first row
-            const int64_t row = static_cast<int64_t>(row0) + lane;
-            const bool row_ok = row < p.m;
-            const int64_t n0 = static_cast<int64_t>(tc.n_tile) * p.bn;
+            const bool row_ok = row0 + lane < pm;
+            const int n0 = tc.n_tile * p.bn;
             const bool partial = p.splits > 1;
             const bool out_bf16 = !partial && p.c_is_bf16;
             // A column unit is what one TMA store carries: 32 rows x 128 bytes.  Everything per step
@@ -724,15 +771,42 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             // Column (inside the tile) of this warp's s-th step.
             auto step_col = [&](int s) { return ((half + 2 * (s >> spu_shift)) << unit_shift) + ((s & (spu - 1)) << 5); };
             int ns = (((p.bn >> unit_shift) + 1 - half) >> 1) << spu_shift;
-            while (ns > 0 && n0 + step_col(ns - 1) >= p.n) --ns;
-            if (row0 >= p.m) ns = 0;  // the whole warp lies below the matrix
+            while (ns > 0 && n0 + step_col(ns - 1) >= pn) --ns;
+            if (row0 >= pm) ns = 0;  // the whole warp lies below the matrix
             // Offset of this thread's row of the tile inside C, in elements.
-            const int64_t c_row_off = c_item_off + row * p.ldc + n0;
-            if (p.beta != 0.0f && !partial && row_ok) {
+            const int64_t c_row_off = c_item_off + static_cast<int64_t>(row0 + lane) * p.ldc + n0;
+            // The epilogue operations of this tile as bits; a split's partial sums get none.
+            constexpr uint32_t kOpAlpha = 1u, kOpBeta = 2u, kOpBias = 4u, kOpGelu = 8u;
+            const float alpha = p.alpha, beta = p.beta;
+            const bool c_bf16 = p.c_is_bf16 != 0;
+            const void* const c_ptr = p.c;
+            uint32_t ops = 0;
+            if (!partial) {
+                if (alpha != 1.0f) ops |= kOpAlpha;
+                if (beta != 0.0f && row_ok) ops |= kOpBeta;
+                if (p.epi_flags & kEpiBias) ops |= kOpBias;
+                if (p.epi_flags & kEpiGelu) ops |= kOpGelu;
+            }
+            // Every row of a step adds the same 32 bias values: lane j fetches the j-th of each of
+            // the (at most four) steps now, while the tile's main loop is still running, and the
+            // warp passes them round by shuffle when the step comes.
+            float bias_mine[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (ops & kOpBias) {
+                const bool bias_bf16 = p.bias_is_bf16 != 0;
+                const void* const bias_ptr = p.bias;
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const int col = n0 + step_col(s) + lane;
+                    if (s < ns && col < pn)
+                        bias_mine[s] = bias_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(bias_ptr)[col])
+                                                 : static_cast<const float*>(bias_ptr)[col];
+                }
+            }
+            if (ops & kOpBeta) {
                 // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
                 // lines now, while the tile's main loop is still running.
-                const int esz = p.c_is_bf16 ? 2 : 4;
-                const char* base = static_cast<const char*>(p.c) + c_row_off * esz;
+                const int esz = c_bf16 ? 2 : 4;
+                const char* base = static_cast<const char*>(c_ptr) + c_row_off * esz;
                 for (int s = 0; s < ns; s += spu)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<int64_t>(step_col(s)) * esz));
             }
@@ -755,46 +829,48 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             // One 32-column step: epilogue arithmetic on the values of this thread's row, then
             // into the staging buffer; once the unit is complete it leaves by TMA or, for a
             // ragged unit or a C that TMA cannot address, by the warp's own row-wise stores.
-            auto emit = [&](const uint32_t (&r)[32], int s) {
+            auto emit = [&](const uint32_t (&r)[32], int s, float my_bias) {
                 const int c0 = step_col(s);
-                const int64_t col = n0 + c0;
-                const int valid = static_cast<int>(min(static_cast<int64_t>(32), p.n - col));
+                const int col = n0 + c0;
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                const int64_t c_off = c_row_off + c0;
-                if (!partial) {
-                    if (p.alpha != 1.0f) {
+                if (ops != 0u) {
+                    if (ops & kOpAlpha) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+                        for (int j = 0; j < 32; ++j) v[j] *= alpha;
                     }
-                    if (p.beta != 0.0f && row_ok) {
+                    if (ops & kOpBeta) {
+                        const int valid = min(32, pn - col);
+                        const int64_t c_off = c_row_off + c0;
                         float cin[32];
-                        if (p.c_is_bf16)
-                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.c) + c_off, cin, valid);
+                        if (c_bf16)
+                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(c_ptr) + c_off, cin, valid);
                         else
-                            load_chunk_f32(static_cast<const float*>(p.c) + c_off, cin, valid);
+                            load_chunk_f32(static_cast<const float*>(c_ptr) + c_off, cin, valid);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = fmaf(p.beta, cin[j], v[j]);
+                        for (int j = 0; j < 32; ++j) v[j] = fmaf(beta, cin[j], v[j]);
                     }
-                    if (p.epi_flags & kEpiBias) {
-                        // every row of the step needs the same 32 bias values: lane j fetches the
-                        // j-th, the warp passes them round
-                        float mine = 0.0f;
-                        if (lane < valid)
-                            mine = p.bias_is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + lane])
-                                                  : static_cast<const float*>(p.bias)[col + lane];
+                    if (ops & kOpBias) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
+                        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
                     }
-                    if (p.epi_flags & kEpiGelu) {
+                    if (ops & kOpGelu) {
+                        // A bf16 result rounds at 2^-9: the hardware tanh (2^-11) is exact enough for
+                        // it and halves the special-function work, which bounds this step; an fp32
+                        // result gets the form that is accurate to 1e-6.
+                        if (out_bf16) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_hw(v[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
+                        }
                     }
                 }
                 const int sub = s & (spu - 1);
-                const int64_t unit_col = col - sub * 32;
-                const bool by_tma = tma_ok && unit_col + unit_cols <= p.n;
+                const int unit_col = col - sub * 32;
+                const bool by_tma = tma_ok && unit_col + unit_cols <= pn;
                 const uint32_t buf = my_bufs + (buf_seq % kStoreBufs) * kStoreBufBytes;
                 if (sub == 0) {
                     // The buffer is free once the TMA store that last read it has done so.
@@ -826,7 +902,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_4d(out_map, buf, static_cast<int32_t>(unit_col), row0, out_z, out_w);
+                        tma_store_4d(out_map, buf, unit_col, row0, out_z, out_w);
                         bulk_commit_group();
                     }
                     ++buf_seq;
@@ -836,12 +912,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 // copies the staged rows out itself, one row per instruction, so that every store
                 // instruction writes up to 128 contiguous bytes.
                 __syncwarp();
-                const int unit_valid = static_cast<int>(min(static_cast<int64_t>(unit_cols), p.n - unit_col));
+                const int unit_valid = min(unit_cols, pn - unit_col);
                 const uint32_t word = ((static_cast<uint32_t>(lane) >> 2) << 4) | ((static_cast<uint32_t>(lane) & 3u) << 2);
 #pragma unroll 1
                 for (int rr = 0; rr < 32; ++rr) {
                     const int64_t grow = static_cast<int64_t>(row0) + rr;
-                    if (grow >= p.m) break;
+                    if (grow >= pm) break;
                     uint32_t w;
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w)
                                  : "r"(buf + static_cast<uint32_t>(rr) * 128u + (word ^ ((static_cast<uint32_t>(rr) & 7u) << 4))));
@@ -855,7 +931,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         }
                     } else if (lane < unit_valid) {
                         float* dst = partial
-                            ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * p.m + grow) * p.n + unit_col + lane
+                            ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * pm + grow) * pn + unit_col + lane
                             : static_cast<float*>(p.c) + c_item_off + grow * p.ldc + unit_col + lane;
                         *dst = __uint_as_float(w);
                     }
@@ -879,7 +955,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
                     if (s + 1 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 1)), nxt);
                     else release_acc();
-                    emit(cur, s);
+                    emit(cur, s, s == 0 ? bias_mine[0] : s == 1 ? bias_mine[1] : s == 2 ? bias_mine[2] : bias_mine[3]);
                 }
             }
             ++acc_seq;
