@@ -91,14 +91,29 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kDbiasRowsPerCta = 16;                 // mode 2: rows of op(A) one CTA sums per dbias ticket
 constexpr int kDbiasFinishPerCta = 256;              // mode 1: values of i one CTA finishes per ticket
 
-struct __align__(8) Control {
+// A ticket as the scheduler publishes it: already decoded, so that the warps that read it
+// (producers, MMA issuer, epilogue) go from one tile to the next on a few shared-memory reads.
+// The decode runs once, in the scheduler, ahead of need.
+struct __align__(16) TileCoord {
+    int t;                 // the ticket; -1: no more work
+    int prob;
+    int kb0, kb1;
+    int m_tile, n_tile;
+    int bz, bw;            // the batch item as (index inside its group, group): (batch, 0) for a plain batch
+    int split, batch;
+    int pad0, pad1;
+};
+static_assert(sizeof(TileCoord) == 48, "three 16-byte words");
+
+struct __align__(16) Control {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t sched_full[kRing];
     uint64_t sched_empty[kRing];
-    int32_t ring[kRing];
+    TileCoord ring[kRing];
+    uint4 mma_consts[kMaxGroupProblems];    // per problem: instruction descriptor, operand descriptor bases, k-steps
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -134,12 +149,6 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
     }
 }
 
-struct TileCoord {
-    int prob;
-    int m_tile, n_tile, split, batch;
-    int bz, bw;   // the batch item as (index inside its group, group): (batch, 0) for a plain batch
-    int kb0, kb1;
-};
 
 // n / d with the reciprocal of d at hand.  One thread of the MMA warp decodes a ticket between
 // two tiles, where a hardware-emulated integer division (a long dependent chain) is exposed:
@@ -155,6 +164,8 @@ __device__ __forceinline__ uint32_t div_by(uint32_t n, uint32_t d, float inv_d) 
 
 __device__ __forceinline__ TileCoord decode_tile(const ProblemScalars* sp, int num_problems, int t) {
     TileCoord tc;
+    tc.t = t;
+    tc.pad0 = tc.pad1 = 0;
     int pi = 0;
 #pragma unroll 1
     for (int i = 1; i < num_problems; ++i)
@@ -390,6 +401,19 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
+    if (static_cast<int>(threadIdx.x) < gp.num_problems) {
+        // Shared-memory descriptors, 128-byte swizzle: K-major = k-step 32 bytes along the
+        // row, LBO unused (16), SBO 1024; MN-major = k-step 16 k-rows of 128 bytes, LBO =
+        // one 64-wide block, SBO 1024.  Only the 14-bit start-address field changes between
+        // k-steps and stages, so the issuing thread does one add per operand.
+        const ProblemScalars& q = gp.prob[threadIdx.x];
+        uint4 c;
+        c.x = make_idesc_bf16(kTileRows, q.bn, q.a_mn, q.b_mn);
+        c.y = (smem_base >> 4) | (((q.a_mn ? kBlock64Bytes : 16u) >> 4) << 16);
+        c.z = ((smem_base + kATileBytes) >> 4) | (((q.b_mn ? kBlock64Bytes : 16u) >> 4) << 16);
+        c.w = ((q.a_mn ? UMMA_K * 128u : UMMA_K * 2u) >> 4) | (((q.b_mn ? UMMA_K * 128u : UMMA_K * 2u) >> 4) << 16);
+        ctl->mma_consts[threadIdx.x] = c;
+    }
     {
         constexpr int kWords = static_cast<int>(sizeof(ProblemScalars) / 4);
         for (int i = threadIdx.x; i < gp.num_problems * kWords; i += kThreads) {
@@ -443,8 +467,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         // waiting at a stage's barrier when the stage frees, and the work between two tiles
         // (reading the ticket, decoding it: ~1000 cycles) must fit into the time until that warp's
         // next k-block is due.  With two warps it did not (measured: the first load of a tile left
-        // ~1500 cycles after its stage was free).  In each warp the whole warp walks the loop; lane 0 does the barrier bookkeeping and
-        // lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
+        // ~1500 cycles after its stage was free).  In each warp the whole warp walks the loop;
+        // lane 0 does the barrier bookkeeping and lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
         // (MN-major operands come in 64-wide blocks) leave in one issue slot.  Warp 0 of the
         // leader also runs the scheduler.
         const bool scheduler = warp == 0 && leader;
@@ -466,20 +490,20 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         // 84 us launch).
         const bool dynamic = gp.static_schedule == 0;
         int prev_ticket = 0;
-        constexpr int kDrawAhead = 6;   // k-blocks before the end of a tile at which the next ticket is drawn
+        constexpr int kDrawAhead = 8;   // k-blocks before the end of a tile at which the next ticket is drawn
         constexpr int kNotDrawn = -2;
         int next_ticket = kNotDrawn;
-        // The other producer warps (this CTA's helper, both of the peer's) can stream a tile only
-        // once they have read its ticket from the ring, and the operand pipeline has no slack to
-        // absorb a late one (a stage is refilled about as fast as it is consumed): publishing a
-        // ticket one ticket-decode later than possible measured 5 % slower on the GPT-2 GEMMs.  So
-        // on long tiles the drawn ticket is published a few k-blocks before the current tile's
-        // last loads, as soon as its ring slot is free; otherwise at the top of the next iteration.
-        constexpr int kPublishAhead = 3;     // k-blocks before the end of a tile
-        constexpr int kMinEarlyKblocks = 8;  // shorter tiles publish at the top (the draw has not returned yet)
+        // The per-tile code of every role runs once in thousands of cycles, from a cold
+        // instruction cache, on the critical path of the operand pipeline (a stage is refilled
+        // about as fast as it is consumed, so a load that is issued late is a bubble in the tensor
+        // pipe later).  So the ticket is decoded once, here, and on long tiles ahead of need: a few
+        // k-blocks before the current tile's last loads, right after one of this warp's own
+        // k-blocks (two k-block times before its next one is due), as soon as the ring slot is
+        // free.  Short tiles publish at the top of the next iteration.
+        constexpr int kPublishAhead = 5;     // earliest k-block, counted from the end of the tile
+        constexpr int kMinEarlyKblocks = 10; // shorter tiles publish at the top (the draw has not returned yet)
         bool early = false;                  // the next iteration's ticket is already in the ring
-        int early_t = -1;
-        // Ring entry `slot` <- ticket `raw` (out-of-range: the end marker).  Returns what was published.
+        // Ring entry `slot` <- ticket `raw`, decoded (out-of-range: the end marker).
         auto publish = [&](int slot, int raw) {
             int t = raw;
             prev_ticket = raw;
@@ -488,21 +512,29 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 if (dynamic && t == gp.total_tiles + n_sched - 1) *gp.sched_counter = 0;
                 t = -1;
             }
-            ctl->ring[slot] = t;
+            TileCoord e;
+            if (t >= gp.colsum_total && t < gp.fin_begin) {
+                e = decode_tile(sp, gp.num_problems, t);
+            } else {
+                e.t = t;  // the end, or a dbias ticket: the readers look at nothing else
+                e.prob = e.kb0 = e.kb1 = e.m_tile = e.n_tile = e.bz = e.bw = e.split = e.batch = e.pad0 = e.pad1 = 0;
+            }
+            ctl->ring[slot] = e;
             mbar_arrive(smem_u32(&ctl->sched_full[slot]));
-            // The peer's copy travels as an async store that completes its barrier.
-            if (kPair)
-                st_async_cluster_u32(mapa_shared(smem_u32(&ctl->ring[slot]), 1u), static_cast<uint32_t>(t),
-                                     mapa_shared(smem_u32(&ctl->sched_full[slot]), 1u));
-            return t;
+            // The peer's copy travels as async stores that complete its barrier.
+            if (kPair) {
+                const uint32_t dst = mapa_shared(smem_u32(&ctl->ring[slot]), 1u);
+                const uint32_t bar = mapa_shared(smem_u32(&ctl->sched_full[slot]), 1u);
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(&e);
+#pragma unroll
+                for (int q = 0; q < 3; ++q) st_async_cluster_v4(dst + 16u * q, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3], bar);
+            }
         };
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
             const uint32_t sphase = static_cast<uint32_t>(it / kRing) & 1u;
-            int t = -1;
             if (lane == 0) {
                 if (scheduler && early) {
-                    t = early_t;
                     early = false;
                 } else if (scheduler) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, abort_flag, status,
@@ -512,24 +544,25 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                       : !dynamic ? prev_ticket + n_sched
                                       : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1);
                         next_ticket = kNotDrawn;
-                        t = publish(slot, raw);
+                        publish(slot, raw);
                     }
                 } else {
-                    // In the peer CTA warp 0 arms the ring barrier for the leader's 4-byte store.
-                    if (kPair && warp == 0) mbar_arrive_expect_tx(smem_u32(&ctl->sched_full[slot]), 4u);
+                    // In the peer CTA warp 0 arms the ring barrier for the leader's stores.
+                    if (kPair && warp == 0)
+                        mbar_arrive_expect_tx(smem_u32(&ctl->sched_full[slot]), static_cast<uint32_t>(sizeof(TileCoord)));
                     ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
                                              kDevWaitSched, 48 + slot, wait_ns);
-                    if (ok) {
-                        t = ctl->ring[slot];
-                        release_ring_slot(slot);
-                    }
                 }
             }
+            __syncwarp();  // lane 0's ring write is visible to the warp
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            t = __shfl_sync(0xffffffffu, t, 0);
-            if (!ok || t < 0) break;
+            if (!ok) break;
+            const TileCoord tc = ctl->ring[slot];
+            __syncwarp();
+            if (!scheduler && lane == 0) release_ring_slot(slot);
+            const int t = tc.t;
+            if (t < 0) break;
             if (t < gp.colsum_total || t >= gp.fin_begin) continue;  // a dbias ticket: work for the epilogue warps only
-            const TileCoord tc = decode_tile(sp, gp.num_problems, t);
             const ProblemScalars& p = sp[tc.prob];
             const GroupProblem& pm = gp.prob[tc.prob];  // for the addresses of its tensor maps only
             const int bn = p.bn, a_mn = p.a_mn, b_mn = p.b_mn;
@@ -556,16 +589,17 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 else      { my_y = n0; k_is_x = true; }
             }
             const int draw_kb = tc.kb1 - kDrawAhead > tc.kb0 ? tc.kb1 - kDrawAhead : tc.kb0;
-            const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : -1;
+            const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : 0x7fffffff;
+            const int after_own = n_turns > 1 ? 1 : 0;
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
                 if (scheduler && lane == 0) {
                     if (dynamic && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
-                    if (kb == publish_kb) {
+                    if (kb >= publish_kb && !early && turn == after_own) {
                         const int nslot = (it + 1) % kRing;
                         const uint32_t nphase = static_cast<uint32_t>((it + 1) / kRing) & 1u;
-                        // one poll: a ring that is still full is waited for at the top, as before
+                        // one poll: a ring that is still full is waited for at the top
                         if (mbar_try_wait(smem_u32(&ctl->sched_empty[nslot]), nphase ^ 1u)) {
-                            early_t = publish(nslot, dynamic ? next_ticket : prev_ticket + n_sched);
+                            publish(nslot, dynamic ? next_ticket : prev_ticket + n_sched);
                             next_ticket = kNotDrawn;
                             early = true;
                         }
@@ -595,10 +629,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0 && leader) {
-            // Shared-memory descriptor, 128-byte swizzle: K-major = k-step 32 bytes along the
-            // row, LBO unused (16), SBO 1024; MN-major = k-step 16 k-rows of 128 bytes, LBO =
-            // one 64-wide block, SBO 1024.  Only the 14-bit start-address field changes between
-            // k-steps and stages, so the issuing thread does one add per operand.
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
             int stage = 0;
             uint32_t phase = 0;
@@ -611,25 +641,22 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 ok = bounded_wait(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
                                   kDevWaitSched, 16 + slot, wait_ns);
                 if (!ok) break;
-                const int t = ctl->ring[slot];
+                const int4 head = *reinterpret_cast<const int4*>(&ctl->ring[slot]);  // t, prob, kb0, kb1
                 release_ring_slot(slot);
+                const int t = head.x;
                 if (t < 0) break;
                 if (t < gp.colsum_total || t >= gp.fin_begin) continue;
-                const TileCoord tc = decode_tile(sp, gp.num_problems, t);
-                const ProblemScalars& p = sp[tc.prob];
-                const uint32_t idesc = make_idesc_bf16(kTileRows, p.bn, p.a_mn, p.b_mn);
-                const uint32_t step_a = (p.a_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
-                const uint32_t step_b = (p.b_mn ? UMMA_K * 128 : UMMA_K * 2) >> 4;
-                const uint32_t a_lo_base = (smem_base >> 4) | (((p.a_mn ? kBlock64Bytes : 16u) >> 4) << 16);
-                const uint32_t b_lo_base = ((smem_base + kATileBytes) >> 4) |
-                                           (((p.b_mn ? kBlock64Bytes : 16u) >> 4) << 16);
+                const int nkb = head.w - head.z;
+                const uint4 mc = ctl->mma_consts[head.y];
+                const uint32_t idesc = mc.x, a_lo_base = mc.y, b_lo_base = mc.z;
+                const uint32_t step_a = mc.w & 0xFFFFu, step_b = mc.w >> 16;
                 const int acc = static_cast<int>(acc_seq & 1u);
                 ok = bounded_wait<kPair>(smem_u32(&ctl->tmem_empty[acc]), ((acc_seq >> 1) & 1u) ^ 1u, abort_flag,
                                          status, kDevWaitTmemEmpty, acc, wait_ns);
                 if (!ok) break;
                 tc_fence_after_thread_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
-                for (int kb = tc.kb0; kb < tc.kb1; ++kb) {
+                for (int i = 0; i < nkb; ++i) {
                     ok = bounded_wait<kPair>(smem_u32(&ctl->full[stage]), phase, abort_flag, status,
                                              kDevWaitSmemFull, stage, wait_ns);
                     if (!ok) break;
@@ -643,7 +670,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                             static_cast<uint64_t>(a_lo + kk * step_a);
                         const uint64_t db = (static_cast<uint64_t>(kDescHi) << 32) |
                                             static_cast<uint64_t>(b_lo + kk * step_b);
-                        umma_bf16_cg<CG>(d_tmem, da, db, idesc, (kb > tc.kb0 || kk > 0) ? 1u : 0u);
+                        umma_bf16_cg<CG>(d_tmem, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit_cg<CG>(smem_u32(&ctl->empty[stage]));  // frees the stage when the MMAs retire
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -668,9 +695,10 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             ok = bounded_wait<kPair>(smem_u32(&ctl->sched_full[slot]), sphase, abort_flag, status,
                                      kDevWaitSched, 32 + slot, wait_ns);
             if (!ok) break;
-            const int t = ctl->ring[slot];
+            const TileCoord tc = ctl->ring[slot];
             __syncwarp();
             if (lane == 0) release_ring_slot(slot);
+            const int t = tc.t;
             if (t < 0) break;
             if (t < gp.colsum_total) {
                 // A dbias reduction ticket of the problem that owns it.
@@ -743,7 +771,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 }
                 continue;
             }
-            const TileCoord tc = decode_tile(sp, gp.num_problems, t);
             const ProblemScalars& p = sp[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
             // Everything a step needs is read from the problem's scalars ONCE per tile, into

@@ -240,6 +240,12 @@ __device__ __forceinline__ void st_async_cluster_u32(uint32_t cluster_addr, uint
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
                  ::"r"(cluster_addr), "r"(v), "r"(cluster_bar) : "memory");
 }
+// The same for 16 bytes.
+__device__ __forceinline__ void st_async_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                                    uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar) : "memory");
+}
 // try_wait whose acquire covers writes made by the peer CTA.
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
