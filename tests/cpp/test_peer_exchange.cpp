@@ -99,6 +99,7 @@ int run_rank(int rank, int world, int to_hub, int from_hub) {
         allgather(&token, tokens.data(), 1);  // nobody refills its span before everybody has read it
     }
     std::printf("rank %d of %d: %lld floats, 3 exchanges, %d failures\n", rank, world, static_cast<long long>(n), failures);
+    std::fflush(stdout);  // the rank leaves through _exit, which flushes nothing
     return failures == 0 ? 0 : 1;
 }
 
