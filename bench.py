@@ -215,20 +215,23 @@ class LinearStep:
         # N > 1: the span lives in peer-mapped memory and is summed by the library's own kernel
         # over NVLink ("peer" / "nvls"), or stays private and goes through NCCL ("nccl")
         self.exchange = None
-        if world > 1 and exchange in ("peer", "nvls"):
+        self.ride = False   # slices ride along in later backward launches (llmt_b200_gemm_grouped_exchange)
+        if world > 1 and exchange in ("peer", "nvls", "ride"):
             try:
                 self.exchange = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=comm_ctas,
-                                             multicast=(exchange == "nvls"))
+                                             multicast=(exchange in ("nvls", "ride")))
             except Exception as exc:  # no peer mapping on this machine: every rank falls back to NCCL
                 print(f"[bench] peer-mapped span unavailable ({exc}); using NCCL", file=sys.stderr)
             ok = torch.tensor([1 if self.exchange is not None else 0], device=dev)
             torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
             if int(ok.item()) == 0:
                 self.exchange = None
-            elif exchange == "nvls" and not self.exchange.multicast:
+            elif exchange in ("nvls", "ride") and not self.exchange.multicast:
                 # no multicast mapping offered: the peer-copy kernel needs SMs of its own
                 self.exchange.ctas = 16
                 L.set_sm_budget(torch.cuda.get_device_properties(dev).multi_processor_count - 16)
+            elif exchange == "ride":
+                self.ride = True
         self.bucket = GradBucket(shapes, dev, storage=self.exchange.attach if self.exchange else None)
         self.layers = []
         for n, i, o, gelu in spec:
@@ -280,17 +283,16 @@ class LinearStep:
         out = []
         for t in self.layers:
             f = 2.0 * self.m * t["i"] * t["o"]
-            out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), []))
+            out.append((t["name"] + ".fwd", f, (lambda t=t: self.L.gemm_desc(t["d_fwd"], t["y"], t["x"], t["w"])), [], None))
         for t in reversed(self.layers):
             label = t["name"] + ".bwd(dX" + "".join("+dW_" + u["name"] for u in t["carries"]) + ")"
-            out.append((label, t["bwd_flops"], t["bwd"].run, t["carries"]))
+            out.append((label, t["bwd_flops"], t["bwd"].run, t["carries"], t["bwd"]))
         return out
 
-    def exchange_layers(self, layers):
-        """Sums the dW + dbias slices of `layers` over the ranks, on the side stream.  A layer's dW
-        and dbias are adjacent in the flat span, and so are the slices of neighbouring layers: one
-        call covers every run of neighbours."""
-        torch = self.torch
+    def slice_runs(self, layers):
+        """(offset, count) of the dW + dbias slices of `layers`: a layer's dW and dbias are adjacent
+        in the flat span, and so are the slices of neighbouring layers, so every run of neighbours
+        is one range."""
         order = [t["name"] for t in self.layers]
         idx = sorted(order.index(t["name"]) for t in layers)
         runs, start = [], None
@@ -300,33 +302,62 @@ class LinearStep:
             if j + 1 == len(idx) or idx[j + 1] != i + 1:
                 runs.append((start, i))
                 start = None
+        out = []
         for lo_i, hi_i in runs:
             names = [order[i] + sfx for i in range(lo_i, hi_i + 1) for sfx in (".dW", ".dbias")]
-            off, cnt = self.bucket.span_of(names)
+            out.append(self.bucket.span_of(names) + ([self.layers[i] for i in range(lo_i, hi_i + 1)],))
+        return out
+
+    def exchange_layers(self, layers, stream=None):
+        """Sums the dW + dbias slices of `layers` over the ranks with one call per range, on the
+        side stream (or on `stream`)."""
+        torch = self.torch
+        stream = stream if stream is not None else self.comm_stream
+        for off, cnt, _ in self.slice_runs(layers):
             if self.exchange is not None:
-                self.exchange.allreduce(off, cnt, stream=self.comm_stream)
+                self.exchange.allreduce(off, cnt, stream=stream)
             else:
-                with torch.cuda.stream(self.comm_stream):
+                with torch.cuda.stream(stream):
                     torch.distributed.all_reduce(self.bucket.flat[off:off + cnt])
 
-    def run(self, world=1, events=None):
-        """Enqueues one step on the current stream. With world > 1 every layer's gradient
-        slice is all-reduced on a side stream as soon as the launch that completes it is
-        enqueued, so the exchange overlaps the backward of the remaining layers."""
+    def run(self, world=1, events=None, exchange=True, zero=True):
+        """Enqueues one step on the current stream.  With world > 1 the gradients are summed over
+        the ranks.  "ride": the slice a backward launch completes travels inside the NEXT backward
+        launch (its epilogue warps sum it through the switch while the tensor pipe runs that
+        launch's tiles); only the last launch's slice needs a call of its own.  Otherwise every
+        slice is all-reduced on a side stream as soon as the launch that completes it is enqueued."""
         torch = self.torch
-        self.bucket.zero_()
-        for label, _, fn, done in self.launches():
+        if zero:
+            self.bucket.zero_()
+        exchange = exchange and world > 1
+        ride = exchange and self.ride
+        if ride:
+            self.L.exchange_begin_step(self.exchange.desc)
+        pending, index = [], 0
+        for label, _, fn, done, group in self.launches():
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record()
-            fn()
+            if ride and pending and group is not None:
+                off, cnt, covered = self.slice_runs(pending)[0]
+                group.run_with_exchange(self.exchange.desc, off, cnt, index)
+                index += 1
+                pending = [t for t in pending if all(t is not u for u in covered)]
+            else:
+                fn()
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record()
                 events.append((label, e0, e1))
-            if world > 1 and done:
+            if ride:
+                pending += done
+            elif exchange and done:
                 ready = torch.cuda.Event(); ready.record()
                 self.comm_stream.wait_event(ready)
                 self.exchange_layers(done)
-        if world > 1:
+        if ride:
+            # what no later launch could carry; its flag rounds also close the step for the slices
+            # that rode along (every rank has finished every earlier launch)
+            self.exchange_layers(pending, stream=torch.cuda.current_stream())
+        elif exchange:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
 
@@ -389,7 +420,10 @@ class AttentionStep:
 def make_step(workload, m, dev, seed, world=1, args=None):
     if workload == "c4":
         return AttentionStep(dev, seed)
-    defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) else None
+    # N > 1 with ride-along exchanges: every layer keeps its dW in its own backward launch, so that
+    # its slice is complete early enough to travel inside the next launch
+    riding = world > 1 and args is not None and args.exchange == "ride"
+    defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) and not riding else None
     return LinearStep(workload, m, dev, seed, world=world, exchange=args.exchange if args else "nccl",
                       comm_ctas=(args.comm_ctas if args and args.comm_ctas else 8), defer=defer)
 
@@ -857,16 +891,26 @@ def roofline_of(step, workload, ms, peaks):
 
 
 def exchange_check(torch, step, world, rank, dev):
-    """The exchange of the timed step on fresh per-rank partial sums, against two references:
-    NCCL's all-reduce of the same partial sums and their sum in rank order.  Two ranks: bitwise
-    equal to both.  Peer-copy form: bitwise equal to the rank-order sum.  Sum formed inside the
-    switch with more than two ranks: within 1e-6 of NCCL's (the order of the additions is the
-    switch's).  In every case a rerun must reproduce its own bits and all ranks must hold the
-    same bits."""
+    """The timed step itself, started from random per-rank contents of the span, with and without
+    its exchange.  Without: this rank's partial sums (the GEMMs are deterministic), which NCCL's
+    all-reduce and a sum in rank order turn into the two references.  With: what the step leaves in
+    the span.  Two ranks: bitwise equal to both references.  Peer-copy form: bitwise equal to the
+    rank-order sum.  Sum formed inside the switch with more than two ranks: within 1e-6 of NCCL's
+    (the order of the additions is the switch's).  In every case a rerun must reproduce its own
+    bits and all ranks must hold the same bits."""
     import torch.distributed as dist
     flat = step.bucket.flat
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    part = torch.randn(flat.numel(), device=dev, generator=g)
+    start = torch.randn(flat.numel(), device=dev, generator=g)
+
+    def run_from_start(exchange):
+        flat.copy_(start)
+        torch.cuda.synchronize(); dist.barrier()
+        step.run(world, exchange=exchange, zero=False)
+        torch.cuda.synchronize(); dist.barrier()
+        return flat.clone()
+
+    part = run_from_start(False)
     want_nccl = part.clone()
     dist.all_reduce(want_nccl)
     parts = [torch.empty_like(part) for _ in range(world)]
@@ -875,17 +919,7 @@ def exchange_check(torch, step, world, rank, dev):
     for p_ in parts[1:]:
         want_order += p_
     del parts
-    results = []
-    for _ in range(2):
-        flat.copy_(part)
-        torch.cuda.synchronize(); dist.barrier()
-        # the calls the timed step makes, in its order
-        for _label, _f, _fn, done in step.launches():
-            if done:
-                step.exchange_layers(done)
-        torch.cuda.current_stream().wait_stream(step.comm_stream)
-        torch.cuda.synchronize(); dist.barrier()
-        results.append(flat.clone())
+    results = [run_from_start(True) for _ in range(2)]
     # only what the exchange covers (the padding between slices is covered too: it is inside the ranges)
     mask = torch.zeros(flat.numel(), dtype=torch.bool, device=dev)
     for layer in step.layers:
@@ -925,10 +959,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="N = 1: skip the other workloads, the per-GEMM comparison and the sustained replay")
-    ap.add_argument("--exchange", choices=["nvls", "peer", "nccl"], default="nvls",
-                    help="N > 1: how the gradient span is summed: the library's kernel through NVSwitch "
-                         "multicast (falls back to peer copies where no multicast mapping is offered), "
-                         "its peer-copy kernel, or NCCL")
+    ap.add_argument("--exchange", choices=["ride", "nvls", "peer", "nccl"], default="ride",
+                    help="N > 1: how the gradient span is summed: ride = inside the next backward launch, by "
+                         "its epilogue warps, through NVSwitch multicast (llmt_b200_gemm_grouped_exchange; the "
+                         "last slice by the library's exchange kernel); nvls = that kernel per layer slice on a "
+                         "side stream (both fall back to peer copies where no multicast mapping is offered); "
+                         "peer = its peer-copy form; nccl = NCCL")
     ap.add_argument("--comm-ctas", type=int, default=None,
                     help="N > 1: CTAs of the exchange kernel (default 64 for nvls, 16 for peer; "
                          "with nccl: NCCL_MAX_CTAS, default unlimited)")
@@ -958,14 +994,14 @@ def main():
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.comm_ctas is None:
-            args.comm_ctas = {"nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
+            args.comm_ctas = {"ride": 128, "nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
         if args.exchange != "nccl":
             args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
         elif args.comm_ctas > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_ctas))
         if args.comm_sms is None:
             # the multicast kernel's CTAs (no shared memory, 50 registers) fit beside a GEMM CTA
-            args.comm_sms = {"nvls": 0, "peer": args.comm_ctas, "nccl": 0}[args.exchange]
+            args.comm_sms = {"ride": 0, "nvls": 0, "peer": args.comm_ctas, "nccl": 0}[args.exchange]
         if args.comm_sms > 0:
             # The GEMM kernels are persistent and fill every SM they are given; the gradient
             # exchange on the side stream only overlaps them if some SMs stay free for it.
@@ -1032,6 +1068,8 @@ def main():
 
     ar_bytes = step.bucket.nbytes() if (world > 1 and not attention) else 0
     exchange_name = (None if world == 1 or attention else "nccl" if step.exchange is None else
+                     "llmt_b200_gemm_grouped_exchange (slices ride inside the next backward launch, NVSwitch multicast) + "
+                     "llmt_b200_grad_allreduce for the last slice" if getattr(step, "ride", False) else
                      "llmt_b200_grad_allreduce, " + ("NVSwitch multicast" if step.exchange.multicast else "peer copies"))
 
     # release the headline step before the other workloads are built

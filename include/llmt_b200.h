@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LLMT_B200_ABI_VERSION 3
+#define LLMT_B200_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define LLMT_B200_API __attribute__((visibility("default")))
@@ -269,7 +269,7 @@ LLMT_B200_API int llmt_b200_set_sm_budget(int32_t sms);
  * Run it beside the GEMM kernels by lowering their SM budget by `ctas`. */
 #define LLMT_B200_COMM_MAX_RANKS 8
 #define LLMT_B200_COMM_MAX_CTAS 128
-#define LLMT_B200_COMM_FLAG_BYTES (2 * LLMT_B200_COMM_MAX_RANKS * LLMT_B200_COMM_MAX_CTAS * 4)
+#define LLMT_B200_COMM_FLAG_BYTES (2 * LLMT_B200_COMM_MAX_RANKS * LLMT_B200_COMM_MAX_CTAS * 4 + 256)
 #define LLMT_B200_COMM_EPOCH_BYTES (LLMT_B200_COMM_MAX_CTAS * 4)
 #define LLMT_B200_DEV_WAIT_PEER 6
 
@@ -289,6 +289,28 @@ typedef struct llmt_b200_comm_desc {
 
 LLMT_B200_API int llmt_b200_grad_allreduce(const llmt_b200_comm_desc* comm, int64_t offset, int64_t count,
                              int32_t ctas, void* stream);
+
+/* A grouped launch that also sums a range of the gradient span over the ranks ("rides along"):
+ * llmt_b200_gemm_grouped plus, inside the same kernel, the all-reduce of floats
+ * [offset, offset + count) of the span, done by the launch's epilogue warps through the NVSwitch
+ * multicast mapping (comm->grad_mc, required: LLMT_B200_ERR_UNSUPPORTED without it) while the
+ * tensor pipe runs the launch's tiles, so the transfer costs no launch, no SM and no exposed time.
+ * No counterpart in llmt (it has no collective).
+ *   - The range must have been completed by EARLIER work on this stream (e.g. the previous
+ *     layer's backward launch); a launch that writes into it is refused.
+ *   - Every rank makes the same call with the same offset, count and index.  `index`
+ *     (0..15) numbers the ride-along exchanges of one step; llmt_b200_exchange_begin_step starts
+ *     a step (it advances a counter on the device, so a captured step can be replayed).
+ *   - The sums are in every rank's span once a later llmt_b200_grad_allreduce call on the same
+ *     stream has returned on the device (any range: typically the last layer's slice, which no
+ *     later launch can carry); until then other ranks may still be writing them.
+ *   - Every cross-rank wait is bounded (llmt_b200_set_wait_limit_ns); a rank that never arrives
+ *     ends the launch with LLMT_B200_DEV_WAIT_PEER in the status word. */
+LLMT_B200_API int llmt_b200_gemm_grouped_exchange(const llmt_b200_gemm_desc* descs, void* const* c,
+                                    const void* const* a, const void* const* b, int32_t count,
+                                    const llmt_b200_comm_desc* comm, int64_t offset, int64_t count_floats,
+                                    int32_t index, void* stream);
+LLMT_B200_API int llmt_b200_exchange_begin_step(const llmt_b200_comm_desc* comm, void* stream);
 
 /* The same exchange with all `world` ranks living on ONE device (comms[r] is rank r's
  * descriptor, every pointer local): a single cooperative launch of world * ctas CTAs.

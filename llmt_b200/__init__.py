@@ -27,10 +27,12 @@ EXPORTS = [
     "llmt_b200_set_sm_budget", "llmt_b200_grad_allreduce", "llmt_b200_grad_allreduce_emulated",
     "llmt_b200_zero_grads", "llmt_b200_gemm_workspace_bytes_for", "llmt_b200_set_wait_limit_ns",
     "llmt_b200_tensor_map_cache_stats", "llmt_b200_head_merge", "llmt_b200_head_split",
+    "llmt_b200_gemm_grouped_exchange", "llmt_b200_exchange_begin_step",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
-COMM_FLAG_BYTES = 2 * COMM_MAX_RANKS * COMM_MAX_CTAS * 4
+COMM_FLAG_BYTES = 2 * COMM_MAX_RANKS * COMM_MAX_CTAS * 4 + 256
+MAX_RIDES_PER_STEP = 16
 COMM_EPOCH_BYTES = COMM_MAX_CTAS * 4
 DEV_WAIT_PEER = 6
 
@@ -127,6 +129,13 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_grad_allreduce_emulated.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_int32, ctypes.c_int64,
                                                         ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
         L.llmt_b200_grad_allreduce_emulated.restype = ctypes.c_int
+        L.llmt_b200_gemm_grouped_exchange.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_void_p),
+                                                      ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                                      ctypes.c_int32, ctypes.POINTER(CommDesc), ctypes.c_int64,
+                                                      ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_gemm_grouped_exchange.restype = ctypes.c_int
+        L.llmt_b200_exchange_begin_step.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_void_p]
+        L.llmt_b200_exchange_begin_step.restype = ctypes.c_int
         L.llmt_b200_zero_grads.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
         L.llmt_b200_zero_grads.restype = ctypes.c_int
         L.llmt_b200_set_sm_budget.argtypes = [ctypes.c_int32]
@@ -273,6 +282,16 @@ class Group:
         _check(lib().llmt_b200_gemm_grouped(self.descs, self.c, self.a, self.b, self.n,
                                             ctypes.c_void_p(s.cuda_stream)))
 
+    def run_with_exchange(self, comm: "CommDesc", offset: int, count: int, index: int, stream=None):
+        """llmt_b200_gemm_grouped_exchange: the same launch, whose epilogue warps also sum floats
+        [offset, offset + count) of the gradient span over the ranks through the NVSwitch
+        multicast mapping.  The range must be complete before the launch starts."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        _check(lib().llmt_b200_gemm_grouped_exchange(self.descs, self.c, self.a, self.b, self.n, ctypes.byref(comm),
+                                                     ctypes.c_int64(int(offset)), ctypes.c_int64(int(count)),
+                                                     ctypes.c_int32(int(index)), ctypes.c_void_p(s.cuda_stream)))
+
 
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -350,6 +369,11 @@ def device_status():
 def grad_allreduce(desc: "CommDesc", offset: int, count: int, ctas: int = 8, stream=None) -> None:
     """Sums floats [offset, offset + count) of the span over the ranks of `desc`, in place."""
     _check(lib().llmt_b200_grad_allreduce(ctypes.byref(desc), int(offset), int(count), int(ctas), _stream(stream)))
+
+
+def exchange_begin_step(desc: "CommDesc", stream=None) -> None:
+    """Starts a step of ride-along exchanges (Group.run_with_exchange) on this rank's stream."""
+    _check(lib().llmt_b200_exchange_begin_step(ctypes.byref(desc), _stream(stream)))
 
 
 def grad_allreduce_emulated(descs, offset: int, count: int, ctas: int = 4, stream=None) -> None:

@@ -679,7 +679,7 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
 
 // Launches the tensor-core kernel over `count` filled problems (longest tiles first),
 // then the fixed-order reduction of every problem that was split.
-int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream) {
+int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream, const RideExchange* ride = nullptr) {
     DeviceGlobals* g = nullptr;
     int st = device_globals(&g);
     if (st != LLMT_B200_OK) return st;
@@ -705,6 +705,13 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         fin_total += p.fin_tiles;
         gp.prob[n++] = p;
     }
+    // The tickets of an exchange that rides along come after the dbias reductions: like them they
+    // keep only the epilogue warps busy.
+    const int64_t ride_begin = colsum_total;
+    if (ride != nullptr) {
+        if (n == 0) return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: the launch has no tile to ride along with");
+        colsum_total += ride->tiles;
+    }
     int64_t total = colsum_total;
     for (int i = 0; i < n; ++i) {
         if (total + gp.prob[i].num_tiles + fin_total > 0x7fffff00)
@@ -716,6 +723,9 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         const unsigned slot = g->next++ % kSchedSlots;
         gp.num_problems = n;
         gp.colsum_total = static_cast<int32_t>(colsum_total);
+        gp.ride_begin = static_cast<int32_t>(ride_begin);
+        if (ride != nullptr) gp.ride = *ride;
+        else gp.ride.tiles = 0;
         gp.fin_begin = static_cast<int32_t>(total);
         total += fin_total;
         gp.total_tiles = static_cast<int32_t>(total);
@@ -868,8 +878,10 @@ int llmt_b200_gemm_static_scratch(const llmt_b200_gemm_desc* d, void* c, const v
     return run_bf16(&local, ck, c, a, b, s);
 }
 
-int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, const void* const* a,
-                           const void* const* b, int32_t count, void* stream) {
+namespace {
+int gemm_grouped_impl(const llmt_b200_gemm_desc* descs, void* const* c, const void* const* a,
+                      const void* const* b, int32_t count, void* stream, const llmt_b200_comm_desc* comm,
+                      int64_t xoffset, int64_t xcount, int32_t xindex) {
     if (descs == nullptr || c == nullptr || a == nullptr || b == nullptr)
         return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: null argument");
     if (count < 1 || count > kMaxGroupProblems)
@@ -907,6 +919,31 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
                 return fail(LLMT_B200_ERR_INVALID, "gemm_grouped: problems %d and %d are not independent", j, i);
         }
     }
+    if (comm != nullptr) {
+        // The exchange that rides along: its arguments are checked before anything is planned.
+        if (comm->world < 2 || comm->world > kMaxCommRanks || comm->rank < 0 || comm->rank >= comm->world)
+            return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: bad rank/world");
+        if (comm->grad_mc == nullptr)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "gemm_grouped_exchange: needs the span's NVSwitch multicast mapping "
+                        "(comm.grad_mc); use llmt_b200_grad_allreduce after the launch instead");
+        if (xoffset < 0 || xcount <= 0 || xoffset % 4 != 0 || xcount % 4 != 0)
+            return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: offset and count must be positive multiples of 4 floats");
+        if (xindex < 0 || xindex >= kMaxRidesPerStep)
+            return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: index must be 0..%d", kMaxRidesPerStep - 1);
+        for (int r = 0; r < comm->world; ++r)
+            if (comm->grad[r] == nullptr || comm->flags[r] == nullptr)
+                return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: null buffer for rank %d", r);
+        // The range must be complete before this launch starts: nothing in the launch may write it.
+        const char* x_lo = static_cast<const char*>(comm->grad[comm->rank]) + xoffset * 4;
+        for (int i = 0; i < count; ++i) {
+            const bool hits = overlaps(x_lo, static_cast<size_t>(xcount) * 4, c[i], ck[i].c_bytes) ||
+                              (descs[i].dbias != nullptr &&
+                               overlaps(x_lo, static_cast<size_t>(xcount) * 4, descs[i].dbias, static_cast<size_t>(descs[i].m) * 4));
+            if (hits)
+                return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: problem %d writes into the exchanged range; "
+                            "only ranges that earlier launches completed may ride along", i);
+        }
+    }
     TcPlan plans[kMaxGroupProblems];
     const bool pairs = plan_group(descs, count, plans);
     for (int i = 0; i < count; ++i)
@@ -936,8 +973,49 @@ int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, con
         if (st != LLMT_B200_OK) return st;
         ++n;
     }
-    if (n == 0) return LLMT_B200_OK;
-    return launch_group(probs, n, pairs, static_cast<cudaStream_t>(stream));
+    if (comm == nullptr) {
+        if (n == 0) return LLMT_B200_OK;
+        return launch_group(probs, n, pairs, static_cast<cudaStream_t>(stream));
+    }
+    RideExchange ride{};
+    ride.mc = static_cast<float*>(comm->grad_mc) + xoffset;
+    ride.n4 = xcount / 4;
+    ride.local = static_cast<uint32_t*>(comm->flags[comm->rank]);
+    for (int r = 0; r < comm->world; ++r)
+        ride.peer_ready[r] = static_cast<uint32_t*>(comm->flags[r]) + kRideReady + comm->rank;
+    ride.world = comm->world;
+    ride.rank = comm->rank;
+    ride.index = xindex;
+    // About 64 KB of this rank's share per ticket; no more tickets than a few per CTA (pair).
+    const int64_t share_bytes = (ride.n4 + comm->world - 1) / comm->world * 16;
+    const int units = pairs ? pair_units() : sm_count();
+    int64_t tiles = (share_bytes + 65535) / 65536;
+    if (tiles > 4 * units) tiles = 4 * units;
+    if (tiles < 1) tiles = 1;
+    ride.tiles = static_cast<int32_t>(tiles);
+    return launch_group(probs, n, pairs, static_cast<cudaStream_t>(stream), &ride);
+}
+}  // namespace
+
+int llmt_b200_gemm_grouped(const llmt_b200_gemm_desc* descs, void* const* c, const void* const* a,
+                           const void* const* b, int32_t count, void* stream) {
+    return gemm_grouped_impl(descs, c, a, b, count, stream, nullptr, 0, 0, 0);
+}
+
+int llmt_b200_gemm_grouped_exchange(const llmt_b200_gemm_desc* descs, void* const* c, const void* const* a,
+                                    const void* const* b, int32_t count, const llmt_b200_comm_desc* comm,
+                                    int64_t offset, int64_t count_floats, int32_t index, void* stream) {
+    if (comm == nullptr) return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: null exchange descriptor");
+    return gemm_grouped_impl(descs, c, a, b, count, stream, comm, offset, count_floats, index);
+}
+
+int llmt_b200_exchange_begin_step(const llmt_b200_comm_desc* comm, void* stream) {
+    if (comm == nullptr || comm->rank < 0 || comm->rank >= kMaxCommRanks || comm->flags[comm->rank] == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "exchange_begin_step: bad exchange descriptor");
+    cudaError_t e = launch_exchange_begin_step(static_cast<uint32_t*>(comm->flags[comm->rank]) + kRideStep,
+                                               static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
 }
 
 namespace {

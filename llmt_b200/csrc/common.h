@@ -78,11 +78,38 @@ struct alignas(64) GroupProblem : ProblemScalars {
     CUtensorMap map_ws;         // split-K partial sums [batch*splits][m][n] fp32, same boxes
 };
 
+// ---- gradient all-reduce over peer memory -------------------------------------------------
+constexpr int kMaxCommRanks = 8;
+constexpr int kMaxCommCtas = 128;
+constexpr int kCommThreads = 256;
+// Words behind the per-CTA flag words of an exchange (offsets in 32-bit words from `flags`):
+// kRideReady + w = "rank w's partial sums of ride-along exchange e are complete" (written by rank w
+// into every other rank's copy), kRideStep = this rank's step counter (local).
+constexpr int kRideWords = 2 * kMaxCommRanks * kMaxCommCtas;
+constexpr int kRideReady = kRideWords;
+constexpr int kRideStep = kRideWords + kMaxCommRanks;
+constexpr int kMaxRidesPerStep = 16;
+
+// A range of the gradient span that a GEMM launch sums over the ranks on the side ("rides along"):
+// tickets that only the epilogue warps work on, through the NVSwitch multicast mapping of the
+// span, while the tensor pipe runs the launch's tiles.  tiles == 0: none.
+struct RideExchange {
+    float* mc;                             // multicast address of the first float of the range
+    int64_t n4;                            // length of the range in 16-byte units
+    uint32_t* local;                       // this rank's flag words
+    uint32_t* peer_ready[kMaxCommRanks];   // [r]: where this rank announces itself to rank r
+    int32_t world, rank;
+    int32_t index;                         // which ride-along exchange of the step (0 .. kMaxRidesPerStep-1)
+    int32_t tiles;                         // tickets
+};
+
 struct GroupParams {
     GroupProblem prob[kMaxGroupProblems];
+    RideExchange ride;
+    int32_t ride_begin;         // tickets [ride_begin, colsum_total) belong to the ride-along exchange
     int32_t num_problems;
-    int32_t total_tiles;        // tickets of the launch: dbias reductions, MMA tiles, dbias finishing tickets
-    int32_t colsum_total;       // tickets [0, colsum_total) are dbias reductions
+    int32_t total_tiles;        // tickets of the launch: dbias reductions, exchange, MMA tiles, dbias finishing tickets
+    int32_t colsum_total;       // tickets [0, colsum_total) keep only the epilogue warps busy: [0, ride_begin) are dbias reductions
     int32_t fin_begin;          // tickets [fin_begin, total_tiles) finish the two-phase dbias reductions
     int32_t* dbias_sync;        // [2] arrival counters of the two phases; zero between launches
     int32_t static_schedule;    // 1 = ticket i goes to CTA i % grid instead of the dynamic queue
@@ -90,11 +117,6 @@ struct GroupParams {
     DeviceStatus* status;
     uint64_t wait_limit_ns;     // every wait inside the kernel gives up after this long
 };
-
-// ---- gradient all-reduce over peer memory -------------------------------------------------
-constexpr int kMaxCommRanks = 8;
-constexpr int kMaxCommCtas = 128;
-constexpr int kCommThreads = 256;
 
 // One rank's view of the exchange: the same three buffers on every rank, as pointers this
 // rank can dereference ([rank] = its own copy), plus its private call counters.
@@ -117,6 +139,7 @@ struct AllreduceParams {
 
 cudaError_t launch_grad_allreduce(const AllreduceParams& p, int ctas, int emulated_ranks, cudaStream_t stream);
 cudaError_t launch_grad_allreduce_mc(const AllreduceParams& p, int ctas, cudaStream_t stream);
+cudaError_t launch_exchange_begin_step(uint32_t* step_word, cudaStream_t stream);
 
 // Plan of one problem: the pure function of the problem (and of the work it shares a
 // launch with) that fixes tile width and split count.

@@ -343,6 +343,58 @@ __device__ __noinline__ void dbias_rows_warp(const ProblemScalars& p, int64_t i0
     }
 }
 
+// One ticket of a ride-along exchange: this rank's share of the range is cut into `tiles` chunks;
+// the `nw` epilogue warps that share ticket j sum chunk j inside the switch and let the switch
+// write the sum into every rank's copy.  First every other rank must have announced that its
+// partial sums of the range are complete (the wait is bounded).  Returns false if it gave up.
+__device__ __noinline__ bool ride_exchange_warp(const RideExchange& x, int j, int wid, int nw, int lane,
+                                                uint64_t wait_ns, DeviceStatus* status) {
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(x.local + kRideStep) * kMaxRidesPerStep +
+                       static_cast<uint32_t>(x.index);
+    int ok = 1;
+    if (lane < x.world && lane != x.rank) {
+        const uint32_t* f = x.local + kRideReady + lane;
+        uint64_t t0 = 0;
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(f) - e) < 0) {
+            if ((++spins & 31u) == 0u) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) {
+                    t0 = now;
+                } else if (now - t0 > wait_ns) {
+                    if (atomicCAS(&status->code, 0, kDevWaitPeer) == 0) {
+                        status->detail = 2048 + lane;
+                        status->block = static_cast<int32_t>(blockIdx.x);
+                    }
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    if (!__all_sync(0xffffffffu, ok)) return false;
+    const int64_t shard4 = (x.n4 + x.world - 1) / x.world;
+    const int64_t lo = static_cast<int64_t>(x.rank) * shard4;
+    const int64_t hi = lo + shard4 < x.n4 ? lo + shard4 : x.n4;
+    const int64_t chunk4 = (shard4 + x.tiles - 1) / x.tiles;
+    const int64_t c_lo = lo + static_cast<int64_t>(j) * chunk4;
+    const int64_t c_hi = c_lo + chunk4 < hi ? c_lo + chunk4 : hi;
+    float4* mc = reinterpret_cast<float4*>(x.mc);
+    const int64_t stride = static_cast<int64_t>(nw) * 32;
+    int64_t i = c_lo + static_cast<int64_t>(wid) * 32 + lane;
+    constexpr int kU = 4;  // switch round trips are long: four 16-byte reductions in flight per thread
+    for (; i + (kU - 1) * stride < c_hi; i += kU * stride) {
+        float4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) v[u] = multimem_ld_reduce_add(mc + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) multimem_st(mc + i + u * stride, v[u]);
+    }
+    for (; i < c_hi; i += stride) multimem_st(mc + i, multimem_ld_reduce_add(mc + i));
+    __threadfence_system();
+    return true;
+}
+
 // tcgen05.ld fills its destination registers asynchronously until tcgen05.wait::ld.  The
 // compiler must not schedule a read of them ahead of the wait: this empty statement, placed
 // after the wait, makes every later use depend on it.
@@ -450,6 +502,15 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     // previous kernel in the stream; nothing below may start before that kernel is done.
     grid_launch_dependents();
     grid_dependency_wait();
+    if (gp.ride.tiles > 0 && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < gp.ride.world &&
+        static_cast<int>(threadIdx.x) != gp.ride.rank) {
+        // Everything earlier in this stream is complete, so this rank's partial sums of the range
+        // that rides along are: tell the other ranks.
+        const uint32_t e = *reinterpret_cast<volatile uint32_t*>(gp.ride.local + kRideStep) * kMaxRidesPerStep +
+                           static_cast<uint32_t>(gp.ride.index);
+        __threadfence_system();
+        st_release_sys(gp.ride.peer_ready[threadIdx.x], e);
+    }
 
     // Barriers that live in the leader CTA of a pair, as cluster addresses usable from both.
     auto on_leader = [&](const void* bar) { return kPair ? mapa_shared(smem_u32(bar), 0u) : smem_u32(bar); };
@@ -700,6 +761,16 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (lane == 0) release_ring_slot(slot);
             const int t = tc.t;
             if (t < 0) break;
+            if (t >= gp.ride_begin && t < gp.colsum_total) {
+                // A ticket of the exchange that rides along.
+                if (!ride_exchange_warp(gp.ride, t - gp.ride_begin, static_cast<int>(rank) * kEpilogueWarps + ew,
+                                        CG * kEpilogueWarps, lane, wait_ns, status)) {
+                    if (lane == 0) ctl->abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                continue;
+            }
             if (t < gp.colsum_total) {
                 // A dbias reduction ticket of the problem that owns it.
                 int pi = 0;

@@ -43,14 +43,6 @@ constexpr uint32_t kSumChunk = 16384;                  // bytes per output buffe
 constexpr int kSumBufs = 4;
 constexpr uint32_t kCommSmemBytes = kPushChunk * kPushBufs;  // 192 KB; the reduce phase reuses the first 64 KB
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 // Staging slots are written by the peers: read them past L1.
 __device__ __forceinline__ float4 ld_stage(const float4* p) {
     float4 v;
@@ -289,20 +281,6 @@ grad_allreduce_kernel(const AllreduceParams P) {
 // broadcast, so all ranks hold the same bits; the order of the additions is the switch's.
 constexpr int kMcThreads = 256;
 
-__device__ __forceinline__ float4 multimem_ld_reduce_add(const float4* mc) {
-    float4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(mc)
-                 : "memory");
-    return v;
-}
-__device__ __forceinline__ void multimem_st(float4* mc, const float4& v) {
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(v.x), "f"(v.y),
-                 "f"(v.z), "f"(v.w)
-                 : "memory");
-}
-
 __global__ void __launch_bounds__(kMcThreads, 2)
 grad_allreduce_mc_kernel(const AllreduceParams P) {
     const CommRank& c = P.ctx[0];
@@ -344,6 +322,16 @@ grad_allreduce_mc_kernel(const AllreduceParams P) {
 }
 
 }  // namespace
+
+// Ride-along exchanges number themselves step * kMaxRidesPerStep + index; the step counter lives
+// on the device so that a captured step can be replayed.
+__global__ void exchange_begin_step_kernel(uint32_t* step_word) { *step_word = *step_word + 1u; }
+
+cudaError_t launch_exchange_begin_step(uint32_t* step_word, cudaStream_t stream) {
+    exchange_begin_step_kernel<<<1, 1, 0, stream>>>(step_word);
+    count_launch(1);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_grad_allreduce_mc(const AllreduceParams& p, int ctas, cudaStream_t stream) {
     grad_allreduce_mc_kernel<<<dim3(ctas, 1), kMcThreads, 0, stream>>>(p);

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(set(declared_symbols())) == sorted(set(L.EXPORTS) | set(declared_symbols()))
-    assert lib.llmt_b200_abi_version() == 3
+    assert lib.llmt_b200_abi_version() == 4
 
 
 def test_descriptor_layout_matches_the_header():
@@ -282,3 +282,34 @@ def test_fused_dbias_products_run_on_pairs_with_full_width_tiles():
     # row sums (A stored [m, k]) need no second phase and no workspace
     r = _desc(m=2304, n=768, k=512, lda=512, ldb=512, ldc=768, dbias=0x5000000)
     assert "dbias_tickets=72 " in L.plan(r) and L.workspace_bytes(r) == 0
+
+
+def test_ride_along_exchange_arguments_are_checked_before_anything_is_planned():
+    """llmt_b200_gemm_grouped_exchange: a missing multicast mapping, a bad range, a bad index and a
+    launch that writes the range it is asked to carry are refused on the host."""
+    d = _desc(m=256, n=256, k=256, trans_a=0, trans_b=1, lda=256, ldb=256, ldc=256, dtype_c=L.FP32)
+    descs = (L.GemmDesc * 1)(d)
+    span = 0x7000000  # fake device addresses: no call below reaches a launch
+    c = (ctypes.c_void_p * 1)(span + 4096)
+    a = (ctypes.c_void_p * 1)(0x1000000)
+    b = (ctypes.c_void_p * 1)(0x2000000)
+    comm = L.CommDesc()
+    comm.rank, comm.world = 0, 2
+    for r in range(2):
+        comm.grad[r] = span + r * 0x1000000
+        comm.flags[r] = 0x9000000 + r * 0x10000
+    lib = L.lib()
+
+    def call(off, cnt, idx):
+        return lib.llmt_b200_gemm_grouped_exchange(descs, c, a, b, 1, ctypes.byref(comm), off, cnt, idx, None)
+
+    assert lib.llmt_b200_gemm_grouped_exchange(descs, c, a, b, 1, None, 0, 4, 0, None) == L.ERR_INVALID
+    assert call(0, 1024, 0) == L.ERR_UNSUPPORTED and "multicast" in L.last_error()
+    comm.grad_mc = 0xA000000
+    assert call(2, 1024, 0) == L.ERR_INVALID and "multiples of 4" in L.last_error()
+    assert call(0, 0, 0) == L.ERR_INVALID
+    assert call(0, 1024, 16) == L.ERR_INVALID and "index" in L.last_error()
+    # C of the problem starts 4096 bytes into the span: a range that reaches it is refused
+    assert call(0, 2048, 0) == L.ERR_INVALID and "writes into the exchanged range" in L.last_error()
+    comm.world = 1
+    assert call(0, 1024, 0) == L.ERR_INVALID and "rank/world" in L.last_error()

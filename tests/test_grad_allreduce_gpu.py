@@ -209,6 +209,107 @@ def test_two_processes_through_switch_multicast(tmp_path):
     assert texts == ["ok"] * world
 
 
+def _ride_worker(rank, world, port, out_dir):
+    """A range of the span rides inside a grouped GEMM launch (llmt_b200_gemm_grouped_exchange): the
+    launch's own result and the exchanged range are both checked, three steps in a row and once
+    more on the same inputs (bitwise)."""
+    import torch.distributed as dist
+    from llmt_b200.dp import GradBucket, PeerExchange
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    msg = "ok"
+    try:
+        shapes = {"a.dW": (768, 2304), "a.dbias": (2304,), "b.dW": (512, 384), "b.dbias": (512,)}
+        ex = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=8, multicast=True)
+        if not ex.multicast:
+            msg = "no multicast"
+        else:
+            bucket = GradBucket(shapes, dev, storage=ex.attach)
+            g = torch.Generator(device=dev).manual_seed(11)  # same stream of numbers on every rank
+            bf = torch.bfloat16
+            # the launch that carries slice a: dW and dbias of layer b (written into slice b) plus an unrelated product
+            dy = [(torch.randn(1024, 512, device=dev, generator=g) * 0.1).to(bf) for _ in range(world)][rank]
+            x = [(torch.randn(1024, 384, device=dev, generator=g)).to(bf) for _ in range(world)][rank]
+            w = (torch.randn(512, 384, device=dev, generator=g) * 0.05).to(bf)
+            dx = torch.empty(1024, 384, device=dev, dtype=bf)
+            dw, db = bucket.view("b.dW"), bucket.view("b.dbias")
+            probs = [(L.make_desc(dx, dy, w, False, False), dx, dy, w),
+                     (L.make_desc(dw, dy, x, True, False, beta=1.0, dbias=db, dbias_beta=1.0), dw, dy, x)]
+            grp = L.Group(probs)
+            bufs = [torch.empty(max(b_, 256), dtype=torch.uint8, device=dev) for b_ in grp.workspace_bytes()]
+            grp.set_workspaces(bufs)
+            off_a, cnt_a = bucket.span_of(["a.dW", "a.dbias"])
+            off_b, cnt_b = bucket.span_of(["b.dW", "b.dbias"])
+            # a launch that writes the range it is asked to carry is refused
+            try:
+                grp.run_with_exchange(ex.desc, off_b, cnt_b, 0)
+                msg = "a launch that writes the exchanged range was accepted"
+            except L.LlmtB200Error as exc:
+                if exc.status != L.ERR_INVALID:
+                    msg = f"unexpected status {exc.status}"
+            for call in range(3):
+                if msg != "ok":
+                    break
+                parts = [torch.randn(bucket.flat.numel(), device=dev, generator=g) * (1.0 + r) for r in range(world)]
+
+                def step():
+                    bucket.flat.copy_(parts[rank])
+                    torch.cuda.synchronize(); dist.barrier()
+                    L.exchange_begin_step(ex.desc)
+                    grp.run_with_exchange(ex.desc, off_a, cnt_a, 0)   # slice a rides, slice b is produced
+                    ex.allreduce(off_b, cnt_b)                        # the last slice, and the step's closing rounds
+                    torch.cuda.synchronize(); dist.barrier()
+                    L.device_status()
+                    return bucket.flat.clone()
+
+                got = step()
+                # reference for slice b: start + this rank's dW/dbias, summed over the ranks
+                bucket.flat.copy_(parts[rank])
+                grp.run()
+                torch.cuda.synchronize()
+                local_b = bucket.flat[off_b:off_b + cnt_b].clone()
+                gathered = [torch.empty_like(local_b) for _ in range(world)]
+                dist.all_gather(gathered, local_b)
+                want_b = _rank_order_sum(gathered)
+                want_a = _rank_order_sum([p_[off_a:off_a + cnt_a] for p_ in parts])
+                ok_a = torch.equal(got[off_a:off_a + cnt_a], want_a) if world == 2 else \
+                    torch.allclose(got[off_a:off_a + cnt_a], want_a, rtol=1e-6, atol=1e-6)
+                ok_b = torch.equal(got[off_b:off_b + cnt_b], want_b) if world == 2 else \
+                    torch.allclose(got[off_b:off_b + cnt_b], want_b, rtol=1e-6, atol=1e-6)
+                if not (ok_a and ok_b):
+                    msg = f"call {call}: mismatch (carried range ok={ok_a}, produced range ok={ok_b})"
+                    break
+                if not torch.equal(step(), got):
+                    msg = f"call {call}: rerun differs"
+                    break
+            if msg == "ok":
+                gathered = [torch.empty_like(bucket.flat) for _ in range(world)]
+                dist.all_gather(gathered, bucket.flat)
+                if not all(torch.equal(gathered[0], t) for t in gathered):
+                    msg = "ranks disagree"
+        dist.barrier()
+    except Exception as exc:  # noqa: BLE001 - report instead of hanging the parent
+        msg = f"exception: {exc!r}"
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(msg)
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_exchange_riding_inside_a_grouped_launch(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_ride_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    texts = [(tmp_path / f"rank{r}.txt").read_text() for r in range(world)]
+    if all(t == "no multicast" for t in texts):
+        pytest.skip("the allocator offers no multicast mapping on this machine")
+    assert texts == ["ok"] * world
+
+
 @pytest.mark.parametrize("offset,count", [(0, 4096), (1, 1031), (3, 5), (2, 0), (0, 7080960)])
 def test_zero_grads_clears_exactly_the_span(offset, count):
     dev = torch.device("cuda", 0)
