@@ -200,7 +200,7 @@ class LinearStep:
     nothing but dy and x of its own layer, so it may run any time after them, and a short
     layer's few long dW tiles balance better inside a larger launch."""
 
-    def __init__(self, workload, m, dev, seed, world=1, exchange="peer", comm_ctas=8, defer=None):
+    def __init__(self, workload, m, dev, seed, world=1, exchange="peer", comm_ctas=8, defer=None, ride_min_gflop=30.0):
         import torch
         import llmt_b200 as L
         from llmt_b200.dp import GradBucket, PeerExchange
@@ -216,6 +216,7 @@ class LinearStep:
         # over NVLink ("peer" / "nvls"), or stays private and goes through NCCL ("nccl")
         self.exchange = None
         self.ride = False   # slices ride along in later backward launches (llmt_b200_gemm_grouped_exchange)
+        self.ride_min_flops = ride_min_gflop * 1e9  # a launch shorter than this carries nothing: the exchange would outlast it
         if world > 1 and exchange in ("peer", "nvls", "ride"):
             try:
                 self.exchange = PeerExchange(GradBucket.layout_numel(shapes), dev, ctas=comm_ctas,
@@ -334,10 +335,10 @@ class LinearStep:
         if ride:
             self.L.exchange_begin_step(self.exchange.desc)
         pending, index = [], 0
-        for label, _, fn, done, group in self.launches():
+        for label, lflops, fn, done, group in self.launches():
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record()
-            if ride and pending and group is not None:
+            if ride and pending and group is not None and lflops >= self.ride_min_flops:
                 off, cnt, covered = self.slice_runs(pending)[0]
                 group.run_with_exchange(self.exchange.desc, off, cnt, index)
                 index += 1
@@ -420,12 +421,10 @@ class AttentionStep:
 def make_step(workload, m, dev, seed, world=1, args=None):
     if workload == "c4":
         return AttentionStep(dev, seed)
-    # N > 1 with ride-along exchanges: every layer keeps its dW in its own backward launch, so that
-    # its slice is complete early enough to travel inside the next launch
-    riding = world > 1 and args is not None and args.exchange == "ride"
-    defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) and not riding else None
+    defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) else None
     return LinearStep(workload, m, dev, seed, world=world, exchange=args.exchange if args else "nccl",
-                      comm_ctas=(args.comm_ctas if args and args.comm_ctas else 8), defer=defer)
+                      comm_ctas=(args.comm_ctas if args and args.comm_ctas else 8), defer=defer,
+                      ride_min_gflop=(args.ride_min_gflop if args else 30.0))
 
 
 def timed_steps(torch, L, step, world, steps, warmup, use_graph, barrier):
@@ -971,6 +970,9 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="N > 1: SMs kept free of GEMM CTAs for the exchange (default 0 for nvls, "
                          "--comm-ctas for peer, 0 for nccl)")
+    ap.add_argument("--ride-min-gflop", type=float, default=30.0,
+                    help="N > 1, --exchange ride: a backward launch with less work than this carries no slice "
+                         "(the exchange would outlast it); its slice waits for the next launch")
     ap.add_argument("--no-defer", action="store_true",
                     help="c2: launch every layer's dW with its own dX (no deferred dW)")
     ap.add_argument("--no-graph", action="store_true",
@@ -994,7 +996,7 @@ def main():
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.comm_ctas is None:
-            args.comm_ctas = {"ride": 128, "nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
+            args.comm_ctas = {"ride": 64, "nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
         if args.exchange != "nccl":
             args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
         elif args.comm_ctas > 0:

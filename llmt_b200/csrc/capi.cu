@@ -493,6 +493,8 @@ static __device__ int32_t g_sched_counters[kSchedSlots];
 // Arrival counters of the two-phase dbias reduction, one pair per launch slot; the kernel
 // re-arms them too.
 static __device__ int32_t g_dbias_sync[kSchedSlots][2];
+// Chunk counters of the exchanges that ride along, one per launch slot; re-armed by the kernel.
+static __device__ int32_t g_ride_counters[kSchedSlots];
 
 // Per-device host state.  Several devices per process are supported as long as each device's
 // calls come from one host thread at a time (llmt's rule: one thread issues the launches,
@@ -501,6 +503,7 @@ struct DeviceGlobals {
     bool ready = false;
     int32_t* counters = nullptr;
     int32_t* dbias_sync = nullptr;
+    int32_t* ride_counters = nullptr;
     unsigned next = 0;
 };
 
@@ -519,14 +522,18 @@ int device_globals(DeviceGlobals** out) {
     if (!g->ready) {
         void* ctr = nullptr;
         void* sync = nullptr;
+        void* ride = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ctr, g_sched_counters);
         if (e == cudaSuccess) e = cudaMemset(ctr, 0, sizeof(int32_t) * kSchedSlots);
         if (e == cudaSuccess) e = cudaGetSymbolAddress(&sync, g_dbias_sync);
         if (e == cudaSuccess) e = cudaMemset(sync, 0, sizeof(int32_t) * kSchedSlots * 2);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ride, g_ride_counters);
+        if (e == cudaSuccess) e = cudaMemset(ride, 0, sizeof(int32_t) * kSchedSlots);
         if (e != cudaSuccess)
             return fail(LLMT_B200_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
         g->counters = static_cast<int32_t*>(ctr);
         g->dbias_sync = static_cast<int32_t*>(sync);
+        g->ride_counters = static_cast<int32_t*>(ride);
         g->ready = true;
     }
     *out = g;
@@ -705,13 +712,8 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         fin_total += p.fin_tiles;
         gp.prob[n++] = p;
     }
-    // The tickets of an exchange that rides along come after the dbias reductions: like them they
-    // keep only the epilogue warps busy.
-    const int64_t ride_begin = colsum_total;
-    if (ride != nullptr) {
-        if (n == 0) return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: the launch has no tile to ride along with");
-        colsum_total += ride->tiles;
-    }
+    if (ride != nullptr && n == 0)
+        return fail(LLMT_B200_ERR_INVALID, "gemm_grouped_exchange: the launch has no tile to ride along with");
     int64_t total = colsum_total;
     for (int i = 0; i < n; ++i) {
         if (total + gp.prob[i].num_tiles + fin_total > 0x7fffff00)
@@ -723,11 +725,12 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         const unsigned slot = g->next++ % kSchedSlots;
         gp.num_problems = n;
         gp.colsum_total = static_cast<int32_t>(colsum_total);
-        gp.ride_begin = static_cast<int32_t>(ride_begin);
-        if (ride != nullptr) gp.ride = *ride;
-        else gp.ride.tiles = 0;
         gp.fin_begin = static_cast<int32_t>(total);
         total += fin_total;
+        // An exchange that rides along is the side warps' work: its chunks are not tickets.
+        if (ride != nullptr) gp.ride = *ride;
+        else gp.ride.tiles = 0;
+        gp.ride_counter = g->ride_counters + slot;
         gp.total_tiles = static_cast<int32_t>(total);
         gp.sched_counter = g->counters + slot;
         gp.dbias_sync = g->dbias_sync + 2 * slot;
@@ -736,7 +739,8 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         gp.status = device_status_ptr();
         if (gp.status == nullptr) return fail(LLMT_B200_ERR_CUDA, "cannot resolve the device status word");
         const int units = pairs ? pair_units() : sm_count();
-        const int grid = static_cast<int>(total < units ? total : units) * (pairs ? 2 : 1);
+        // (with an exchange riding along every unit is launched: its side warps share the chunks)
+        const int grid = static_cast<int>(total < units && ride == nullptr ? total : units) * (pairs ? 2 : 1);
         cudaError_t e = launch_tc_grouped(gp, grid, pairs, stream);
         if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     }
@@ -986,12 +990,11 @@ int gemm_grouped_impl(const llmt_b200_gemm_desc* descs, void* const* c, const vo
     ride.world = comm->world;
     ride.rank = comm->rank;
     ride.index = xindex;
-    // About 64 KB of this rank's share per ticket; no more tickets than a few per CTA (pair).
+    // About 32 KB of this rank's share per chunk: four passes of a side warp with 8 KB in flight.
     const int64_t share_bytes = (ride.n4 + comm->world - 1) / comm->world * 16;
-    const int units = pairs ? pair_units() : sm_count();
-    int64_t tiles = (share_bytes + 65535) / 65536;
-    if (tiles > 4 * units) tiles = 4 * units;
+    int64_t tiles = (share_bytes + 32767) / 32768;
     if (tiles < 1) tiles = 1;
+    if (tiles > 0x3fffffff) tiles = 0x3fffffff;
     ride.tiles = static_cast<int32_t>(tiles);
     return launch_group(probs, n, pairs, static_cast<cudaStream_t>(stream), &ride);
 }
@@ -1153,6 +1156,7 @@ int llmt_b200_device_status(int32_t* code, int32_t* detail) {
         if (g != nullptr && g->ready) {
             cudaMemset(g->counters, 0, sizeof(int32_t) * kSchedSlots);
             cudaMemset(g->dbias_sync, 0, sizeof(int32_t) * kSchedSlots * 2);
+            cudaMemset(g->ride_counters, 0, sizeof(int32_t) * kSchedSlots);
         }
         return fail(LLMT_B200_ERR_DEVICE, "a kernel gave up on a bounded wait: code %d detail %d block %d",
                     h.code, h.detail, h.block);

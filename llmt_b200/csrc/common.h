@@ -100,16 +100,16 @@ struct RideExchange {
     uint32_t* peer_ready[kMaxCommRanks];   // [r]: where this rank announces itself to rank r
     int32_t world, rank;
     int32_t index;                         // which ride-along exchange of the step (0 .. kMaxRidesPerStep-1)
-    int32_t tiles;                         // tickets
+    int32_t tiles;                         // chunks this rank's share of the range is cut into
 };
 
 struct GroupParams {
     GroupProblem prob[kMaxGroupProblems];
     RideExchange ride;
-    int32_t ride_begin;         // tickets [ride_begin, colsum_total) belong to the ride-along exchange
+    int32_t* ride_counter;      // the side warps draw the exchange's chunks from it; zero between launches
     int32_t num_problems;
-    int32_t total_tiles;        // tickets of the launch: dbias reductions, exchange, MMA tiles, dbias finishing tickets
-    int32_t colsum_total;       // tickets [0, colsum_total) keep only the epilogue warps busy: [0, ride_begin) are dbias reductions
+    int32_t total_tiles;        // tickets of the launch: dbias reductions, MMA tiles, dbias finishing tickets
+    int32_t colsum_total;       // tickets [0, colsum_total) are dbias reductions
     int32_t fin_begin;          // tickets [fin_begin, total_tiles) finish the two-phase dbias reductions
     int32_t* dbias_sync;        // [2] arrival counters of the two phases; zero between launches
     int32_t static_schedule;    // 1 = ticket i goes to CTA i % grid instead of the dynamic queue

@@ -7,8 +7,11 @@
 //   warp 0      scheduler + TMA producer: draws the next ticket from a global counter,
 //               publishes it to the other roles through a small ring in shared memory,
 //               then streams the even k-blocks of that tile's operands
-//   warps 10-11 helper TMA producers (CTA pairs only): the three producer warps take the
-//               k-blocks round robin
+//   warp 10     helper TMA producer (CTA pairs only): the two producer warps take the k-blocks
+//               in turn
+//   warp 11     side warp: when the launch carries a gradient exchange (see RideExchange), it
+//               sums chunks of that range over the ranks through the NVSwitch while the other
+//               warps run the launch's tiles; idle otherwise
 //   warp 1      MMA issuer (one lane issues tcgen05.mma / tcgen05.commit; the warp
 //               owns the TMEM allocation)
 //   warps 2-9   epilogue: tcgen05.ld, alpha/beta/bias/GELU/cast, store C.  Two warps per
@@ -58,7 +61,8 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 384;
 constexpr int kEpilogueWarps = 8;
 constexpr int kProducerHelperWarp = 10;  // first of the helper TMA producer warps (CTA pairs only)
-constexpr int kProducerHelpers = 2;
+constexpr int kProducerHelpers = 1;
+constexpr int kSideWarp = 11;            // works on the exchange that rides along, nothing else
 constexpr int kMaxStages = 6;
 constexpr int kRing = 4;                             // scheduler ring entries
 constexpr uint32_t kATileBytes = BM * BK * 2;        // 16 KB
@@ -71,6 +75,12 @@ constexpr uint32_t kStoreBufBytes = 32 * 128;        // one staging buffer: 32 r
 // tensor pipe (measured with five stages: 0.34-0.43 us per k-block).
 #ifndef LLMT_B200_PAIR_STAGES
 #define LLMT_B200_PAIR_STAGES 6
+#endif
+// 16-byte sums one lane of a side warp keeps in flight.  More is slower, not faster: at 16 the
+// exchange's requests crowd the GEMM's own loads out of the memory system (two GPUs, GPT-2 step:
+// 0.427 ms at 8, 0.435 at 4, 0.453 at 16, 0.550 at 32).
+#ifndef LLMT_B200_RIDE_UNROLL
+#define LLMT_B200_RIDE_UNROLL 8
 #endif
 #ifndef LLMT_B200_PAIR_STORE_BUFS
 #define LLMT_B200_PAIR_STORE_BUFS 1
@@ -343,12 +353,14 @@ __device__ __noinline__ void dbias_rows_warp(const ProblemScalars& p, int64_t i0
     }
 }
 
-// One ticket of a ride-along exchange: this rank's share of the range is cut into `tiles` chunks;
-// the `nw` epilogue warps that share ticket j sum chunk j inside the switch and let the switch
-// write the sum into every rank's copy.  First every other rank must have announced that its
-// partial sums of the range are complete (the wait is bounded).  Returns false if it gave up.
-__device__ __noinline__ bool ride_exchange_warp(const RideExchange& x, int j, int wid, int nw, int lane,
-                                                uint64_t wait_ns, DeviceStatus* status) {
+// The exchange that rides along, as one warp per CTA sees it: this rank's share of the range is
+// cut into `tiles` chunks that the side warps of all CTAs draw from a counter of their own (the
+// tile queue and the warps that serve it never see them, so a slow round trip through the switch
+// cannot hold up an epilogue).  A chunk is summed inside the switch (multimem.ld_reduce) and
+// written into every rank's copy by it (multimem.st).  First every other rank must have
+// announced that its partial sums of the range are complete; the wait is bounded.
+__device__ __noinline__ void ride_exchange_side_warp(const RideExchange& x, int32_t* counter, int lane,
+                                                     uint64_t wait_ns, DeviceStatus* status) {
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(x.local + kRideStep) * kMaxRidesPerStep +
                        static_cast<uint32_t>(x.index);
     int ok = 1;
@@ -372,27 +384,37 @@ __device__ __noinline__ bool ride_exchange_warp(const RideExchange& x, int j, in
             }
         }
     }
-    if (!__all_sync(0xffffffffu, ok)) return false;
+    ok = __all_sync(0xffffffffu, ok);
     const int64_t shard4 = (x.n4 + x.world - 1) / x.world;
     const int64_t lo = static_cast<int64_t>(x.rank) * shard4;
     const int64_t hi = lo + shard4 < x.n4 ? lo + shard4 : x.n4;
     const int64_t chunk4 = (shard4 + x.tiles - 1) / x.tiles;
-    const int64_t c_lo = lo + static_cast<int64_t>(j) * chunk4;
-    const int64_t c_hi = c_lo + chunk4 < hi ? c_lo + chunk4 : hi;
     float4* mc = reinterpret_cast<float4*>(x.mc);
-    const int64_t stride = static_cast<int64_t>(nw) * 32;
-    int64_t i = c_lo + static_cast<int64_t>(wid) * 32 + lane;
-    constexpr int kU = 4;  // switch round trips are long: four 16-byte reductions in flight per thread
-    for (; i + (kU - 1) * stride < c_hi; i += kU * stride) {
-        float4 v[kU];
+    constexpr int kU = LLMT_B200_RIDE_UNROLL;  // sums of 16 bytes in flight per lane
+    const int n_side = static_cast<int>(gridDim.x);
+    for (;;) {
+        // Every side warp draws until it gets a ticket past the end; the last such draw re-arms the counter.
+        int j = 0;
+        if (lane == 0) j = atomicAdd(counter, 1);
+        j = __shfl_sync(0xffffffffu, j, 0);
+        if (j >= x.tiles) {
+            if (lane == 0 && j == x.tiles + n_side - 1) *counter = 0;
+            break;
+        }
+        if (!ok) continue;  // gave up on a peer: the tickets are still drawn, so that the counter re-arms
+        const int64_t c_lo = lo + static_cast<int64_t>(j) * chunk4;
+        const int64_t c_hi = c_lo + chunk4 < hi ? c_lo + chunk4 : hi;
+        int64_t i = c_lo + lane;
+        for (; i + (kU - 1) * 32 < c_hi; i += kU * 32) {
+            float4 v[kU];
 #pragma unroll
-        for (int u = 0; u < kU; ++u) v[u] = multimem_ld_reduce_add(mc + i + u * stride);
+            for (int u = 0; u < kU; ++u) v[u] = multimem_ld_reduce_add(mc + i + u * 32);
 #pragma unroll
-        for (int u = 0; u < kU; ++u) multimem_st(mc + i + u * stride, v[u]);
+            for (int u = 0; u < kU; ++u) multimem_st(mc + i + u * 32, v[u]);
+        }
+        for (; i < c_hi; i += 32) multimem_st(mc + i, multimem_ld_reduce_add(mc + i));
     }
-    for (; i < c_hi; i += stride) multimem_st(mc + i, multimem_ld_reduce_add(mc + i));
     __threadfence_system();
-    return true;
 }
 
 // tcgen05.ld fills its destination registers asynchronously until tcgen05.wait::ld.  The
@@ -520,16 +542,15 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         else mbar_arrive(smem_u32(&ctl->sched_empty[slot]));
     };
 
-    if (warp == 0 || (kPair && warp >= kProducerHelperWarp)) {
+    if (warp == 0 || (kPair && warp >= kProducerHelperWarp && warp < kProducerHelperWarp + kProducerHelpers)) {
         // ------------------------------------------- scheduler + TMA producers
-        // Three producer warps take the k-blocks round robin.  The operand pipeline is bound by
-        // bytes in flight (six stages against a load latency of about six k-block times), so a
-        // load that is issued late is a bubble in the tensor pipe later: a producer must be
-        // waiting at a stage's barrier when the stage frees, and the work between two tiles
-        // (reading the ticket, decoding it: ~1000 cycles) must fit into the time until that warp's
-        // next k-block is due.  With two warps it did not (measured: the first load of a tile left
-        // ~1500 cycles after its stage was free).  In each warp the whole warp walks the loop;
-        // lane 0 does the barrier bookkeeping and lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
+        // Two producer warps take the k-blocks in turn.  The operand pipeline is bound by bytes
+        // in flight (six stages against a load latency of about six k-block times), so a load
+        // that is issued late is a bubble in the tensor pipe later: a producer must be waiting at
+        // a stage's barrier when the stage frees.  One iteration costs a few hundred cycles of
+        // barrier and issue latency, which a single warp cannot hide (a third warp measured no
+        // further gain).  In each warp the whole warp walks the loop; lane 0 does the barrier
+        // bookkeeping and lane L issues the L-th box of a stage, so the up to six TMA boxes of a k-block
         // (MN-major operands come in 64-wide blocks) leave in one issue slot.  Warp 0 of the
         // leader also runs the scheduler.
         const bool scheduler = warp == 0 && leader;
@@ -741,6 +762,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 ++acc_seq;
             }
         }
+    } else if (warp == kSideWarp) {
+        // ------------------------------------------------------------ side warp
+        if (gp.ride.tiles > 0) ride_exchange_side_warp(gp.ride, gp.ride_counter, lane, wait_ns, status);
     } else if (warp < 2 + kEpilogueWarps) {
         // ---------------------------------------------------------- epilogue
         const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
@@ -761,16 +785,6 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (lane == 0) release_ring_slot(slot);
             const int t = tc.t;
             if (t < 0) break;
-            if (t >= gp.ride_begin && t < gp.colsum_total) {
-                // A ticket of the exchange that rides along.
-                if (!ride_exchange_warp(gp.ride, t - gp.ride_begin, static_cast<int>(rank) * kEpilogueWarps + ew,
-                                        CG * kEpilogueWarps, lane, wait_ns, status)) {
-                    if (lane == 0) ctl->abort_flag = 1;
-                    ok = false;
-                    break;
-                }
-                continue;
-            }
             if (t < gp.colsum_total) {
                 // A dbias reduction ticket of the problem that owns it.
                 int pi = 0;
