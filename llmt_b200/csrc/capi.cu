@@ -112,6 +112,16 @@ int kblock_cost(int bn, bool pairs) {
 
 int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
+// Debug hook, read once: LLMT_B200_DBIAS_TICKETS=1 keeps the ticket form of the fused dbias.
+bool dbias_tickets_forced() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LLMT_B200_DBIAS_TICKETS");
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // dbias_mode: 0 none, 1 column sums of A stored [k, m] (two phases), 2 row sums of A stored [m, k].
 void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode, int bn, int splits,
                  bool pairs) {
@@ -133,9 +143,17 @@ void finish_plan(TcPlan* pl, int64_t m, int64_t n, int64_t k, int64_t batch, int
     // The fused dbias runs as tickets of its own, independent of the product's tiling.
     const int cg = pairs ? 2 : 1;
     pl->dbias_mode = k > 0 ? dbias_mode : 0;
+    // Column sums of a single (unbatched) product come from the A stages in shared memory (mode 3);
+    // the ticket form (mode 1) remains for batches.
+    if (pl->dbias_mode == 1 && batch <= 1 && !dbias_tickets_forced()) pl->dbias_mode = 3;
     pl->colsum_tiles = pl->dbias_rows = pl->fin_tiles = 0;
     pl->ws_dbias_off = 0;
-    if (pl->dbias_mode == 1) {
+    if (pl->dbias_mode == 3) {
+        if (pl->splits > 1) {  // one row of sums per split; the split-K reduction adds them
+            pl->ws_dbias_off = pl->workspace_bytes;
+            pl->workspace_bytes += (static_cast<size_t>(pl->splits) * m * sizeof(float) + 255) / 256 * 256;
+        }
+    } else if (pl->dbias_mode == 1) {
         // chunks of at least 64 rows of A, at most 512 chunks
         const int64_t rows = ceil_div(k, 512) > 64 ? ceil_div(k, 512) : 64;
         pl->dbias_rows = static_cast<int>(rows);
@@ -650,7 +668,8 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->dbias_rows = pl.dbias_rows;
     p->fin_tiles = pl.fin_tiles;
     if (pl.splits > 1) p->ws = static_cast<float*>(d->workspace);
-    if (pl.dbias_mode == 1) p->ws_dbias = reinterpret_cast<float*>(static_cast<char*>(d->workspace) + pl.ws_dbias_off);
+    if (pl.dbias_mode == 1 || (pl.dbias_mode == 3 && pl.splits > 1))
+        p->ws_dbias = reinterpret_cast<float*>(static_cast<char*>(d->workspace) + pl.ws_dbias_off);
     if (d->k == 0) return LLMT_B200_OK;  // no operand is read
     int st = encode_operand_map(&p->map_a, a, ck.a_rows, ck.a_cols, d->lda,
                                 batch_layout(d->batch, d->batch_inner, d->stride_a, d->stride_a_outer), p->a_mn ? 64 : 128);

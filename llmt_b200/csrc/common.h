@@ -47,7 +47,8 @@ struct ProblemScalars {
     int32_t a_mn, b_mn;         // operand stored with M / N contiguous (transposed use)
     int32_t tile_begin;         // first MMA tile of this problem in the group's queue
     int32_t num_tiles;          // tiles_m * tiles_n * splits * batch
-    int32_t dbias_mode;         // 0 none; 1 column sums of A stored [k, m] (two phases); 2 row sums of A stored [m, k]
+    int32_t dbias_mode;         // 0 none; 1 column sums of A stored [k, m] by tickets (two phases); 2 row sums of A stored
+                                // [m, k] by tickets; 3 column sums of A stored [k, m] from the stages in shared memory
     int32_t colsum_begin;       // first dbias ticket of this problem in the group's queue
     int32_t colsum_tiles;       // mode 1: chunks of rows of A; mode 2: blocks of rows of op(A)
     int32_t dbias_rows;         // mode 1: rows of A per ticket
@@ -68,7 +69,7 @@ struct ProblemScalars {
     float* ws;                  // split-K partial sums [batch][splits][m][n] fp32 (splits > 1)
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
-    float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums
+    float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums; mode 3 with splits: [splits][m]
 };
 static_assert(sizeof(ProblemScalars) % 8 == 0 && sizeof(ProblemScalars) <= 256, "ProblemScalars is copied to shared memory");
 
@@ -150,7 +151,7 @@ struct TcPlan {
     int tiles_m, tiles_n;
     int kblocks_total, kblocks_per_split;
     int64_t num_tiles;
-    int dbias_mode;     // 0 none, 1 column sums in two phases, 2 row sums
+    int dbias_mode;     // 0 none, 1 column sums in two phases, 2 row sums, 3 column sums from shared memory
     int colsum_tiles;   // dbias reduction tickets
     int dbias_rows;     // mode 1: rows of A per ticket
     int fin_tiles;      // mode 1: finishing tickets

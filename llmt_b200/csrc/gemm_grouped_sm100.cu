@@ -120,6 +120,8 @@ struct __align__(16) Control {
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t landed[kMaxStages];   // peer CTA of a pair: "this stage's operands are in" (the full barrier lives in the leader)
+    uint64_t sum_bar[2];           // the epilogue warps among themselves, around the cross-warp dbias sum
     uint64_t sched_full[kRing];
     uint64_t sched_empty[kRing];
     TileCoord ring[kRing];
@@ -462,8 +464,14 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
-            mbar_init(smem_u32(&ctl->empty[s]), 1);
+            // A stage is released by the MMAs that read it (one commit) and by the eight epilogue
+            // warps, which read it too when the tile sums its A operand for a bias gradient; for
+            // every other tile the producer arrives in their place.
+            mbar_init(smem_u32(&ctl->empty[s]), 1 + kEpilogueWarps);
+            mbar_init(smem_u32(&ctl->landed[s]), 1);
         }
+        mbar_init(smem_u32(&ctl->sum_bar[0]), kEpilogueWarps);
+        mbar_init(smem_u32(&ctl->sum_bar[1]), kEpilogueWarps);
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
             mbar_init(smem_u32(&ctl->tmem_empty[a]), CG * kEpilogueWarps);      // both CTAs' epilogues
@@ -670,6 +678,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
             }
+            const bool tile_sums = p.dbias_mode == 3 && tc.n_tile == 0;  // the epilogue warps read this tile's A stages
             const int draw_kb = tc.kb1 - kDrawAhead > tc.kb0 ? tc.kb1 - kDrawAhead : tc.kb0;
             const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : 0x7fffffff;
             const int after_own = n_turns > 1 ? 1 : 0;
@@ -696,6 +705,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     // The leader's barrier counts the bytes of both CTAs of a pair.  Bytes that land
                     // before this arrival are counted all the same; the phase cannot complete without it.
                     if (lane == 0 && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
+                    // the stage's next release: nobody but the MMAs will read it
+                    if (lane == 0 && !tile_sums) mbar_arrive_count(smem_u32(&ctl->empty[stage]), kEpilogueWarps);
                     if (my_map != nullptr) {
                         const int k0 = kb * BK;
                         const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
@@ -773,6 +784,10 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         const uint32_t my_bufs = staging_base + static_cast<uint32_t>(ew * kStoreBufs) * kStoreBufBytes;
         uint32_t buf_seq = 0;  // TMA stores this warp has issued so far
         uint32_t acc_seq = 0;  // accumulator slot counter, in step with the MMA issuer's
+        int e_stage = 0;       // stage and phase of the next tile's first k-block: the epilogue warps follow
+        uint32_t e_phase = 0;  // the CTA's k-block sequence, because on some tiles they read the stages too
+        uint32_t sum_phase = 0;
+        uint32_t landed_bits = 0;  // peer CTA: parity of each stage's `landed` barrier (it moves on summing tiles only)
         bool ok = true;
         for (int it = 0; ok; ++it) {
             const int slot = it % kRing;
@@ -858,6 +873,117 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             }
             const ProblemScalars& p = sp[tc.prob];
             const int acc = static_cast<int>(acc_seq & 1u);
+            const int nkb = tc.kb1 - tc.kb0;
+            if (p.dbias_mode == 3 && tc.n_tile == 0) {
+                // ---- bias gradient of a dW product: dbias[i] = sum over k of op(A)[i, k], A stored
+                // [k, m].  The tile's A operand passes through shared memory anyway, and these warps
+                // have nothing to do until the accumulator is complete: they add up every A stage
+                // as it lands (a second reader of the stage beside the MMAs; both release it), so dy
+                // is not read from memory a second time and nothing competes with the operand loads.
+                // Warp w takes k-rows 8w..8w+7 of a stage; lane L the four m-columns 4 (L % 16) ..+3
+                // of the 64-wide block L / 16 (one 8-byte read per row, 128-byte swizzle undone by
+                // hand); rows, k-blocks and warps are added in ascending order: fixed order, no atomics.
+                float dsum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint32_t blk = static_cast<uint32_t>(lane >> 4) * kBlock64Bytes;
+                const uint32_t chunk = static_cast<uint32_t>(lane & 15) >> 1, half8 = static_cast<uint32_t>(lane & 1) * 8u;
+                for (int i = 0; i < nkb && ok; ++i) {
+                    if (lane == 0) {
+                        if (leader) {
+                            ok = bounded_wait<kPair>(smem_u32(&ctl->full[e_stage]), e_phase, abort_flag, status,
+                                                     kDevWaitSmemFull, 64 + e_stage, wait_ns);
+                            // the peer CTA cannot see the leader's barrier: pass the news on
+                            if (kPair && ok && ew == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&ctl->landed[e_stage]), 1u));
+                        } else {
+                            uint64_t t0 = 0;
+                            uint32_t spins = 0;
+                            while (!mbar_try_wait_cluster(smem_u32(&ctl->landed[e_stage]), (landed_bits >> e_stage) & 1u)) {
+                                if ((++spins & 255u) == 0u) {
+                                    const uint64_t now = globaltimer_ns();
+                                    if (*abort_flag) { ok = false; break; }
+                                    if (t0 == 0) {
+                                        t0 = now;
+                                    } else if (now - t0 > wait_ns) {
+                                        if (atomicCAS(&status->code, 0, kDevWaitSmemFull) == 0) {
+                                            status->detail = 96 + e_stage;
+                                            status->block = static_cast<int32_t>(blockIdx.x);
+                                        }
+                                        *abort_flag = 1;
+                                        ok = false;
+                                        break;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    landed_bits ^= 1u << e_stage;
+                    const uint32_t base = smem_base + static_cast<uint32_t>(e_stage) * kStageBytes + blk + half8;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const uint32_t row = static_cast<uint32_t>(8 * ew + r);
+                        uint32_t lo, hi;
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi)
+                                     : "r"(base + row * 128u + ((chunk ^ (row & 7u)) << 4)));
+                        dsum[0] += __uint_as_float(lo << 16);
+                        dsum[1] += __uint_as_float(lo & 0xFFFF0000u);
+                        dsum[2] += __uint_as_float(hi << 16);
+                        dsum[3] += __uint_as_float(hi & 0xFFFF0000u);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[e_stage]));  // this warp is done with the stage
+                    if (++e_stage == kStages) { e_stage = 0; e_phase ^= 1u; }
+                }
+                if (!ok) break;
+                // The eight warps' sums meet in the staging buffers (free once the TMA stores that
+                // last read them have done so); warp 0 adds them in warp order and writes the result.
+                if (lane == 0) bulk_wait_group_read_n<0>();
+                __syncwarp();
+                const uint32_t slot_off = static_cast<uint32_t>(64 * (lane >> 4) + 4 * (lane & 15)) * 4u;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(my_bufs + slot_off), "r"(__float_as_uint(dsum[0])), "r"(__float_as_uint(dsum[1])),
+                               "r"(__float_as_uint(dsum[2])), "r"(__float_as_uint(dsum[3])) : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->sum_bar[0]));
+                if (lane == 0)
+                    ok = bounded_wait(smem_u32(&ctl->sum_bar[0]), sum_phase, abort_flag, status, kDevWaitSched, 80, wait_ns);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                if (ew == 0) {
+                    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int w = 0; w < kEpilogueWarps; ++w) {
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                     : "r"(staging_base + static_cast<uint32_t>(w * kStoreBufs) * kStoreBufBytes + slot_off));
+                        tot[0] += __uint_as_float(v0); tot[1] += __uint_as_float(v1);
+                        tot[2] += __uint_as_float(v2); tot[3] += __uint_as_float(v3);
+                    }
+                    const int64_t i0 = static_cast<int64_t>(tc.m_tile) * kTileRows + static_cast<int64_t>(rank) * BM +
+                                       64 * (lane >> 4) + 4 * (lane & 15);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (i0 + e >= p.m) break;
+                        if (p.splits > 1) {
+                            p.ws_dbias[static_cast<int64_t>(tc.split) * p.m + i0 + e] = tot[e];  // the split-K reduction adds the splits
+                        } else {
+                            const float prev = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i0 + e] : 0.0f;
+                            p.dbias[i0 + e] = prev + tot[e];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->sum_bar[1]));  // the staging buffers may be written again
+                if (lane == 0)
+                    ok = bounded_wait(smem_u32(&ctl->sum_bar[1]), sum_phase, abort_flag, status, kDevWaitSched, 81, wait_ns);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                sum_phase ^= 1u;
+            } else {
+                const int total = e_stage + nkb;
+                e_phase ^= static_cast<uint32_t>(total / kStages) & 1u;
+                e_stage = total % kStages;
+            }
             // Everything a step needs is read from the problem's scalars ONCE per tile, into
             // registers: a step is a chain of dependent instructions executed by a warp that has
             // one other warp to share its scheduler with, so every shared-memory read and every
@@ -1149,9 +1275,17 @@ __global__ void splitk_reduce_kernel(const GroupProblem p) {
                 static_cast<float*>(p.c)[c_off + j] = v;
         }
     }
-    // An empty reduction (k == 0) sums nothing into the bias gradient either.
-    if (p.splits == 0 && p.dbias != nullptr && i < p.m)
-        p.dbias[i] = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+    if (p.dbias != nullptr && i < p.m) {
+        if (p.splits == 0) {
+            // An empty reduction (k == 0) sums nothing into the bias gradient either.
+            p.dbias[i] = p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f;
+        } else if (p.dbias_mode == 3) {
+            // The tiles summed their A stages per split; the splits are added here, in order.
+            float acc = 0.0f;
+            for (int s = 0; s < p.splits; ++s) acc += p.ws_dbias[static_cast<int64_t>(s) * p.m + i];
+            p.dbias[i] = (p.dbias_beta != 0.0f ? p.dbias_beta * p.dbias[i] : 0.0f) + acc;
+        }
+    }
 }
 
 }  // namespace

@@ -266,19 +266,26 @@ def test_exchange_layout_is_aligned_and_large_enough():
 
 
 def test_fused_dbias_products_run_on_pairs_with_full_width_tiles():
-    # dW + dbias: the bias gradient is reduced by tickets of its own (chunks of 64 rows of dy over all
-    # columns, then one finishing ticket per 256 values per CTA), so the product keeps 256-wide tiles
-    # on CTA pairs (the QKV layer of GPT-2-small: 2304 x 768 over 8192 tokens, split in two so that
-    # its 27 tiles fill the 74 pairs)
+    # dW + dbias of one (unbatched) product: the epilogue warps add up the A stages in shared memory, so
+    # the product keeps 256-wide tiles on CTA pairs and there are no dbias tickets (the QKV layer of
+    # GPT-2-small: 2304 x 768 over 8192 tokens, split in two so that its 27 tiles fill the 74 pairs)
     d = _desc(m=2304, n=768, k=8192, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
               dtype_c=L.FP32, beta=1.0, dbias=0x5000000, dbias_beta=1.0)
     plan = L.plan(d)
     assert "cta-pair tile=256x256x64" in plan and "splits=2 " in plan
-    assert "dbias_tickets=133 " in plan  # 8192 / 64 chunks of rows + 2304 / (2 x 256) finishing tickets
-    # the partial sums of the bias gradient live in the workspace, after the split-K partial sums
-    assert L.workspace_bytes(d) == 2 * 2304 * 768 * 4 + 128 * 2304 * 4
+    assert "dbias_tickets=0 " in plan
+    # one row of sums per split lives in the workspace, after the split-K partial sums
+    assert L.workspace_bytes(d) == 2 * 2304 * 768 * 4 + 2 * 2304 * 4
     d.plan_cta_pairs = 1
-    assert "1-cta tile=128x" in L.plan(d) and "dbias_tickets=137 " in L.plan(d)
+    assert "1-cta tile=128x" in L.plan(d) and "dbias_tickets=0 " in L.plan(d)
+    d.plan_cta_pairs = 0
+    d.plan_splits = 1
+    assert L.workspace_bytes(d) == 0  # unsplit: the tiles write dbias themselves
+    # a batch keeps the ticket form: chunks of 64 rows of A over all columns, then finishing tickets
+    bt = _desc(m=2304, n=768, k=8192, batch=2, trans_a=1, trans_b=0, lda=2304, ldb=768, ldc=768,
+               stride_a=8192 * 2304, stride_b=8192 * 768, stride_c=2304 * 768,
+               dtype_c=L.FP32, dbias=0x5000000)
+    assert "dbias_tickets=133 " in L.plan(bt)
     # row sums (A stored [m, k]) need no second phase and no workspace
     r = _desc(m=2304, n=768, k=512, lda=512, ldb=512, ldc=768, dbias=0x5000000)
     assert "dbias_tickets=72 " in L.plan(r) and L.workspace_bytes(r) == 0
