@@ -996,7 +996,7 @@ def main():
         import torch.distributed as dist  # noqa: F401 (also binds torch.distributed)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.comm_ctas is None:
-            args.comm_ctas = {"ride": 64, "nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
+            args.comm_ctas = {"ride": 48, "nvls": 64, "peer": 16, "nccl": 0}[args.exchange]
         if args.exchange != "nccl":
             args.comm_ctas = max(1, min(args.comm_ctas, L.COMM_MAX_CTAS))
         elif args.comm_ctas > 0:

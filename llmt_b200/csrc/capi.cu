@@ -601,23 +601,54 @@ Repack repack_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* 
 
 // Copies the operands that need it behind the split-K region of the workspace and rewrites
 // the (local) descriptor and pointers to use the copies.
+// Copies made for earlier problems of the same grouped launch: an operand that several problems
+// share (dy is the A operand of a layer's dX and of its dW) is copied once.
+struct RepackDone {
+    const void* src;
+    int64_t rows, cols, ld, nb, stride;
+    const void* dst;
+};
+struct RepackCache {
+    RepackDone done[2 * kMaxGroupProblems];
+    int n = 0;
+    const void* find(const void* src, int64_t rows, int64_t cols, int64_t ld, int64_t nb, int64_t stride) const {
+        for (int i = 0; i < n; ++i) {
+            const RepackDone& r = done[i];
+            if (r.src == src && r.rows == rows && r.cols == cols && r.ld == ld && r.nb == nb && r.stride == stride) return r.dst;
+        }
+        return nullptr;
+    }
+    void add(const void* src, int64_t rows, int64_t cols, int64_t ld, int64_t nb, int64_t stride, const void* dst) {
+        if (n < 2 * kMaxGroupProblems) done[n++] = RepackDone{src, rows, cols, ld, nb, stride, dst};
+    }
+};
+
 int apply_repack(llmt_b200_gemm_desc* d, const Checked& ck, const Repack& rp, size_t ws_offset,
-                 const void** a, const void** b, cudaStream_t stream) {
+                 const void** a, const void** b, cudaStream_t stream, RepackCache* cache = nullptr) {
     char* base = static_cast<char*>(d->workspace) + ws_offset;
+    const int64_t nb = d->batch > 1 ? d->batch : 1;
+    auto one = [&](const void** src, int64_t rows, int64_t cols, int64_t ld, int64_t stride, int64_t new_ld,
+                   int64_t new_stride, char* dst) -> int {
+        const void* have = cache != nullptr ? cache->find(*src, rows, cols, ld, nb, stride) : nullptr;
+        if (have == nullptr) {
+            cudaError_t e = launch_repack_bf16(dst, *src, rows, cols, ld, new_ld, nb, stride, new_stride, stream);
+            if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+            if (cache != nullptr) cache->add(*src, rows, cols, ld, nb, stride, dst);
+            have = dst;
+        }
+        *src = have;
+        return LLMT_B200_OK;
+    };
     if (rp.a) {
-        cudaError_t e = launch_repack_bf16(base, *a, ck.a_rows, ck.a_cols, d->lda, rp.lda, d->batch > 1 ? d->batch : 1,
-                                           d->batch > 1 ? d->stride_a : 0, rp.stride_a, stream);
-        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
-        *a = base;
+        const int st = one(a, ck.a_rows, ck.a_cols, d->lda, d->batch > 1 ? d->stride_a : 0, rp.lda, rp.stride_a, base);
+        if (st != LLMT_B200_OK) return st;
         d->lda = rp.lda;
         d->stride_a = rp.stride_a;
         base += rp.bytes_a;
     }
     if (rp.b) {
-        cudaError_t e = launch_repack_bf16(base, *b, ck.b_rows, ck.b_cols, d->ldb, rp.ldb, d->batch > 1 ? d->batch : 1,
-                                           d->batch > 1 ? d->stride_b : 0, rp.stride_b, stream);
-        if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
-        *b = base;
+        const int st = one(b, ck.b_rows, ck.b_cols, d->ldb, d->batch > 1 ? d->stride_b : 0, rp.ldb, rp.stride_b, base);
+        if (st != LLMT_B200_OK) return st;
         d->ldb = rp.ldb;
         d->stride_b = rp.stride_b;
     }
@@ -975,6 +1006,7 @@ int gemm_grouped_impl(const llmt_b200_gemm_desc* descs, void* const* c, const vo
                         "gemm_grouped: problem %d asks for CTA pairs, but another problem of the launch cannot run "
                         "on pairs (a launch is all pairs or all single CTAs)", i);
     GroupProblem probs[kMaxGroupProblems];
+    RepackCache repacked;
     int n = 0;
     for (int i = 0; i < count; ++i) {
         if (descs[i].m == 0 || descs[i].n == 0 || descs[i].batch == 0) continue;
@@ -989,7 +1021,7 @@ int gemm_grouped_impl(const llmt_b200_gemm_desc* descs, void* const* c, const vo
         const void* bi = b[i];
         if (rp.total() > 0) {
             st = apply_repack(&local, ck[i], rp, plans[i].workspace_bytes, &ai, &bi,
-                              static_cast<cudaStream_t>(stream));
+                              static_cast<cudaStream_t>(stream), &repacked);
             if (st != LLMT_B200_OK) return st;
         }
         st = fill_problem(&probs[n], &local, ck[i], plans[i], c[i], ai, bi);

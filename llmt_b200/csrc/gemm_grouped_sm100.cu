@@ -419,6 +419,38 @@ __device__ __noinline__ void ride_exchange_side_warp(const RideExchange& x, int3
     __threadfence_system();
 }
 
+// Copies a staged unit (up to 32 rows x 128 bytes, 128-byte swizzle) to a destination that TMA
+// cannot address or that is ragged: one row per store instruction (up to 128 contiguous bytes),
+// eight rows in flight.  `dst` is the unit's first element, `ld` the row pitch in elements,
+// `valid` the unit's columns that lie inside the matrix.
+template <typename T>
+__device__ __noinline__ void copy_out_rows(uint32_t buf, T* dst, int64_t ld, int rows, int valid, int lane) {
+    const uint32_t word = ((static_cast<uint32_t>(lane) >> 2) << 4) | ((static_cast<uint32_t>(lane) & 3u) << 2);
+    constexpr int kPer = sizeof(T) == 4 ? 1 : 2;  // elements per 32-bit word
+    for (int r0 = 0; r0 < rows; r0 += 8) {
+        uint32_t w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t rr = static_cast<uint32_t>(r0 + u);
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w[u]) : "r"(buf + (rr & 31u) * 128u + (word ^ ((rr & 7u) << 4))));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u >= rows) break;
+            T* row = dst + static_cast<int64_t>(r0 + u) * ld + kPer * lane;
+            if (kPer == 1) {
+                if (lane < valid) *reinterpret_cast<uint32_t*>(row) = w[u];
+            } else if (2 * lane + 1 < valid && (reinterpret_cast<uintptr_t>(row) & 3u) == 0u) {
+                *reinterpret_cast<uint32_t*>(row) = w[u];
+            } else {
+                uint16_t* h = reinterpret_cast<uint16_t*>(row);
+                if (2 * lane < valid) h[0] = static_cast<uint16_t>(w[u] & 0xFFFFu);
+                if (2 * lane + 1 < valid) h[1] = static_cast<uint16_t>(w[u] >> 16);
+            }
+        }
+    }
+}
+
 // tcgen05.ld fills its destination registers asynchronously until tcgen05.wait::ld.  The
 // compiler must not schedule a read of them ahead of the wait: this empty statement, placed
 // after the wait, makes every later use depend on it.
@@ -1150,28 +1182,17 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 // copies the staged rows out itself, one row per instruction, so that every store
                 // instruction writes up to 128 contiguous bytes.
                 __syncwarp();
-                const int unit_valid = min(unit_cols, pn - unit_col);
-                const uint32_t word = ((static_cast<uint32_t>(lane) >> 2) << 4) | ((static_cast<uint32_t>(lane) & 3u) << 2);
-#pragma unroll 1
-                for (int rr = 0; rr < 32; ++rr) {
-                    const int64_t grow = static_cast<int64_t>(row0) + rr;
-                    if (grow >= pm) break;
-                    uint32_t w;
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w)
-                                 : "r"(buf + static_cast<uint32_t>(rr) * 128u + (word ^ ((static_cast<uint32_t>(rr) & 7u) << 4))));
+                {
+                    const int unit_valid = min(unit_cols, pn - unit_col);
+                    const int rows = min(32, pm - row0);
                     if (out_bf16) {
-                        uint16_t* dst = static_cast<uint16_t*>(p.c) + c_item_off + grow * p.ldc + unit_col + 2 * lane;
-                        if (2 * lane + 1 < unit_valid && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0u) {
-                            *reinterpret_cast<uint32_t*>(dst) = w;
-                        } else {
-                            if (2 * lane < unit_valid) dst[0] = static_cast<uint16_t>(w & 0xFFFFu);
-                            if (2 * lane + 1 < unit_valid) dst[1] = static_cast<uint16_t>(w >> 16);
-                        }
-                    } else if (lane < unit_valid) {
-                        float* dst = partial
-                            ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * pm + grow) * pn + unit_col + lane
-                            : static_cast<float*>(p.c) + c_item_off + grow * p.ldc + unit_col + lane;
-                        *dst = __uint_as_float(w);
+                        copy_out_rows<uint16_t>(buf, static_cast<uint16_t*>(p.c) + c_item_off + static_cast<int64_t>(row0) * p.ldc + unit_col,
+                                                p.ldc, rows, unit_valid, lane);
+                    } else {
+                        float* base = partial
+                            ? p.ws + ((static_cast<int64_t>(tc.batch) * p.splits + tc.split) * pm + row0) * pn + unit_col
+                            : static_cast<float*>(p.c) + c_item_off + static_cast<int64_t>(row0) * p.ldc + unit_col;
+                        copy_out_rows<float>(buf, base, partial ? static_cast<int64_t>(pn) : p.ldc, rows, unit_valid, lane);
                     }
                 }
                 __syncwarp();  // the buffer may be rewritten once every lane has read its words
