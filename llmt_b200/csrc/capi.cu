@@ -183,8 +183,12 @@ int choose_splits(int64_t tiles, int kblocks_total, int sms) {
 // of waves of equal tiles.  A pure function of its arguments.
 // `pairs`: the launch uses CTA pairs (256-row tiles, `units` = number of pairs); with
 // MN-major B a pair needs a tile width that is a multiple of 128.
+// `epi_step`: estimated cycles of one 32-column epilogue step of this problem, `c_bf16`: its result type.
+// A tile is done when its main loop AND its epilogue are (they overlap across tiles): an epilogue
+// warp takes every other 128-byte column unit, so a 192-wide bf16 tile (three units) costs it as many
+// steps as a 256-wide one.
 TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode, int units,
-                 int force_bn, int force_splits, bool pairs, bool b_mn) {
+                 int force_bn, int force_splits, bool pairs, bool b_mn, int epi_step = 1000, bool c_bf16 = true) {
     const int sms = units;
     const int cands[4] = {256, 192, 128, 64};
     const int tiles_m = ceil_div(m, pairs ? 256 : 128);
@@ -201,8 +205,12 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int dbias_mode,
         if (splits > kblocks_total) splits = kblocks_total > 0 ? kblocks_total : 1;
         const int kps = ceil_div(kblocks_total, splits);
         const int64_t waves = (tiles * splits + sms - 1) / sms;
-        // Estimated cycles: main loops, an epilogue per wave, one pass over the partials when split.
-        int64_t cost = waves * (static_cast<int64_t>(kblock_cost(bn, pairs)) * (kps > 0 ? kps : 1) + 4 * bn);
+        // Estimated cycles: per wave the longer of main loop and epilogue, one pass over the partials when split.
+        const int unit_cols = (c_bf16 && splits == 1) ? 64 : 32;
+        const int steps = ((bn / unit_cols + 1) / 2) * (unit_cols / 32);
+        const int64_t main_loop = static_cast<int64_t>(kblock_cost(bn, pairs)) * (kps > 0 ? kps : 1);
+        const int64_t epilogue = static_cast<int64_t>(steps) * (splits == 1 ? epi_step : 1000);
+        int64_t cost = waves * ((main_loop > epilogue ? main_loop : epilogue) + 4 * bn);
         if (splits > 1) cost += static_cast<int64_t>(splits) * 64 + 4000;
         if (best_bn == 0 || cost < best_cost) {
             best_bn = bn;
@@ -291,8 +299,10 @@ int pair_units() {
 int dbias_mode_of(const llmt_b200_gemm_desc* d) { return d->dbias == nullptr ? 0 : (d->trans_a ? 1 : 2); }
 TcPlan plan_single(const llmt_b200_gemm_desc* d) {
     const bool pairs = pair_eligible(d);
+    const int epi_step = 1000 + ((d->epilogue & LLMT_B200_EPI_BIAS) ? 100 : 0) + ((d->epilogue & LLMT_B200_EPI_GELU) ? 500 : 0) +
+                         (d->beta != 0.0f ? 300 : 0);
     return make_plan(d->m, d->n, d->k, d->batch, dbias_mode_of(d), pairs ? pair_units() : sm_count(),
-                     d->plan_tile_n, d->plan_splits, pairs, d->trans_b == 0);
+                     d->plan_tile_n, d->plan_splits, pairs, d->trans_b == 0, epi_step, d->dtype_c == LLMT_B200_BF16);
 }
 
 bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
