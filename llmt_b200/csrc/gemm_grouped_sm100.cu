@@ -715,7 +715,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : 0x7fffffff;
             const int after_own = n_turns > 1 ? 1 : 0;
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
-                if (scheduler && lane == 0) {
+                if (kb >= draw_kb && scheduler && lane == 0) {  // (the first test is warp-uniform and false on most k-blocks)
                     if (dynamic && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
                     if (kb >= publish_kb && !early && turn == after_own) {
                         const int nslot = (it + 1) % kRing;
@@ -734,17 +734,22 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                                  kDevWaitSmemEmpty, stage, wait_ns);
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (!ok) break;
-                    // The leader's barrier counts the bytes of both CTAs of a pair.  Bytes that land
-                    // before this arrival are counted all the same; the phase cannot complete without it.
-                    if (lane == 0 && leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
-                    // the stage's next release: nobody but the MMAs will read it
-                    if (lane == 0 && !tile_sums) mbar_arrive_count(smem_u32(&ctl->empty[stage]), kEpilogueWarps);
+                    // The loads leave first: the latency from "stage free" to "load issued" is part of
+                    // every stage's cycle.  The bookkeeping follows; bytes that land before the
+                    // barrier is armed are counted all the same (the phase cannot complete without
+                    // the arming arrival).
                     if (my_map != nullptr) {
                         const int k0 = kb * BK;
                         const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes + my_off;
                         const int x = my_x + (k_is_x ? k0 : 0), y = my_y + (k_is_y ? k0 : 0);
                         if (kPair) tma_load_4d_pair(dst, my_map, on_leader(&ctl->full[stage]), x, y, tc.bz, tc.bw);
                         else tma_load_4d(dst, my_map, smem_u32(&ctl->full[stage]), x, y, tc.bz, tc.bw);
+                    }
+                    if (lane == 0) {
+                        // The leader's barrier counts the bytes of both CTAs of a pair.
+                        if (leader) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), tx * CG);
+                        // the stage's next release: nobody but the MMAs will read it
+                        if (!tile_sums) mbar_arrive_count(smem_u32(&ctl->empty[stage]), kEpilogueWarps);
                     }
                 }
                 if (++turn == n_turns) turn = 0;
