@@ -572,6 +572,52 @@ def _loop_ms(torch, fns, iters=20, warm=3):
     return e0.elapsed_time(e1) / iters
 
 
+def lm_head_ce_comparison(torch, L, m, dev):
+    """The LM-head forward of config 3 with its consumer, the cross-entropy (llmt
+    src/kernels/cross_entropy.cu): the product stored as fp32 logits and read back by
+    cross_entropy_fwd, against llmt_b200_lm_head_ce_fwd, whose epilogue keeps the row statistics so
+    that the 1.65 GB of logits are never written.  Same loss (checked), times by CUDA events."""
+    bf = torch.bfloat16
+    V, C, LD = 50257, 768, 50264
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(m, C, device=dev, generator=g).to(bf)
+    w = (torch.randn(V, C, device=dev, generator=g) * 0.02).to(bf)
+    tg = torch.randint(0, V, (m,), device=dev, generator=g, dtype=torch.int32)
+    mk = torch.ones(m, device=dev)
+    logits = torch.empty(m, LD, device=dev)[:, :V]
+    d1 = L.make_desc(logits, x, w, False, True)
+    loss1, nll1 = torch.empty(1, device=dev), torch.empty(m, device=dev)
+
+    def unfused():
+        L.gemm_desc(d1, logits, x, w)
+        L.cross_entropy_fwd(loss1, nll1, logits, tg, mk)
+
+    d2 = L.GemmDesc()
+    d2.m, d2.n, d2.k, d2.batch = m, V, C, 1
+    d2.lda, d2.ldb, d2.ldc = C, C, V
+    d2.trans_a, d2.trans_b = 0, 1
+    d2.dtype_ab, d2.dtype_c = L.BF16, L.FP32
+    d2.alpha = 1.0
+    need = L.lm_head_ce_workspace_bytes(d2, x, w)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    d2.workspace, d2.workspace_bytes = ws.data_ptr(), need
+    loss2, nll2 = torch.empty(1, device=dev), torch.empty(m, device=dev)
+
+    def fused():
+        L.lm_head_ce_fwd(d2, None, x, w, tg, mk, nll2, loss2)
+
+    ms_u = _loop_ms(torch, [unfused], iters=10, warm=3)
+    ms_f = _loop_ms(torch, [fused], iters=10, warm=3)
+    L.device_status()
+    flops = 2.0 * m * V * C
+    return {"shape": f"{m} x {V} x {C}, bf16 operands, fp32 logits (pitch {LD})",
+            "gemm_then_cross_entropy_ms": round(ms_u, 4), "fused_ms": round(ms_f, 4),
+            "gemm_then_cross_entropy_tflops": round(flops / ms_u / 1e9, 1), "fused_tflops": round(flops / ms_f / 1e9, 1),
+            "loss_unfused": float(loss1.item()), "loss_fused": float(loss2.item()),
+            "losses_agree": bool(abs(float(loss1.item()) - float(loss2.item())) <= 1e-4 * abs(float(loss1.item()))),
+            "logit_bytes_not_written": int(m) * V * 4}
+
+
 def per_gemm_comparison(torch, L, workload, m, dev, want_cublaslt=True):
     """Each GEMM of the step timed on its own, back to back on rotating buffer sets (> 2 x L2
     in total), for this library and for cuBLASLt called the way llmt calls it (operand swap,
@@ -1130,6 +1176,11 @@ def main():
                 extras["comparators"] = per_gemm_comparison(torch, L, args.workload, M_PER_GPU, dev)
             except Exception as exc:
                 extras["comparators"] = {"error": str(exc)}
+            torch.cuda.empty_cache()
+            try:
+                extras["lm_head_ce"] = lm_head_ce_comparison(torch, L, M_PER_GPU, dev)
+            except Exception as exc:
+                extras["lm_head_ce"] = {"error": str(exc)}
             torch.cuda.empty_cache()
         h, mi = L.tensor_map_cache_stats()
         extras["tensor_map_cache"] = {"hits": h, "misses": mi}

@@ -312,6 +312,26 @@ LLMT_B200_API int llmt_b200_gemm_grouped_exchange(const llmt_b200_gemm_desc* des
                                     int32_t index, void* stream);
 LLMT_B200_API int llmt_b200_exchange_begin_step(const llmt_b200_comm_desc* comm, void* stream);
 
+/* ---- the consumer of the LM-head logits (llmt include/llmt/kernels/cross_entropy.h:36-37) ----
+ *
+ * llmt_b200_cross_entropy_fwd: llmt's cross_entropy_fwd on fp32 logits [rows, vocab] (row pitch
+ * ld), int32 targets [rows], fp32 mask [rows]:
+ *   row_nll[r] = mask[r] * (log sum_v exp(logits[r, v]) - logits[r, targets[r]]),
+ *   loss[0]    = sum_r row_nll[r] / sum_r mask[r]     (fixed-order sums: same bits every run).
+ *
+ * llmt_b200_lm_head_ce_fwd: the same result straight from the LM-head product
+ * logits = alpha * op(A) * op(B) (+ bias), without the [rows, vocab] tensor having to exist: the GEMM's
+ * epilogue keeps, per row and per half tile, the maximum and the sum of exponentials of the columns it
+ * produced and the target's logit, and a small kernel combines them.  `logits` may be NULL (nothing is
+ * stored) or the tensor to store as llmt_b200_gemm would.  bf16 operands, one product (no batch), no
+ * GELU, no dbias; desc.workspace must hold llmt_b200_lm_head_ce_workspace_bytes(desc, a, b) bytes.
+ * No counterpart in llmt (its cross_entropy_fwd reads logits from memory). */
+LLMT_B200_API int llmt_b200_cross_entropy_fwd(float* loss, float* row_nll, const float* logits, const int32_t* targets,
+                                const float* mask, int64_t rows, int64_t vocab, int64_t ld, void* stream);
+LLMT_B200_API uint64_t llmt_b200_lm_head_ce_workspace_bytes(const llmt_b200_gemm_desc* desc, const void* a, const void* b);
+LLMT_B200_API int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* desc, void* logits, const void* a, const void* b,
+                             const int32_t* targets, const float* mask, float* row_nll, float* loss, void* stream);
+
 /* The same exchange with all `world` ranks living on ONE device (comms[r] is rank r's
  * descriptor, every pointer local): a single cooperative launch of world * ctas CTAs.
  * For tests of the algorithm where fewer GPUs than ranks are at hand. */

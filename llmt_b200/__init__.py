@@ -28,6 +28,7 @@ EXPORTS = [
     "llmt_b200_zero_grads", "llmt_b200_gemm_workspace_bytes_for", "llmt_b200_set_wait_limit_ns",
     "llmt_b200_tensor_map_cache_stats", "llmt_b200_head_merge", "llmt_b200_head_split",
     "llmt_b200_gemm_grouped_exchange", "llmt_b200_exchange_begin_step",
+    "llmt_b200_cross_entropy_fwd", "llmt_b200_lm_head_ce_workspace_bytes", "llmt_b200_lm_head_ce_fwd",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
@@ -134,6 +135,12 @@ def lib() -> ctypes.CDLL:
                                                       ctypes.c_int32, ctypes.POINTER(CommDesc), ctypes.c_int64,
                                                       ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
         L.llmt_b200_gemm_grouped_exchange.restype = ctypes.c_int
+        L.llmt_b200_cross_entropy_fwd.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int64] * 3 + [ctypes.c_void_p]
+        L.llmt_b200_cross_entropy_fwd.restype = ctypes.c_int
+        L.llmt_b200_lm_head_ce_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p]
+        L.llmt_b200_lm_head_ce_workspace_bytes.restype = ctypes.c_uint64
+        L.llmt_b200_lm_head_ce_fwd.argtypes = [ctypes.POINTER(GemmDesc)] + [ctypes.c_void_p] * 8
+        L.llmt_b200_lm_head_ce_fwd.restype = ctypes.c_int
         L.llmt_b200_exchange_begin_step.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_void_p]
         L.llmt_b200_exchange_begin_step.restype = ctypes.c_int
         L.llmt_b200_zero_grads.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
@@ -369,6 +376,32 @@ def device_status():
 def grad_allreduce(desc: "CommDesc", offset: int, count: int, ctas: int = 8, stream=None) -> None:
     """Sums floats [offset, offset + count) of the span over the ranks of `desc`, in place."""
     _check(lib().llmt_b200_grad_allreduce(ctypes.byref(desc), int(offset), int(count), int(ctas), _stream(stream)))
+
+
+def cross_entropy_fwd(loss, row_nll, logits, targets, mask, stream=None) -> None:
+    """llmt's cross_entropy_fwd (include/llmt/kernels/cross_entropy.h:36-37) on fp32 logits [..., V]:
+    row_nll = mask * (lse - logit of the target), loss = sum(row_nll) / sum(mask)."""
+    import torch
+    v = logits.shape[-1]
+    rows = logits.numel() // v
+    if logits.dtype != torch.float32 or targets.dtype != torch.int32 or mask.dtype != torch.float32:
+        raise LlmtB200Error(ERR_INVALID, "cross_entropy_fwd: fp32 logits and mask, int32 targets")
+    _check(lib().llmt_b200_cross_entropy_fwd(loss.data_ptr(), row_nll.data_ptr(), logits.data_ptr(), targets.data_ptr(),
+                                             mask.data_ptr(), rows, v, logits.stride(-2) if logits.dim() > 1 else v,
+                                             _stream(stream)))
+
+
+def lm_head_ce_workspace_bytes(desc: GemmDesc, a=None, b=None) -> int:
+    return int(lib().llmt_b200_lm_head_ce_workspace_bytes(ctypes.byref(desc), a.data_ptr() if a is not None else None,
+                                                          b.data_ptr() if b is not None else None))
+
+
+def lm_head_ce_fwd(desc: GemmDesc, logits, a, b, targets, mask, row_nll, loss, stream=None) -> None:
+    """The LM-head product and its cross-entropy in one pass (llmt_b200_lm_head_ce_fwd); `logits`
+    may be None: then the [rows, vocab] tensor is never written."""
+    _check(lib().llmt_b200_lm_head_ce_fwd(ctypes.byref(desc), logits.data_ptr() if logits is not None else None,
+                                          a.data_ptr(), b.data_ptr(), targets.data_ptr(), mask.data_ptr(),
+                                          row_nll.data_ptr(), loss.data_ptr(), _stream(stream)))
 
 
 def exchange_begin_step(desc: "CommDesc", stream=None) -> None:

@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(HERE, "_build")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libllmt_b200.so")
 
-SOURCES = ["capi.cu", "gemm_grouped_sm100.cu", "gemm_fp32_simt.cu", "grad_allreduce_sm100.cu"]
+SOURCES = ["capi.cu", "gemm_grouped_sm100.cu", "gemm_fp32_simt.cu", "grad_allreduce_sm100.cu", "cross_entropy.cu"]
 HEADERS = ["common.h", "ptx_sm100.cuh", os.path.join("..", "..", "include", "llmt_b200.h")]
 
 NVCC_FLAGS = [
@@ -82,7 +82,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 CPP_DIR = os.path.join(HERE, "cpp")
-CPP_SOURCES = ["runtime.cpp", "matmul.cpp", "layers.cpp", "attention.cpp", "peer_exchange.cpp"]
+CPP_SOURCES = ["runtime.cpp", "matmul.cpp", "layers.cpp", "attention.cpp", "peer_exchange.cpp", "cross_entropy.cpp"]
 HOST_LIB = os.path.join(LIB_DIR, "libllmt_b200_host.so")
 ROOT = os.path.dirname(HERE)
 CPP_TEST_SRC = os.path.join(ROOT, "tests", "cpp", "test_llmt_goldens.cpp")

@@ -318,9 +318,11 @@ struct Checked {
 
 // Shape/pointer contract; the order and wording follow llmt's check()
 // (src/kernels/matmul.cpp:175-214) where a counterpart exists.
-int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const void* b, Checked* out) {
+// c_optional: C may be null (the caller does not want the product itself stored).
+int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const void* b, Checked* out,
+             bool c_optional = false) {
     if (d == nullptr) return fail(LLMT_B200_ERR_INVALID, "matmul: null descriptor");
-    if (c == nullptr || a == nullptr || b == nullptr)
+    if ((c == nullptr && !c_optional) || a == nullptr || b == nullptr)
         return fail(LLMT_B200_ERR_INVALID, "matmul: invalid tensor (null data)");
     if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: negative dimension");
@@ -389,10 +391,10 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
                                                    (out->a_rows - 1) * d->lda + out->a_cols) * es_ab;
         const size_t b_bytes = static_cast<size_t>(batch_span(d->stride_b, d->stride_b_outer) +
                                                    (out->b_rows - 1) * d->ldb + out->b_cols) * es_ab;
-        const size_t c_bytes = static_cast<size_t>(batch_span(d->stride_c, d->stride_c_outer) +
-                                                   (d->m - 1) * d->ldc + d->n) * es_c;
+        const size_t c_bytes = c == nullptr ? 0 : static_cast<size_t>(batch_span(d->stride_c, d->stride_c_outer) +
+                                                                      (d->m - 1) * d->ldc + d->n) * es_c;
         out->a_bytes = a_bytes; out->b_bytes = b_bytes; out->c_bytes = c_bytes;
-        if (overlaps(c, c_bytes, a, a_bytes) || overlaps(c, c_bytes, b, b_bytes))
+        if (c_bytes != 0 && (overlaps(c, c_bytes, a, a_bytes) || overlaps(c, c_bytes, b, b_bytes)))
             return fail(LLMT_B200_ERR_INVALID, "matmul: C overlaps an input");
         // Nothing the call writes (C, dbias, workspace) may overlap anything else it touches.
         const size_t dbias_bytes = d->dbias != nullptr ? static_cast<size_t>(d->m) * 4 : 0;
@@ -732,7 +734,7 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
         return LLMT_B200_OK;
     }
     const int ces = p->c_is_bf16 ? 2 : 4;
-    if ((reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
+    if (c != nullptr && (reinterpret_cast<uintptr_t>(c) & 15u) == 0 && (d->ldc * ces) % 16 == 0 &&
         (d->batch <= 1 || (d->stride_c * ces) % 16 == 0) &&
         (d->batch_inner <= 0 || (d->stride_c_outer * ces) % 16 == 0)) {
         st = cached_map(&p->map_c, c, ces, d->m, d->n, d->ldc,
@@ -746,7 +748,8 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
 
 // Launches the tensor-core kernel over `count` filled problems (longest tiles first),
 // then the fixed-order reduction of every problem that was split.
-int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream, const RideExchange* ride = nullptr) {
+int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream, const RideExchange* ride = nullptr,
+                 bool lse = false) {
     DeviceGlobals* g = nullptr;
     int st = device_globals(&g);
     if (st != LLMT_B200_OK) return st;
@@ -801,7 +804,7 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
         const int units = pairs ? pair_units() : sm_count();
         // (with an exchange riding along every unit is launched: its side warps share the chunks)
         const int grid = static_cast<int>(total < units && ride == nullptr ? total : units) * (pairs ? 2 : 1);
-        cudaError_t e = launch_tc_grouped(gp, grid, pairs, stream);
+        cudaError_t e = launch_tc_grouped(gp, grid, pairs, stream, lse);
         if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     }
     for (int i = 0; i < count; ++i) {
@@ -1073,15 +1076,6 @@ int llmt_b200_gemm_grouped_exchange(const llmt_b200_gemm_desc* descs, void* cons
     return gemm_grouped_impl(descs, c, a, b, count, stream, comm, offset, count_floats, index);
 }
 
-int llmt_b200_exchange_begin_step(const llmt_b200_comm_desc* comm, void* stream) {
-    if (comm == nullptr || comm->rank < 0 || comm->rank >= kMaxCommRanks || comm->flags[comm->rank] == nullptr)
-        return fail(LLMT_B200_ERR_INVALID, "exchange_begin_step: bad exchange descriptor");
-    cudaError_t e = launch_exchange_begin_step(static_cast<uint32_t*>(comm->flags[comm->rank]) + kRideStep,
-                                               static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
-    return LLMT_B200_OK;
-}
-
 namespace {
 void shape_only(const llmt_b200_gemm_desc& d, Checked* ck) {
     ck->a_rows = d.trans_a ? d.k : d.m; ck->a_cols = d.trans_a ? d.m : d.k;
@@ -1091,6 +1085,107 @@ bool is_tc_problem(const llmt_b200_gemm_desc& d) {
     return d.dtype_ab == LLMT_B200_BF16 && d.m > 0 && d.n > 0 && d.k > 0 && d.batch > 0;
 }
 }  // namespace
+
+namespace {
+// Layout of the workspace of llmt_b200_lm_head_ce_fwd: the GEMM's own scratch (repacked operands),
+// then the per-part (maximum, sum of exponentials) pairs, then the target logits.
+struct LmHeadCePlan {
+    TcPlan pl;
+    size_t gemm_bytes, stats_off, tgt_off, total;
+    int parts;
+};
+LmHeadCePlan lm_head_ce_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* a, const void* b) {
+    LmHeadCePlan r;
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;  // the epilogue sees whole reductions
+    r.pl = plan_single(&local);
+    r.gemm_bytes = r.pl.workspace_bytes + repack_plan(&local, ck, a, b).total();
+    r.parts = 2 * r.pl.tiles_n;
+    r.stats_off = (r.gemm_bytes + 255) / 256 * 256;
+    r.tgt_off = r.stats_off + (static_cast<size_t>(r.parts) * d->m * 8 + 255) / 256 * 256;
+    r.total = r.tgt_off + (static_cast<size_t>(d->m) * 4 + 255) / 256 * 256;
+    return r;
+}
+int lm_head_ce_check(const llmt_b200_gemm_desc* d) {
+    if (d->dtype_ab != LLMT_B200_BF16)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_fwd: bf16 operands only");
+    if (d->batch > 1) return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_fwd: one product, no batch");
+    if (d->dbias != nullptr || (d->epilogue & LLMT_B200_EPI_GELU))
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_fwd: no dbias, no GELU");
+    if (d->m < 1 || d->n < 1 || d->k < 1) return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_fwd: empty problem");
+    return LLMT_B200_OK;
+}
+}  // namespace
+
+uint64_t llmt_b200_lm_head_ce_workspace_bytes(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
+    if (d == nullptr || !is_tc_problem(*d) || d->batch > 1) return 0;
+    Checked ck{};
+    shape_only(*d, &ck);
+    return lm_head_ce_plan(d, ck, a, b).total;
+}
+
+int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* d, void* logits, const void* a, const void* b,
+                             const int32_t* targets, const float* mask, float* row_nll, float* loss,
+                             void* stream) {
+    Checked ck{};
+    int st = validate(d, logits, a, b, &ck, /*c_optional=*/true);
+    if (st != LLMT_B200_OK) return st;
+    st = lm_head_ce_check(d);
+    if (st != LLMT_B200_OK) return st;
+    if (targets == nullptr || mask == nullptr || row_nll == nullptr || loss == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_fwd: null targets, mask, row_nll or loss");
+    if (logits == nullptr && d->beta != 0.0f)
+        return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_fwd: beta needs the logits tensor");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;
+    const LmHeadCePlan lp = lm_head_ce_plan(d, ck, a, b);
+    if (d->workspace == nullptr || d->workspace_bytes < lp.total)
+        return fail(LLMT_B200_ERR_WORKSPACE, "lm_head_ce_fwd: needs %llu workspace bytes (llmt_b200_lm_head_ce_workspace_bytes), got %llu",
+                    (unsigned long long)lp.total, (unsigned long long)d->workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
+    const Repack rp = repack_plan(&local, ck, a, b);
+    if (rp.total() > 0) {
+        st = apply_repack(&local, ck, rp, lp.pl.workspace_bytes, &a, &b, s);
+        if (st != LLMT_B200_OK) return st;
+    }
+    GroupProblem p;
+    st = fill_problem(&p, &local, ck, lp.pl, logits, a, b);
+    if (st != LLMT_B200_OK) return st;
+    char* ws = static_cast<char*>(d->workspace);
+    p.lse_stats = reinterpret_cast<float2*>(ws + lp.stats_off);
+    p.lse_tgt = reinterpret_cast<float*>(ws + lp.tgt_off);
+    p.lse_targets = targets;
+    st = launch_group(&p, 1, lp.pl.pairs != 0, s, nullptr, /*lse=*/true);
+    if (st != LLMT_B200_OK) return st;
+    cudaError_t e = launch_cross_entropy_from_stats(loss, row_nll, p.lse_stats, p.lse_tgt, mask, d->m, lp.parts, s);
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_cross_entropy_fwd(float* loss, float* row_nll, const float* logits, const int32_t* targets,
+                                const float* mask, int64_t rows, int64_t vocab, int64_t ld, void* stream) {
+    if (loss == nullptr || row_nll == nullptr || logits == nullptr || targets == nullptr || mask == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_fwd: invalid tensor (null data)");
+    if (rows < 1 || vocab < 1 || ld < vocab)
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_fwd: bad shape (rows %lld, vocab %lld, pitch %lld)",
+                    (long long)rows, (long long)vocab, (long long)ld);
+    cudaError_t e = launch_cross_entropy_fwd(loss, row_nll, logits, targets, mask, rows, vocab, ld,
+                                             static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_exchange_begin_step(const llmt_b200_comm_desc* comm, void* stream) {
+    if (comm == nullptr || comm->rank < 0 || comm->rank >= kMaxCommRanks || comm->flags[comm->rank] == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "exchange_begin_step: bad exchange descriptor");
+    cudaError_t e = launch_exchange_begin_step(static_cast<uint32_t*>(comm->flags[comm->rank]) + kRideStep,
+                                               static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
 
 int llmt_b200_gemm_grouped_workspace_bytes(const llmt_b200_gemm_desc* descs, int32_t count,
                                            uint64_t* bytes_per_problem) {

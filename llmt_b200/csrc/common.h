@@ -70,8 +70,13 @@ struct ProblemScalars {
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
     float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums; mode 3 with splits: [splits][m]
+    // log-sum-exp epilogue (the kernels built with it only): per row and per half tile the maximum and
+    // the sum of exponentials of the columns produced, the row's target column and where its logit goes
+    float2* lse_stats;          // [2 * tiles_n][m]
+    float* lse_tgt;             // [m]
+    const int32_t* lse_targets; // [m]
 };
-static_assert(sizeof(ProblemScalars) % 8 == 0 && sizeof(ProblemScalars) <= 256, "ProblemScalars is copied to shared memory");
+static_assert(sizeof(ProblemScalars) % 8 == 0 && sizeof(ProblemScalars) <= 264, "ProblemScalars is copied to shared memory");
 
 struct alignas(64) GroupProblem : ProblemScalars {
     CUtensorMap map_a, map_b;   // operand loads (128B swizzle)
@@ -214,7 +219,11 @@ __device__ __forceinline__ float gelu_tanh_hw(float v) {
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.
-cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream);
+cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream, bool lse = false);
+cudaError_t launch_cross_entropy_fwd(float* loss, float* row_nll, const float* logits, const int32_t* targets,
+                                     const float* mask, int64_t rows, int64_t v, int64_t ld, cudaStream_t stream);
+cudaError_t launch_cross_entropy_from_stats(float* loss, float* row_nll, const void* stats, const float* tgt,
+                                            const float* mask, int64_t rows, int parts, cudaStream_t stream);
 int max_resident_pairs(void);
 cudaError_t launch_splitk_reduce(const GroupProblem& p, cudaStream_t stream);
 size_t tc_grouped_smem_bytes(void);

@@ -465,7 +465,12 @@ template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
-template <int CG>
+// kLse: the log-sum-exp epilogue (the LM head feeding a cross-entropy): beside (or instead of)
+// storing C, every epilogue warp keeps, per row, the maximum and the sum of exponentials of the
+// columns it produces and leaves them in ProblemScalars::lse_stats, and the warp that meets
+// the row's target column leaves that logit in lse_tgt.  A kernel of its own, so that the code
+// costs the other launches nothing.
+template <int CG, bool kLse>
 __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     constexpr int kStages = Geo<CG>::kStages;
     constexpr uint32_t kStageBytes = Geo<CG>::kStageBytes;
@@ -1077,6 +1082,10 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                                  : static_cast<const float*>(bias_ptr)[col];
                 }
             }
+            // log-sum-exp epilogue: this thread's row, over the columns this warp produces
+            float lse_m = -INFINITY, lse_s = 0.0f;
+            int lse_target = -1;
+            if (kLse && row_ok) lse_target = p.lse_targets[row0 + lane];
             if (ops & kOpBeta) {
                 // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
                 // lines now, while the tile's main loop is still running.
@@ -1142,6 +1151,29 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
                         }
                     }
+                }
+                if (kLse) {
+                    const int valid = min(32, pn - col);
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < valid) mx = fmaxf(mx, v[j]);
+                    float sm = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < valid) sm += exp2f((v[j] - mx) * 1.4426950408889634f);
+                    const float nm = fmaxf(lse_m, mx);
+                    lse_s = (lse_m == -INFINITY ? 0.0f : lse_s * exp2f((lse_m - nm) * 1.4426950408889634f)) +
+                            sm * exp2f((mx - nm) * 1.4426950408889634f);
+                    lse_m = nm;
+                    if (lse_target >= col && lse_target < col + 32) {
+                        float tv = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j == lse_target) tv = v[j];
+                        p.lse_tgt[row0 + lane] = tv;
+                    }
+                    if (p.c == nullptr) return;  // the logits themselves are not wanted
                 }
                 const int sub = s & (spu - 1);
                 const int unit_col = col - sub * 32;
@@ -1222,6 +1254,8 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     emit(cur, s, s == 0 ? bias_mine[0] : s == 1 ? bias_mine[1] : s == 2 ? bias_mine[2] : bias_mine[3]);
                 }
             }
+            if (kLse && row_ok)
+                p.lse_stats[static_cast<int64_t>(tc.n_tile * 2 + half) * pm + row0 + lane] = make_float2(lse_m, lse_s);
             ++acc_seq;
         }
         // Outstanding TMA stores must have read their staging buffers before the shared memory goes
@@ -1248,18 +1282,28 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 tc_grouped_kernel(const __grid_constant__ GroupParams gp) {
-    tc_grouped_body<1>(gp);
+    tc_grouped_body<1, false>(gp);
 }
 
 // The same kernel over CTA pairs: clusters of two CTAs, each pair computing 256-row tiles
 // with cta_group::2 MMAs, every CTA staging its own 128 rows of A and half of the B tile.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 tc_grouped_pair_kernel(const __grid_constant__ GroupParams gp) {
-    tc_grouped_body<2>(gp);
+    tc_grouped_body<2, false>(gp);
 }
 
 // C = epilogue(alpha * sum_s ws[s] + beta * C): fixed summation order s = 0..splits-1.
 // Four consecutive columns per thread when the row length allows it.
+// The same kernels with the log-sum-exp epilogue.
+__global__ void __launch_bounds__(kThreads, 1)
+tc_grouped_lse_kernel(const __grid_constant__ GroupParams gp) {
+    tc_grouped_body<1, true>(gp);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+tc_grouped_pair_lse_kernel(const __grid_constant__ GroupParams gp) {
+    tc_grouped_body<2, true>(gp);
+}
+
 __global__ void splitk_reduce_kernel(const GroupProblem p) {
     grid_launch_dependents();
     grid_dependency_wait();
@@ -1334,11 +1378,15 @@ static cudaError_t configure_device(int dev) {
     cudaError_t e = cudaFuncSetAttribute(tc_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(tc_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tc_grouped_lse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tc_grouped_pair_lse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess) g_configured[dev] = true;
     return e;
 }
 
-cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream) {
+cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaStream_t stream, bool lse) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = configure_device(dev);
@@ -1355,8 +1403,12 @@ cudaError_t launch_tc_grouped(const GroupParams& gp, int grid, bool pairs, cudaS
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_kernel, gp)
-              : cudaLaunchKernelEx(&cfg, tc_grouped_kernel, gp);
+    if (lse)
+        e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_lse_kernel, gp)
+                  : cudaLaunchKernelEx(&cfg, tc_grouped_lse_kernel, gp);
+    else
+        e = pairs ? cudaLaunchKernelEx(&cfg, tc_grouped_pair_kernel, gp)
+                  : cudaLaunchKernelEx(&cfg, tc_grouped_kernel, gp);
     count_launch(1);
     return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -170,6 +170,22 @@ def softmax_bwd(p, dp) -> np.ndarray:
     return ds
 
 
+def cross_entropy(logits, targets, mask):
+    """Masked cross-entropy from raw logits [..., V] in fp64 (llmt
+    src/kernels/cross_entropy.cu:26-49 per row, :57-77 the mask-weighted mean):
+    row_nll = mask * (logsumexp(logits) - logits[target]); loss = sum(row_nll) / sum(mask).
+    Returns (loss, row_nll)."""
+    x = np.asarray(logits, dtype=np.float64)
+    v = x.shape[-1]
+    x2 = x.reshape(-1, v)
+    t = np.asarray(targets).reshape(-1).astype(np.int64)
+    w = np.asarray(mask, dtype=np.float64).reshape(-1)
+    m = x2.max(axis=1)
+    lse = m + np.log(np.exp(x2 - m[:, None]).sum(axis=1))
+    nll = w * (lse - x2[np.arange(x2.shape[0]), t])
+    return nll.sum() / w.sum(), nll.reshape(np.asarray(targets).shape)
+
+
 def gelu(x) -> np.ndarray:
     x = np.asarray(x, dtype=np.float64)
     k0, k1 = 0.7978845608028654, 0.044715

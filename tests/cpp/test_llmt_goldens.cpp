@@ -20,6 +20,7 @@
 #include "llmt/kernels/algo_cache.h"
 #include "llmt/kernels/attention.h"
 #include "llmt/kernels/matmul.h"
+#include "llmt/kernels/cross_entropy.h"
 #include "llmt/kernels/permute.h"
 #include "llmt/layers/linear.h"
 #include "llmt/layers/mlp.h"
@@ -57,6 +58,28 @@ HostTensor load(const std::string& c, const std::string& name) {
     t.v.resize(static_cast<size_t>(t.shape.numel()));
     f.read(reinterpret_cast<char*>(t.v.data()), static_cast<std::streamsize>(t.v.size() * 4));
     return t;
+}
+
+// The same format with an int32 payload (dtype code 2): the targets of the cross_entropy case.
+std::vector<int32_t> load_i32(const std::string& c, const std::string& name, Shape* shape) {
+    const std::string path = g_root + "/" + c + "/" + name + ".bin";
+    std::ifstream f(path, std::ios::binary);
+    if (!f) { std::fprintf(stderr, "cannot open %s\n", path.c_str()); std::exit(2); }
+    uint32_t hdr[4];
+    f.read(reinterpret_cast<char*>(hdr), 16);
+    if (hdr[0] != 0x544D4C4Cu || hdr[1] != 1u || hdr[2] != 2u || hdr[3] > 4u) {
+        std::fprintf(stderr, "%s: not an int32 llmt golden tensor\n", path.c_str());
+        std::exit(2);
+    }
+    shape->rank = static_cast<int>(hdr[3]);
+    for (int i = 0; i < shape->rank; ++i) {
+        int64_t d;
+        f.read(reinterpret_cast<char*>(&d), 8);
+        shape->d[static_cast<size_t>(i)] = d;
+    }
+    std::vector<int32_t> v(static_cast<size_t>(shape->numel()));
+    f.read(reinterpret_cast<char*>(v.data()), static_cast<std::streamsize>(v.size() * 4));
+    return v;
 }
 
 Tensor upload(Arena& arena, const HostTensor& h, cudaStream_t s) {
@@ -234,10 +257,7 @@ void test_permute(Device& dev) {
     check_close(y, load("permute", "y"), "permute_merge y", 1.0, 1e-6, 1e-7);
 }
 
-// bf16 Linear with bias through the same C++ interface: forward with the fused bias,
-// backward as ONE grouped launch (dx, dW and dbias).  Checked against the strict-fp32
-// path of the same layer run on the same bf16-rounded values (relative Frobenius:
-// 1e-2 for bf16 outputs, 1e-3 for the fp32 gradients) and a host column sum for dbias.
+// bf16 <-> fp32 on the host (round to nearest even).
 uint16_t to_bf16(float f) {
     uint32_t u;
     std::memcpy(&u, &f, 4);
@@ -250,6 +270,69 @@ float from_bf16(uint16_t h) {
     std::memcpy(&f, &u, 4);
     return f;
 }
+
+// llmt tests/unit/test_cross_entropy.cu:19-54: masked NLL and weighted mean against the
+// `cross_entropy` case, and the same bits on a second run.  Then the fused form: the LM-head
+// product and its cross-entropy in one pass must agree with cross_entropy_fwd on the logits the
+// same call stored, and with a run that stores nothing.
+void test_cross_entropy(Device& dev, const RunCtx& ctx) {
+    Arena arena(16 << 20, "ce-test");
+    const Tensor logits = upload(arena, load("cross_entropy", "logits"), ctx.stream);
+    const Tensor mask = upload(arena, load("cross_entropy", "mask"), ctx.stream);
+    Shape tshape;
+    const std::vector<int32_t> th = load_i32("cross_entropy", "targets", &tshape);
+    Tensor targets = arena.alloc(tshape, DType::I32);
+    CUDA_CHECK(cudaMemcpyAsync(targets.data, th.data(), th.size() * 4, cudaMemcpyHostToDevice, ctx.stream));
+    Tensor row_nll = arena.alloc({2, 4}, DType::FP32);
+    Tensor l1 = arena.alloc({1}, DType::FP32), l2 = arena.alloc({1}, DType::FP32);
+    kernels::cross_entropy_fwd(ctx, l1, row_nll, logits, targets, mask);
+    dev.synchronize();
+    check_close(row_nll, load("cross_entropy", "wnll"), "cross_entropy row_nll");
+    check_close(l1, load("cross_entropy", "loss"), "cross_entropy loss");
+    kernels::cross_entropy_fwd(ctx, l2, row_nll, logits, targets, mask);
+    dev.synchronize();
+    ++g_checks;
+    if (download(l1) != download(l2)) { ++g_failures; std::fprintf(stderr, "FAIL cross_entropy: reruns differ\n"); }
+
+    const int64_t B = 2, T = 160, C = 128, V = 1000;
+    std::vector<uint16_t> xh(static_cast<size_t>(B * T * C)), wh(static_cast<size_t>(V * C));
+    uint32_t seed = 12345u;
+    auto rnd = [&]() { seed = seed * 1664525u + 1013904223u; return static_cast<float>(seed >> 8) / 16777216.0f - 0.5f; };
+    for (auto& e : xh) e = to_bf16(2.0f * rnd());
+    for (auto& e : wh) e = to_bf16(0.5f * rnd());
+    std::vector<int32_t> tg(static_cast<size_t>(B * T));
+    std::vector<float> mk(static_cast<size_t>(B * T));
+    for (size_t i = 0; i < tg.size(); ++i) { tg[i] = static_cast<int32_t>((i * 37u) % V); mk[i] = 0.25f + 0.5f * static_cast<float>(i % 3); }
+    Tensor x = arena.alloc({B, T, C}, DType::BF16), w = arena.alloc({V, C}, DType::BF16);
+    Tensor t2 = arena.alloc({B, T}, DType::I32), m2 = arena.alloc({B, T}, DType::FP32);
+    CUDA_CHECK(cudaMemcpy(x.data, xh.data(), xh.size() * 2, cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(w.data, wh.data(), wh.size() * 2, cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(t2.data, tg.data(), tg.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(m2.data, mk.data(), mk.size() * 4, cudaMemcpyHostToDevice));
+    Tensor lg = arena.alloc({B, T, V}, DType::FP32);
+    Tensor nll_f = arena.alloc({B, T}, DType::FP32), nll_u = arena.alloc({B, T}, DType::FP32), nll_n = arena.alloc({B, T}, DType::FP32);
+    Tensor loss_f = arena.alloc({1}, DType::FP32), loss_u = arena.alloc({1}, DType::FP32), loss_n = arena.alloc({1}, DType::FP32);
+    RunCtx c2 = ctx;
+    const size_t need = kernels::lm_head_cross_entropy_workspace_bytes(x, w);
+    Tensor ws = arena.alloc({static_cast<int64_t>((need + 3) / 4 + 64)}, DType::FP32);
+    c2.blas_workspace = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data) + 255u) & ~static_cast<uintptr_t>(255u));
+    c2.blas_workspace_bytes = need;
+    kernels::lm_head_cross_entropy_fwd(c2, loss_f, nll_f, &lg, x, w, nullptr, t2, m2);   // stores the logits too
+    kernels::cross_entropy_fwd(ctx, loss_u, nll_u, lg, t2, m2);                          // llmt's form on those logits
+    kernels::lm_head_cross_entropy_fwd(c2, loss_n, nll_n, nullptr, x, w, nullptr, t2, m2);  // stores nothing
+    dev.synchronize();
+    HostTensor want; want.shape = Shape{B, T}; want.v = download(nll_u);
+    check_close(nll_f, want, "lm_head_cross_entropy_fwd row_nll vs cross_entropy_fwd", 1.0, 1e-5, 1e-5);
+    check_close(nll_n, want, "lm_head_cross_entropy_fwd (no logits) row_nll", 1.0, 1e-5, 1e-5);
+    HostTensor wl; wl.shape = Shape{1}; wl.v = download(loss_u);
+    check_close(loss_f, wl, "lm_head_cross_entropy_fwd loss");
+    check_close(loss_n, wl, "lm_head_cross_entropy_fwd (no logits) loss");
+}
+
+// bf16 Linear with bias through the same C++ interface: forward with the fused bias,
+// backward as ONE grouped launch (dx, dW and dbias).  Checked against the strict-fp32
+// path of the same layer run on the same bf16-rounded values (relative Frobenius:
+// 1e-2 for bf16 outputs, 1e-3 for the fp32 gradients) and a host column sum for dbias.
 double rel_fro(const std::vector<float>& a, const std::vector<float>& b) {
     double num = 0, den = 0;
     for (size_t i = 0; i < a.size(); ++i) { num += (a[i] - b[i]) * double(a[i] - b[i]); den += double(b[i]) * b[i]; }
@@ -341,6 +424,7 @@ int main(int argc, char** argv) {
     test_attention(dev, ctx);
     test_permute(dev);
     test_attention_packed(dev, ctx);
+    test_cross_entropy(dev, ctx);
     test_bf16_linear(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());

@@ -3,10 +3,11 @@
 path into tests/golden/llmt/ so the parity tests can run where the llmt source
 tree is not present.
 
-Source: <llmt>/tests/golden/{matmul,matmul_rank3,linear,mlp,attention,gelu,permute}/*.bin
+Source: <llmt>/tests/golden/{matmul,matmul_rank3,linear,mlp,attention,gelu,permute,cross_entropy}/*.bin
 (written by llmt's tools/gen_golden.py with PyTorch on CPU; asserted by
 tests/unit/test_matmul.cu, test_linear.cu, test_mlp.cu, test_attention.cu and
-test_kernels_fwd.cu at rtol 1e-5 / atol 1e-6; the permute case at 1e-6 / 1e-7).
+test_kernels_fwd.cu at rtol 1e-5 / atol 1e-6; the permute case at 1e-6 / 1e-7; cross_entropy
+(the consumer of the LM-head logits) by test_cross_entropy.cu at 1e-5 / 1e-6).
 
 The files are data, copied byte for byte. Usage:
     python tests/golden/import_llmt_goldens.py <path-to-llmt-tree>
@@ -15,7 +16,7 @@ import os
 import shutil
 import sys
 
-CASES = ["matmul", "matmul_rank3", "linear", "mlp", "attention", "gelu", "permute"]
+CASES = ["matmul", "matmul_rank3", "linear", "mlp", "attention", "gelu", "permute", "cross_entropy"]
 
 
 def main() -> int:

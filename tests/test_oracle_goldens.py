@@ -114,3 +114,11 @@ def test_f32_port_matches_f64():
     bn = np.ascontiguousarray(b.T)
     got2 = oracle.gemm_f32(at, bn, trans_a=True, trans_b=False)
     assert oracle.rel_fro(got2, ref) < 1e-6
+
+
+def test_oracle_cross_entropy_matches_llmt_golden():
+    # the consumer of the LM-head logits: llmt tests/unit/test_cross_entropy.cu:19-35
+    g = GoldenCase("cross_entropy")
+    loss, nll = oracle.cross_entropy(g.tensor("logits"), g.tensor("targets"), g.tensor("mask"))
+    assert_close(nll, g.tensor("wnll"), what="cross_entropy row_nll")
+    assert_close(np.array([loss]), g.tensor("loss"), what="cross_entropy loss")
