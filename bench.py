@@ -618,6 +618,65 @@ def lm_head_ce_comparison(torch, L, m, dev):
             "logit_bytes_not_written": int(m) * V * 4}
 
 
+def attention_softmax_comparison(torch, L, dev):
+    """Config 4's softmax, forward and backward (llmt src/kernels/attention.cpp:60-62,
+    docs/TODO.md:226-228), at B*H = 96, T = 1024, hd = 64, bf16, causal: llmt's composition (scores
+    GEMM, softmax kernel in place; dP GEMM, softmax-backward kernel) against the fused launches
+    (llmt_b200_gemm_softmax_fwd: the scores are never stored; llmt_b200_gemm_softmax_bwd: dP is never
+    stored).  Rotating buffer sets larger than L2, times by CUDA events, results compared."""
+    bf = torch.bfloat16
+    BH, T, HD = 96, 1024, 64
+    g = torch.Generator(device=dev).manual_seed(11)
+    sets = []
+    for _ in range(2):  # 2 x (4 x 201 MB of T x T tensors) > L2
+        q, k, v = (torch.randn(BH, T, HD, device=dev, generator=g).to(bf) for _ in range(3))
+        do = (torch.randn(BH, T, HD, device=dev, generator=g) * 0.01).to(bf)
+        s_u, p_f, ds_u, ds_f = (torch.empty(BH, T, T, device=dev, dtype=bf) for _ in range(4))
+        o = torch.empty(BH, T, HD, device=dev, dtype=bf)
+        dvec = torch.empty(BH, T, device=dev)
+        d_s = L.make_desc(p_f, q, k, False, True, alpha=0.125)
+        need = L.gemm_softmax_workspace_bytes(d_s, q, k)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        d_s.workspace, d_s.workspace_bytes = ws.data_ptr(), need
+        d_b = L.make_desc(ds_f, do, v, False, True)
+        wsb = torch.empty(max(L.workspace_bytes(d_b, do, v), 256), dtype=torch.uint8, device=dev)
+        d_b.workspace, d_b.workspace_bytes = wsb.data_ptr(), wsb.numel()
+        sets.append(dict(q=q, k=k, v=v, do=do, s_u=s_u, p_f=p_f, ds_u=ds_u, ds_f=ds_f, o=o, dvec=dvec,
+                         d_s=d_s, d_b=d_b, ws=ws, wsb=wsb))
+
+    def fwd_unfused(z):
+        L.gemm(z["s_u"], z["q"], z["k"], False, True, alpha=0.125)
+        L.softmax_fwd(z["s_u"], z["s_u"], causal=True)
+
+    def fwd_fused(z):
+        L.gemm_softmax_fwd(z["d_s"], z["p_f"], z["q"], z["k"], True)
+
+    def bwd_unfused(z):
+        L.gemm(z["ds_u"], z["do"], z["v"], False, True)
+        L.softmax_bwd(z["ds_u"], z["p_f"], z["ds_u"])
+
+    def bwd_fused(z):
+        L.rowdot(z["dvec"], z["do"], z["o"])
+        L.gemm_softmax_bwd(z["d_b"], z["ds_f"], z["do"], z["v"], z["p_f"], z["dvec"], True)
+
+    out = {"shape": f"B*H = {BH}, T = {T}, hd = {HD}, bf16, causal; one T x T tensor is {BH * T * T * 2} bytes"}
+    for name, fn in (("fwd_gemm_then_softmax_ms", fwd_unfused), ("fwd_fused_ms", fwd_fused)):
+        out[name] = round(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=10, warm=3), 4)
+    for z in sets:
+        L.gemm(z["o"], z["p_f"], z["v"], False, False)
+    for name, fn in (("bwd_gemm_then_softmax_bwd_ms", bwd_unfused), ("bwd_fused_ms", bwd_fused)):
+        out[name] = round(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=10, warm=3), 4)
+    L.device_status()
+    z = sets[0]
+    p_u, p_f = z["s_u"].float(), z["p_f"].float()
+    out["fwd_max_abs_diff"] = float((p_u - p_f).abs().max().item())
+    out["fwd_masked_exact_zero"] = bool((torch.triu(p_f[0], 1) == 0).all().item())
+    ds_u, ds_f = z["ds_u"].float(), z["ds_f"].float()
+    out["bwd_rel_fro_diff"] = float(((ds_u - ds_f).norm() / ds_u.norm()).item())
+    out["t_x_t_bytes_not_moved"] = {"fwd": 2 * BH * T * T * 2, "bwd": 2 * BH * T * T * 2}
+    return out
+
+
 def per_gemm_comparison(torch, L, workload, m, dev, want_cublaslt=True):
     """Each GEMM of the step timed on its own, back to back on rotating buffer sets (> 2 x L2
     in total), for this library and for cuBLASLt called the way llmt calls it (operand swap,
@@ -1181,6 +1240,11 @@ def main():
                 extras["lm_head_ce"] = lm_head_ce_comparison(torch, L, M_PER_GPU, dev)
             except Exception as exc:
                 extras["lm_head_ce"] = {"error": str(exc)}
+            torch.cuda.empty_cache()
+            try:
+                extras["attention_softmax"] = attention_softmax_comparison(torch, L, dev)
+            except Exception as exc:
+                extras["attention_softmax"] = {"error": str(exc)}
             torch.cuda.empty_cache()
         h, mi = L.tensor_map_cache_stats()
         extras["tensor_map_cache"] = {"hits": h, "misses": mi}

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LLMT_B200_ABI_VERSION 4
+#define LLMT_B200_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define LLMT_B200_API __attribute__((visibility("default")))
@@ -331,6 +331,40 @@ LLMT_B200_API int llmt_b200_cross_entropy_fwd(float* loss, float* row_nll, const
 LLMT_B200_API uint64_t llmt_b200_lm_head_ce_workspace_bytes(const llmt_b200_gemm_desc* desc, const void* a, const void* b);
 LLMT_B200_API int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* desc, void* logits, const void* a, const void* b,
                              const int32_t* targets, const float* mask, float* row_nll, float* loss, void* stream);
+
+/* ---- the softmax of an attention layer fused around its GEMMs --------------------------------
+ * (llmt src/kernels/attention.cpp:60-62: scores = alpha q k^T, softmax in place, y = probs v;
+ *  src/kernels/softmax.cu:25-51: the masking rule; docs/TODO.md:226-228: the backward products.)
+ *
+ * llmt_b200_gemm_softmax_fwd: probs = softmax over each row of S = alpha * op(A) * op(B) (every item of
+ * a batch by itself), under llmt's causal rule when `causal` != 0 (row q sees columns 0..q; the others
+ * are stored as exact zeros), WITHOUT S ever being stored: the GEMM kernel runs twice over the same
+ * tiles.  The first launch stores nothing; its epilogue leaves, per row and per half tile, the maximum
+ * and the sum of exponentials; a small kernel turns them into the rows' log-sum-exp; the second launch
+ * makes the same tiles again (same plan, same bits) and stores exp(S - lse[row]) in C's type.  What
+ * llmt writes and reads three times (scores out, scores in, probs out) is written once.  The
+ * arithmetic is fp32 on the fp32 accumulators (llmt rounds the scores to the tensor's type first).
+ *   lse: fp32 [batch * m], optional; receives the rows' log-sum-exp.
+ * bf16 operands; beta 0; no bias, GELU, dbias; desc.workspace must hold
+ * llmt_b200_gemm_softmax_workspace_bytes(desc, a, b) bytes.
+ *
+ * llmt_b200_gemm_softmax_bwd: dS = probs ⊙ (alpha * op(A) * op(B) - row_dot[row]) as the epilogue of
+ * the product that makes dP = dO v^T: dP itself is never stored.  `probs` has C's type, pitch and
+ * batch strides and must not overlap dS; row_dot is fp32 [batch * m] and holds
+ * sum_j dP[r, j] * probs[r, j], which equals sum_d dO[r, d] * O[r, d] for O = probs v
+ * (llmt_b200_rowdot on dO and O computes it).  Workspace as llmt_b200_gemm.
+ *
+ * llmt_b200_rowdot: out[r] = sum_j x[r, j] * y[r, j] in fp32 over [rows, cols] tensors with row
+ * pitches ldx, ldy (elements).
+ * No counterparts in llmt (its softmax is a kernel of its own between the GEMMs; it has no attention
+ * backward). */
+LLMT_B200_API uint64_t llmt_b200_gemm_softmax_workspace_bytes(const llmt_b200_gemm_desc* desc, const void* a, const void* b);
+LLMT_B200_API int llmt_b200_gemm_softmax_fwd(const llmt_b200_gemm_desc* desc, void* probs, const void* a, const void* b,
+                               int32_t causal, float* lse, void* stream);
+LLMT_B200_API int llmt_b200_gemm_softmax_bwd(const llmt_b200_gemm_desc* desc, void* ds, const void* a, const void* b,
+                               const void* probs, const float* row_dot, int32_t causal, void* stream);
+LLMT_B200_API int llmt_b200_rowdot(float* out, const void* x, const void* y, int64_t rows, int64_t cols, int64_t ldx,
+                     int64_t ldy, int32_t dtype, void* stream);
 
 /* The same exchange with all `world` ranks living on ONE device (comms[r] is rank r's
  * descriptor, every pointer local): a single cooperative launch of world * ctas CTAs.

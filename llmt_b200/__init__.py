@@ -29,6 +29,8 @@ EXPORTS = [
     "llmt_b200_tensor_map_cache_stats", "llmt_b200_head_merge", "llmt_b200_head_split",
     "llmt_b200_gemm_grouped_exchange", "llmt_b200_exchange_begin_step",
     "llmt_b200_cross_entropy_fwd", "llmt_b200_lm_head_ce_workspace_bytes", "llmt_b200_lm_head_ce_fwd",
+    "llmt_b200_gemm_softmax_workspace_bytes", "llmt_b200_gemm_softmax_fwd", "llmt_b200_gemm_softmax_bwd",
+    "llmt_b200_rowdot",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
@@ -141,6 +143,16 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_lm_head_ce_workspace_bytes.restype = ctypes.c_uint64
         L.llmt_b200_lm_head_ce_fwd.argtypes = [ctypes.POINTER(GemmDesc)] + [ctypes.c_void_p] * 8
         L.llmt_b200_lm_head_ce_fwd.restype = ctypes.c_int
+        L.llmt_b200_gemm_softmax_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p]
+        L.llmt_b200_gemm_softmax_workspace_bytes.restype = ctypes.c_uint64
+        L.llmt_b200_gemm_softmax_fwd.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                 ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+        L.llmt_b200_gemm_softmax_fwd.restype = ctypes.c_int
+        L.llmt_b200_gemm_softmax_bwd.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_gemm_softmax_bwd.restype = ctypes.c_int
+        L.llmt_b200_rowdot.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 4 + [ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_rowdot.restype = ctypes.c_int
         L.llmt_b200_exchange_begin_step.argtypes = [ctypes.POINTER(CommDesc), ctypes.c_void_p]
         L.llmt_b200_exchange_begin_step.restype = ctypes.c_int
         L.llmt_b200_zero_grads.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
@@ -402,6 +414,36 @@ def lm_head_ce_fwd(desc: GemmDesc, logits, a, b, targets, mask, row_nll, loss, s
     _check(lib().llmt_b200_lm_head_ce_fwd(ctypes.byref(desc), logits.data_ptr() if logits is not None else None,
                                           a.data_ptr(), b.data_ptr(), targets.data_ptr(), mask.data_ptr(),
                                           row_nll.data_ptr(), loss.data_ptr(), _stream(stream)))
+
+
+def gemm_softmax_workspace_bytes(desc: GemmDesc, a=None, b=None) -> int:
+    return int(lib().llmt_b200_gemm_softmax_workspace_bytes(ctypes.byref(desc), a.data_ptr() if a is not None else None,
+                                                            b.data_ptr() if b is not None else None))
+
+
+def gemm_softmax_fwd(desc: GemmDesc, probs, a, b, causal: bool, lse=None, stream=None) -> None:
+    """probs = row softmax of alpha * op(a) * op(b), the scores never stored (llmt_b200_gemm_softmax_fwd)."""
+    _check(lib().llmt_b200_gemm_softmax_fwd(ctypes.byref(desc), probs.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                            1 if causal else 0, lse.data_ptr() if lse is not None else None,
+                                            _stream(stream)))
+
+
+def gemm_softmax_bwd(desc: GemmDesc, ds, a, b, probs, row_dot, causal: bool, stream=None) -> None:
+    """ds = probs * (alpha * op(a) * op(b) - row_dot[row]), dP never stored (llmt_b200_gemm_softmax_bwd)."""
+    _check(lib().llmt_b200_gemm_softmax_bwd(ctypes.byref(desc), ds.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                            probs.data_ptr(), row_dot.data_ptr(), 1 if causal else 0, _stream(stream)))
+
+
+def rowdot(out, x, y, stream=None) -> None:
+    """out[r] = sum_j x[r, j] * y[r, j] (fp32) over the last dimension of two same-shaped tensors."""
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if x.shape != y.shape or x.dtype != y.dtype or _dtype_code(out) != FP32 or out.numel() != rows:
+        raise LlmtB200Error(ERR_INVALID, "rowdot: x and y of one shape and type, out fp32 with one value per row")
+    if not (x.is_contiguous() and y.is_contiguous()):
+        raise LlmtB200Error(ERR_INVALID, "rowdot: contiguous tensors")
+    _check(lib().llmt_b200_rowdot(out.data_ptr(), x.data_ptr(), y.data_ptr(), rows, cols, cols, cols,
+                                  _dtype_code(x), _stream(stream)))
 
 
 def exchange_begin_step(desc: "CommDesc", stream=None) -> None:

@@ -11,6 +11,10 @@ namespace llmt::kernels {
 // q,k,v,y_heads [B,H,T,hd]; scores [B,H,T,T] (holds the probabilities on
 // return).  The head merge into [B,T,H*hd] token rows is a pure copy outside
 // the GEMM path; pass y with data == nullptr to skip it.
+// bf16 tensors take the softmax inside the scores GEMM (two launches over the same tiles: row
+// statistics, then exp(s - lse) stored as the probabilities; the scores themselves are never
+// stored) when ctx.blas_workspace holds the statistics; otherwise, and for fp32, llmt's
+// composition GEMM -> softmax_fwd in place.
 void attention_fwd(const RunCtx& ctx, Tensor& y, Tensor& scores, Tensor& y_heads, const Tensor& q,
                    const Tensor& k, const Tensor& v, MaskSpec mask) noexcept;
 
@@ -20,6 +24,14 @@ void attention_fwd(const RunCtx& ctx, Tensor& y, Tensor& scores, Tensor& y_heads
 void attention_bwd(const RunCtx& ctx, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dscores,
                    const Tensor& d_y_heads, const Tensor& probs, const Tensor& q, const Tensor& k,
                    const Tensor& v) noexcept;
+
+// The same with the forward pass's pre-merge output y_heads [B,H,T,hd] (what attention_fwd left)
+// and the mask of the forward pass: for bf16 tensors D = rowsum(dO * O) replaces rowsum(dP * P)
+// and dS leaves the launch that makes dP, so dP is never stored and P is read once (for dS) instead
+// of twice.  `mask` lets the launch skip the arithmetic where P is zero by construction.
+void attention_bwd(const RunCtx& ctx, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dscores,
+                   const Tensor& d_y_heads, const Tensor& probs, const Tensor& q, const Tensor& k,
+                   const Tensor& v, const Tensor* y_heads, MaskSpec mask) noexcept;
 
 void softmax_fwd(const RunCtx& ctx, Tensor& y, const Tensor& x, MaskSpec mask) noexcept;
 

@@ -1112,7 +1112,7 @@ int lm_head_ce_check(const llmt_b200_gemm_desc* d) {
     if (d->batch > 1) return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_fwd: one product, no batch");
     if (d->dbias != nullptr || (d->epilogue & LLMT_B200_EPI_GELU))
         return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_fwd: no dbias, no GELU");
-    if (d->m < 1 || d->n < 1 || d->k < 1) return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_fwd: empty problem");
+    if (d->m < 1 || d->n < 1 || d->k < 1 || d->batch < 1) return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_fwd: empty problem");
     return LLMT_B200_OK;
 }
 }  // namespace
@@ -1154,12 +1154,155 @@ int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* d, void* logits, const v
     st = fill_problem(&p, &local, ck, lp.pl, logits, a, b);
     if (st != LLMT_B200_OK) return st;
     char* ws = static_cast<char*>(d->workspace);
-    p.lse_stats = reinterpret_cast<float2*>(ws + lp.stats_off);
-    p.lse_tgt = reinterpret_cast<float*>(ws + lp.tgt_off);
-    p.lse_targets = targets;
+    p.ext_stats = reinterpret_cast<float2*>(ws + lp.stats_off);
+    p.ext_rowvec = reinterpret_cast<float*>(ws + lp.tgt_off);
+    p.ext_ptr = targets;
+    p.epi_flags |= kEpiLse;
     st = launch_group(&p, 1, lp.pl.pairs != 0, s, nullptr, /*lse=*/true);
     if (st != LLMT_B200_OK) return st;
-    cudaError_t e = launch_cross_entropy_from_stats(loss, row_nll, p.lse_stats, p.lse_tgt, mask, d->m, lp.parts, s);
+    cudaError_t e = launch_cross_entropy_from_stats(loss, row_nll, p.ext_stats, p.ext_rowvec, mask, d->m, lp.parts, s);
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+namespace {
+// Workspace of the softmax fused around a GEMM: the GEMM's own scratch (repacked operands), the
+// per-part (maximum, sum of exponentials) pairs of every row, the rows' log-sum-exp.
+struct GemmSoftmaxPlan {
+    TcPlan pl;
+    size_t gemm_bytes, stats_off, lse_off, total;
+    int parts;
+    int64_t rows;  // batch * m
+};
+GemmSoftmaxPlan gemm_softmax_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* a, const void* b) {
+    GemmSoftmaxPlan r;
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;  // the epilogue sees whole reductions
+    r.pl = plan_single(&local);
+    r.gemm_bytes = r.pl.workspace_bytes + repack_plan(&local, ck, a, b).total();
+    r.parts = 2 * r.pl.tiles_n;
+    r.rows = d->m * (d->batch > 1 ? d->batch : 1);
+    r.stats_off = (r.gemm_bytes + 255) / 256 * 256;
+    r.lse_off = r.stats_off + (static_cast<size_t>(r.parts) * r.rows * 8 + 255) / 256 * 256;
+    r.total = r.lse_off + (static_cast<size_t>(r.rows) * 4 + 255) / 256 * 256;
+    return r;
+}
+int gemm_softmax_check(const llmt_b200_gemm_desc* d, int32_t causal, const char* who) {
+    if (d->dtype_ab != LLMT_B200_BF16) return fail(LLMT_B200_ERR_UNSUPPORTED, "%s: bf16 operands only", who);
+    if (d->dbias != nullptr || d->epilogue != 0)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "%s: no bias, no GELU, no dbias", who);
+    if (d->beta != 0.0f) return fail(LLMT_B200_ERR_UNSUPPORTED, "%s: beta must be 0", who);
+    if (d->m < 1 || d->n < 1 || d->k < 1 || d->batch < 1) return fail(LLMT_B200_ERR_INVALID, "%s: empty problem", who);
+    if (causal && d->m != d->n)
+        return fail(LLMT_B200_ERR_INVALID, "%s: causal mask requires square scores (Tq=%lld Tk=%lld)", who,
+                    (long long)d->m, (long long)d->n);
+    return LLMT_B200_OK;
+}
+}  // namespace
+
+uint64_t llmt_b200_gemm_softmax_workspace_bytes(const llmt_b200_gemm_desc* d, const void* a, const void* b) {
+    if (d == nullptr || !is_tc_problem(*d)) return 0;
+    Checked ck{};
+    shape_only(*d, &ck);
+    return gemm_softmax_plan(d, ck, a, b).total;
+}
+
+int llmt_b200_gemm_softmax_fwd(const llmt_b200_gemm_desc* d, void* probs, const void* a, const void* b,
+                               int32_t causal, float* lse, void* stream) {
+    Checked ck{};
+    int st = validate(d, probs, a, b, &ck);
+    if (st != LLMT_B200_OK) return st;
+    st = gemm_softmax_check(d, causal, "gemm_softmax_fwd");
+    if (st != LLMT_B200_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;
+    const GemmSoftmaxPlan sp = gemm_softmax_plan(d, ck, a, b);
+    if (d->workspace == nullptr || d->workspace_bytes < sp.total)
+        return fail(LLMT_B200_ERR_WORKSPACE, "gemm_softmax_fwd: needs %llu workspace bytes (llmt_b200_gemm_softmax_workspace_bytes), got %llu",
+                    (unsigned long long)sp.total, (unsigned long long)d->workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
+    const Repack rp = repack_plan(&local, ck, a, b);
+    if (rp.total() > 0) {
+        st = apply_repack(&local, ck, rp, sp.pl.workspace_bytes, &a, &b, s);
+        if (st != LLMT_B200_OK) return st;
+    }
+    char* ws = static_cast<char*>(d->workspace);
+    float* row_lse = lse != nullptr ? lse : reinterpret_cast<float*>(ws + sp.lse_off);
+    const int mask_flag = causal ? kEpiCausal : 0;
+    // Pass 1: the product's tiles are made and looked at, not stored.
+    GroupProblem p;
+    st = fill_problem(&p, &local, ck, sp.pl, nullptr, a, b);
+    if (st != LLMT_B200_OK) return st;
+    p.ext_stats = reinterpret_cast<float2*>(ws + sp.stats_off);
+    p.ext_rowvec = nullptr;
+    p.ext_ptr = nullptr;
+    p.epi_flags |= kEpiLse | mask_flag;
+    st = launch_group(&p, 1, sp.pl.pairs != 0, s, nullptr, /*lse=*/true);
+    if (st != LLMT_B200_OK) return st;
+    cudaError_t e = launch_lse_from_stats(row_lse, p.ext_stats, sp.rows, sp.parts, s);
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    // Pass 2: the same tiles again (the same bits: one plan, one order of additions), leaving as
+    // exp(v - lse[row]).
+    st = fill_problem(&p, &local, ck, sp.pl, probs, a, b);
+    if (st != LLMT_B200_OK) return st;
+    p.ext_stats = nullptr;
+    p.ext_rowvec = row_lse;
+    p.ext_ptr = nullptr;
+    p.epi_flags |= kEpiExpSub | mask_flag;
+    return launch_group(&p, 1, sp.pl.pairs != 0, s, nullptr, /*lse=*/true);
+}
+
+int llmt_b200_gemm_softmax_bwd(const llmt_b200_gemm_desc* d, void* ds, const void* a, const void* b,
+                               const void* probs, const float* row_dot, int32_t causal, void* stream) {
+    Checked ck{};
+    int st = validate(d, ds, a, b, &ck);
+    if (st != LLMT_B200_OK) return st;
+    st = gemm_softmax_check(d, causal, "gemm_softmax_bwd");
+    if (st != LLMT_B200_OK) return st;
+    if (probs == nullptr || row_dot == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "gemm_softmax_bwd: null probabilities or row sums");
+    if (probs == ds || overlaps(probs, ck.c_bytes, ds, ck.c_bytes))
+        return fail(LLMT_B200_ERR_INVALID, "gemm_softmax_bwd: the probabilities and dS must not overlap");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;
+    const TcPlan pl = plan_single(&local);
+    const Repack rp = repack_plan(&local, ck, a, b);
+    const size_t need = pl.workspace_bytes + rp.total();
+    if (need > 0) {
+        if (d->workspace == nullptr || d->workspace_bytes < need)
+            return fail(LLMT_B200_ERR_WORKSPACE, "gemm_softmax_bwd: needs %llu workspace bytes (llmt_b200_gemm_workspace_bytes), got %llu",
+                        (unsigned long long)need, (unsigned long long)d->workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
+            return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
+    }
+    if (rp.total() > 0) {
+        st = apply_repack(&local, ck, rp, pl.workspace_bytes, &a, &b, s);
+        if (st != LLMT_B200_OK) return st;
+    }
+    GroupProblem p;
+    st = fill_problem(&p, &local, ck, pl, ds, a, b);
+    if (st != LLMT_B200_OK) return st;
+    p.ext_stats = nullptr;
+    p.ext_rowvec = const_cast<float*>(row_dot);
+    p.ext_ptr = probs;
+    p.epi_flags |= kEpiMulAux | (causal ? kEpiCausal : 0);
+    return launch_group(&p, 1, pl.pairs != 0, s, nullptr, /*lse=*/true);
+}
+
+int llmt_b200_rowdot(float* out, const void* x, const void* y, int64_t rows, int64_t cols, int64_t ldx,
+                     int64_t ldy, int32_t dtype, void* stream) {
+    if (out == nullptr || x == nullptr || y == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "rowdot: invalid tensor (null data)");
+    if (rows < 0 || cols < 1 || ldx < cols || ldy < cols)
+        return fail(LLMT_B200_ERR_INVALID, "rowdot: bad shape (rows %lld, cols %lld, pitches %lld %lld)",
+                    (long long)rows, (long long)cols, (long long)ldx, (long long)ldy);
+    if (dtype != LLMT_B200_BF16 && dtype != LLMT_B200_FP32)
+        return fail(LLMT_B200_ERR_UNSUPPORTED, "rowdot: no kernel for dtype code %d", dtype);
+    if (rows == 0) return LLMT_B200_OK;
+    cudaError_t e = launch_rowdot(out, x, y, rows, cols, ldx, ldy, dtype == LLMT_B200_BF16, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return LLMT_B200_OK;
 }

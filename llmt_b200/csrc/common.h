@@ -28,6 +28,11 @@ enum DeviceErr : int32_t {
 
 constexpr int kEpiBias = 1;
 constexpr int kEpiGelu = 2;
+// Row-wise epilogues that only the kernels built with the extended epilogue carry out:
+constexpr int kEpiLse = 0x100;     // per row and per half tile: maximum and sum of exponentials -> ext_stats
+constexpr int kEpiCausal = 0x200;  // columns beyond the row's own index do not exist (value exactly 0 when stored)
+constexpr int kEpiExpSub = 0x400;  // v = exp(v - ext_rowvec[row])
+constexpr int kEpiMulAux = 0x800;  // v = aux[row, col] * (v - ext_rowvec[row]), aux laid out like C
 
 constexpr int kMaxGroupProblems = 8;
 
@@ -70,11 +75,15 @@ struct ProblemScalars {
     float* dbias;               // fp32 [m] or null
     float dbias_beta;
     float* ws_dbias;            // mode 1: [colsum_tiles][m] fp32 partial sums; mode 3 with splits: [splits][m]
-    // log-sum-exp epilogue (the kernels built with it only): per row and per half tile the maximum and
-    // the sum of exponentials of the columns produced, the row's target column and where its logit goes
-    float2* lse_stats;          // [2 * tiles_n][m]
-    float* lse_tgt;             // [m]
-    const int32_t* lse_targets; // [m]
+    // Extended epilogue (the kernels built with it only; which parts run: epi_flags).
+    //   kEpiLse: per row and per half tile the maximum and the sum of exponentials of the columns
+    //            produced go to ext_stats; if ext_ptr is set it is the rows' target columns
+    //            (int32 [m], one product only) and the target's value goes to ext_rowvec.
+    //   kEpiExpSub / kEpiMulAux: ext_rowvec is READ, one value per row of every batch item;
+    //            kEpiMulAux reads ext_ptr as the aux tensor (C's element type, pitch and strides).
+    float2* ext_stats;          // [2 * tiles_n][batch][m]
+    float* ext_rowvec;          // [batch][m]
+    const void* ext_ptr;
 };
 static_assert(sizeof(ProblemScalars) % 8 == 0 && sizeof(ProblemScalars) <= 264, "ProblemScalars is copied to shared memory");
 
@@ -244,6 +253,9 @@ cudaError_t launch_head_merge(void* y, const void* x, int64_t B, int64_t H, int6
                               cudaStream_t stream);
 cudaError_t launch_head_split(void* q, void* k, void* v, const void* qkv, int64_t B, int64_t H, int64_t T, int64_t hd,
                               int elem_bytes, cudaStream_t stream);
+cudaError_t launch_lse_from_stats(float* lse, const void* stats, int64_t rows, int parts, cudaStream_t stream);
+cudaError_t launch_rowdot(float* out, const void* x, const void* y, int64_t rows, int64_t cols, int64_t ldx,
+                          int64_t ldy, int is_bf16, cudaStream_t stream);
 DeviceStatus* device_status_ptr(void);
 
 void count_launch(int n);

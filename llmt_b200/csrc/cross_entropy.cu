@@ -99,6 +99,36 @@ ce_mean_kernel(float* loss, const float* row_nll, const float* mask, int64_t row
     if (threadIdx.x == 0) loss[0] = sh_n[0] / sh_m[0];
 }
 
+// The rows' log-sum-exp from the per-part pairs (the first pass of a softmax fused around a GEMM).
+// One thread per row, parts in ascending order: neighbouring threads read neighbouring pairs.
+__global__ void __launch_bounds__(256)
+lse_from_stats_kernel(float* lse, const float2* stats, int64_t rows, int parts) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (row >= rows) return;
+    float m = -INFINITY, s = 0.0f;
+    for (int p = 0; p < parts; ++p) {
+        const float2 t = stats[static_cast<int64_t>(p) * rows + row];
+        lse_merge(m, s, t.x, t.y);
+    }
+    lse[row] = m + logf(s);
+}
+
+// out[r] = sum_j x[r, j] * y[r, j] in fp32, lanes striding the row, a fixed tree across the warp.
+template <typename T>
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+rowdot_kernel(float* out, const T* x, const T* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const T* xr = x + row * ldx;
+    const T* yr = y + row * ldy;
+    float acc = 0.0f;
+    for (int64_t j = lane; j < cols; j += 32) acc = fmaf(static_cast<float>(xr[j]), static_cast<float>(yr[j]), acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) out[row] = acc;
+}
+
 unsigned row_blocks(int64_t rows) { return static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock); }
 
 }  // namespace
@@ -117,6 +147,24 @@ cudaError_t launch_cross_entropy_from_stats(float* loss, float* row_nll, const v
         row_nll, static_cast<const float2*>(stats), tgt, mask, rows, parts);
     ce_mean_kernel<<<1, kMeanThreads, 0, stream>>>(loss, row_nll, mask, rows);
     count_launch(2);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lse_from_stats(float* lse, const void* stats, int64_t rows, int parts, cudaStream_t stream) {
+    lse_from_stats_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, stream>>>(lse, static_cast<const float2*>(stats), rows, parts);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rowdot(float* out, const void* x, const void* y, int64_t rows, int64_t cols, int64_t ldx,
+                          int64_t ldy, int is_bf16, cudaStream_t stream) {
+    if (is_bf16)
+        rowdot_kernel<__nv_bfloat16><<<row_blocks(rows), kRowsPerBlock * 32, 0, stream>>>(
+            out, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y), rows, cols, ldx, ldy);
+    else
+        rowdot_kernel<float><<<row_blocks(rows), kRowsPerBlock * 32, 0, stream>>>(
+            out, static_cast<const float*>(x), static_cast<const float*>(y), rows, cols, ldx, ldy);
+    count_launch(1);
     return cudaGetLastError();
 }
 

@@ -465,11 +465,19 @@ template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
-// kLse: the log-sum-exp epilogue (the LM head feeding a cross-entropy): beside (or instead of)
-// storing C, every epilogue warp keeps, per row, the maximum and the sum of exponentials of the
-// columns it produces and leaves them in ProblemScalars::lse_stats, and the warp that meets
-// the row's target column leaves that logit in lse_tgt.  A kernel of its own, so that the code
-// costs the other launches nothing.
+// kLse: the extended, row-wise epilogue, a kernel of its own so that the code costs the other
+// launches nothing.  Which of its parts run is in the problem's epi_flags:
+//   kEpiLse     beside (or instead of) storing C, every epilogue warp keeps, per row, the maximum and
+//               the sum of exponentials of the columns it produces and leaves them in
+//               ProblemScalars::ext_stats; the warp that meets the row's target column leaves that
+//               value in ext_rowvec (the LM head feeding a cross-entropy; the first pass of a
+//               softmax over the rows of the product)
+//   kEpiCausal  columns beyond the row's own index count as absent and are stored as exact zeros
+//   kEpiExpSub  C = exp(v - ext_rowvec[row]): with the rows' log-sum-exp, the softmax itself
+//   kEpiMulAux  C = aux ⊙ (v - ext_rowvec[row]): the softmax backward dS = P ⊙ (dP - D) as the
+//               epilogue of the product that makes dP
+template <uint32_t V> struct Sig { static constexpr uint32_t value = V; };
+
 template <int CG, bool kLse>
 __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     constexpr int kStages = Geo<CG>::kStages;
@@ -1057,6 +1065,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             const int64_t c_row_off = c_item_off + static_cast<int64_t>(row0 + lane) * p.ldc + n0;
             // The epilogue operations of this tile as bits; a split's partial sums get none.
             constexpr uint32_t kOpAlpha = 1u, kOpBeta = 2u, kOpBias = 4u, kOpGelu = 8u;
+            // A signature: the operation bits, the result type, the extended epilogue's parts; or "generic".
+            constexpr uint32_t kSigBf16 = 0x10u, kSigGeneric = 0x80000000u;
+            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux);
             const float alpha = p.alpha, beta = p.beta;
             const bool c_bf16 = p.c_is_bf16 != 0;
             const void* const c_ptr = p.c;
@@ -1082,10 +1093,26 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                                                  : static_cast<const float*>(bias_ptr)[col];
                 }
             }
-            // log-sum-exp epilogue: this thread's row, over the columns this warp produces
+            // Extended epilogue: this thread's row, over the columns this warp produces
             float lse_m = -INFINITY, lse_s = 0.0f;
             int lse_target = -1;
-            if (kLse && row_ok) lse_target = p.lse_targets[row0 + lane];
+            float row_val = 0.0f;
+            const uint32_t ext = kLse ? static_cast<uint32_t>(p.epi_flags) : 0u;
+            const int64_t ext_row = static_cast<int64_t>(tc.batch) * pm + row0 + lane;
+            // Under the mask, with nothing to store, the steps beyond the diagonal for every row of
+            // this warp have no work at all.
+            if (kLse && (ext & kEpiCausal) && p.c == nullptr)
+                while (ns > 0 && n0 + step_col(ns - 1) > row0 + 31) --ns;
+            if (kLse && row_ok) {
+                if ((ext & kEpiLse) && p.ext_ptr != nullptr) lse_target = static_cast<const int32_t*>(p.ext_ptr)[row0 + lane];
+                if (ext & (kEpiExpSub | kEpiMulAux)) row_val = p.ext_rowvec[ext_row];
+                if (ext & kEpiMulAux) {
+                    const int esz = c_bf16 ? 2 : 4;
+                    const char* base = static_cast<const char*>(p.ext_ptr) + c_row_off * esz;
+                    for (int s = 0; s < ns; s += spu)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + static_cast<int64_t>(step_col(s)) * esz));
+                }
+            }
             if (ops & kOpBeta) {
                 // beta * C_in is read row by row (one row per thread): ask L2 for this thread's
                 // lines now, while the tile's main loop is still running.
@@ -1113,19 +1140,33 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             // One 32-column step: epilogue arithmetic on the values of this thread's row, then
             // into the staging buffer; once the unit is complete it leaves by TMA or, for a
             // ragged unit or a C that TMA cannot address, by the warp's own row-wise stores.
-            auto emit = [&](const uint32_t (&r)[32], int s, float my_bias) {
+            //
+            // The step's code exists once per SIGNATURE (the epilogue operations and the result type
+            // as compile-time constants) for the signatures that matter, plus once with everything
+            // decided at run time: a step is a few hundred instructions run by a warp with one
+            // other warp to hide behind, and every branch it has to resolve and every jump to a cold
+            // instruction-cache line stalls it (batched scores, one k-block per tile: 5100 cycles of
+            // epilogue per tile with run-time operations, 3400 with constants).  The fp32 results
+            // (dW += ..., split-K partial sums) stay with the run-time form: their epilogue hides
+            // behind long main loops, and constants measured slower where it does not (dW with dbias).
+            auto emit = [&](auto sig_c, const uint32_t (&r)[32], int s, float my_bias) {
+                constexpr uint32_t kSig = decltype(sig_c)::value;
+                constexpr bool kGeneric = (kSig & kSigGeneric) != 0;
+                const uint32_t e_ops = kGeneric ? ops : (kSig & 0xFu);
+                const bool e_bf16 = kGeneric ? out_bf16 : (kSig & kSigBf16) != 0;
+                const uint32_t e_ext = !kLse ? 0u : kGeneric ? ext : ((ext & kEpiCausal) | (kSig & kSigExtMask));
                 const int c0 = step_col(s);
                 const int col = n0 + c0;
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (ops != 0u) {
-                    if (ops & kOpAlpha) {
+                if (e_ops != 0u) {
+                    if (e_ops & kOpAlpha) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] *= alpha;
                     }
-                    if (ops & kOpBeta) {
-                        const int valid = min(32, pn - col);
+                    if (e_ops & kOpBeta) {
+                        const int valid = row_ok ? min(32, pn - col) : 0;
                         const int64_t c_off = c_row_off + c0;
                         float cin[32];
                         if (c_bf16)
@@ -1135,15 +1176,15 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = fmaf(beta, cin[j], v[j]);
                     }
-                    if (ops & kOpBias) {
+                    if (e_ops & kOpBias) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
                     }
-                    if (ops & kOpGelu) {
+                    if (e_ops & kOpGelu) {
                         // A bf16 result rounds at 2^-9: the hardware tanh (2^-11) is exact enough for
                         // it and halves the special-function work, which bounds this step; an fp32
                         // result gets the form that is accurate to 1e-6.
-                        if (out_bf16) {
+                        if (e_bf16) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_hw(v[j]);
                         } else {
@@ -1153,27 +1194,74 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     }
                 }
                 if (kLse) {
-                    const int valid = min(32, pn - col);
-                    float mx = -INFINITY;
+                    // Columns of this step that exist for this thread's row (may be <= 0 under the mask).
+                    int valid = min(32, pn - col);
+                    if (e_ext & kEpiCausal) valid = min(valid, row0 + lane + 1 - col);
+                    // Almost every step has all of its columns for all of its rows: that case runs
+                    // without a predicate per value.  A step beyond the mask for all rows does no
+                    // arithmetic at all.
+                    const bool full = __all_sync(0xffffffffu, valid >= 32);
+                    const bool none = !full && __all_sync(0xffffffffu, valid <= 0);
+                    constexpr float kLog2e = 1.4426950408889634f;
+                    if (!full && !none && (e_ext & (kEpiLse | kEpiExpSub))) {
+                        // absent columns count as -inf: no part in the maximum, exp() exactly 0
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < valid) mx = fmaxf(mx, v[j]);
-                    float sm = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (j < valid) sm += exp2f((v[j] - mx) * 1.4426950408889634f);
-                    const float nm = fmaxf(lse_m, mx);
-                    lse_s = (lse_m == -INFINITY ? 0.0f : lse_s * exp2f((lse_m - nm) * 1.4426950408889634f)) +
-                            sm * exp2f((mx - nm) * 1.4426950408889634f);
-                    lse_m = nm;
-                    if (lse_target >= col && lse_target < col + 32) {
-                        float tv = 0.0f;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j == lse_target) tv = v[j];
-                        p.lse_tgt[row0 + lane] = tv;
+                        for (int j = 0; j < 32; ++j) v[j] = j < valid ? v[j] : -INFINITY;
                     }
-                    if (p.c == nullptr) return;  // the logits themselves are not wanted
+                    if ((e_ext & kEpiLse) && !none && valid > 0) {
+                        float t[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) t[j] = fmaxf(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+                        for (int w = 8; w > 0; w >>= 1) {
+#pragma unroll
+                            for (int j = 0; j < w; ++j) t[j] = fmaxf(t[j], t[j + w]);
+                        }
+                        // Exponentials relative to the running maximum itself: one rescaling of the
+                        // sum so far per step instead of one per value.
+                        const float nm = fmaxf(lse_m, t[0]);
+                        const float nms = nm * kLog2e;
+                        float acc4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc4[j & 3] += ex2_approx(fmaf(v[j], kLog2e, -nms));
+                        lse_s = fmaf(lse_s, ex2_approx((lse_m - nm) * kLog2e), (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]));
+                        lse_m = nm;
+                        if (lse_target >= col && lse_target < col + 32) {
+                            float tv = 0.0f;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j == lse_target) tv = v[j];
+                            p.ext_rowvec[row0 + lane] = tv;
+                        }
+                    }
+                    if (p.c == nullptr) return;  // the product itself is not wanted
+                    if (none) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                    } else if (e_ext & kEpiExpSub) {
+                        const float shift = row_val * kLog2e;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], kLog2e, -shift));
+                    } else if (e_ext & kEpiMulAux) {
+                        float aux[32];
+                        const int64_t c_off = c_row_off + c0;
+                        // aux holds exact zeros where the mask applies: whole chunks are read, so
+                        // that the rows on the diagonal keep the vector loads
+                        const int have = row_ok && valid > 0 ? min(32, pn - col) : 0;
+                        if (c_bf16)
+                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.ext_ptr) + c_off, aux, have);
+                        else
+                            load_chunk_f32(static_cast<const float*>(p.ext_ptr) + c_off, aux, have);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = aux[j] * (v[j] - row_val);
+                        if (!full) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = j < valid ? v[j] : 0.0f;
+                        }
+                    } else if (!full) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = j < valid ? v[j] : 0.0f;
+                    }
                 }
                 const int sub = s & (spu - 1);
                 const int unit_col = col - sub * 32;
@@ -1186,7 +1274,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 }
                 const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
-                if (out_bf16) {
+                if (e_bf16) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
@@ -1222,7 +1310,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 {
                     const int unit_valid = min(unit_cols, pn - unit_col);
                     const int rows = min(32, pm - row0);
-                    if (out_bf16) {
+                    if (e_bf16) {
                         copy_out_rows<uint16_t>(buf, static_cast<uint16_t*>(p.c) + c_item_off + static_cast<int64_t>(row0) * p.ldc + unit_col,
                                                 p.ldc, rows, unit_valid, lane);
                     } else {
@@ -1235,12 +1323,9 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 __syncwarp();  // the buffer may be rewritten once every lane has read its words
             };
             // Software pipeline over the steps: the tcgen05.ld of step s+1 is in flight while
-            // step s is converted and staged.  One instance of the step's code (it is long, and the
-            // instruction cache is shared with the other roles): the prefetched values are moved
-            // into `cur` after their wait.
-            if (ns == 0) {
-                release_acc();
-            } else {
+            // step s is converted and staged; the prefetched values are moved into `cur` after
+            // their wait.
+            auto run_steps = [&](auto sig_c) {
                 uint32_t cur[32], nxt[32];
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(0)), nxt);
 #pragma unroll 1
@@ -1251,11 +1336,37 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
                     if (s + 1 < ns) tmem_ld_32x32(t_row + static_cast<uint32_t>(step_col(s + 1)), nxt);
                     else release_acc();
-                    emit(cur, s, s == 0 ? bias_mine[0] : s == 1 ? bias_mine[1] : s == 2 ? bias_mine[2] : bias_mine[3]);
+                    emit(sig_c, cur, s, s == 0 ? bias_mine[0] : s == 1 ? bias_mine[1] : s == 2 ? bias_mine[2] : bias_mine[3]);
+                }
+            };
+            if (ns == 0) {
+                release_acc();
+            } else {
+                // The tile's signature: uniform over the CTA (beta counts even where this thread's
+                // row lies below the matrix; the step itself looks at the row).
+                uint32_t sig = (ops & ~kOpBeta) | (!partial && beta != 0.0f ? kOpBeta : 0u) | (out_bf16 ? kSigBf16 : 0u);
+                if (kLse) sig |= ext & kSigExtMask;
+                if (!kLse) {
+                    switch (sig) {
+                        case kSigBf16: run_steps(Sig<kSigBf16>{}); break;                                  // dX
+                        case kSigBf16 | kOpAlpha: run_steps(Sig<kSigBf16 | kOpAlpha>{}); break;            // attention scores
+                        case kSigBf16 | kOpBias: run_steps(Sig<kSigBf16 | kOpBias>{}); break;              // Linear forward
+                        case kSigBf16 | kOpBias | kOpGelu: run_steps(Sig<kSigBf16 | kOpBias | kOpGelu>{}); break;  // MLP fc
+                        default: run_steps(Sig<kSigGeneric>{}); break;
+                    }
+                } else {
+                    switch (sig) {
+                        case kEpiLse | kSigBf16 | kOpAlpha: run_steps(Sig<kEpiLse | kSigBf16 | kOpAlpha>{}); break;        // softmax, first pass
+                        case kEpiExpSub | kSigBf16 | kOpAlpha: run_steps(Sig<kEpiExpSub | kSigBf16 | kOpAlpha>{}); break;  // softmax, second pass
+                        case kEpiMulAux | kSigBf16: run_steps(Sig<kEpiMulAux | kSigBf16>{}); break;                         // softmax backward
+                        case kEpiLse: run_steps(Sig<kEpiLse>{}); break;                                                     // LM head + loss
+                        case kEpiLse | kOpBias: run_steps(Sig<kEpiLse | kOpBias>{}); break;
+                        default: run_steps(Sig<kSigGeneric>{}); break;
+                    }
                 }
             }
-            if (kLse && row_ok)
-                p.lse_stats[static_cast<int64_t>(tc.n_tile * 2 + half) * pm + row0 + lane] = make_float2(lse_m, lse_s);
+            if (kLse && (ext & kEpiLse) && row_ok)
+                p.ext_stats[static_cast<int64_t>(tc.n_tile * 2 + half) * p.batch * pm + ext_row] = make_float2(lse_m, lse_s);
             ++acc_seq;
         }
         // Outstanding TMA stores must have read their staging buffers before the shared memory goes

@@ -385,4 +385,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_ma
 }
 
 }  // namespace ptx
+// 2^x by the special-function unit (relative error about 2^-22; 2^-inf = 0 exactly).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 }  // namespace llmt_b200

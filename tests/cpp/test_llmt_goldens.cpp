@@ -6,6 +6,7 @@
 // code 0 = all checks passed.
 //
 //   test_llmt_goldens <dir with the llmt golden cases>
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -410,6 +411,92 @@ void test_bf16_linear(Device& dev) {
     expect(rel_fro(download(l32.bias_param()->grad), db), 1e-5, "fp32 Linear dbias accumulates");
 }
 
+// bf16 attention through the same C++ interface: attention_fwd takes the softmax inside the scores
+// GEMM (the context's workspace holds the row statistics), attention_bwd with the forward's
+// y_heads takes dS out of the dP launch.  Checked against a host computation in double on the
+// same bf16 values, and the fused backward against llmt's composition (dP stored, softmax
+// backward as a kernel of its own) on the same probabilities.
+void test_bf16_attention_fused(Device& dev) {
+    const int64_t B = 2, H = 3, T = 160, HD = 64;
+    const RunCtx c16 = dev.make_ctx(1, KernelBackend::Naive, PrecisionPolicy::bf16_mixed());
+    Arena arena(64 << 20, "bf16-attn-test");
+    uint32_t lcg = 777u;
+    auto rnd = [&](float scale) { lcg = lcg * 1664525u + 1013904223u; return scale * (static_cast<float>(lcg >> 8) / 8388608.0f - 1.0f); };
+    auto make = [&](const Shape& shape, float scale, std::vector<float>* keep) {
+        Tensor t = arena.alloc(shape, DType::BF16);
+        std::vector<uint16_t> hb(static_cast<size_t>(t.numel()));
+        keep->resize(hb.size());
+        for (size_t i = 0; i < hb.size(); ++i) { hb[i] = to_bf16(rnd(scale)); (*keep)[i] = from_bf16(hb[i]); }
+        CUDA_CHECK(cudaMemcpy(t.data, hb.data(), hb.size() * 2, cudaMemcpyHostToDevice));
+        return t;
+    };
+    auto widen = [&](const Tensor& t) {
+        std::vector<uint16_t> hb(static_cast<size_t>(t.numel()));
+        CUDA_CHECK(cudaMemcpy(hb.data(), t.data, hb.size() * 2, cudaMemcpyDeviceToHost));
+        std::vector<float> h(hb.size());
+        for (size_t i = 0; i < h.size(); ++i) h[i] = from_bf16(hb[i]);
+        return h;
+    };
+    auto expect = [&](double err, double tol, const char* what) {
+        ++g_checks;
+        if (!(err <= tol)) { ++g_failures; std::fprintf(stderr, "FAIL %s: rel %.3e > %.1e\n", what, err, tol); }
+        else std::printf("ok   %s (rel %.2e)\n", what, err);
+    };
+    std::vector<float> qh, kh, vh, doh;
+    const Shape hs{B, H, T, HD};
+    const Tensor q = make(hs, 1.5f, &qh), k = make(hs, 1.5f, &kh), v = make(hs, 1.0f, &vh), d_o = make(hs, 0.02f, &doh);
+    Tensor scores = arena.alloc({B, H, T, T}, DType::BF16), yh = arena.alloc(hs, DType::BF16);
+    Tensor y = arena.alloc({B, T, H * HD}, DType::BF16);
+    const kernels::MaskSpec causal{kernels::MaskKind::Causal};
+    kernels::attention_fwd(c16, y, scores, yh, q, k, v, causal);
+    dev.synchronize();
+    // host: P = causal softmax(q k^T / sqrt(hd)), O = P v
+    std::vector<float> p_ref(static_cast<size_t>(B * H * T * T), 0.0f), o_ref(static_cast<size_t>(B * H * T * HD), 0.0f);
+    const double scale = 1.0 / std::sqrt(static_cast<double>(HD));
+    for (int64_t bh = 0; bh < B * H; ++bh)
+        for (int64_t i = 0; i < T; ++i) {
+            std::vector<double> srow(static_cast<size_t>(i + 1));
+            double mx = -1e300;
+            for (int64_t j = 0; j <= i; ++j) {
+                double acc = 0;
+                for (int64_t d = 0; d < HD; ++d)
+                    acc += double(qh[static_cast<size_t>((bh * T + i) * HD + d)]) * kh[static_cast<size_t>((bh * T + j) * HD + d)];
+                srow[static_cast<size_t>(j)] = acc * scale;
+                mx = std::max(mx, acc * scale);
+            }
+            double sum = 0;
+            for (double& e : srow) { e = std::exp(e - mx); sum += e; }
+            for (int64_t j = 0; j <= i; ++j) {
+                const double pij = srow[static_cast<size_t>(j)] / sum;
+                p_ref[static_cast<size_t>((bh * T + i) * T + j)] = static_cast<float>(pij);
+                for (int64_t d = 0; d < HD; ++d)
+                    o_ref[static_cast<size_t>((bh * T + i) * HD + d)] += static_cast<float>(pij * vh[static_cast<size_t>((bh * T + j) * HD + d)]);
+            }
+        }
+    const std::vector<float> p_got = widen(scores);
+    expect(rel_fro(p_got, p_ref), 1e-2, "bf16 attention_fwd probabilities (softmax inside the scores GEMM) vs host");
+    expect(rel_fro(widen(yh), o_ref), 1e-2, "bf16 attention_fwd y_heads vs host");
+    ++g_checks;
+    bool zeros = true;
+    for (int64_t bh = 0; bh < B * H && zeros; ++bh)
+        for (int64_t i = 0; i < T && zeros; ++i)
+            for (int64_t j = i + 1; j < T; ++j)
+                if (p_got[static_cast<size_t>((bh * T + i) * T + j)] != 0.0f) { zeros = false; break; }
+    if (!zeros) { ++g_failures; std::fprintf(stderr, "FAIL bf16 attention_fwd: a masked probability is not exactly 0\n"); }
+    else std::printf("ok   bf16 attention_fwd masked probabilities are exact zeros\n");
+    // backward: dS out of the dP launch vs llmt's composition
+    Tensor dq1 = arena.alloc(hs, DType::BF16), dk1 = arena.alloc(hs, DType::BF16), dv1 = arena.alloc(hs, DType::BF16);
+    Tensor dq2 = arena.alloc(hs, DType::BF16), dk2 = arena.alloc(hs, DType::BF16), dv2 = arena.alloc(hs, DType::BF16);
+    Tensor ds1 = arena.alloc({B, H, T, T}, DType::BF16), ds2 = arena.alloc({B, H, T, T}, DType::BF16);
+    kernels::attention_bwd(c16, dq1, dk1, dv1, ds1, d_o, scores, q, k, v, &yh, causal);
+    kernels::attention_bwd(c16, dq2, dk2, dv2, ds2, d_o, scores, q, k, v);
+    dev.synchronize();
+    expect(rel_fro(widen(ds1), widen(ds2)), 2e-2, "bf16 attention_bwd dS (out of the dP launch) vs composition");
+    expect(rel_fro(widen(dq1), widen(dq2)), 2e-2, "bf16 attention_bwd dQ");
+    expect(rel_fro(widen(dk1), widen(dk2)), 2e-2, "bf16 attention_bwd dK");
+    expect(rel_fro(widen(dv1), widen(dv2)), 1e-6, "bf16 attention_bwd dV");
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -426,6 +513,7 @@ int main(int argc, char** argv) {
     test_attention_packed(dev, ctx);
     test_cross_entropy(dev, ctx);
     test_bf16_linear(dev);
+    test_bf16_attention_fused(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());
     return g_failures == 0 ? 0 : 1;

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(set(declared_symbols())) == sorted(set(L.EXPORTS) | set(declared_symbols()))
-    assert lib.llmt_b200_abi_version() == 4
+    assert lib.llmt_b200_abi_version() == 5
 
 
 def test_descriptor_layout_matches_the_header():
