@@ -609,13 +609,41 @@ def lm_head_ce_comparison(torch, L, m, dev):
     ms_u = _loop_ms(torch, [unfused], iters=10, warm=3)
     ms_f = _loop_ms(torch, [fused], iters=10, warm=3)
     L.device_status()
+    # backward: dlogits in place of the stored logits (llmt's plan, docs/TODO.md:216-217) against the
+    # product made again with the gradient as its epilogue (bf16 dlogits, no logits in memory)
+    dl = torch.empty(m, LD, device=dev, dtype=bf)[:, :V]
+    d3 = L.GemmDesc()
+    d3.m, d3.n, d3.k, d3.batch = m, V, C, 1
+    d3.lda, d3.ldb, d3.ldc = C, C, LD
+    d3.trans_a, d3.trans_b = 0, 1
+    d3.dtype_ab, d3.dtype_c = L.BF16, L.BF16
+    d3.alpha = 1.0
+    d3.workspace, d3.workspace_bytes = ws.data_ptr(), need
+
+    def bwd_unfused():
+        L.cross_entropy_bwd(logits, logits, tg, mk)
+
+    def bwd_fused():
+        L.lm_head_ce_bwd(d3, dl, x, w, tg, mk, 1.0, True)
+
+    fused()  # leaves the statistics the fused backward reuses
+    ms_bf = _loop_ms(torch, [bwd_fused], iters=10, warm=3)
+    unfused()
+    ref = torch.empty_like(logits)
+    L.cross_entropy_bwd(ref, logits, tg, mk)
+    bwd_err = float(((dl.float() - ref).norm() / ref.norm()).item())
+    del ref
+    ms_bu = _loop_ms(torch, [bwd_unfused], iters=10, warm=3)  # (in place: later iterations read gradients, same traffic)
+    L.device_status()
     flops = 2.0 * m * V * C
     return {"shape": f"{m} x {V} x {C}, bf16 operands, fp32 logits (pitch {LD})",
             "gemm_then_cross_entropy_ms": round(ms_u, 4), "fused_ms": round(ms_f, 4),
             "gemm_then_cross_entropy_tflops": round(flops / ms_u / 1e9, 1), "fused_tflops": round(flops / ms_f / 1e9, 1),
             "loss_unfused": float(loss1.item()), "loss_fused": float(loss2.item()),
             "losses_agree": bool(abs(float(loss1.item()) - float(loss2.item())) <= 1e-4 * abs(float(loss1.item()))),
-            "logit_bytes_not_written": int(m) * V * 4}
+            "logit_bytes_not_written": int(m) * V * 4,
+            "bwd_cross_entropy_bwd_in_place_ms": round(ms_bu, 4), "bwd_fused_ms": round(ms_bf, 4),
+            "bwd_rel_fro_diff": bwd_err}
 
 
 def attention_softmax_comparison(torch, L, dev):

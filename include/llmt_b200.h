@@ -332,6 +332,25 @@ LLMT_B200_API uint64_t llmt_b200_lm_head_ce_workspace_bytes(const llmt_b200_gemm
 LLMT_B200_API int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* desc, void* logits, const void* a, const void* b,
                              const int32_t* targets, const float* mask, float* row_nll, float* loss, void* stream);
 
+/* The backward pass of the same loss (llmt docs/TODO.md:216-217, planned there as cross_entropy_bwd:
+ * dlogits = (softmax - onehot) * mask / sum(mask), written in place of the logits).
+ *
+ * llmt_b200_cross_entropy_bwd: that kernel on fp32 logits in memory; dlogits may be the logits tensor
+ * itself (in place, one pitch) or a tensor that does not overlap it.  `dloss` scales the result
+ * (the upstream gradient of the mean loss, 1 for a plain backward pass).
+ *
+ * llmt_b200_lm_head_ce_bwd: the same gradient without logits in memory: the LM-head product is made
+ * again and leaves as (exp(logit - lse[row]) - [col == target[row]]) * dloss * mask[row] / sum(mask)
+ * in desc.dtype_c (bf16: directly the operand of the LM head's dX and dW products), pitch desc.ldc.
+ * Same desc (apart from dtype_c / ldc), operands and workspace size as llmt_b200_lm_head_ce_fwd.
+ * stats_valid != 0: desc.workspace still holds what llmt_b200_lm_head_ce_fwd left there for this
+ * product (nothing else has used it since), so the statistics pass is skipped; 0: it is run first.
+ * No counterparts in llmt (planned, not written). */
+LLMT_B200_API int llmt_b200_cross_entropy_bwd(float* dlogits, const float* logits, const int32_t* targets, const float* mask,
+                                float dloss, int64_t rows, int64_t vocab, int64_t ld_in, int64_t ld_out, void* stream);
+LLMT_B200_API int llmt_b200_lm_head_ce_bwd(const llmt_b200_gemm_desc* desc, void* dlogits, const void* a, const void* b,
+                             const int32_t* targets, const float* mask, float dloss, int32_t stats_valid, void* stream);
+
 /* ---- the softmax of an attention layer fused around its GEMMs --------------------------------
  * (llmt src/kernels/attention.cpp:60-62: scores = alpha q k^T, softmax in place, y = probs v;
  *  src/kernels/softmax.cu:25-51: the masking rule; docs/TODO.md:226-228: the backward products.)

@@ -30,7 +30,7 @@ EXPORTS = [
     "llmt_b200_gemm_grouped_exchange", "llmt_b200_exchange_begin_step",
     "llmt_b200_cross_entropy_fwd", "llmt_b200_lm_head_ce_workspace_bytes", "llmt_b200_lm_head_ce_fwd",
     "llmt_b200_gemm_softmax_workspace_bytes", "llmt_b200_gemm_softmax_fwd", "llmt_b200_gemm_softmax_bwd",
-    "llmt_b200_rowdot",
+    "llmt_b200_rowdot", "llmt_b200_cross_entropy_bwd", "llmt_b200_lm_head_ce_bwd",
 ]
 
 COMM_MAX_RANKS, COMM_MAX_CTAS = 8, 128
@@ -143,6 +143,10 @@ def lib() -> ctypes.CDLL:
         L.llmt_b200_lm_head_ce_workspace_bytes.restype = ctypes.c_uint64
         L.llmt_b200_lm_head_ce_fwd.argtypes = [ctypes.POINTER(GemmDesc)] + [ctypes.c_void_p] * 8
         L.llmt_b200_lm_head_ce_fwd.restype = ctypes.c_int
+        L.llmt_b200_cross_entropy_bwd.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_float] + [ctypes.c_int64] * 4 + [ctypes.c_void_p]
+        L.llmt_b200_cross_entropy_bwd.restype = ctypes.c_int
+        L.llmt_b200_lm_head_ce_bwd.argtypes = [ctypes.POINTER(GemmDesc)] + [ctypes.c_void_p] * 5 + [ctypes.c_float, ctypes.c_int32, ctypes.c_void_p]
+        L.llmt_b200_lm_head_ce_bwd.restype = ctypes.c_int
         L.llmt_b200_gemm_softmax_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p]
         L.llmt_b200_gemm_softmax_workspace_bytes.restype = ctypes.c_uint64
         L.llmt_b200_gemm_softmax_fwd.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -414,6 +418,26 @@ def lm_head_ce_fwd(desc: GemmDesc, logits, a, b, targets, mask, row_nll, loss, s
     _check(lib().llmt_b200_lm_head_ce_fwd(ctypes.byref(desc), logits.data_ptr() if logits is not None else None,
                                           a.data_ptr(), b.data_ptr(), targets.data_ptr(), mask.data_ptr(),
                                           row_nll.data_ptr(), loss.data_ptr(), _stream(stream)))
+
+
+def cross_entropy_bwd(dlogits, logits, targets, mask, dloss: float = 1.0, stream=None) -> None:
+    """dlogits = (softmax(logits) - onehot(targets)) * dloss * mask / sum(mask) on fp32 logits [..., V];
+    dlogits may be `logits` itself (in place)."""
+    v = logits.shape[-1]
+    rows = logits.numel() // v
+    if _dtype_code(logits) != FP32 or _dtype_code(dlogits) != FP32 or dlogits.shape != logits.shape:
+        raise LlmtB200Error(ERR_INVALID, "cross_entropy_bwd: fp32 logits and dlogits of one shape")
+    _check(lib().llmt_b200_cross_entropy_bwd(dlogits.data_ptr(), logits.data_ptr(), targets.data_ptr(), mask.data_ptr(),
+                                             float(dloss), rows, v, logits.stride(-2) if logits.dim() > 1 else v,
+                                             dlogits.stride(-2) if dlogits.dim() > 1 else v, _stream(stream)))
+
+
+def lm_head_ce_bwd(desc: GemmDesc, dlogits, a, b, targets, mask, dloss: float = 1.0, stats_valid: bool = False,
+                   stream=None) -> None:
+    """dLogits of the LM head's cross-entropy from the product itself (llmt_b200_lm_head_ce_bwd)."""
+    _check(lib().llmt_b200_lm_head_ce_bwd(ctypes.byref(desc), dlogits.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                          targets.data_ptr(), mask.data_ptr(), float(dloss), 1 if stats_valid else 0,
+                                          _stream(stream)))
 
 
 def gemm_softmax_workspace_bytes(desc: GemmDesc, a=None, b=None) -> int:

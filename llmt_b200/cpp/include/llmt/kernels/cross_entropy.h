@@ -24,4 +24,16 @@ void lm_head_cross_entropy_fwd(const RunCtx& ctx, Tensor& loss, Tensor& row_nll,
                                const Tensor& w, const Tensor* bias, const Tensor& targets,
                                const Tensor& mask) noexcept;
 
+// The backward pass (llmt docs/TODO.md:216-217, planned as cross_entropy_bwd, not written there):
+//   dlogits = (softmax(logits) - onehot(targets)) * dloss * mask / sum(mask)
+// cross_entropy_bwd: from fp32 logits in memory; dlogits may be the logits tensor itself (in place).
+// lm_head_cross_entropy_bwd: from the LM-head product made again, so that no logits need exist;
+// dlogits [B, T, V] bf16 (the operand of the LM head's dX and dW products) or fp32.  stats_valid:
+// ctx.blas_workspace still holds what lm_head_cross_entropy_fwd left there for the same x and w.
+void cross_entropy_bwd(const RunCtx& ctx, Tensor& dlogits, const Tensor& logits, const Tensor& targets,
+                       const Tensor& mask, float dloss = 1.0f) noexcept;
+void lm_head_cross_entropy_bwd(const RunCtx& ctx, Tensor& dlogits, const Tensor& x, const Tensor& w, const Tensor* bias,
+                               const Tensor& targets, const Tensor& mask, float dloss = 1.0f,
+                               bool stats_valid = false) noexcept;
+
 }  // namespace llmt::kernels

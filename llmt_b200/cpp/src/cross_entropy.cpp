@@ -92,4 +92,50 @@ void lm_head_cross_entropy_fwd(const RunCtx& ctx, Tensor& loss, Tensor& row_nll,
     if (st != LLMT_B200_OK) detail::fatal(who, "%s", llmt_b200_last_error());
 }
 
+void cross_entropy_bwd(const RunCtx& ctx, Tensor& dlogits, const Tensor& logits, const Tensor& targets,
+                       const Tensor& mask, float dloss) noexcept {
+    const char* who = "cross_entropy_bwd";
+    if (logits.shape.rank != 3) detail::fatal(who, "logits must be [B, T, V]");
+    if (dlogits.shape != logits.shape) detail::fatal(who, "dlogits/logits shape mismatch");
+    if (logits.dtype != DType::FP32 || dlogits.dtype != DType::FP32) detail::fatal(who, "logits and dlogits must be fp32");
+    const Shape bt{logits.shape[0], logits.shape[1]};
+    if (targets.shape != bt || targets.dtype != DType::I32) detail::fatal(who, "targets must be [B, T] I32");
+    if (mask.shape != bt || mask.dtype != DType::FP32) detail::fatal(who, "mask must be [B, T] fp32");
+    for (const Tensor* t : std::initializer_list<const Tensor*>{&dlogits, &logits, &targets, &mask})
+        if (!t->valid()) detail::fatal(who, "invalid tensor (null data)");
+    const int64_t v = logits.shape[2];
+    const int st = llmt_b200_cross_entropy_bwd(static_cast<float*>(dlogits.data), static_cast<const float*>(logits.data),
+                                               static_cast<const int32_t*>(targets.data), static_cast<const float*>(mask.data),
+                                               dloss, bt[0] * bt[1], v, v, v, ctx.stream);
+    if (st != LLMT_B200_OK) detail::fatal(who, "%s", llmt_b200_last_error());
+}
+
+void lm_head_cross_entropy_bwd(const RunCtx& ctx, Tensor& dlogits, const Tensor& x, const Tensor& w, const Tensor* bias,
+                               const Tensor& targets, const Tensor& mask, float dloss, bool stats_valid) noexcept {
+    const char* who = "lm_head_cross_entropy_bwd";
+    if (x.shape.rank != 3) detail::fatal(who, "x must be [B, T, C]");
+    if (w.shape.rank != 2 || w.shape[1] != x.shape[2]) detail::fatal(who, "w must be [V, C]");
+    if (x.dtype != DType::BF16 || w.dtype != DType::BF16) detail::fatal(who, "x and w must be bf16");
+    const Shape bt{x.shape[0], x.shape[1]};
+    if (dlogits.shape != Shape{bt[0], bt[1], w.shape[0]}) detail::fatal(who, "dlogits must be [B, T, V]");
+    if (dlogits.dtype != DType::BF16 && dlogits.dtype != DType::FP32) detail::fatal(who, "dlogits must be bf16 or fp32");
+    if (targets.shape != bt || targets.dtype != DType::I32) detail::fatal(who, "targets must be [B, T] I32");
+    if (mask.shape != bt || mask.dtype != DType::FP32) detail::fatal(who, "mask must be [B, T] fp32");
+    for (const Tensor* t : std::initializer_list<const Tensor*>{&dlogits, &x, &w, &targets, &mask})
+        if (!t->valid()) detail::fatal(who, "invalid tensor (null data)");
+    llmt_b200_gemm_desc d = lm_head_desc(x, w);
+    d.dtype_c = static_cast<int32_t>(dlogits.dtype);
+    if (bias != nullptr) {
+        if (!bias->valid() || bias->numel() != w.shape[0]) detail::fatal(who, "bias must be [V]");
+        d.epilogue = LLMT_B200_EPI_BIAS;
+        d.bias = bias->data;
+        d.bias_dtype = static_cast<int32_t>(bias->dtype);
+    }
+    d.workspace = ctx.blas_workspace;
+    d.workspace_bytes = ctx.blas_workspace_bytes;
+    const int st = llmt_b200_lm_head_ce_bwd(&d, dlogits.data, x.data, w.data, static_cast<const int32_t*>(targets.data),
+                                            static_cast<const float*>(mask.data), dloss, stats_valid ? 1 : 0, ctx.stream);
+    if (st != LLMT_B200_OK) detail::fatal(who, "%s", llmt_b200_last_error());
+}
+
 }  // namespace llmt::kernels

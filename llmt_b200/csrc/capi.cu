@@ -1091,19 +1091,24 @@ namespace {
 // then the per-part (maximum, sum of exponentials) pairs, then the target logits.
 struct LmHeadCePlan {
     TcPlan pl;
-    size_t gemm_bytes, stats_off, tgt_off, total;
+    size_t gemm_bytes, stats_off, tgt_off, grad_off, sum_off, total;
     int parts;
 };
+// One plan for the forward and the backward call on the same product, whatever type each of them
+// stores: the backward pass may reuse the statistics the forward pass left in the workspace.
 LmHeadCePlan lm_head_ce_plan(const llmt_b200_gemm_desc* d, const Checked& ck, const void* a, const void* b) {
     LmHeadCePlan r;
     llmt_b200_gemm_desc local = *d;
     local.plan_splits = 1;  // the epilogue sees whole reductions
+    local.dtype_c = LLMT_B200_FP32;
     r.pl = plan_single(&local);
     r.gemm_bytes = r.pl.workspace_bytes + repack_plan(&local, ck, a, b).total();
     r.parts = 2 * r.pl.tiles_n;
     r.stats_off = (r.gemm_bytes + 255) / 256 * 256;
     r.tgt_off = r.stats_off + (static_cast<size_t>(r.parts) * d->m * 8 + 255) / 256 * 256;
-    r.total = r.tgt_off + (static_cast<size_t>(d->m) * 4 + 255) / 256 * 256;
+    r.grad_off = r.tgt_off + (static_cast<size_t>(d->m) * 4 + 255) / 256 * 256;    // (lse, weight) per row
+    r.sum_off = r.grad_off + (static_cast<size_t>(d->m) * 8 + 255) / 256 * 256;    // the mask's sum
+    r.total = r.sum_off + 256;
     return r;
 }
 int lm_head_ce_check(const llmt_b200_gemm_desc* d) {
@@ -1161,6 +1166,75 @@ int llmt_b200_lm_head_ce_fwd(const llmt_b200_gemm_desc* d, void* logits, const v
     st = launch_group(&p, 1, lp.pl.pairs != 0, s, nullptr, /*lse=*/true);
     if (st != LLMT_B200_OK) return st;
     cudaError_t e = launch_cross_entropy_from_stats(loss, row_nll, p.ext_stats, p.ext_rowvec, mask, d->m, lp.parts, s);
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    return LLMT_B200_OK;
+}
+
+int llmt_b200_lm_head_ce_bwd(const llmt_b200_gemm_desc* d, void* dlogits, const void* a, const void* b,
+                             const int32_t* targets, const float* mask, float dloss, int32_t stats_valid,
+                             void* stream) {
+    Checked ck{};
+    int st = validate(d, dlogits, a, b, &ck);
+    if (st != LLMT_B200_OK) return st;
+    st = lm_head_ce_check(d);
+    if (st != LLMT_B200_OK) return st;
+    if (targets == nullptr || mask == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "lm_head_ce_bwd: null targets or mask");
+    if (d->beta != 0.0f) return fail(LLMT_B200_ERR_UNSUPPORTED, "lm_head_ce_bwd: beta must be 0");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    llmt_b200_gemm_desc local = *d;
+    local.plan_splits = 1;
+    const LmHeadCePlan lp = lm_head_ce_plan(d, ck, a, b);
+    if (d->workspace == nullptr || d->workspace_bytes < lp.total)
+        return fail(LLMT_B200_ERR_WORKSPACE, "lm_head_ce_bwd: needs %llu workspace bytes (llmt_b200_lm_head_ce_workspace_bytes), got %llu",
+                    (unsigned long long)lp.total, (unsigned long long)d->workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(d->workspace) & 255u)
+        return fail(LLMT_B200_ERR_INVALID, "matmul: workspace must be 256-byte aligned");
+    const Repack rp = repack_plan(&local, ck, a, b);
+    if (rp.total() > 0) {
+        st = apply_repack(&local, ck, rp, lp.pl.workspace_bytes, &a, &b, s);
+        if (st != LLMT_B200_OK) return st;
+    }
+    char* ws = static_cast<char*>(d->workspace);
+    float2* stats = reinterpret_cast<float2*>(ws + lp.stats_off);
+    GroupProblem p;
+    if (!stats_valid) {
+        // the statistics pass of the forward call, storing nothing
+        st = fill_problem(&p, &local, ck, lp.pl, nullptr, a, b);
+        if (st != LLMT_B200_OK) return st;
+        p.ext_stats = stats;
+        p.ext_rowvec = nullptr;
+        p.ext_ptr = nullptr;
+        p.epi_flags |= kEpiLse;
+        st = launch_group(&p, 1, lp.pl.pairs != 0, s, nullptr, /*lse=*/true);
+        if (st != LLMT_B200_OK) return st;
+    }
+    float2* rows = reinterpret_cast<float2*>(ws + lp.grad_off);
+    cudaError_t e = launch_ce_grad_rows(rows, stats, nullptr, mask, reinterpret_cast<float*>(ws + lp.sum_off), dloss,
+                                        d->m, lp.parts, s);
+    if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
+    st = fill_problem(&p, &local, ck, lp.pl, dlogits, a, b);
+    if (st != LLMT_B200_OK) return st;
+    p.ext_stats = rows;
+    p.ext_rowvec = nullptr;
+    p.ext_ptr = targets;
+    p.epi_flags |= kEpiCeGrad;
+    return launch_group(&p, 1, lp.pl.pairs != 0, s, nullptr, /*lse=*/true);
+}
+
+int llmt_b200_cross_entropy_bwd(float* dlogits, const float* logits, const int32_t* targets, const float* mask,
+                                float dloss, int64_t rows, int64_t vocab, int64_t ld_in, int64_t ld_out, void* stream) {
+    if (dlogits == nullptr || logits == nullptr || targets == nullptr || mask == nullptr)
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_bwd: invalid tensor (null data)");
+    if (rows < 1 || vocab < 1 || ld_in < vocab || ld_out < vocab)
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_bwd: bad shape (rows %lld, vocab %lld, pitches %lld %lld)",
+                    (long long)rows, (long long)vocab, (long long)ld_in, (long long)ld_out);
+    if (dlogits != logits && overlaps(dlogits, static_cast<size_t>(rows) * ld_out * 4, logits, static_cast<size_t>(rows) * ld_in * 4))
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_bwd: dlogits must be the logits tensor itself or not overlap it");
+    if (dlogits == logits && ld_in != ld_out)
+        return fail(LLMT_B200_ERR_INVALID, "cross_entropy_bwd: in place needs one pitch");
+    cudaError_t e = launch_cross_entropy_bwd(dlogits, logits, targets, mask, dloss, rows, vocab, ld_in, ld_out,
+                                             static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LLMT_B200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(e));
     return LLMT_B200_OK;
 }

@@ -33,6 +33,7 @@ constexpr int kEpiLse = 0x100;     // per row and per half tile: maximum and sum
 constexpr int kEpiCausal = 0x200;  // columns beyond the row's own index do not exist (value exactly 0 when stored)
 constexpr int kEpiExpSub = 0x400;  // v = exp(v - ext_rowvec[row])
 constexpr int kEpiMulAux = 0x800;  // v = aux[row, col] * (v - ext_rowvec[row]), aux laid out like C
+constexpr int kEpiCeGrad = 0x1000; // v = (exp(v - lse[row]) - [col == target[row]]) * g[row]: the cross-entropy's dLogits
 
 constexpr int kMaxGroupProblems = 8;
 
@@ -81,6 +82,8 @@ struct ProblemScalars {
     //            (int32 [m], one product only) and the target's value goes to ext_rowvec.
     //   kEpiExpSub / kEpiMulAux: ext_rowvec is READ, one value per row of every batch item;
     //            kEpiMulAux reads ext_ptr as the aux tensor (C's element type, pitch and strides).
+    //   kEpiCeGrad: ext_stats is READ as one (lse, g) pair per row, ext_ptr is the rows' target
+    //            columns (int32 [m], one product only).
     float2* ext_stats;          // [2 * tiles_n][batch][m]
     float* ext_rowvec;          // [batch][m]
     const void* ext_ptr;
@@ -253,6 +256,11 @@ cudaError_t launch_head_merge(void* y, const void* x, int64_t B, int64_t H, int6
                               cudaStream_t stream);
 cudaError_t launch_head_split(void* q, void* k, void* v, const void* qkv, int64_t B, int64_t H, int64_t T, int64_t hd,
                               int elem_bytes, cudaStream_t stream);
+cudaError_t launch_cross_entropy_bwd(float* dlogits, const float* logits, const int32_t* targets, const float* mask,
+                                     float dloss, int64_t rows, int64_t v, int64_t ld_in, int64_t ld_out,
+                                     cudaStream_t stream);
+cudaError_t launch_ce_grad_rows(void* out, const void* stats, const float* lse_in, const float* mask, float* mask_sum,
+                                float dloss, int64_t rows, int parts, cudaStream_t stream);
 cudaError_t launch_lse_from_stats(float* lse, const void* stats, int64_t rows, int parts, cudaStream_t stream);
 cudaError_t launch_rowdot(float* out, const void* x, const void* y, int64_t rows, int64_t cols, int64_t ldx,
                           int64_t ldy, int is_bf16, cudaStream_t stream);

@@ -113,6 +113,97 @@ lse_from_stats_kernel(float* lse, const float2* stats, int64_t rows, int parts) 
     lse[row] = m + logf(s);
 }
 
+// sum of the mask in one block's fixed-order tree (the denominator of the mean).
+__global__ void __launch_bounds__(kMeanThreads)
+mask_sum_kernel(float* out, const float* mask, int64_t rows) {
+    __shared__ float sh[kMeanThreads];
+    float w = 0.0f;
+    for (int64_t i = threadIdx.x; i < rows; i += kMeanThreads) w += mask[i];
+    sh[threadIdx.x] = w;
+    __syncthreads();
+    for (int o = kMeanThreads / 2; o > 0; o >>= 1) {
+        if (static_cast<int>(threadIdx.x) < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[0] = sh[0];
+}
+
+// Per row what the dLogits epilogue of the LM-head product needs: (log-sum-exp, weight), the
+// weight being dloss * mask[r] / sum(mask).  The log-sum-exp comes from the per-part pairs of a
+// statistics pass, or from `lse_in` where the forward pass kept it.
+__global__ void __launch_bounds__(256)
+ce_grad_rows_kernel(float2* out, const float2* stats, const float* lse_in, const float* mask, const float* mask_sum,
+                    float dloss, int64_t rows, int parts) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (row >= rows) return;
+    float lse;
+    if (lse_in != nullptr) {
+        lse = lse_in[row];
+    } else {
+        float m = -INFINITY, s = 0.0f;
+        for (int p = 0; p < parts; ++p) {
+            const float2 t = stats[static_cast<int64_t>(p) * rows + row];
+            lse_merge(m, s, t.x, t.y);
+        }
+        lse = m + logf(s);
+    }
+    out[row] = make_float2(lse, dloss * mask[row] / mask_sum[0]);
+}
+
+// llmt's planned cross_entropy_bwd (docs/TODO.md:216-217): dlogits = (softmax - onehot) * mask / sum(mask),
+// written in place of the logits if the caller passes the same tensor.  One warp per row: the
+// log-sum-exp in one pass, the gradient in a second (every element is read and written by the same lane).
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
+ce_bwd_rows_kernel(float* dlogits, const float* logits, const int32_t* targets, const float* mask,
+                   float dloss, int64_t rows, int64_t v, int64_t ld_in, int64_t ld_out) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = logits + row * ld_in;
+    float* y = dlogits + row * ld_out;
+    // 16-byte accesses where both rows allow them; the ragged end by single values
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0u;
+    const int64_t v4 = vec ? v / 4 : 0;
+    float m = -INFINITY, s = 0.0f;
+    auto take = [&](float xi) {
+        if (xi > m) {
+            s = s * __expf(m - xi) + 1.0f;
+            m = xi;
+        } else {
+            s += __expf(xi - m);
+        }
+    };
+    for (int64_t i = lane; i < v4; i += 32) {
+        const float4 q = reinterpret_cast<const float4*>(x)[i];
+        const float mx = fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w));
+        if (mx > m) {
+            s *= __expf(m - mx);  // exp(-inf) = 0 covers the first group
+            m = mx;
+        }
+        s += (__expf(q.x - m) + __expf(q.y - m)) + (__expf(q.z - m) + __expf(q.w - m));
+    }
+    for (int64_t i = 4 * v4 + lane; i < v; i += 32) take(x[i]);
+    lse_warp_combine(m, s);
+    const float lse = m + logf(s);
+    // The mask's sum by every warp for itself, in one fixed order: no scratch, same bits everywhere.
+    float w = 0.0f;
+    for (int64_t i = lane; i < rows; i += 32) w += mask[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+    const float g = dloss * mask[row] / w;
+    const int64_t t = targets[row];
+    for (int64_t i = lane; i < v4; i += 32) {
+        float4 q = reinterpret_cast<const float4*>(x)[i];
+        q.x = __expf(q.x - lse) * g; q.y = __expf(q.y - lse) * g; q.z = __expf(q.z - lse) * g; q.w = __expf(q.w - lse) * g;
+        if ((t >> 2) == i) {
+            const int e = static_cast<int>(t & 3);
+            if (e == 0) q.x -= g; else if (e == 1) q.y -= g; else if (e == 2) q.z -= g; else q.w -= g;
+        }
+        reinterpret_cast<float4*>(y)[i] = q;
+    }
+    for (int64_t i = 4 * v4 + lane; i < v; i += 32) y[i] = (__expf(x[i] - lse) - (i == t ? 1.0f : 0.0f)) * g;
+}
+
 // out[r] = sum_j x[r, j] * y[r, j] in fp32, lanes striding the row, a fixed tree across the warp.
 template <typename T>
 __global__ void __launch_bounds__(kRowsPerBlock * 32)
@@ -146,6 +237,24 @@ cudaError_t launch_cross_entropy_from_stats(float* loss, float* row_nll, const v
     ce_from_stats_kernel<<<row_blocks(rows), kRowsPerBlock * 32, 0, stream>>>(
         row_nll, static_cast<const float2*>(stats), tgt, mask, rows, parts);
     ce_mean_kernel<<<1, kMeanThreads, 0, stream>>>(loss, row_nll, mask, rows);
+    count_launch(2);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_cross_entropy_bwd(float* dlogits, const float* logits, const int32_t* targets, const float* mask,
+                                     float dloss, int64_t rows, int64_t v, int64_t ld_in, int64_t ld_out,
+                                     cudaStream_t stream) {
+    ce_bwd_rows_kernel<<<row_blocks(rows), kRowsPerBlock * 32, 0, stream>>>(dlogits, logits, targets, mask, dloss,
+                                                                            rows, v, ld_in, ld_out);
+    count_launch(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ce_grad_rows(void* out, const void* stats, const float* lse_in, const float* mask, float* mask_sum,
+                                float dloss, int64_t rows, int parts, cudaStream_t stream) {
+    mask_sum_kernel<<<1, kMeanThreads, 0, stream>>>(mask_sum, mask, rows);
+    ce_grad_rows_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, stream>>>(
+        static_cast<float2*>(out), static_cast<const float2*>(stats), lse_in, mask, mask_sum, dloss, rows, parts);
     count_launch(2);
     return cudaGetLastError();
 }

@@ -476,6 +476,8 @@ template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
 //   kEpiExpSub  C = exp(v - ext_rowvec[row]): with the rows' log-sum-exp, the softmax itself
 //   kEpiMulAux  C = aux ⊙ (v - ext_rowvec[row]): the softmax backward dS = P ⊙ (dP - D) as the
 //               epilogue of the product that makes dP
+//   kEpiCeGrad  C = (exp(v - lse[row]) - [col = target[row]]) * g[row]: the cross-entropy's gradient
+//               with respect to the logits, from the LM-head product made a second time
 template <uint32_t V> struct Sig { static constexpr uint32_t value = V; };
 
 template <int CG, bool kLse>
@@ -1067,7 +1069,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             constexpr uint32_t kOpAlpha = 1u, kOpBeta = 2u, kOpBias = 4u, kOpGelu = 8u;
             // A signature: the operation bits, the result type, the extended epilogue's parts; or "generic".
             constexpr uint32_t kSigBf16 = 0x10u, kSigGeneric = 0x80000000u;
-            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux);
+            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux | kEpiCeGrad);
             const float alpha = p.alpha, beta = p.beta;
             const bool c_bf16 = p.c_is_bf16 != 0;
             const void* const c_ptr = p.c;
@@ -1096,7 +1098,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             // Extended epilogue: this thread's row, over the columns this warp produces
             float lse_m = -INFINITY, lse_s = 0.0f;
             int lse_target = -1;
-            float row_val = 0.0f;
+            float row_val = 0.0f, row_scale = 0.0f;
             const uint32_t ext = kLse ? static_cast<uint32_t>(p.epi_flags) : 0u;
             const int64_t ext_row = static_cast<int64_t>(tc.batch) * pm + row0 + lane;
             // Under the mask, with nothing to store, the steps beyond the diagonal for every row of
@@ -1106,6 +1108,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             if (kLse && row_ok) {
                 if ((ext & kEpiLse) && p.ext_ptr != nullptr) lse_target = static_cast<const int32_t*>(p.ext_ptr)[row0 + lane];
                 if (ext & (kEpiExpSub | kEpiMulAux)) row_val = p.ext_rowvec[ext_row];
+                if (ext & kEpiCeGrad) {
+                    const float2 lg = p.ext_stats[row0 + lane];
+                    row_val = lg.x;
+                    row_scale = lg.y;
+                    lse_target = static_cast<const int32_t*>(p.ext_ptr)[row0 + lane];
+                }
                 if (ext & kEpiMulAux) {
                     const int esz = c_bf16 ? 2 : 4;
                     const char* base = static_cast<const char*>(p.ext_ptr) + c_row_off * esz;
@@ -1242,6 +1250,16 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         const float shift = row_val * kLog2e;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], kLog2e, -shift));
+                    } else if (e_ext & kEpiCeGrad) {
+                        // softmax minus one-hot, times the row's weight; absent columns are not stored
+                        const float shift = row_val * kLog2e;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], kLog2e, -shift)) * row_scale;
+                        if (lse_target >= col && lse_target < col + 32) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j == lse_target) v[j] -= row_scale;
+                        }
                     } else if (e_ext & kEpiMulAux) {
                         float aux[32];
                         const int64_t c_off = c_row_off + c0;
@@ -1360,6 +1378,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         case kEpiExpSub | kSigBf16 | kOpAlpha: run_steps(Sig<kEpiExpSub | kSigBf16 | kOpAlpha>{}); break;  // softmax, second pass
                         case kEpiMulAux | kSigBf16: run_steps(Sig<kEpiMulAux | kSigBf16>{}); break;                         // softmax backward
                         case kEpiLse: run_steps(Sig<kEpiLse>{}); break;                                                     // LM head + loss
+                        case kEpiCeGrad | kSigBf16: run_steps(Sig<kEpiCeGrad | kSigBf16>{}); break;                         // dLogits
                         case kEpiLse | kOpBias: run_steps(Sig<kEpiLse | kOpBias>{}); break;
                         default: run_steps(Sig<kSigGeneric>{}); break;
                     }

@@ -186,6 +186,22 @@ def cross_entropy(logits, targets, mask):
     return nll.sum() / w.sum(), nll.reshape(np.asarray(targets).shape)
 
 
+def cross_entropy_bwd(logits, targets, mask, dloss=1.0) -> np.ndarray:
+    """Gradient of the masked mean cross-entropy with respect to the logits, in fp64 (llmt
+    docs/TODO.md:216-217: dlogits = (softmax - onehot) * mask / sum(mask))."""
+    x = np.asarray(logits, dtype=np.float64)
+    v = x.shape[-1]
+    x2 = x.reshape(-1, v)
+    t = np.asarray(targets).reshape(-1).astype(np.int64)
+    w = np.asarray(mask, dtype=np.float64).reshape(-1)
+    m = x2.max(axis=1, keepdims=True)
+    e = np.exp(x2 - m)
+    g = e / e.sum(axis=1, keepdims=True)
+    g[np.arange(x2.shape[0]), t] -= 1.0
+    g *= (dloss * w / w.sum())[:, None]
+    return g.reshape(x.shape)
+
+
 def gelu(x) -> np.ndarray:
     x = np.asarray(x, dtype=np.float64)
     k0, k1 = 0.7978845608028654, 0.044715

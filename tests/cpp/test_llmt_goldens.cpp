@@ -328,6 +328,26 @@ void test_cross_entropy(Device& dev, const RunCtx& ctx) {
     HostTensor wl; wl.shape = Shape{1}; wl.v = download(loss_u);
     check_close(loss_f, wl, "lm_head_cross_entropy_fwd loss");
     check_close(loss_n, wl, "lm_head_cross_entropy_fwd (no logits) loss");
+
+    // Backward: dlogits from the product made again (the statistics of the call above are still in
+    // the workspace) against cross_entropy_bwd on the stored logits, the latter also in place.
+    Tensor dl_f = arena.alloc({B, T, V}, DType::FP32), dl_u = arena.alloc({B, T, V}, DType::FP32);
+    kernels::lm_head_cross_entropy_bwd(c2, dl_f, x, w, nullptr, t2, m2, 1.0f, /*stats_valid=*/true);
+    kernels::cross_entropy_bwd(ctx, dl_u, lg, t2, m2);
+    kernels::cross_entropy_bwd(ctx, lg, lg, t2, m2);  // in place of the logits
+    dev.synchronize();
+    HostTensor wd; wd.shape = Shape{B, T, V}; wd.v = download(dl_u);
+    check_close(dl_f, wd, "lm_head_cross_entropy_bwd dlogits vs cross_entropy_bwd", 1.0, 1e-4, 1e-8);
+    check_close(lg, wd, "cross_entropy_bwd in place of the logits", 1.0, 0.0, 0.0);
+    double worst = 0;
+    for (int64_t r = 0; r < B * T; ++r) {
+        double sum = 0;
+        for (int64_t c = 0; c < V; ++c) sum += wd.v[static_cast<size_t>(r * V + c)];
+        worst = std::max(worst, std::fabs(sum));
+    }
+    ++g_checks;
+    if (worst > 1e-6) { ++g_failures; std::fprintf(stderr, "FAIL cross_entropy_bwd: a row of dlogits sums to %.3e\n", worst); }
+    else std::printf("ok   cross_entropy_bwd rows sum to zero (%.1e)\n", worst);
 }
 
 // bf16 Linear with bias through the same C++ interface: forward with the fused bias,

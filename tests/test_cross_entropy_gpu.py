@@ -115,3 +115,64 @@ def test_lm_head_ce_refuses_what_it_cannot_do():
     with pytest.raises(L.LlmtB200Error) as ei:
         L.lm_head_ce_fwd(d, None, xb, xb, t, o, o, o)  # no workspace
     assert ei.value.status == L.ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("rows,vocab,in_place", [(1, 1, True), (7, 33, False), (64, 50257, True), (300, 1000, False)])
+def test_cross_entropy_bwd_against_the_oracle(rows, vocab, in_place):
+    """llmt's planned cross_entropy_bwd (docs/TODO.md:216-217): (softmax - onehot) * mask / sum(mask),
+    in place of the logits or into another tensor."""
+    rng = np.random.default_rng(rows * 7 + vocab)
+    x = (rng.standard_normal((rows, vocab)) * 3.0).astype(np.float32)
+    x[0, :] += 80.0
+    t = rng.integers(0, vocab, size=rows).astype(np.int32)
+    w = rng.random(rows).astype(np.float32) + 0.1
+    w[rows // 2] = 0.0 if rows > 1 else 1.0
+    xd = torch.from_numpy(x).to(DEV)
+    out = xd if in_place else torch.full_like(xd, float("nan"))
+    L.cross_entropy_bwd(out, xd, torch.from_numpy(t).to(DEV), torch.from_numpy(w).to(DEV), dloss=0.5)
+    L.device_status()
+    want = oracle.cross_entropy_bwd(x, t, w, dloss=0.5)
+    assert_close(out.cpu().numpy(), want, rtol=5e-5, atol=1e-7, what="dlogits")
+
+
+@pytest.mark.parametrize("m,vocab,k,out_dtype,reuse", [(256, 512, 128, torch.bfloat16, True), (300, 1000, 192, torch.float32, False),
+                                                       (1024, 50257, 768, torch.bfloat16, True)])
+def test_lm_head_dlogits_from_the_product(m, vocab, k, out_dtype, reuse):
+    """dLogits of the LM head's cross-entropy without logits in memory: the product made again,
+    leaving as (softmax - onehot) * weight.  `reuse`: the statistics of the forward call are still
+    in the workspace and the statistics pass is skipped; both ways must give the same bits."""
+    rng = np.random.default_rng(m + vocab + k + 1)
+    x = oracle.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = oracle.round_bf16((rng.standard_normal((vocab, k)) * 0.2).astype(np.float32))
+    t = rng.integers(0, vocab, size=m).astype(np.int32)
+    msk = rng.random(m).astype(np.float32)
+    xd = torch.from_numpy(x).to(DEV).to(torch.bfloat16)
+    wd = torch.from_numpy(w).to(DEV).to(torch.bfloat16)
+    td, md = torch.from_numpy(t).to(DEV), torch.from_numpy(msk).to(DEV)
+    ld = (vocab + 7) // 8 * 8
+    dl = torch.full((m, ld), float("nan"), device=DEV, dtype=out_dtype)[:, :vocab]
+    d = L.GemmDesc()
+    d.m, d.n, d.k, d.batch = m, vocab, k, 1
+    d.lda, d.ldb, d.ldc = k, k, ld
+    d.trans_a, d.trans_b = 0, 1
+    d.dtype_ab, d.dtype_c = L.BF16, (L.BF16 if out_dtype == torch.bfloat16 else L.FP32)
+    d.alpha, d.beta = 1.0, 0.0
+    need = L.lm_head_ce_workspace_bytes(d, xd, wd)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    d.workspace, d.workspace_bytes = ws.data_ptr(), need
+    if reuse:
+        loss, nll = torch.empty(1, device=DEV), torch.empty(m, device=DEV)
+        L.lm_head_ce_fwd(d, None, xd, wd, td, md, nll, loss)
+    L.lm_head_ce_bwd(d, dl, xd, wd, td, md, dloss=1.0, stats_valid=reuse)
+    L.device_status()
+    want = oracle.cross_entropy_bwd(oracle.gemm(x, w, False, True), t, msk)
+    got = dl.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    tol = 4e-3 if out_dtype == torch.bfloat16 else 2e-4
+    assert oracle.rel_fro(got, want) <= tol
+    # the gradient of every row sums to zero (softmax minus one-hot), up to the result type's rounding
+    assert np.abs(got.sum(-1)).max() <= (5e-3 if out_dtype == torch.bfloat16 else 1e-6)
+    # the other way round gives the same bits
+    dl2 = torch.full((m, ld), float("nan"), device=DEV, dtype=out_dtype)[:, :vocab]
+    L.lm_head_ce_bwd(d, dl2, xd, wd, td, md, dloss=1.0, stats_valid=False)
+    assert torch.equal(dl, dl2)

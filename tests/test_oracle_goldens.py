@@ -122,3 +122,26 @@ def test_oracle_cross_entropy_matches_llmt_golden():
     loss, nll = oracle.cross_entropy(g.tensor("logits"), g.tensor("targets"), g.tensor("mask"))
     assert_close(nll, g.tensor("wnll"), what="cross_entropy row_nll")
     assert_close(np.array([loss]), g.tensor("loss"), what="cross_entropy loss")
+
+
+def test_oracle_cross_entropy_bwd_matches_torch_autograd():
+    # llmt has no cross_entropy_bwd yet (docs/TODO.md:216-217 gives the formula); its golden
+    # generator differentiates through torch, so the oracle is pinned against torch autograd on
+    # llmt's own cross_entropy inputs and on a larger seeded case.
+    import torch
+    g = GoldenCase("cross_entropy")
+    cases = [(g.tensor("logits"), g.tensor("targets"), g.tensor("mask"))]
+    rng = np.random.default_rng(3)
+    cases.append(((rng.standard_normal((3, 5, 97)) * 4).astype(np.float32), rng.integers(0, 97, (3, 5)).astype(np.int32),
+                  rng.random((3, 5)).astype(np.float32)))
+    for logits, targets, mask in cases:
+        x = torch.tensor(logits, dtype=torch.float64, requires_grad=True)
+        v = x.shape[-1]
+        nll = torch.nn.functional.cross_entropy(x.reshape(-1, v), torch.tensor(targets).reshape(-1).long(), reduction="none")
+        w = torch.tensor(mask, dtype=torch.float64).reshape(-1)
+        loss = (nll * w).sum() / w.sum()
+        loss.backward()
+        got = oracle.cross_entropy_bwd(logits, targets, mask)
+        assert_close(got, x.grad.numpy(), rtol=1e-9, atol=1e-12, what="cross_entropy_bwd")
+        got2 = oracle.cross_entropy_bwd(logits, targets, mask, dloss=0.5)
+        assert_close(got2, 0.5 * x.grad.numpy(), rtol=1e-9, atol=1e-12, what="cross_entropy_bwd scaled")
