@@ -50,7 +50,12 @@ enum llmt_b200_dtype { LLMT_B200_FP32 = 0, LLMT_B200_BF16 = 1 };
 enum llmt_b200_epilogue {
     LLMT_B200_EPI_NONE = 0,
     LLMT_B200_EPI_BIAS = 1,
-    LLMT_B200_EPI_GELU = 2
+    LLMT_B200_EPI_GELU = 2,
+    /* C = (alpha * op(A) * op(B)) * gelu'(aux): the dX product of the layer that follows a tanh-GELU,
+     * leaving directly as the gradient with respect to the GELU's input.  desc.aux = the saved
+     * pre-activation, in C's type, pitch and batch strides.  bf16 operands, beta = 0, alone among
+     * the epilogue flags.  (llmt docs/TODO.md:223: gelu_bwd, planned as a kernel of its own.) */
+    LLMT_B200_EPI_GELU_BWD = 4
 };
 
 enum llmt_b200_status {
@@ -123,6 +128,7 @@ typedef struct llmt_b200_gemm_desc {
      * pitches and strides multiples of 8 elements). */
     int64_t batch_inner;
     int64_t stride_a_outer, stride_b_outer, stride_c_outer;
+    const void* aux;       /* second operand of the epilogue (LLMT_B200_EPI_GELU_BWD), else ignored */
 } llmt_b200_gemm_desc;
 
 /* Replaces llmt's kernels::matmul body (src/kernels/matmul.cpp:218-222 ->

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("LLMT_B200_LIB") or os.path.join(_HERE, "lib", "libllmt_b200.so")
 
 FP32, BF16 = 0, 1
-EPI_NONE, EPI_BIAS, EPI_GELU = 0, 1, 2
+EPI_NONE, EPI_BIAS, EPI_GELU, EPI_GELU_BWD = 0, 1, 2, 4
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4, 5
 
 EXPORTS = [
@@ -64,6 +64,7 @@ class GemmDesc(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
         ("batch_inner", ctypes.c_int64), ("stride_a_outer", ctypes.c_int64),
         ("stride_b_outer", ctypes.c_int64), ("stride_c_outer", ctypes.c_int64),
+        ("aux", ctypes.c_void_p),
     ]
 
 
@@ -200,7 +201,7 @@ def _row_pitch(t) -> int:
 
 
 def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
-              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0, cta_pairs=0) -> GemmDesc:
+              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0, cta_pairs=0, gelu_bwd_of=None) -> GemmDesc:
     """Builds the descriptor for C = epilogue(alpha*op(A)*op(B) + beta*C) from rank-2
     or rank-3 torch tensors (row-major views with a contiguous last dimension)."""
     if not (a.dim() == b.dim() == c.dim()) or a.dim() not in (2, 3):
@@ -235,6 +236,12 @@ def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=N
         d.dbias = dbias.data_ptr()
         d.dbias_beta = float(dbias_beta)
     d.plan_tile_n, d.plan_splits, d.plan_cta_pairs = int(tile_n), int(splits), int(cta_pairs)
+    if gelu_bwd_of is not None:
+        # C = (alpha * op(A) * op(B)) * gelu'(pre): `gelu_bwd_of` is the saved pre-activation, laid out like C
+        if gelu_bwd_of.shape != c.shape or gelu_bwd_of.dtype != c.dtype or gelu_bwd_of.stride() != c.stride():
+            raise LlmtB200Error(ERR_INVALID, "matmul: the pre-activation must have C's shape, type and strides")
+        d.epilogue |= EPI_GELU_BWD
+        d.aux = gelu_bwd_of.data_ptr()
     if workspace is not None:
         d.workspace = workspace.data_ptr()
         d.workspace_bytes = workspace.numel() * workspace.element_size()

@@ -297,12 +297,14 @@ int pair_units() {
     return (r > 0 && r < by_sm) ? r : by_sm;
 }
 int dbias_mode_of(const llmt_b200_gemm_desc* d) { return d->dbias == nullptr ? 0 : (d->trans_a ? 1 : 2); }
+// The row-wise epilogues see whole reductions: such a problem is never split along k.
+int splits_wanted(const llmt_b200_gemm_desc* d) { return (d->epilogue & LLMT_B200_EPI_GELU_BWD) ? 1 : d->plan_splits; }
 TcPlan plan_single(const llmt_b200_gemm_desc* d) {
     const bool pairs = pair_eligible(d);
     const int epi_step = 1000 + ((d->epilogue & LLMT_B200_EPI_BIAS) ? 100 : 0) + ((d->epilogue & LLMT_B200_EPI_GELU) ? 500 : 0) +
                          (d->beta != 0.0f ? 300 : 0);
     return make_plan(d->m, d->n, d->k, d->batch, dbias_mode_of(d), pairs ? pair_units() : sm_count(),
-                     d->plan_tile_n, d->plan_splits, pairs, d->trans_b == 0, epi_step, d->dtype_c == LLMT_B200_BF16);
+                     d->plan_tile_n, splits_wanted(d), pairs, d->trans_b == 0, epi_step, d->dtype_c == LLMT_B200_BF16);
 }
 
 bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
@@ -367,8 +369,17 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
         return fail(LLMT_B200_ERR_INVALID, "matmul: CTA pairs need m > 128 and a tile width of 128 or 256 "
                     "(192 only when B is stored [n, k])");
     if (d->plan_splits < 0) return fail(LLMT_B200_ERR_INVALID, "matmul: negative plan_splits");
-    if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU)) != 0)
+    if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU | LLMT_B200_EPI_GELU_BWD)) != 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: unknown epilogue flags 0x%x", d->epilogue);
+    if (d->epilogue & LLMT_B200_EPI_GELU_BWD) {
+        if (d->epilogue != LLMT_B200_EPI_GELU_BWD)
+            return fail(LLMT_B200_ERR_INVALID, "matmul: EPI_GELU_BWD stands alone among the epilogue flags");
+        if (d->aux == nullptr) return fail(LLMT_B200_ERR_INVALID, "matmul: EPI_GELU_BWD set but aux is null");
+        if (d->dtype_ab != LLMT_B200_BF16)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: EPI_GELU_BWD needs bf16 operands");
+        if (d->beta != 0.0f) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: EPI_GELU_BWD needs beta = 0");
+        if (d->dbias != nullptr) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: EPI_GELU_BWD with dbias is not defined");
+    }
     if ((d->epilogue & LLMT_B200_EPI_BIAS) && d->bias == nullptr)
         return fail(LLMT_B200_ERR_INVALID, "matmul: EPI_BIAS set but bias is null");
     if ((d->epilogue & LLMT_B200_EPI_BIAS) && d->bias_dtype != LLMT_B200_FP32 &&
@@ -703,7 +714,11 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
     p->c_is_bf16 = d->dtype_c == LLMT_B200_BF16;
     p->alpha = d->alpha; p->beta = d->beta;
     p->bias = d->bias; p->bias_is_bf16 = d->bias_dtype == LLMT_B200_BF16;
-    p->epi_flags = d->epilogue;
+    p->epi_flags = d->epilogue & (LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU);
+    if (d->epilogue & LLMT_B200_EPI_GELU_BWD) {
+        p->epi_flags |= kEpiGeluBwd;
+        p->ext_ptr = d->aux;
+    }
     p->dbias = d->dbias; p->dbias_beta = d->dbias_beta;
     p->a_raw = a; p->lda = d->lda;
     p->dbias_mode = pl.dbias_mode;
@@ -754,6 +769,9 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
     int st = device_globals(&g);
     if (st != LLMT_B200_OK) return st;
     thread_local GroupParams gp;
+    // A problem with a row-wise epilogue takes the whole launch to the kernels that carry those.
+    for (int i = 0; i < count; ++i)
+        if (probs[i].epi_flags & (kEpiLse | kEpiCausal | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd)) lse = true;
     // Longest reductions first: with a dynamic queue this is longest-processing-time-first.
     int order[kMaxGroupProblems];
     for (int i = 0; i < count; ++i) order[i] = i;
@@ -852,7 +870,7 @@ bool plan_group(const llmt_b200_gemm_desc* descs, int count, TcPlan* plans) {
         const llmt_b200_gemm_desc& d = descs[i];
         plans[i] = count == 1 ? plan_single(&d)
                               : make_group_plan(d.m, d.n, d.k, d.batch, dbias_mode_of(&d), sms, work,
-                                                d.plan_tile_n, d.plan_splits, pairs, d.trans_b == 0);
+                                                d.plan_tile_n, splits_wanted(&d), pairs, d.trans_b == 0);
     }
     return count == 1 ? plans[0].pairs != 0 : pairs;
 }

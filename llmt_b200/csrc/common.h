@@ -33,6 +33,7 @@ constexpr int kEpiLse = 0x100;     // per row and per half tile: maximum and sum
 constexpr int kEpiCausal = 0x200;  // columns beyond the row's own index do not exist (value exactly 0 when stored)
 constexpr int kEpiExpSub = 0x400;  // v = exp(v - ext_rowvec[row])
 constexpr int kEpiMulAux = 0x800;  // v = aux[row, col] * (v - ext_rowvec[row]), aux laid out like C
+constexpr int kEpiGeluBwd = 0x2000; // v = v * gelu'(aux[row, col]), aux (the pre-activation) laid out like C
 constexpr int kEpiCeGrad = 0x1000; // v = (exp(v - lse[row]) - [col == target[row]]) * g[row]: the cross-entropy's dLogits
 
 constexpr int kMaxGroupProblems = 8;
@@ -82,6 +83,7 @@ struct ProblemScalars {
     //            (int32 [m], one product only) and the target's value goes to ext_rowvec.
     //   kEpiExpSub / kEpiMulAux: ext_rowvec is READ, one value per row of every batch item;
     //            kEpiMulAux reads ext_ptr as the aux tensor (C's element type, pitch and strides).
+    //   kEpiGeluBwd: ext_ptr is the aux tensor (the pre-activation; C's element type, pitch and strides).
     //   kEpiCeGrad: ext_stats is READ as one (lse, g) pair per row, ext_ptr is the rows' target
     //            columns (int32 [m], one product only).
     float2* ext_stats;          // [2 * tiles_n][batch][m]
@@ -228,6 +230,30 @@ __device__ __forceinline__ float gelu_tanh_hw(float v) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
     const float h = 0.5f * v;
     return fmaf(h, t, h);
+}
+
+// Derivative of the tanh-GELU, gelu'(x) = 0.5 (1 + t) + 0.5 x (1 - t^2) u'(x) with
+// t = tanh(u), u = k0 (x + k1 x^3), u' = k0 (1 + 3 k1 x^2); hardware tanh (2^-11): for results
+// that are rounded to bf16.
+__device__ __forceinline__ float dgelu_tanh_hw(float x) {
+    const float k0 = 0.7978845608028654f;
+    const float k1 = k0 * 0.044715f;
+    const float x2 = x * x;
+    const float u = x * fmaf(k1, x2, k0);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    const float du = fmaf(3.0f * k1, x2, k0);
+    const float hx = 0.5f * x;
+    return fmaf(hx * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
+}
+// The same with tanhf: for fp32 results.
+__device__ __forceinline__ float dgelu_tanh_precise(float x) {
+    const float k0 = 0.7978845608028654f;
+    const float k1 = k0 * 0.044715f;
+    const float x2 = x * x;
+    const float t = tanhf(x * fmaf(k1, x2, k0));
+    const float du = fmaf(3.0f * k1, x2, k0);
+    return fmaf(0.5f * x * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
 }
 
 // Launchers implemented in the .cu files.  All return a cudaError_t from the launch.

@@ -476,6 +476,8 @@ template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
 //   kEpiExpSub  C = exp(v - ext_rowvec[row]): with the rows' log-sum-exp, the softmax itself
 //   kEpiMulAux  C = aux ⊙ (v - ext_rowvec[row]): the softmax backward dS = P ⊙ (dP - D) as the
 //               epilogue of the product that makes dP
+//   kEpiGeluBwd C = v * gelu'(aux): the dX product of the layer after a GELU, leaving as the gradient
+//               with respect to the GELU's input (aux = the saved pre-activation)
 //   kEpiCeGrad  C = (exp(v - lse[row]) - [col = target[row]]) * g[row]: the cross-entropy's gradient
 //               with respect to the logits, from the LM-head product made a second time
 template <uint32_t V> struct Sig { static constexpr uint32_t value = V; };
@@ -1069,7 +1071,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             constexpr uint32_t kOpAlpha = 1u, kOpBeta = 2u, kOpBias = 4u, kOpGelu = 8u;
             // A signature: the operation bits, the result type, the extended epilogue's parts; or "generic".
             constexpr uint32_t kSigBf16 = 0x10u, kSigGeneric = 0x80000000u;
-            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux | kEpiCeGrad);
+            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd);
             const float alpha = p.alpha, beta = p.beta;
             const bool c_bf16 = p.c_is_bf16 != 0;
             const void* const c_ptr = p.c;
@@ -1114,7 +1116,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     row_scale = lg.y;
                     lse_target = static_cast<const int32_t*>(p.ext_ptr)[row0 + lane];
                 }
-                if (ext & kEpiMulAux) {
+                if (ext & (kEpiMulAux | kEpiGeluBwd)) {
                     const int esz = c_bf16 ? 2 : 4;
                     const char* base = static_cast<const char*>(p.ext_ptr) + c_row_off * esz;
                     for (int s = 0; s < ns; s += spu)
@@ -1250,6 +1252,20 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         const float shift = row_val * kLog2e;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], kLog2e, -shift));
+                    } else if (e_ext & kEpiGeluBwd) {
+                        float aux[32];
+                        const int have = row_ok ? min(32, pn - col) : 0;
+                        if (c_bf16)
+                            load_chunk_bf16(static_cast<const __nv_bfloat16*>(p.ext_ptr) + c_row_off + c0, aux, have);
+                        else
+                            load_chunk_f32(static_cast<const float*>(p.ext_ptr) + c_row_off + c0, aux, have);
+                        if (e_bf16) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] *= dgelu_tanh_hw(aux[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] *= dgelu_tanh_precise(aux[j]);
+                        }
                     } else if (e_ext & kEpiCeGrad) {
                         // softmax minus one-hot, times the row's weight; absent columns are not stored
                         const float shift = row_val * kLog2e;
@@ -1379,6 +1395,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         case kEpiMulAux | kSigBf16: run_steps(Sig<kEpiMulAux | kSigBf16>{}); break;                         // softmax backward
                         case kEpiLse: run_steps(Sig<kEpiLse>{}); break;                                                     // LM head + loss
                         case kEpiCeGrad | kSigBf16: run_steps(Sig<kEpiCeGrad | kSigBf16>{}); break;                         // dLogits
+                        case kEpiGeluBwd | kSigBf16: run_steps(Sig<kEpiGeluBwd | kSigBf16>{}); break;                       // dX through the GELU
                         case kEpiLse | kOpBias: run_steps(Sig<kEpiLse | kOpBias>{}); break;
                         default: run_steps(Sig<kSigGeneric>{}); break;
                     }

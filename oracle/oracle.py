@@ -208,6 +208,15 @@ def gelu(x) -> np.ndarray:
     return 0.5 * x * (1.0 + np.tanh(k0 * (x + k1 * x ** 3)))
 
 
+def gelu_bwd(x) -> np.ndarray:
+    """Derivative of the tanh-GELU (src/kernels/gelu.cu:23-26 gives the function; llmt plans
+    gelu_bwd in docs/TODO.md:223) in fp64."""
+    x = np.asarray(x, dtype=np.float64)
+    k0, k1 = 0.7978845608028654, 0.044715
+    t = np.tanh(k0 * (x + k1 * x ** 3))
+    return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * k0 * (1.0 + 3.0 * k1 * x * x)
+
+
 def rel_fro(x, ref) -> float:
     """Relative Frobenius error ||x-ref|| / ||ref|| in fp64."""
     x = np.asarray(x, dtype=np.float64)

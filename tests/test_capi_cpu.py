@@ -34,10 +34,27 @@ def test_library_exports_every_declared_symbol():
 
 def test_descriptor_layout_matches_the_header():
     # field order and sizes of struct llmt_b200_gemm_desc as the C compiler lays them out
-    assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8 + 4 * 8
+    assert ctypes.sizeof(L.GemmDesc) == 10 * 8 + 4 * 4 + 2 * 4 + 2 * 4 + 2 * 8 + 4 * 4 + 2 * 8 + 4 * 8 + 8
     assert L.GemmDesc.batch_inner.offset == L.GemmDesc.workspace_bytes.offset + 8
     assert L.GemmDesc.plan_cta_pairs.offset == L.GemmDesc.plan_splits.offset + 4
     assert L.GemmDesc.workspace.offset % 8 == 0
+    assert L.GemmDesc.aux.offset == L.GemmDesc.stride_c_outer.offset + 8
+    # and what gcc makes of the header itself
+    import shutil
+    import subprocess
+    import tempfile
+    if shutil.which("gcc"):
+        src = ('#include <stddef.h>\n#include <stdio.h>\n#include "llmt_b200.h"\n'
+               'int main(void) { printf("%zu %zu %zu %zu\\n", sizeof(llmt_b200_gemm_desc), offsetof(llmt_b200_gemm_desc, bias), '
+               'offsetof(llmt_b200_gemm_desc, workspace), offsetof(llmt_b200_gemm_desc, aux)); return 0; }\n')
+        with tempfile.TemporaryDirectory() as tmp:
+            c = os.path.join(tmp, "layout.c")
+            with open(c, "w") as f:
+                f.write(src)
+            exe = os.path.join(tmp, "layout")
+            subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+            got = [int(x) for x in subprocess.check_output([exe]).split()]
+        assert got == [ctypes.sizeof(L.GemmDesc), L.GemmDesc.bias.offset, L.GemmDesc.workspace.offset, L.GemmDesc.aux.offset]
 
 
 def _desc(**kw):

@@ -145,3 +145,12 @@ def test_oracle_cross_entropy_bwd_matches_torch_autograd():
         assert_close(got, x.grad.numpy(), rtol=1e-9, atol=1e-12, what="cross_entropy_bwd")
         got2 = oracle.cross_entropy_bwd(logits, targets, mask, dloss=0.5)
         assert_close(got2, 0.5 * x.grad.numpy(), rtol=1e-9, atol=1e-12, what="cross_entropy_bwd scaled")
+
+
+def test_oracle_gelu_bwd_matches_torch_autograd():
+    # llmt plans gelu_bwd (docs/TODO.md:223); its goldens come from torch, so the oracle's derivative
+    # of the tanh-GELU is pinned against torch autograd.
+    import torch
+    x = torch.linspace(-8.0, 8.0, 4001, dtype=torch.float64, requires_grad=True)
+    torch.nn.functional.gelu(x, approximate="tanh").sum().backward()
+    assert_close(oracle.gelu_bwd(x.detach().numpy()), x.grad.numpy(), rtol=1e-12, atol=1e-14, what="gelu_bwd")
