@@ -55,7 +55,13 @@ enum llmt_b200_epilogue {
      * leaving directly as the gradient with respect to the GELU's input.  desc.aux = the saved
      * pre-activation, in C's type, pitch and batch strides.  bf16 operands, beta = 0, alone among
      * the epilogue flags.  (llmt docs/TODO.md:223: gelu_bwd, planned as a kernel of its own.) */
-    LLMT_B200_EPI_GELU_BWD = 4
+    LLMT_B200_EPI_GELU_BWD = 4,
+    /* With EPI_GELU: the value the GELU sees (after alpha, beta and bias) is stored as a second
+     * result at desc.aux, in C's type, pitch and batch strides: the pre-activation that
+     * EPI_GELU_BWD reads in the backward pass.  One launch gives h = gelu(pre) and pre, where llmt's
+     * MLP (src/layers/mlp.cpp:14-18) keeps only the tensor its gelu kernel overwrote.  bf16
+     * operands; aux must not overlap anything else the call touches. */
+    LLMT_B200_EPI_SAVE_PRE = 8
 };
 
 enum llmt_b200_status {
@@ -128,7 +134,7 @@ typedef struct llmt_b200_gemm_desc {
      * pitches and strides multiples of 8 elements). */
     int64_t batch_inner;
     int64_t stride_a_outer, stride_b_outer, stride_c_outer;
-    const void* aux;       /* second operand of the epilogue (LLMT_B200_EPI_GELU_BWD), else ignored */
+    const void* aux;       /* EPI_GELU_BWD: read; EPI_SAVE_PRE: written (the library casts the const away); else ignored */
 } llmt_b200_gemm_desc;
 
 /* Replaces llmt's kernels::matmul body (src/kernels/matmul.cpp:218-222 ->

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("LLMT_B200_LIB") or os.path.join(_HERE, "lib", "libllmt_b200.so")
 
 FP32, BF16 = 0, 1
-EPI_NONE, EPI_BIAS, EPI_GELU, EPI_GELU_BWD = 0, 1, 2, 4
+EPI_NONE, EPI_BIAS, EPI_GELU, EPI_GELU_BWD, EPI_SAVE_PRE = 0, 1, 2, 4, 8
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE = 0, 1, 2, 3, 4, 5
 
 EXPORTS = [
@@ -201,7 +201,8 @@ def _row_pitch(t) -> int:
 
 
 def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=None, gelu=False,
-              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0, cta_pairs=0, gelu_bwd_of=None) -> GemmDesc:
+              dbias=None, dbias_beta=0.0, workspace=None, tile_n=0, splits=0, cta_pairs=0, gelu_bwd_of=None,
+              save_pre=None) -> GemmDesc:
     """Builds the descriptor for C = epilogue(alpha*op(A)*op(B) + beta*C) from rank-2
     or rank-3 torch tensors (row-major views with a contiguous last dimension)."""
     if not (a.dim() == b.dim() == c.dim()) or a.dim() not in (2, 3):
@@ -242,6 +243,12 @@ def make_desc(c, a, b, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, bias=N
             raise LlmtB200Error(ERR_INVALID, "matmul: the pre-activation must have C's shape, type and strides")
         d.epilogue |= EPI_GELU_BWD
         d.aux = gelu_bwd_of.data_ptr()
+    if save_pre is not None:
+        # with gelu=True: the value the GELU sees is stored in `save_pre` (laid out like C) as well
+        if save_pre.shape != c.shape or save_pre.dtype != c.dtype or save_pre.stride() != c.stride():
+            raise LlmtB200Error(ERR_INVALID, "matmul: the pre-activation must have C's shape, type and strides")
+        d.epilogue |= EPI_SAVE_PRE
+        d.aux = save_pre.data_ptr()
     if workspace is not None:
         d.workspace = workspace.data_ptr()
         d.workspace_bytes = workspace.numel() * workspace.element_size()

@@ -298,7 +298,9 @@ int pair_units() {
 }
 int dbias_mode_of(const llmt_b200_gemm_desc* d) { return d->dbias == nullptr ? 0 : (d->trans_a ? 1 : 2); }
 // The row-wise epilogues see whole reductions: such a problem is never split along k.
-int splits_wanted(const llmt_b200_gemm_desc* d) { return (d->epilogue & LLMT_B200_EPI_GELU_BWD) ? 1 : d->plan_splits; }
+int splits_wanted(const llmt_b200_gemm_desc* d) {
+    return (d->epilogue & (LLMT_B200_EPI_GELU_BWD | LLMT_B200_EPI_SAVE_PRE)) ? 1 : d->plan_splits;
+}
 TcPlan plan_single(const llmt_b200_gemm_desc* d) {
     const bool pairs = pair_eligible(d);
     const int epi_step = 1000 + ((d->epilogue & LLMT_B200_EPI_BIAS) ? 100 : 0) + ((d->epilogue & LLMT_B200_EPI_GELU) ? 500 : 0) +
@@ -369,7 +371,15 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
         return fail(LLMT_B200_ERR_INVALID, "matmul: CTA pairs need m > 128 and a tile width of 128 or 256 "
                     "(192 only when B is stored [n, k])");
     if (d->plan_splits < 0) return fail(LLMT_B200_ERR_INVALID, "matmul: negative plan_splits");
-    if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU | LLMT_B200_EPI_GELU_BWD)) != 0)
+    if (d->epilogue & LLMT_B200_EPI_SAVE_PRE) {
+        if (!(d->epilogue & LLMT_B200_EPI_GELU) || (d->epilogue & LLMT_B200_EPI_GELU_BWD))
+            return fail(LLMT_B200_ERR_INVALID, "matmul: EPI_SAVE_PRE goes with EPI_GELU (and EPI_BIAS) only");
+        if (d->aux == nullptr) return fail(LLMT_B200_ERR_INVALID, "matmul: EPI_SAVE_PRE set but aux is null");
+        if (d->dtype_ab != LLMT_B200_BF16)
+            return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: EPI_SAVE_PRE needs bf16 operands");
+        if (d->dbias != nullptr) return fail(LLMT_B200_ERR_UNSUPPORTED, "matmul: EPI_SAVE_PRE with dbias is not defined");
+    }
+    if ((d->epilogue & ~(LLMT_B200_EPI_BIAS | LLMT_B200_EPI_GELU | LLMT_B200_EPI_GELU_BWD | LLMT_B200_EPI_SAVE_PRE)) != 0)
         return fail(LLMT_B200_ERR_INVALID, "matmul: unknown epilogue flags 0x%x", d->epilogue);
     if (d->epilogue & LLMT_B200_EPI_GELU_BWD) {
         if (d->epilogue != LLMT_B200_EPI_GELU_BWD)
@@ -413,8 +423,13 @@ int validate(const llmt_b200_gemm_desc* d, const void* c, const void* a, const v
                                       ? static_cast<size_t>(d->n) * (d->bias_dtype == LLMT_B200_BF16 ? 2 : 4) : 0;
         const size_t ws_bytes = d->workspace != nullptr ? static_cast<size_t>(d->workspace_bytes) : 0;
         struct Range { const void* p; size_t n; const char* what; };
-        const Range reads[4] = {{a, a_bytes, "A"}, {b, b_bytes, "B"}, {d->bias, bias_bytes, "bias"}, {c, c_bytes, "C"}};
-        const Range writes[2] = {{d->dbias, dbias_bytes, "dbias"}, {d->workspace, ws_bytes, "workspace"}};
+        // aux has C's extent; it is read (EPI_GELU_BWD) or written (EPI_SAVE_PRE)
+        const size_t aux_r = (d->epilogue & LLMT_B200_EPI_GELU_BWD) ? c_bytes : 0;
+        const size_t aux_w = (d->epilogue & LLMT_B200_EPI_SAVE_PRE) ? c_bytes : 0;
+        const Range reads[5] = {{a, a_bytes, "A"}, {b, b_bytes, "B"}, {d->bias, bias_bytes, "bias"}, {c, c_bytes, "C"},
+                                {d->aux, aux_r, "aux"}};
+        const Range writes[3] = {{d->dbias, dbias_bytes, "dbias"}, {d->workspace, ws_bytes, "workspace"}, {d->aux, aux_w, "aux"}};
+        if (aux_r != 0 && overlaps(c, c_bytes, d->aux, aux_r)) return fail(LLMT_B200_ERR_INVALID, "matmul: C overlaps aux");
         for (const Range& w : writes) {
             if (w.n == 0) continue;
             for (const Range& r : reads)
@@ -719,6 +734,10 @@ int fill_problem(GroupProblem* p, const llmt_b200_gemm_desc* d, const Checked& c
         p->epi_flags |= kEpiGeluBwd;
         p->ext_ptr = d->aux;
     }
+    if (d->epilogue & LLMT_B200_EPI_SAVE_PRE) {
+        p->epi_flags |= kEpiSavePre;
+        p->ext_ptr = d->aux;
+    }
     p->dbias = d->dbias; p->dbias_beta = d->dbias_beta;
     p->a_raw = a; p->lda = d->lda;
     p->dbias_mode = pl.dbias_mode;
@@ -771,7 +790,7 @@ int launch_group(GroupProblem* probs, int count, bool pairs, cudaStream_t stream
     thread_local GroupParams gp;
     // A problem with a row-wise epilogue takes the whole launch to the kernels that carry those.
     for (int i = 0; i < count; ++i)
-        if (probs[i].epi_flags & (kEpiLse | kEpiCausal | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd)) lse = true;
+        if (probs[i].epi_flags & (kEpiLse | kEpiCausal | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd | kEpiSavePre)) lse = true;
     // Longest reductions first: with a dynamic queue this is longest-processing-time-first.
     int order[kMaxGroupProblems];
     for (int i = 0; i < count; ++i) order[i] = i;

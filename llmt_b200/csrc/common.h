@@ -33,6 +33,7 @@ constexpr int kEpiLse = 0x100;     // per row and per half tile: maximum and sum
 constexpr int kEpiCausal = 0x200;  // columns beyond the row's own index do not exist (value exactly 0 when stored)
 constexpr int kEpiExpSub = 0x400;  // v = exp(v - ext_rowvec[row])
 constexpr int kEpiMulAux = 0x800;  // v = aux[row, col] * (v - ext_rowvec[row]), aux laid out like C
+constexpr int kEpiSavePre = 0x4000; // the value before the GELU is stored too, at aux[row, col] (aux laid out like C)
 constexpr int kEpiGeluBwd = 0x2000; // v = v * gelu'(aux[row, col]), aux (the pre-activation) laid out like C
 constexpr int kEpiCeGrad = 0x1000; // v = (exp(v - lse[row]) - [col == target[row]]) * g[row]: the cross-entropy's dLogits
 
@@ -83,6 +84,7 @@ struct ProblemScalars {
     //            (int32 [m], one product only) and the target's value goes to ext_rowvec.
     //   kEpiExpSub / kEpiMulAux: ext_rowvec is READ, one value per row of every batch item;
     //            kEpiMulAux reads ext_ptr as the aux tensor (C's element type, pitch and strides).
+    //   kEpiSavePre: ext_ptr is WRITTEN: the pre-activation, C's element type, pitch and strides.
     //   kEpiGeluBwd: ext_ptr is the aux tensor (the pre-activation; C's element type, pitch and strides).
     //   kEpiCeGrad: ext_stats is READ as one (lse, g) pair per row, ext_ptr is the rows' target
     //            columns (int32 [m], one product only).

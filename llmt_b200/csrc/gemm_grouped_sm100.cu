@@ -246,6 +246,32 @@ __device__ __forceinline__ void load_chunk_bf16(const __nv_bfloat16* src, float*
     }
 }
 
+// One thread's 32 consecutive values of a row to global memory (the second result of an epilogue
+// that has two): 16-byte stores where the row allows them.
+__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* dst, const float* v, int valid) {
+    if (__builtin_expect(valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0u, 1)) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(pack_bf16(v[8 * q + 0], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
+                                                                pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < valid) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+__device__ __forceinline__ void store_chunk_f32(float* dst, const float* v, int valid) {
+    if (__builtin_expect(valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0u, 1)) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < valid) dst[j] = v[j];
+    }
+}
+
 // 16 bytes of an operand that this kernel only reads.
 __device__ __forceinline__ uint4 ld_operand16(const void* p) {
     uint4 v;
@@ -476,6 +502,7 @@ template <int N> __device__ __forceinline__ void bulk_wait_group_read_n() {
 //   kEpiExpSub  C = exp(v - ext_rowvec[row]): with the rows' log-sum-exp, the softmax itself
 //   kEpiMulAux  C = aux ⊙ (v - ext_rowvec[row]): the softmax backward dS = P ⊙ (dP - D) as the
 //               epilogue of the product that makes dP
+//   kEpiSavePre the value before the GELU (after alpha, beta, bias) is stored as a second result
 //   kEpiGeluBwd C = v * gelu'(aux): the dX product of the layer after a GELU, leaving as the gradient
 //               with respect to the GELU's input (aux = the saved pre-activation)
 //   kEpiCeGrad  C = (exp(v - lse[row]) - [col = target[row]]) * g[row]: the cross-entropy's gradient
@@ -1071,7 +1098,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
             constexpr uint32_t kOpAlpha = 1u, kOpBeta = 2u, kOpBias = 4u, kOpGelu = 8u;
             // A signature: the operation bits, the result type, the extended epilogue's parts; or "generic".
             constexpr uint32_t kSigBf16 = 0x10u, kSigGeneric = 0x80000000u;
-            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd);
+            constexpr uint32_t kSigExtMask = static_cast<uint32_t>(kEpiLse | kEpiExpSub | kEpiMulAux | kEpiCeGrad | kEpiGeluBwd | kEpiSavePre);
             const float alpha = p.alpha, beta = p.beta;
             const bool c_bf16 = p.c_is_bf16 != 0;
             const void* const c_ptr = p.c;
@@ -1189,6 +1216,12 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     if (e_ops & kOpBias) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
+                    }
+                    if (kLse && (e_ext & kEpiSavePre)) {
+                        // the value the GELU is about to see, for the backward pass
+                        const int have = row_ok ? min(32, pn - col) : 0;
+                        if (c_bf16) store_chunk_bf16(static_cast<__nv_bfloat16*>(const_cast<void*>(p.ext_ptr)) + c_row_off + c0, v, have);
+                        else store_chunk_f32(static_cast<float*>(const_cast<void*>(p.ext_ptr)) + c_row_off + c0, v, have);
                     }
                     if (e_ops & kOpGelu) {
                         // A bf16 result rounds at 2^-9: the hardware tanh (2^-11) is exact enough for
@@ -1396,6 +1429,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                         case kEpiLse: run_steps(Sig<kEpiLse>{}); break;                                                     // LM head + loss
                         case kEpiCeGrad | kSigBf16: run_steps(Sig<kEpiCeGrad | kSigBf16>{}); break;                         // dLogits
                         case kEpiGeluBwd | kSigBf16: run_steps(Sig<kEpiGeluBwd | kSigBf16>{}); break;                       // dX through the GELU
+                        case kEpiSavePre | kSigBf16 | kOpBias | kOpGelu: run_steps(Sig<kEpiSavePre | kSigBf16 | kOpBias | kOpGelu>{}); break;  // MLP fc, training
                         case kEpiLse | kOpBias: run_steps(Sig<kEpiLse | kOpBias>{}); break;
                         default: run_steps(Sig<kSigGeneric>{}); break;
                     }

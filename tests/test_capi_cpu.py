@@ -82,7 +82,10 @@ def _call(d, c=C, a=A, b=B):
     (dict(m=-1), L.ERR_INVALID, "negative"),
     (dict(dtype_ab=7), L.ERR_UNSUPPORTED, "dtype code 7"),
     (dict(dtype_ab=L.FP32, dtype_c=L.BF16), L.ERR_UNSUPPORTED, "mixed dtypes"),
-    (dict(epilogue=8), L.ERR_INVALID, "epilogue"),
+    (dict(epilogue=16), L.ERR_INVALID, "epilogue"),
+    (dict(epilogue=L.EPI_SAVE_PRE), L.ERR_INVALID, "EPI_SAVE_PRE goes with EPI_GELU"),
+    (dict(epilogue=L.EPI_GELU_BWD), L.ERR_INVALID, "aux is null"),
+    (dict(epilogue=L.EPI_GELU_BWD | L.EPI_GELU), L.ERR_INVALID, "stands alone"),
     (dict(epilogue=L.EPI_BIAS), L.ERR_INVALID, "bias is null"),
     (dict(plan_tile_n=100), L.ERR_INVALID, "plan_tile_n"),
     (dict(plan_cta_pairs=3), L.ERR_INVALID, "plan_cta_pairs"),

@@ -90,3 +90,76 @@ def test_gelu_bwd_flag_is_checked():
     d = L.make_desc(cf, af, af, False, False, gelu_bwd_of=cf.clone())
     with pytest.raises(L.LlmtB200Error, match="bf16 operands"):
         L.gemm_desc(d, cf, af, af)
+
+
+@pytest.mark.parametrize("m,f,c,out", [(256, 512, 128, torch.bfloat16), (300, 1000, 192, torch.bfloat16),
+                                       (2048, 3072, 768, torch.bfloat16), (200, 264, 64, torch.float32)])
+def test_forward_keeps_the_pre_activation(m, f, c, out):
+    """h = gelu(x W^T + b) and pre = x W^T + b from one launch; h must equal the launch without
+    the second result bit for bit, pre must equal the bias-only launch bit for bit."""
+    rng = np.random.default_rng(m * 3 + f + c)
+    x = oracle.round_bf16(rng.standard_normal((m, c)))
+    w = oracle.round_bf16(rng.standard_normal((f, c)) * 0.05)
+    bias = (rng.standard_normal(f) * 0.1).astype(np.float32)
+    xd, wd, bd = dev_bf16(x), dev_bf16(w), torch.from_numpy(bias).to(DEV)
+    h = torch.full((m, f), float("nan"), device=DEV, dtype=out)
+    pre = torch.full((m, f), float("nan"), device=DEV, dtype=out)
+    d = L.make_desc(h, xd, wd, False, True, bias=bd, gelu=True, save_pre=pre)
+    ws = torch.empty(max(L.workspace_bytes(d, xd, wd), 256), dtype=torch.uint8, device=DEV)
+    d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.gemm_desc(d, h, xd, wd)
+    L.device_status()
+    h_only = torch.empty_like(h)
+    L.gemm(h_only, xd, wd, False, True, bias=bd, gelu=True)
+    pre_only = torch.empty_like(pre)
+    L.gemm(pre_only, xd, wd, False, True, bias=bd)
+    assert torch.equal(pre, pre_only)
+    assert torch.equal(h, h_only)
+    want_pre = oracle.gemm(x, w, False, True) + bias.astype(np.float64)
+    assert oracle.rel_fro(host(pre), want_pre) <= (4e-3 if out == torch.bfloat16 else 1e-5)
+    assert oracle.rel_fro(host(h), oracle.gelu(want_pre)) <= (4e-3 if out == torch.bfloat16 else 1e-5)
+
+
+def test_mlp_forward_and_backward_chain():
+    """x -> fc (+bias, GELU, pre kept) -> proj; backward: proj's dX through the GELU in one launch
+    with proj's dW, then fc's dX and dW: against the oracle's chain on the same bf16 tensors."""
+    m, c, f = 512, 256, 1024
+    rng = np.random.default_rng(77)
+    x = oracle.round_bf16(rng.standard_normal((m, c)))
+    w1 = oracle.round_bf16(rng.standard_normal((f, c)) * 0.05)
+    b1 = (rng.standard_normal(f) * 0.1).astype(np.float32)
+    w2 = oracle.round_bf16(rng.standard_normal((c, f)) * 0.05)
+    dy = oracle.round_bf16(rng.standard_normal((m, c)) * 0.1)
+    xd, w1d, w2d, dyd, b1d = dev_bf16(x), dev_bf16(w1), dev_bf16(w2), dev_bf16(dy), torch.from_numpy(b1).to(DEV)
+    bf = torch.bfloat16
+    h = torch.empty(m, f, device=DEV, dtype=bf)
+    pre = torch.empty(m, f, device=DEV, dtype=bf)
+    d = L.make_desc(h, xd, w1d, False, True, bias=b1d, gelu=True, save_pre=pre)
+    L.gemm_desc(d, h, xd, w1d)
+    y = torch.empty(m, c, device=DEV, dtype=bf)
+    L.gemm(y, h, w2d, False, True)
+    dpre = torch.empty(m, f, device=DEV, dtype=bf)
+    dw2 = torch.zeros(c, f, device=DEV)
+    grp = L.Group([(L.make_desc(dpre, dyd, w2d, False, False, gelu_bwd_of=pre), dpre, dyd, w2d),
+                   (L.make_desc(dw2, dyd, h, True, False, beta=1.0), dw2, dyd, h)])
+    bufs = [torch.empty(max(n, 256), dtype=torch.uint8, device=DEV) for n in grp.workspace_bytes()]
+    grp.set_workspaces(bufs)
+    grp.run()
+    dx = torch.empty(m, c, device=DEV, dtype=bf)
+    dw1 = torch.zeros(f, c, device=DEV)
+    db1 = torch.zeros(f, device=DEV)
+    L.gemm(dx, dpre, w1d, False, False)
+    L.gemm(dw1, dpre, xd, True, False, beta=1.0, dbias=db1, dbias_beta=1.0)
+    L.device_status()
+    # the oracle's chain, rounding where the device stores bf16
+    pre_r = oracle.gemm(x, w1, False, True) + b1.astype(np.float64)
+    pre_b = oracle.round_bf16(pre_r)
+    h_b = oracle.round_bf16(oracle.gelu(pre_r))
+    assert oracle.rel_fro(host(y), oracle.gemm(h_b, w2, False, True)) <= 6e-3
+    dpre_r = oracle.gemm(dy, w2) * oracle.gelu_bwd(pre_b)
+    assert oracle.rel_fro(host(dpre), dpre_r) <= 6e-3
+    dpre_b = host(dpre)
+    assert oracle.rel_fro(host(dx), oracle.gemm(dpre_b, w1)) <= 6e-3
+    assert oracle.rel_fro(host(dw1), oracle.gemm(dpre_b, x, True, False)) <= 1e-3
+    assert oracle.rel_fro(host(db1), oracle.rowsum(dpre_b, trans_a=True)) <= 1e-3
+    assert oracle.rel_fro(host(dw2), oracle.gemm(dy, host(h), True, False)) <= 1e-3
