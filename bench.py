@@ -705,6 +705,65 @@ def attention_softmax_comparison(torch, L, dev):
     return out
 
 
+def mlp_gelu_comparison(torch, L, m, dev):
+    """The GELU between the two MLP GEMMs of config 2 (C = 768, 4C = 3072) in training: forward keeping
+    the pre-activation (llmt src/layers/mlp.cpp:14-18 runs matmul -> gelu kernel -> matmul) and the
+    backward of the down projection with dX passing through the GELU (llmt docs/TODO.md:223 plans a
+    gelu_bwd kernel).  Composition = this library's GEMMs plus torch's element-wise gelu /
+    gelu_backward (tanh form); fused = EPI_SAVE_PRE / EPI_GELU_BWD.  Rotating sets, CUDA events."""
+    bf = torch.bfloat16
+    C, F = 768, 3072
+    g = torch.Generator(device=dev).manual_seed(21)
+    sets = []
+    for _ in range(3):
+        x = torch.randn(m, C, device=dev, generator=g).to(bf)
+        w1 = (torch.randn(F, C, device=dev, generator=g) * 0.02).to(bf)
+        b1 = torch.zeros(F, device=dev)
+        w2 = (torch.randn(C, F, device=dev, generator=g) * 0.02).to(bf)
+        dy = (torch.randn(m, C, device=dev, generator=g) * 0.01).to(bf)
+        z = dict(x=x, w1=w1, b1=b1, w2=w2, dy=dy)
+        for name in ("h", "pre", "h_u", "pre_u", "dpre", "dh_u"):
+            z[name] = torch.empty(m, F, device=dev, dtype=bf)
+        z["dw2"] = torch.zeros(C, F, device=dev)
+        z["dw2_u"] = torch.zeros(C, F, device=dev)
+        z["d_f"] = L.make_desc(z["h"], x, w1, False, True, bias=b1, gelu=True, save_pre=z["pre"])
+        z["d_pre"] = L.make_desc(z["pre_u"], x, w1, False, True, bias=b1)
+        L.gemm_desc(z["d_f"], z["h"], x, w1)
+        gf = L.Group([(L.make_desc(z["dpre"], dy, w2, False, False, gelu_bwd_of=z["pre"]), z["dpre"], dy, w2),
+                      (L.make_desc(z["dw2"], dy, z["h"], True, False, beta=1.0), z["dw2"], dy, z["h"])])
+        gu = L.Group([(L.make_desc(z["dh_u"], dy, w2, False, False), z["dh_u"], dy, w2),
+                      (L.make_desc(z["dw2_u"], dy, z["h"], True, False, beta=1.0), z["dw2_u"], dy, z["h"])])
+        for grp in (gf, gu):
+            bufs = [torch.empty(max(n, 256), dtype=torch.uint8, device=dev) for n in grp.workspace_bytes()]
+            grp.set_workspaces(bufs)
+        z["gf"], z["gu"] = gf, gu
+        sets.append(z)
+
+    def fwd_fused(z):
+        L.gemm_desc(z["d_f"], z["h"], z["x"], z["w1"])
+
+    def fwd_composed2(z):
+        L.gemm_desc(z["d_pre"], z["pre_u"], z["x"], z["w1"])
+        z["h_u"].copy_(torch.nn.functional.gelu(z["pre_u"], approximate="tanh"))
+
+    def bwd_fused(z):
+        z["gf"].run()
+
+    def bwd_composed(z):
+        z["gu"].run()
+        z["dh_u"].copy_(torch.ops.aten.gelu_backward(z["dh_u"], z["pre"], approximate="tanh"))
+
+    out = {"shape": f"M = {m}, C = {C}, 4C = {F}, bf16"}
+    for name, fn in (("fwd_fused_two_results_ms", fwd_fused), ("fwd_gemm_then_gelu_ms", fwd_composed2),
+                     ("bwd_fused_ms", bwd_fused), ("bwd_grouped_then_gelu_backward_ms", bwd_composed)):
+        out[name] = round(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=12, warm=3), 4)
+    L.device_status()
+    z = sets[0]
+    out["fwd_h_max_abs_diff"] = float((z["h"].float() - z["h_u"].float()).abs().max().item())
+    out["bwd_rel_fro_diff"] = float(((z["dpre"].float() - z["dh_u"].float()).norm() / z["dh_u"].float().norm()).item())
+    return out
+
+
 def per_gemm_comparison(torch, L, workload, m, dev, want_cublaslt=True):
     """Each GEMM of the step timed on its own, back to back on rotating buffer sets (> 2 x L2
     in total), for this library and for cuBLASLt called the way llmt calls it (operand swap,
@@ -1268,6 +1327,11 @@ def main():
                 extras["lm_head_ce"] = lm_head_ce_comparison(torch, L, M_PER_GPU, dev)
             except Exception as exc:
                 extras["lm_head_ce"] = {"error": str(exc)}
+            torch.cuda.empty_cache()
+            try:
+                extras["mlp_gelu"] = mlp_gelu_comparison(torch, L, M_PER_GPU, dev)
+            except Exception as exc:
+                extras["mlp_gelu"] = {"error": str(exc)}
             torch.cuda.empty_cache()
             try:
                 extras["attention_softmax"] = attention_softmax_comparison(torch, L, dev)

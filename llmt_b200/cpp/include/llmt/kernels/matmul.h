@@ -18,11 +18,17 @@ void matmul(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool
 // Fused-epilogue extension.  Applied after alpha/beta:  + bias[n]  -> tanh-GELU
 // -> cast.  dbias (fp32 [M]) receives  dbias_beta*dbias + row sums of op(A).
 // A default-constructed Epilogue makes matmul_ex identical to matmul.
+// save_pre (with gelu): the value the GELU sees is stored there too (C's shape and dtype).
+// gelu_bwd_of: C = (alpha*op(A)*op(B)) * gelu'(*gelu_bwd_of), the saved pre-activation (C's shape
+// and dtype): the dX product of the layer after a GELU leaves as the gradient before it.  Both
+// are bf16-path only (llmt plans gelu_bwd as a kernel of its own, docs/TODO.md:223).
 struct Epilogue {
     const Tensor* bias = nullptr;
     bool gelu = false;
     Tensor* dbias = nullptr;
     float dbias_beta = 1.0f;
+    Tensor* save_pre = nullptr;
+    const Tensor* gelu_bwd_of = nullptr;
 };
 void matmul_ex(const RunCtx& ctx, Tensor& c, const Tensor& a, const Tensor& b, bool trans_a,
                bool trans_b, float alpha, float beta, const Epilogue& epi) noexcept;

@@ -21,7 +21,13 @@ class Linear {
     void forward(const RunCtx& ctx, Tensor& y, const Tensor& x) const noexcept;
     // Forward with tanh-GELU fused into the GEMM epilogue (after the bias).
     void forward_gelu(const RunCtx& ctx, Tensor& y, const Tensor& x) const noexcept;
+    // The same, also storing the value the GELU sees in `pre` (y's shape and dtype; bf16 path).
+    void forward_gelu(const RunCtx& ctx, Tensor& y, Tensor& pre, const Tensor& x) const noexcept;
     void backward(const RunCtx& ctx, Tensor& dx, const Tensor& dy, const Tensor& x) const noexcept;
+    // Backward of a layer whose INPUT came out of a GELU: dx is the gradient before that GELU,
+    // dx = (dy W) * gelu'(pre), in the same launch as dW += dy^T x (bf16 path).
+    void backward_through_gelu(const RunCtx& ctx, Tensor& dx, const Tensor& dy, const Tensor& x,
+                               const Tensor& pre) const noexcept;
 
     const Param& param() const noexcept { return weight_; }
     const Param* bias_param() const noexcept { return bias_; }

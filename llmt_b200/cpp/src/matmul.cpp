@@ -90,6 +90,14 @@ llmt_b200_gemm_desc make_desc(const RunCtx& ctx, const Tensor& c, const Tensor& 
         d.bias_dtype = static_cast<int32_t>(epi.bias->dtype);
     }
     if (epi.gelu) d.epilogue |= LLMT_B200_EPI_GELU;
+    if (epi.save_pre != nullptr || epi.gelu_bwd_of != nullptr) {
+        const Tensor* aux = epi.save_pre != nullptr ? epi.save_pre : epi.gelu_bwd_of;
+        if (epi.save_pre != nullptr && epi.gelu_bwd_of != nullptr) detail::fatal("matmul", "save_pre and gelu_bwd_of exclude each other");
+        if (!aux->valid() || aux->shape != c.shape || aux->dtype != c.dtype)
+            detail::fatal("matmul", "the pre-activation must have C's shape and dtype");
+        d.epilogue |= epi.save_pre != nullptr ? LLMT_B200_EPI_SAVE_PRE : LLMT_B200_EPI_GELU_BWD;
+        d.aux = aux->data;
+    }
     if (epi.dbias != nullptr) {
         if (!epi.dbias->valid() || epi.dbias->numel() != p.m || epi.dbias->dtype != DType::FP32)
             detail::fatal("matmul", "dbias must be fp32 [M]");
@@ -99,7 +107,7 @@ llmt_b200_gemm_desc make_desc(const RunCtx& ctx, const Tensor& c, const Tensor& 
     if (ctx.algo_cache != nullptr) {
         const AlgoKey key{p.m, p.n, p.k, p.batch, (trans_a ? 1LL : 0LL) | (trans_b ? 2LL : 0LL),
                           static_cast<int64_t>(a.dtype), static_cast<int64_t>(c.dtype),
-                          static_cast<int64_t>(d.epilogue) | (d.dbias != nullptr ? 4LL : 0LL)};
+                          static_cast<int64_t>(d.epilogue) | (d.dbias != nullptr ? 256LL : 0LL)};
         auto& map = ctx.algo_cache->map;
         if (map.find(key) == map.end()) {
             char buf[256];

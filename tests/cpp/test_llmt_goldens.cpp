@@ -517,6 +517,109 @@ void test_bf16_attention_fused(Device& dev) {
     expect(rel_fro(widen(dv1), widen(dv2)), 1e-6, "bf16 attention_bwd dV");
 }
 
+// bf16 MLP, training form: forward keeps the pre-activation (one launch, two results), backward runs
+// dX through the GELU inside the down projection's grouped launch.  Against a host computation in
+// double on the same bf16 parameters and inputs (intermediate tensors rounded to bf16 where the
+// device stores bf16).
+void test_bf16_mlp_training(Device& dev) {
+    const int64_t M = 192, C = 64, F = 256;
+    const RunCtx c16 = dev.make_ctx(1, KernelBackend::Naive, PrecisionPolicy::bf16_mixed());
+    Arena arena(32 << 20, "bf16-mlp-test");
+    uint32_t lcg = 4242u;
+    auto rnd = [&](float scale) { lcg = lcg * 1664525u + 1013904223u; return scale * (static_cast<float>(lcg >> 8) / 8388608.0f - 1.0f); };
+    auto fill = [&](Tensor& t, float scale, std::vector<float>* keep) {
+        std::vector<uint16_t> hb(static_cast<size_t>(t.numel()));
+        keep->resize(hb.size());
+        for (size_t i = 0; i < hb.size(); ++i) { hb[i] = to_bf16(rnd(scale)); (*keep)[i] = from_bf16(hb[i]); }
+        CUDA_CHECK(cudaMemcpy(t.data, hb.data(), hb.size() * 2, cudaMemcpyHostToDevice));
+    };
+    auto widen = [&](const Tensor& t) {
+        std::vector<uint16_t> hb(static_cast<size_t>(t.numel()));
+        CUDA_CHECK(cudaMemcpy(hb.data(), t.data, hb.size() * 2, cudaMemcpyDeviceToHost));
+        std::vector<float> h(hb.size());
+        for (size_t i = 0; i < h.size(); ++i) h[i] = from_bf16(hb[i]);
+        return h;
+    };
+    auto expect = [&](double err, double tol, const char* what) {
+        ++g_checks;
+        if (!(err <= tol)) { ++g_failures; std::fprintf(stderr, "FAIL %s: rel %.3e > %.1e\n", what, err, tol); }
+        else std::printf("ok   %s (rel %.2e)\n", what, err);
+    };
+    auto rb = [&](double v) { return static_cast<double>(from_bf16(to_bf16(static_cast<float>(v)))); };
+    ParamStore ps(StateDtypes::mixed(DType::BF16));
+    const MLP mlp(ps, "mlp", C, F, /*bias=*/true);
+    ps.finalize();
+    std::vector<float> wu, wd, xh, dyh;
+    Tensor wup = mlp.up().weight, wdown = mlp.down().weight;
+    fill(wup, 0.2f, &wu);
+    fill(wdown, 0.2f, &wd);
+    Tensor x = arena.alloc({M, C}, DType::BF16), dy = arena.alloc({M, C}, DType::BF16);
+    fill(x, 1.0f, &xh);
+    fill(dy, 0.1f, &dyh);
+    Tensor y = arena.alloc({M, C}, DType::BF16), h = arena.alloc({M, F}, DType::BF16), pre = arena.alloc({M, F}, DType::BF16);
+    Tensor dx = arena.alloc({M, C}, DType::BF16), d_pre = arena.alloc({M, F}, DType::BF16);
+    mlp.forward(c16, y, h, pre, x);
+    mlp.backward(c16, dx, d_pre, dy, x, h, pre);
+    dev.synchronize();
+    // host chain (the biases are zero after finalize)
+    const double k0 = 0.7978845608028654, k1 = 0.044715;
+    std::vector<float> pre_r(static_cast<size_t>(M * F)), h_r(pre_r.size()), dpre_r(pre_r.size());
+    std::vector<float> y_r(static_cast<size_t>(M * C)), dx_r(y_r.size()), dwu_r(static_cast<size_t>(F * C)), dwd_r(static_cast<size_t>(C * F)), dbu_r(static_cast<size_t>(F));
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t f = 0; f < F; ++f) {
+            double acc = 0;
+            for (int64_t c = 0; c < C; ++c) acc += double(xh[static_cast<size_t>(i * C + c)]) * wu[static_cast<size_t>(f * C + c)];
+            const double t = std::tanh(k0 * (acc + k1 * acc * acc * acc));
+            pre_r[static_cast<size_t>(i * F + f)] = static_cast<float>(rb(acc));
+            h_r[static_cast<size_t>(i * F + f)] = static_cast<float>(rb(0.5 * acc * (1.0 + t)));
+        }
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t c = 0; c < C; ++c) {
+            double acc = 0;
+            for (int64_t f = 0; f < F; ++f) acc += double(h_r[static_cast<size_t>(i * F + f)]) * wd[static_cast<size_t>(c * F + f)];
+            y_r[static_cast<size_t>(i * C + c)] = static_cast<float>(acc);
+        }
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t f = 0; f < F; ++f) {
+            double acc = 0;
+            for (int64_t c = 0; c < C; ++c) acc += double(dyh[static_cast<size_t>(i * C + c)]) * wd[static_cast<size_t>(c * F + f)];
+            const double p = pre_r[static_cast<size_t>(i * F + f)];
+            const double t = std::tanh(k0 * (p + k1 * p * p * p));
+            const double dg = 0.5 * (1.0 + t) + 0.5 * p * (1.0 - t * t) * k0 * (1.0 + 3.0 * k1 * p * p);
+            dpre_r[static_cast<size_t>(i * F + f)] = static_cast<float>(rb(acc * dg));
+        }
+    for (int64_t i = 0; i < M; ++i)
+        for (int64_t c = 0; c < C; ++c) {
+            double acc = 0;
+            for (int64_t f = 0; f < F; ++f) acc += double(dpre_r[static_cast<size_t>(i * F + f)]) * wu[static_cast<size_t>(f * C + c)];
+            dx_r[static_cast<size_t>(i * C + c)] = static_cast<float>(acc);
+        }
+    for (int64_t f = 0; f < F; ++f) {
+        double sb = 0;
+        for (int64_t i = 0; i < M; ++i) sb += dpre_r[static_cast<size_t>(i * F + f)];
+        dbu_r[static_cast<size_t>(f)] = static_cast<float>(sb);
+        for (int64_t c = 0; c < C; ++c) {
+            double acc = 0;
+            for (int64_t i = 0; i < M; ++i) acc += double(dpre_r[static_cast<size_t>(i * F + f)]) * xh[static_cast<size_t>(i * C + c)];
+            dwu_r[static_cast<size_t>(f * C + c)] = static_cast<float>(acc);
+        }
+    }
+    for (int64_t c = 0; c < C; ++c)
+        for (int64_t f = 0; f < F; ++f) {
+            double acc = 0;
+            for (int64_t i = 0; i < M; ++i) acc += double(dyh[static_cast<size_t>(i * C + c)]) * h_r[static_cast<size_t>(i * F + f)];
+            dwd_r[static_cast<size_t>(c * F + f)] = static_cast<float>(acc);
+        }
+    expect(rel_fro(widen(pre), pre_r), 5e-3, "bf16 MLP forward keeps the pre-activation");
+    expect(rel_fro(widen(h), h_r), 5e-3, "bf16 MLP forward h = gelu(pre)");
+    expect(rel_fro(widen(y), y_r), 1e-2, "bf16 MLP forward y");
+    expect(rel_fro(widen(d_pre), dpre_r), 1e-2, "bf16 MLP backward: dX through the GELU");
+    expect(rel_fro(widen(dx), dx_r), 1e-2, "bf16 MLP backward dx");
+    expect(rel_fro(download(mlp.up().grad), dwu_r), 5e-3, "bf16 MLP backward dW up");
+    expect(rel_fro(download(mlp.down().grad), dwd_r), 5e-3, "bf16 MLP backward dW down");
+    expect(rel_fro(download(mlp.up_layer().bias_param()->grad), dbu_r), 5e-3, "bf16 MLP backward dbias up");
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -534,6 +637,7 @@ int main(int argc, char** argv) {
     test_cross_entropy(dev, ctx);
     test_bf16_linear(dev);
     test_bf16_attention_fused(dev);
+    test_bf16_mlp_training(dev);
     std::printf("%d checks, %d failures; %zu plans recorded\n", g_checks, g_failures,
                 ctx.algo_cache->map.size());
     return g_failures == 0 ? 0 : 1;
