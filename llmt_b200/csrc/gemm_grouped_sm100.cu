@@ -559,6 +559,22 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         ctl->abort_flag = 0;
         fence_barrier_init();
     }
+    // The peer must see these barriers before anything is sent to them: arrive now, wait after the
+    // rest of the set-up (the cluster barrier's round trip overlaps it).
+    __syncwarp();  // (thread 0 is back with its warp: the arrive is a warp-wide instruction)
+    if (kPair) cluster_arrive_all();
+    // Independent of everything else, and slow: the tensor maps' descriptors on their way to the
+    // TMA unit.  (The first ticket needs no round trip at all: see the scheduler.)
+    if (warp == 0 && leader) {
+        if (lane >= 1 && lane <= 3 * gp.num_problems && lane <= 24) {
+            const GroupProblem& q = gp.prob[(lane - 1) / 3];
+            const int which = (lane - 1) % 3;
+            if (which < 2 || q.c_tma) prefetch_tensormap(which == 0 ? &q.map_a : which == 1 ? &q.map_b : &q.map_c);
+        }
+    } else if (warp == 0 && lane >= 1 && lane <= 2 * gp.num_problems && lane <= 16) {
+        const GroupProblem& q = gp.prob[(lane - 1) / 2];
+        prefetch_tensormap((lane - 1) % 2 == 0 ? &q.map_a : &q.map_b);
+    }
     if (static_cast<int>(threadIdx.x) < gp.num_problems) {
         // Shared-memory descriptors, 128-byte swizzle: K-major = k-step 32 bytes along the
         // row, LBO unused (16), SBO 1024; MN-major = k-step 16 k-rows of 128 bytes, LBO =
@@ -586,36 +602,30 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
     }
     tc_fence_before_thread_sync();
     __syncthreads();
-    if (kPair) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+    if (kPair) cluster_wait_all();
     tc_fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
-    // Still independent of the previous kernel in the stream: the first ticket (this
-    // launch's counter was re-armed by the launch that used it 64 launches ago) and the tensor
-    // maps, which the host encoded.
-    int first_ticket = 0;
-    if (warp == 0 && leader) {
-        if (lane == 0) first_ticket = gp.static_schedule == 0 ? atomicAdd(gp.sched_counter, 1) : sched_id;
-        else if (lane <= 3 * gp.num_problems && lane <= 24) {
-            const GroupProblem& q = gp.prob[(lane - 1) / 3];
-            const int which = (lane - 1) % 3;
-            if (which < 2 || q.c_tma) prefetch_tensormap(which == 0 ? &q.map_a : which == 1 ? &q.map_b : &q.map_c);
-        }
-    } else if (warp == 0 && lane >= 1 && lane <= 2 * gp.num_problems && lane <= 16) {
-        const GroupProblem& q = gp.prob[(lane - 1) / 2];
-        prefetch_tensormap((lane - 1) % 2 == 0 ? &q.map_a : &q.map_b);
-    }
+    // The first ticket of every drawer is its own index (any order of arrival would hand the
+    // first n_sched tickets to the n_sched drawers anyway); the queue's counter serves the tickets
+    // from n_sched on, so no atomic's round trip stands before the first load.
+    const int first_ticket = sched_id;
     // Everything above touched only this CTA's own state, so it may overlap the tail of the
-    // previous kernel in the stream; nothing below may start before that kernel is done.
+    // previous kernel in the stream.  What depends on that kernel is global memory, and every
+    // warp that touches any waits for it itself, as late as it can: the producers only before
+    // their first load, so that the first tile's ticket, its decoding and the boxes' set-up (some
+    // two microseconds of code that runs from a cold instruction cache at this point) are done
+    // by the time the previous kernel's results are visible; the MMA issuer touches none.
     grid_launch_dependents();
-    grid_dependency_wait();
-    if (gp.ride.tiles > 0 && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < gp.ride.world &&
-        static_cast<int>(threadIdx.x) != gp.ride.rank) {
-        // Everything earlier in this stream is complete, so this rank's partial sums of the range
-        // that rides along are: tell the other ranks.
-        const uint32_t e = *reinterpret_cast<volatile uint32_t*>(gp.ride.local + kRideStep) * kMaxRidesPerStep +
-                           static_cast<uint32_t>(gp.ride.index);
-        __threadfence_system();
-        st_release_sys(gp.ride.peer_ready[threadIdx.x], e);
+    if (gp.ride.tiles > 0 && blockIdx.x == 0 && static_cast<int>(threadIdx.x) < gp.ride.world) {
+        grid_dependency_wait();
+        if (static_cast<int>(threadIdx.x) != gp.ride.rank) {
+            // Everything earlier in this stream is complete, so this rank's partial sums of the range
+            // that rides along are: tell the other ranks.
+            const uint32_t e = *reinterpret_cast<volatile uint32_t*>(gp.ride.local + kRideStep) * kMaxRidesPerStep +
+                               static_cast<uint32_t>(gp.ride.index);
+            __threadfence_system();
+            st_release_sys(gp.ride.peer_ready[threadIdx.x], e);
+        }
     }
 
     // Barriers that live in the leader CTA of a pair, as cluster addresses usable from both.
@@ -669,6 +679,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         constexpr int kPublishAhead = 5;     // earliest k-block, counted from the end of the tile
         constexpr int kMinEarlyKblocks = 10; // shorter tiles publish at the top (the draw has not returned yet)
         bool early = false;                  // the next iteration's ticket is already in the ring
+        bool dep_waited = false;             // this warp has waited for the previous kernel in the stream
         // Ring entry `slot` <- ticket `raw`, decoded (out-of-range: the end marker).
         auto publish = [&](int slot, int raw) {
             int t = raw;
@@ -708,7 +719,7 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                     if (ok) {
                         const int raw = it == 0 ? first_ticket
                                       : !dynamic ? prev_ticket + n_sched
-                                      : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1);
+                                      : next_ticket != kNotDrawn ? next_ticket : atomicAdd(gp.sched_counter, 1) + n_sched;
                         next_ticket = kNotDrawn;
                         publish(slot, raw);
                     }
@@ -754,13 +765,17 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
                 if (b_mn) { my_off += j * kBlock64Bytes; my_x = n0 + 64 * j; k_is_y = true; }
                 else      { my_y = n0; k_is_x = true; }
             }
+            if (!dep_waited) {   // the first loads are next: the previous kernel must be done
+                grid_dependency_wait();
+                dep_waited = true;
+            }
             const bool tile_sums = p.dbias_mode == 3 && tc.n_tile == 0;  // the epilogue warps read this tile's A stages
             const int draw_kb = tc.kb1 - kDrawAhead > tc.kb0 ? tc.kb1 - kDrawAhead : tc.kb0;
             const int publish_kb = tc.kb1 - tc.kb0 >= kMinEarlyKblocks ? tc.kb1 - kPublishAhead : 0x7fffffff;
             const int after_own = n_turns > 1 ? 1 : 0;
             for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++seq) {
                 if (kb >= draw_kb && scheduler && lane == 0) {  // (the first test is warp-uniform and false on most k-blocks)
-                    if (dynamic && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1);
+                    if (dynamic && kb == draw_kb) next_ticket = atomicAdd(gp.sched_counter, 1) + n_sched;
                     if (kb >= publish_kb && !early && turn == after_own) {
                         const int nslot = (it + 1) % kRing;
                         const uint32_t nphase = static_cast<uint32_t>((it + 1) / kRing) & 1u;
@@ -856,9 +871,13 @@ __device__ __forceinline__ void tc_grouped_body(const GroupParams& gp) {
         }
     } else if (warp == kSideWarp) {
         // ------------------------------------------------------------ side warp
-        if (gp.ride.tiles > 0) ride_exchange_side_warp(gp.ride, gp.ride_counter, lane, wait_ns, status);
+        if (gp.ride.tiles > 0) {
+            grid_dependency_wait();
+            ride_exchange_side_warp(gp.ride, gp.ride_counter, lane, wait_ns, status);
+        }
     } else if (warp < 2 + kEpilogueWarps) {
         // ---------------------------------------------------------- epilogue
+        grid_dependency_wait();              // bias, C_in, dbias tickets and the result itself are global memory
         const int quarter = warp & 3;        // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
         const int half = (warp - 2) >> 2;    // this warp takes the column units u with u % 2 == half
         const int ew = warp - 2;             // 0..7
