@@ -369,7 +369,7 @@ class AttentionStep:
     every product moves one [96, T, T] matrix."""
     BH, T, HD = 96, 1024, 64
 
-    def __init__(self, dev, seed):
+    def __init__(self, dev, seed, fused=False):
         import torch
         import llmt_b200 as L
         self.L, self.torch = L, torch
@@ -402,10 +402,41 @@ class AttentionStep:
         self.flops = 6 * self.flops_each
         # minimum bytes of one product: the [BH,T,T] matrix once plus three [BH,T,hd] tensors
         self.bytes_each = 2.0 * (BH * T * T + 3 * BH * T * HD)
+        self.bytes_step = 6 * self.bytes_each
+        self.fused = fused
+        if fused:
+            # Configuration 4 with the softmax inside the timed set, fused around the products
+            # (llmt_b200_gemm_softmax_fwd / _bwd): S and dP are never stored.  The FLOP count stays
+            # the six dense products' (the second pass over the score tiles is not counted);
+            # bytes: P written once, read by O, dV and dS, dS written once, read by dQ and dK.
+            self.lse = torch.empty(BH, T, device=dev)
+            self.dvec = torch.empty(BH, T, device=dev)
+            self.d_s = md(self.p, self.q, self.k, False, True, alpha=a)
+            need = L.gemm_softmax_workspace_bytes(self.d_s, self.q, self.k)
+            self.ws_s = torch.empty(need, dtype=torch.uint8, device=dev)
+            self.d_s.workspace, self.d_s.workspace_bytes = self.ws_s.data_ptr(), need
+            self.d_b = md(self.ds, self.d_o, self.v, False, True)
+            self.ws_b = torch.empty(max(L.workspace_bytes(self.d_b, self.d_o, self.v), 256), dtype=torch.uint8, device=dev)
+            self.d_b.workspace, self.d_b.workspace_bytes = self.ws_b.data_ptr(), self.ws_b.numel()
+            L.gemm_desc(self.calls[1][1], self.o, self.p, self.v)
+            self.bytes_step = 2.0 * (7 * BH * T * T + 16 * BH * T * HD)
 
     def launches(self):
-        return [(lab, self.flops_each, (lambda d=d, c=c, a=a, b=b: self.L.gemm_desc(d, c, a, b)), [])
-                for lab, d, c, a, b in self.calls]
+        plain = [(lab, self.flops_each, (lambda d=d, c=c, a=a, b=b: self.L.gemm_desc(d, c, a, b)), [])
+                 for lab, d, c, a, b in self.calls]
+        if not self.fused:
+            return plain
+        L = self.L
+
+        def fwd():
+            L.gemm_softmax_fwd(self.d_s, self.p, self.q, self.k, True, self.lse)
+
+        def bwd():
+            L.rowdot(self.dvec, self.d_o, self.o)
+            L.gemm_softmax_bwd(self.d_b, self.ds, self.d_o, self.v, self.p, self.dvec, True)
+
+        return [("P=softmax(aQK^T)", self.flops_each, fwd, []), plain[1], plain[2],
+                ("dS=P*(dOV^T-D)", self.flops_each, bwd, []), plain[4], plain[5]]
 
     def run(self, world=1, events=None):
         torch = self.torch
@@ -419,8 +450,8 @@ class AttentionStep:
 
 
 def make_step(workload, m, dev, seed, world=1, args=None):
-    if workload == "c4":
-        return AttentionStep(dev, seed)
+    if workload in ("c4", "c4f"):
+        return AttentionStep(dev, seed, fused=workload == "c4f")
     defer = {"attn_out": "qkv"} if workload == "c2" and not (args and args.no_defer) else None
     return LinearStep(workload, m, dev, seed, world=world, exchange=args.exchange if args else "nccl",
                       comm_ctas=(args.comm_ctas if args and args.comm_ctas else 8), defer=defer,
@@ -1057,6 +1088,10 @@ def workload_text(workload, m):
     if workload == "c4":
         return ("c4: strided-batched attention products, B*H=96, T=1024, hd=64: S, O, dV, dP, dQ, dK "
                 "(dense FLOP count); P and dS from the softmax helpers outside the timed set")
+    if workload == "c4f":
+        return ("c4f: the same six products with the causal softmax and its backward INSIDE the timed set, fused "
+                "around them (P = softmax(aQK^T) in two launches over the score tiles, dS in the dP launch); "
+                "FLOP count of the six dense products")
     cfg = LAYERS[workload]
     return (f"{workload}: {cfg['name']}, M={m} tokens per GPU, fwd+dX+dW(+dbias) per layer"
             + (", bias+GELU fused in mlp_fc" if cfg.get("bias", True) else ""))
@@ -1065,14 +1100,16 @@ def workload_text(workload, m):
 def roofline_of(step, workload, ms, peaks):
     """Roofline entry of a workload from the CUDA-event time of its timed loop (the loop is the
     GEMM kernel back to back)."""
-    if workload == "c4":
-        gbs = 6 * step.bytes_each / ms / 1e6
+    if workload in ("c4", "c4f"):
+        gbs = step.bytes_step / ms / 1e6
         return {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["bw"], "unit": "GB/s",
                 "frac": round(gbs / peaks["bw"], 4), "traffic": recorded_traffic(workload),
-                "algorithmic_bytes": int(6 * step.bytes_each), "peak_source": f"of {peaks['which']}",
+                "algorithmic_bytes": int(step.bytes_step), "peak_source": f"of {peaks['which']}",
                 "tflops": round(step.flops / ms / 1e9, 1),
-                "kernel": "tc_grouped_pair_kernel (six batched launches; algorithmic bytes = one [96,T,T] "
-                          "bf16 matrix + three [96,T,64] tensors per product)"}
+                "kernel": ("tc_grouped_pair_kernel (six batched launches; algorithmic bytes = one [96,T,T] "
+                           "bf16 matrix + three [96,T,64] tensors per product)") if workload == "c4" else
+                          ("tc_grouped_pair_kernel / tc_grouped_pair_lse_kernel (P written once and read three times, "
+                           "dS written once and read twice: seven [96,T,T] bf16 matrices per step)")}
     tf = step.flops / ms / 1e9
     return {"bound": "tensor", "achieved": round(tf, 1), "peak": peaks["tf"], "unit": "TFLOP/s",
             "frac": round(tf / peaks["tf"], 4), "traffic": recorded_traffic(workload),
@@ -1145,7 +1182,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4"], default="c2")
+    ap.add_argument("--workload", choices=sorted(LAYERS) + ["c4", "c4f"], default="c2")
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
@@ -1208,7 +1245,7 @@ def main():
         torch.cuda.synchronize()
 
     peaks = measured_peaks()
-    attention = args.workload == "c4"
+    attention = args.workload in ("c4", "c4f")
     step = make_step(args.workload, M_PER_GPU, dev, seed=rank, world=world, args=args)
     flops = step.flops
     sampler = make_sampler(torch, dev)
@@ -1297,7 +1334,7 @@ def main():
 
     if world == 1 and not args.no_extras:
         others = {}
-        for wl in ("c3", "c3c", "c4", "c5"):
+        for wl in ("c3", "c3c", "c4", "c4f", "c5"):
             if wl == args.workload:
                 continue
             try:
