@@ -719,12 +719,15 @@ def attention_softmax_comparison(torch, L, dev):
         L.gemm_softmax_bwd(z["d_b"], z["ds_f"], z["do"], z["v"], z["p_f"], z["dvec"], True)
 
     out = {"shape": f"B*H = {BH}, T = {T}, hd = {HD}, bf16, causal; one T x T tensor is {BH * T * T * 2} bytes"}
+    def best_of_two(fn):  # (the first loop after the allocations above has been seen to run long once)
+        return min(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=10, warm=3) for _ in range(2))
+
     for name, fn in (("fwd_gemm_then_softmax_ms", fwd_unfused), ("fwd_fused_ms", fwd_fused)):
-        out[name] = round(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=10, warm=3), 4)
+        out[name] = round(best_of_two(fn), 4)
     for z in sets:
         L.gemm(z["o"], z["p_f"], z["v"], False, False)
     for name, fn in (("bwd_gemm_then_softmax_bwd_ms", bwd_unfused), ("bwd_fused_ms", bwd_fused)):
-        out[name] = round(_loop_ms(torch, [lambda z=z, fn=fn: fn(z) for z in sets], iters=10, warm=3), 4)
+        out[name] = round(best_of_two(fn), 4)
     L.device_status()
     z = sets[0]
     p_u, p_f = z["s_u"].float(), z["p_f"].float()
