@@ -1,3 +1,5 @@
-// Forwarding header: the types live in llmt/core/types.h.
+// llmt's sources include "llmt/core/shape.h" (its include/llmt/core/shape.h); here those types live in
+// one header, llmt/core/types.h, and this path only forwards to it so that such sources compile
+// against this tree unchanged.
 #pragma once
 #include "llmt/core/types.h"
