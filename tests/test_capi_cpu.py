@@ -340,3 +340,74 @@ def test_ride_along_exchange_arguments_are_checked_before_anything_is_planned():
     assert call(0, 2048, 0) == L.ERR_INVALID and "writes into the exchanged range" in L.last_error()
     comm.world = 1
     assert call(0, 1024, 0) == L.ERR_INVALID and "rank/world" in L.last_error()
+
+
+def test_row_wise_epilogue_entry_points_check_their_arguments_first():
+    """llmt_b200_gemm_softmax_fwd/_bwd, lm_head_ce_fwd/_bwd, cross_entropy_bwd, rowdot: every
+    refusal below happens on the host, before anything is planned, encoded or launched."""
+    lib = L.lib()
+    P, Q, K, V = 0x100000, 0x200000, 0x300000, 0x400000
+    ws = 0x800000
+
+    def sm_desc(**kw):
+        d = _desc(m=128, n=128, k=64, batch=2, lda=64, ldb=64, ldc=128, stride_a=128 * 64, stride_b=128 * 64,
+                  stride_c=128 * 128, dtype_c=L.BF16, workspace=ws, workspace_bytes=1 << 20)
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    def fwd(d, causal=1):
+        return lib.llmt_b200_gemm_softmax_fwd(ctypes.byref(d), ctypes.c_void_p(P), ctypes.c_void_p(Q), ctypes.c_void_p(K),
+                                              causal, None, None)
+
+    assert fwd(sm_desc(n=256, ldc=256, stride_b=256 * 64, stride_c=128 * 256)) == L.ERR_INVALID and "square scores" in L.last_error()
+    assert fwd(sm_desc(beta=1.0)) == L.ERR_UNSUPPORTED and "beta must be 0" in L.last_error()
+    assert fwd(sm_desc(dtype_ab=L.FP32, dtype_c=L.FP32)) == L.ERR_UNSUPPORTED and "bf16 operands only" in L.last_error()
+    assert fwd(sm_desc(epilogue=L.EPI_GELU)) == L.ERR_UNSUPPORTED
+    assert fwd(sm_desc(workspace_bytes=0)) == L.ERR_WORKSPACE and "llmt_b200_gemm_softmax_workspace_bytes" in L.last_error()
+    assert lib.llmt_b200_gemm_softmax_workspace_bytes(ctypes.byref(sm_desc()), None, None) > 2 * 128 * 8
+
+    def bwd(d, probs=V, rowdot=0x500000, ds=P):
+        return lib.llmt_b200_gemm_softmax_bwd(ctypes.byref(d), ctypes.c_void_p(ds), ctypes.c_void_p(Q), ctypes.c_void_p(K),
+                                              ctypes.c_void_p(probs), ctypes.c_void_p(rowdot), 1, None)
+
+    assert bwd(sm_desc(), probs=None) == L.ERR_INVALID and "null probabilities" in L.last_error()
+    assert bwd(sm_desc(), probs=P + 64) == L.ERR_INVALID and "must not overlap" in L.last_error()
+
+    def ce_desc(**kw):
+        d = _desc(m=128, n=1000, k=64, lda=64, ldb=64, ldc=1000, workspace=ws, workspace_bytes=1 << 22)
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    T, M_, NLL, LOSS = 0x600000, 0x610000, 0x620000, 0x630000
+    ce_fwd = lambda d, targets=T: lib.llmt_b200_lm_head_ce_fwd(ctypes.byref(d), None, ctypes.c_void_p(Q), ctypes.c_void_p(K),
+                                                              ctypes.c_void_p(targets), ctypes.c_void_p(M_),
+                                                              ctypes.c_void_p(NLL), ctypes.c_void_p(LOSS), None)
+    assert ce_fwd(ce_desc(), targets=None) == L.ERR_INVALID
+    assert ce_fwd(ce_desc(batch=0)) == L.ERR_INVALID and "empty problem" in L.last_error()
+    assert ce_fwd(ce_desc(beta=1.0)) == L.ERR_INVALID and "beta needs the logits" in L.last_error()
+    assert ce_fwd(ce_desc(workspace_bytes=16)) == L.ERR_WORKSPACE
+    ce_bwd = lambda d, dl=P: lib.llmt_b200_lm_head_ce_bwd(ctypes.byref(d), ctypes.c_void_p(dl), ctypes.c_void_p(Q), ctypes.c_void_p(K),
+                                                         ctypes.c_void_p(T), ctypes.c_void_p(M_), 1.0, 0, None)
+    assert ce_bwd(ce_desc(), dl=None) == L.ERR_INVALID
+    assert ce_bwd(ce_desc(beta=0.5)) == L.ERR_UNSUPPORTED
+    assert ce_bwd(ce_desc(workspace_bytes=16)) == L.ERR_WORKSPACE
+
+    assert lib.llmt_b200_cross_entropy_bwd(ctypes.c_void_p(P), ctypes.c_void_p(P), ctypes.c_void_p(T), ctypes.c_void_p(M_),
+                                           1.0, 8, 100, 100, 104, None) == L.ERR_INVALID and "one pitch" in L.last_error()
+    assert lib.llmt_b200_cross_entropy_bwd(ctypes.c_void_p(P + 16), ctypes.c_void_p(P), ctypes.c_void_p(T), ctypes.c_void_p(M_),
+                                           1.0, 8, 100, 100, 100, None) == L.ERR_INVALID and "overlap" in L.last_error()
+    assert lib.llmt_b200_rowdot(ctypes.c_void_p(P), ctypes.c_void_p(Q), ctypes.c_void_p(K), 8, 64, 32, 64, L.BF16, None) == L.ERR_INVALID
+    assert lib.llmt_b200_rowdot(ctypes.c_void_p(P), ctypes.c_void_p(Q), ctypes.c_void_p(K), 8, 64, 64, 64, 7, None) == L.ERR_UNSUPPORTED
+    assert lib.llmt_b200_rowdot(ctypes.c_void_p(P), ctypes.c_void_p(Q), ctypes.c_void_p(K), 0, 64, 64, 64, L.BF16, None) == L.OK
+
+
+def test_aux_epilogues_are_never_split_along_k():
+    # a row-wise epilogue sees whole reductions: the plan of such a problem has one split, forced or not
+    d = _desc(m=256, n=256, k=8192, lda=8192, ldb=8192, ldc=256, dtype_c=L.BF16)
+    assert "splits=1" not in L.plan(d)            # alone, this shape is split
+    d.epilogue, d.aux = L.EPI_GELU_BWD, 0x700000
+    assert "splits=1" in L.plan(d)
+    d.plan_splits = 4
+    assert "splits=1" in L.plan(d)
